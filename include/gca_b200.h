@@ -1,0 +1,256 @@
+/*
+ * gca_b200.h -- C ABI of libgca_b200.so: Grouped Cross-Attention (GCA) and landmark
+ * retrieval for the DRT long-context model, written for NVIDIA B200 (sm_100a).
+ *
+ * The reference project is pure Python; its boundary for this path is a set of Python
+ * callables.  Each entry point below names the reference callable it stands in for
+ * (paths relative to the reference project).  The Python host layer of this repository
+ * binds these symbols with ctypes and re-exposes them under the reference's names.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller (also workspaces and the
+ *     optional status word); the library keeps nothing after the call returns except work
+ *     already enqueued on `stream`;
+ *   - all launches are asynchronous on `stream` (a cudaStream_t passed as void*);
+ *   - strides are in ELEMENTS; the innermost (head_dim) axis must be contiguous;
+ *   - return value: 0 = ok, negative = argument rejected on the host before any launch
+ *     (GCA_ERR_*), positive = CUDA runtime error code;
+ *   - nothing throws or aborts; there is no CPU fallback.
+ */
+#ifndef GCA_B200_H_
+#define GCA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GCA_ABI_VERSION 1
+
+enum GcaDtype { GCA_BF16 = 0, GCA_F32 = 1 };
+
+enum GcaError {
+  GCA_OK = 0,
+  GCA_ERR_NULL = -1,        /* a required pointer is NULL */
+  GCA_ERR_DTYPE = -2,       /* unknown dtype / dtype not supported by this kernel */
+  GCA_ERR_SHAPE = -3,       /* a dimension is outside the supported envelope */
+  GCA_ERR_STRIDE = -4,      /* a stride is not usable (alignment, overlap) */
+  GCA_ERR_ALIGN = -5,       /* a base pointer is not 16-byte aligned */
+  GCA_ERR_WORKSPACE = -6,   /* workspace missing or too small */
+  GCA_ERR_ALGO = -7,        /* requested kernel variant cannot run this problem */
+  GCA_ERR_TMA = -8,         /* the driver rejected a tensor-map encoding */
+  GCA_ERR_TOO_LARGE = -9    /* a size exceeds a fixed built-in limit */
+};
+
+/* kernel variants (GcaFwdArgs.algo / GcaBwdArgs.algo) */
+enum GcaAlgo {
+  GCA_ALGO_AUTO = 0,        /* bf16 + S=L=D=64 -> tensor-core kernel, everything else -> SIMT */
+  GCA_ALGO_SIMT = 1,        /* fp32-accumulating CUDA-core kernel (bf16 or fp32 data) */
+  GCA_ALGO_TC = 2           /* tcgen05/TMEM/TMA kernel (bf16 only) */
+};
+
+/* device-side soft status bits written (OR-ed) into *status when it is given */
+enum GcaStatus {
+  GCA_STATUS_OK = 0,
+  GCA_STATUS_BAD_INDEX = 1, /* a retrieved chunk index was >= C; the slot was skipped */
+  GCA_STATUS_TIMEOUT = 2    /* a bounded on-chip wait expired; outputs are not valid */
+};
+
+/*
+ * Forward.  Stands in for `_attention.forward` (ltriton/gca.py:683-738, kernel
+ * `_attn_fwd` :94-211) and, without `lse`, for `gca_kv_cache` (ltriton/gca.py:846-888,
+ * kernel `_attn_inf` :214-314) -- with the chunk gather of
+ * `ChunkKVManager.retrieve_chunks` (model/DRT.py:193-199) and the layout copy of
+ * `TritonGroupCrossAttention.preprocess_chunk_kv_cache` (model/DRT.py:321-332) folded in:
+ * K/V are read from the cache by retrieved chunk index.
+ *
+ *   q, out   (N, J, Hq, S, D)      addressed with *_stride = {n, j, h, s}
+ *   k_cache, v_cache (N, C, L, Hkv, D) addressed with *_stride = {n, c, l, h}
+ *   indices  (N, J, K) int32, contiguous; < 0 marks a padding slot (skipped)
+ *   weights  (N, J, K) float32, contiguous (shared by all heads)
+ *   lse      (N*J, Hq, K, S) float32 base-2 log-sum-exp per slot, or NULL
+ *
+ *   out[n,j,h] = sum_k weights[n,j,k] * softmax(sm_scale * q K_k^T) V_k,
+ *   K_k = k_cache[n, indices[n,j,k], :, h / (Hq/Hkv), :].
+ *
+ * The pre-gathered call of the reference (k of shape (Z, Hkv, K, L, D)) is the same
+ * kernel with N=Z, J=1, C=K, indices = 0..K-1 and the matching strides.
+ * `off_by_one` > 0 adds a virtual zero logit of that weight to every softmax; 0 gives
+ * the behaviour of the reference kernels (whose `sm_n` argument has no effect).
+ */
+typedef struct GcaFwdArgs {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int32_t* indices;
+  const float* weights;
+  void* out;
+  float* lse;
+  int32_t* status;
+  int64_t q_stride[4];
+  int64_t o_stride[4];
+  int64_t k_stride[4];
+  int64_t v_stride[4];
+  int32_t N, J, Hq, Hkv, S, L, D, K, C;
+  int32_t dtype;
+  int32_t algo;
+  float sm_scale;
+  float off_by_one;
+} GcaFwdArgs;
+
+int gca_fwd(const GcaFwdArgs* args, void* stream);
+
+/*
+ * Decode / short-query forward: S in [1, 16] query rows (the model uses 1 or 2).
+ * Stands in for `gca_kv_cache` with q of shape (N, Hq, 1|2, D) (model/DRT.py:382,
+ * ltriton/gca.py:846-888).  Same argument block as gca_fwd; `lse` is ignored.
+ */
+int gca_decode(const GcaFwdArgs* args, void* stream);
+
+/*
+ * Backward.  Stands in for `_attention.backward` (ltriton/gca.py:740-841: the scaled copy
+ * of K :776, kernels `kernel_attn_bwd_dkdv` :484-572 and `kernel_attn_bwd_dq` :575-675,
+ * the `delta` reduction :839-840) plus the scatter-add into the chunk cache that autograd
+ * performs behind the reference's gather (index_put_ with accumulate).
+ *
+ *   dout, dq        like q (strides do_stride / dq_stride)
+ *   dk_cache, dv_cache like the caches (strides dk_stride / dv_stride); every (n, c, h)
+ *                   tile is written: the sum over all (j, k) that retrieved chunk c, or 0
+ *   dw              (N, J, K) float32: sum over heads and rows of <dout, O_k>
+ *   lse             as written by gca_fwd with the same arguments
+ *   workspace       gca_bwd_workspace_bytes() bytes, 256-byte aligned
+ */
+typedef struct GcaBwdArgs {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int32_t* indices;
+  const float* weights;
+  const void* dout;
+  const float* lse;
+  void* dq;
+  void* dk_cache;
+  void* dv_cache;
+  float* dw;
+  void* workspace;
+  int32_t* status;
+  size_t workspace_bytes;
+  int64_t q_stride[4];
+  int64_t do_stride[4];
+  int64_t dq_stride[4];
+  int64_t k_stride[4];
+  int64_t v_stride[4];
+  int64_t dk_stride[4];
+  int64_t dv_stride[4];
+  int32_t N, J, Hq, Hkv, S, L, D, K, C;
+  int32_t dtype;
+  int32_t algo;
+  float sm_scale;
+  float off_by_one;
+} GcaBwdArgs;
+
+int gca_bwd(const GcaBwdArgs* args, void* stream);
+size_t gca_bwd_workspace_bytes(const GcaBwdArgs* args);
+
+/*
+ * Landmark scoring + causal chunk mask + top-k + retrieval weights, fused.  Stands in for
+ * the tensor program of `DRT._perform_batch_retrieval` (model/DRT.py:612-627: einsum,
+ * masked_fill with `_enc_dec_score_mask` :590-607, optional Gumbel noise, topk, softmax,
+ * nan_to_num) and of the decode-time block (model/DRT.py:836-845).
+ *
+ *   lmk_q    (N, Cq, D)  bf16  query landmarks,  row stride q_row_stride, batch q_batch_stride
+ *   lmk_k    (N, E, D)   bf16  cached landmarks, row stride k_row_stride, batch k_batch_stride
+ *   noise    (N, Cq, E)  float32 or NULL; added for the selection only
+ *   row i of a sequence sees cached chunk e iff  e_base + e < q_pos0 + i
+ *   (the reference: q_pos0 = E_total - Cq, e_base = 0).
+ *   head_dim == 0: one score per (row, chunk) over all D, scaled 1/sqrt(D)   (the reference)
+ *   head_dim  > 0: one score per (row, head, chunk) over head_dim, scaled 1/sqrt(head_dim);
+ *                  outputs gain a head axis after Cq.
+ *   score_round 0: float32 scores; 1: scores rounded to bf16 twice like the reference
+ *                  under autocast (bf16 einsum output, bf16 division).
+ *
+ * Outputs, R = N*Cq (*H in per-head mode) rows, contiguous:
+ *   out_keys    (R, K) uint64   packed (orderable score << 32 | ~index), 0 = empty; descending
+ *   out_indices (R, K) int32    global chunk ids (e_base + e), -1 = padding      (may be NULL)
+ *   out_scores  (R, K) float32  noise-free scores of the selected chunks         (may be NULL)
+ *   out_weights (R, K) float32  softmax over the valid slots, padding 0          (may be NULL)
+ *   out_nvalid  (R)    int32                                                   (may be NULL)
+ * Scores are float32 sums in one fixed order, ties go to the lower index, so the result
+ * is bit-reproducible and independent of the launch geometry.
+ *   workspace: lmk_topk_workspace_bytes() bytes (partial candidate lists).
+ */
+typedef struct LmkTopkArgs {
+  const void* lmk_q;
+  const void* lmk_k;
+  const float* noise;
+  uint64_t* out_keys;
+  int32_t* out_indices;
+  float* out_scores;
+  float* out_weights;
+  int32_t* out_nvalid;
+  void* workspace;
+  size_t workspace_bytes;
+  int64_t q_batch_stride, q_row_stride;
+  int64_t k_batch_stride, k_row_stride;
+  int64_t q_pos0;
+  int64_t e_base;
+  int32_t N, Cq, E, D, K;
+  int32_t head_dim;
+  int32_t score_round;
+  int32_t splits;            /* 0 = choose; otherwise number of E-ranges scanned by separate CTAs */
+} LmkTopkArgs;
+
+int lmk_score_topk(const LmkTopkArgs* args, void* stream);
+size_t lmk_topk_workspace_bytes(const LmkTopkArgs* args);
+
+/*
+ * Merge of candidate lists (the exchange step of the chunk-range-sharded cache; no
+ * counterpart in the reference, which never shards retrieval): keys (R, P) packed uint64
+ * candidates (P = shards * K, any order, 0 = empty) -> the K best per row, descending,
+ * with indices / scores / weights / nvalid decoded as above.
+ */
+typedef struct LmkMergeArgs {
+  const uint64_t* keys;
+  uint64_t* out_keys;
+  int32_t* out_indices;
+  float* out_scores;
+  float* out_weights;
+  int32_t* out_nvalid;
+  int32_t R, P, K;
+} LmkMergeArgs;
+
+int lmk_topk_merge(const LmkMergeArgs* args, void* stream);
+
+/*
+ * Chunk cache append with the landmark row cleared.  Stands in for the tensor work of
+ * model/DRT.py:770-784 + ChunkKVManager.append (:87-133): copies `count` new chunks of K
+ * and V (N, count, L, Hkv*D) into a preallocated cache (N, capacity, L, Hkv*D) at chunk
+ * position `pos`, writing zeros into the last row of every chunk when zero_landmark != 0,
+ * and copies the landmark embeddings (N, count, Dm) into the landmark cache.
+ */
+typedef struct CacheAppendArgs {
+  const void* new_k;
+  const void* new_v;
+  const void* new_lmk;       /* may be NULL */
+  void* k_cache;
+  void* v_cache;
+  void* lmk_cache;           /* may be NULL */
+  int64_t new_batch_stride;  /* elements between sequences in new_k / new_v */
+  int64_t cache_batch_stride;
+  int64_t new_lmk_batch_stride, lmk_cache_batch_stride;
+  int32_t N, count, pos, L, HD, Dm;
+  int32_t dtype;
+  int32_t zero_landmark;
+} CacheAppendArgs;
+
+int gca_cache_append(const CacheAppendArgs* args, void* stream);
+
+const char* gca_strerror(int code);
+int gca_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GCA_B200_H_ */

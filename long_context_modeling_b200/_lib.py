@@ -1,0 +1,132 @@
+"""ctypes binding of libgca_b200.so (the C ABI declared in include/gca_b200.h).
+
+The library is built in-tree by ``long_context_modeling_b200.build``.  There is no
+fallback of any kind: if the shared object is missing, or a call is rejected, an
+exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libgca_b200.so")
+
+BF16, F32 = 0, 1
+ALGO_AUTO, ALGO_SIMT, ALGO_TC = 0, 1, 2
+STATUS_BAD_INDEX, STATUS_TIMEOUT = 1, 2
+
+_i64x4 = C.c_int64 * 4
+
+
+class GcaFwdArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("indices", C.c_void_p), ("weights", C.c_void_p), ("out", C.c_void_p),
+        ("lse", C.c_void_p), ("status", C.c_void_p),
+        ("q_stride", _i64x4), ("o_stride", _i64x4), ("k_stride", _i64x4), ("v_stride", _i64x4),
+        ("N", C.c_int32), ("J", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("S", C.c_int32),
+        ("L", C.c_int32), ("D", C.c_int32), ("K", C.c_int32), ("C", C.c_int32),
+        ("dtype", C.c_int32), ("algo", C.c_int32), ("sm_scale", C.c_float), ("off_by_one", C.c_float),
+    ]
+
+
+class GcaBwdArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("indices", C.c_void_p), ("weights", C.c_void_p), ("dout", C.c_void_p), ("lse", C.c_void_p),
+        ("dq", C.c_void_p), ("dk_cache", C.c_void_p), ("dv_cache", C.c_void_p), ("dw", C.c_void_p),
+        ("workspace", C.c_void_p), ("status", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("q_stride", _i64x4), ("do_stride", _i64x4), ("dq_stride", _i64x4),
+        ("k_stride", _i64x4), ("v_stride", _i64x4), ("dk_stride", _i64x4), ("dv_stride", _i64x4),
+        ("N", C.c_int32), ("J", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("S", C.c_int32),
+        ("L", C.c_int32), ("D", C.c_int32), ("K", C.c_int32), ("C", C.c_int32),
+        ("dtype", C.c_int32), ("algo", C.c_int32), ("sm_scale", C.c_float), ("off_by_one", C.c_float),
+    ]
+
+
+class LmkTopkArgs(C.Structure):
+    _fields_ = [
+        ("lmk_q", C.c_void_p), ("lmk_k", C.c_void_p), ("noise", C.c_void_p),
+        ("out_keys", C.c_void_p), ("out_indices", C.c_void_p), ("out_scores", C.c_void_p),
+        ("out_weights", C.c_void_p), ("out_nvalid", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("q_batch_stride", C.c_int64), ("q_row_stride", C.c_int64),
+        ("k_batch_stride", C.c_int64), ("k_row_stride", C.c_int64),
+        ("q_pos0", C.c_int64), ("e_base", C.c_int64),
+        ("N", C.c_int32), ("Cq", C.c_int32), ("E", C.c_int32), ("D", C.c_int32), ("K", C.c_int32),
+        ("head_dim", C.c_int32), ("score_round", C.c_int32), ("splits", C.c_int32),
+    ]
+
+
+class LmkMergeArgs(C.Structure):
+    _fields_ = [
+        ("keys", C.c_void_p), ("out_keys", C.c_void_p), ("out_indices", C.c_void_p),
+        ("out_scores", C.c_void_p), ("out_weights", C.c_void_p), ("out_nvalid", C.c_void_p),
+        ("R", C.c_int32), ("P", C.c_int32), ("K", C.c_int32),
+    ]
+
+
+class CacheAppendArgs(C.Structure):
+    _fields_ = [
+        ("new_k", C.c_void_p), ("new_v", C.c_void_p), ("new_lmk", C.c_void_p),
+        ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("lmk_cache", C.c_void_p),
+        ("new_batch_stride", C.c_int64), ("cache_batch_stride", C.c_int64),
+        ("new_lmk_batch_stride", C.c_int64), ("lmk_cache_batch_stride", C.c_int64),
+        ("N", C.c_int32), ("count", C.c_int32), ("pos", C.c_int32), ("L", C.c_int32),
+        ("HD", C.c_int32), ("Dm", C.c_int32), ("dtype", C.c_int32), ("zero_landmark", C.c_int32),
+    ]
+
+
+EXPORTS = {
+    "gca_fwd": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
+    "gca_decode": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
+    "gca_bwd": (C.c_int, [C.POINTER(GcaBwdArgs), C.c_void_p]),
+    "gca_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(GcaBwdArgs)]),
+    "lmk_score_topk": (C.c_int, [C.POINTER(LmkTopkArgs), C.c_void_p]),
+    "lmk_topk_workspace_bytes": (C.c_size_t, [C.POINTER(LmkTopkArgs)]),
+    "lmk_topk_merge": (C.c_int, [C.POINTER(LmkMergeArgs), C.c_void_p]),
+    "gca_cache_append": (C.c_int, [C.POINTER(CacheAppendArgs), C.c_void_p]),
+    "gca_strerror": (C.c_char_p, [C.c_int]),
+    "gca_abi_version": (C.c_int, []),
+}
+
+_lib: Optional[C.CDLL] = None
+
+
+def lib() -> C.CDLL:
+    """Load the shared library once.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m long_context_modeling_b200.build` "
+                "(there is no fallback path)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, argtypes) in EXPORTS.items():
+            fn = getattr(handle, name)          # AttributeError if a symbol is missing
+            fn.restype = res
+            fn.argtypes = argtypes
+        if handle.gca_abi_version() != 1:
+            raise RuntimeError("libgca_b200.so has an unexpected ABI version")
+        _lib = handle
+    return _lib
+
+
+class GcaError(RuntimeError):
+    pass
+
+
+def check(code: int, what: str) -> None:
+    """0 -> ok; negative -> ValueError (argument rejected); positive -> CUDA runtime error."""
+    if code == 0:
+        return
+    msg = lib().gca_strerror(code).decode()
+    if code < 0:
+        raise ValueError(f"{what}: {msg} (code {code})")
+    raise GcaError(f"{what}: CUDA error {code}: {msg}")
+
+
+def strides4(*vals) -> "_i64x4":
+    return _i64x4(*[int(v) for v in vals])

@@ -1,0 +1,152 @@
+"""GPU-resident chunk K/V + landmark cache: mirror of ``ChunkKVManager``
+(``model/DRT.py:75-233``).
+
+The reference grows its cache with ``torch.cat`` on every append (quadratic copying over a
+long generation) and can park K/V on the host.  Here the cache is a preallocated device
+buffer that is filled in place by one CUDA kernel per append and doubled when full; the
+kernels read it by chunk index, so ``retrieve_chunks`` (the materialised gather) is needed
+only by callers that want the reference's gathered tensors.  The public methods keep the
+reference's names and argument meaning.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+
+class ChunkKVManager:
+    def __init__(self, offloading: bool = False, group_size: int = 1, capacity: int = 0,
+                 zero_landmark: bool = False):
+        # `offloading` is accepted for signature compatibility; the cache always stays in
+        # device memory (180 GB of HBM hold > 50 sequences of 1M tokens at DRT-small scale).
+        self._offloading = offloading
+        self.group_size = group_size
+        self._capacity_hint = capacity
+        self._zero_landmark = zero_landmark
+        self._k: Optional[torch.Tensor] = None       # (N, capacity, L, HD)
+        self._v: Optional[torch.Tensor] = None
+        self._lmk: Optional[torch.Tensor] = None     # (N, capacity, Dm)
+        self._len = 0
+        self._cur_idx: List[Optional[torch.Tensor]] = [None] * group_size
+        self._cur_w: List[Optional[torch.Tensor]] = [None] * group_size
+        self._current_hidden_states = None
+
+    # ------------------------------------------------------------------ storage
+    def __len__(self) -> int:
+        return self._len
+
+    @property
+    def chunk_k(self) -> Optional[torch.Tensor]:
+        return None if self._k is None else self._k[:, :self._len]
+
+    @property
+    def chunk_v(self) -> Optional[torch.Tensor]:
+        return None if self._v is None else self._v[:, :self._len]
+
+    @property
+    def lmk_embs(self) -> Optional[torch.Tensor]:
+        return None if self._lmk is None else self._lmk[:, :self._len]
+
+    @property
+    def past_lmk_embeds(self) -> Optional[torch.Tensor]:
+        return self.lmk_embs
+
+    def _reserve(self, need: int, like_k: torch.Tensor, like_lmk: torch.Tensor) -> None:
+        cap = 0 if self._k is None else self._k.shape[1]
+        if need <= cap:
+            return
+        new_cap = max(need, 2 * cap, self._capacity_hint, 16)
+        n, _, l, hd = like_k.shape
+        k = torch.empty((n, new_cap, l, hd), dtype=like_k.dtype, device=like_k.device)
+        v = torch.empty_like(k)
+        lmk = torch.empty((n, new_cap, like_lmk.shape[-1]), dtype=like_lmk.dtype, device=like_lmk.device)
+        if self._len:
+            k[:, :self._len].copy_(self._k[:, :self._len])
+            v[:, :self._len].copy_(self._v[:, :self._len])
+            lmk[:, :self._len].copy_(self._lmk[:, :self._len])
+        self._k, self._v, self._lmk = k, v, lmk
+
+    def append(self, chunk_k: torch.Tensor, chunk_v: torch.Tensor, lmk_embs: torch.Tensor) -> None:
+        """chunk_k, chunk_v (N, D, S, dim); lmk_embs (N, D, dim)  (``model/DRT.py:87-133``)."""
+        if not chunk_k.is_cuda:
+            raise RuntimeError("ChunkKVManager holds device memory only (there is no CPU path)")
+        if chunk_k.shape != chunk_v.shape or chunk_k.dim() != 4 or lmk_embs.dim() != 3:
+            raise ValueError("expected chunk_k/chunk_v (N, D, S, dim) and lmk_embs (N, D, dim)")
+        if self._k is not None and (chunk_k.shape[-2] != self._k.shape[-2] or chunk_k.shape[0] != self._k.shape[0]):
+            raise ValueError("chunk shape does not match the cache")
+        if self._k is not None:
+            chunk_k, chunk_v = chunk_k.to(self._k.dtype), chunk_v.to(self._k.dtype)
+            lmk_embs = lmk_embs.to(self._lmk.dtype)
+        chunk_k, chunk_v, lmk_embs = chunk_k.contiguous(), chunk_v.contiguous(), lmk_embs.contiguous()
+        n, count, l, hd = chunk_k.shape
+        self._reserve(self._len + count, chunk_k, lmk_embs)
+        if chunk_k.dtype != lmk_embs.dtype:
+            # landmarks kept in another precision than K/V: two launches of the same kernel path
+            self._lmk[:, self._len:self._len + count].copy_(lmk_embs)
+            lmk_src = None
+        else:
+            lmk_src = lmk_embs
+        a = _lib.CacheAppendArgs()
+        a.new_k, a.new_v = chunk_k.data_ptr(), chunk_v.data_ptr()
+        a.k_cache, a.v_cache = self._k.data_ptr(), self._v.data_ptr()
+        a.new_lmk = lmk_src.data_ptr() if lmk_src is not None else None
+        a.lmk_cache = self._lmk.data_ptr() if lmk_src is not None else None
+        a.new_batch_stride, a.cache_batch_stride = chunk_k.stride(0), self._k.stride(0)
+        a.new_lmk_batch_stride, a.lmk_cache_batch_stride = lmk_embs.stride(0), self._lmk.stride(0)
+        a.N, a.count, a.pos, a.L, a.HD, a.Dm = n, count, self._len, l, hd, lmk_embs.shape[-1]
+        a.dtype = _lib.BF16 if chunk_k.dtype == torch.bfloat16 else _lib.F32
+        if chunk_k.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"unsupported cache dtype {chunk_k.dtype}")
+        a.zero_landmark = 1 if self._zero_landmark else 0
+        with torch.cuda.device(chunk_k.device):
+            _lib.check(_lib.lib().gca_cache_append(C.byref(a), torch.cuda.current_stream().cuda_stream),
+                       "gca_cache_append")
+        self._len += count
+
+    # ------------------------------------------------------------------ retrieval state
+    def retrieve_chunks(self, indices: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """indices (N, M) -> gathered k, v (N, M, S, dim)  (``model/DRT.py:193-199``).
+        Compatibility path: the GCA kernels read the cache by index and do not need this."""
+        n = indices.shape[0]
+        batch = torch.arange(n, device=indices.device).unsqueeze(1)
+        idx = indices.clamp(min=0).long()
+        return self.chunk_k[batch, idx], self.chunk_v[batch, idx]
+
+    def update_current_retrieved_chunk(self, indices: torch.Tensor, weights: torch.Tensor, group_idx: int) -> None:
+        """Remember the chunks retrieved for the tokens to come (``model/DRT.py:158-191``):
+        indices (N, K) or (N, Cq, K) (last row is used); weights (N, Cq, K)."""
+        if indices.dim() == 3:
+            indices = indices[:, -1, :]
+        self._cur_idx[group_idx] = indices.to(torch.int32).contiguous()
+        self._cur_w[group_idx] = weights[:, -1:, :].to(torch.float32).contiguous()
+
+    def current_retrieved_indices(self, group_idx: int = 0):
+        """(indices (N, K) int32 with -1 padding, weights (N, 1, K)) for ``gca_indexed``."""
+        return self._cur_idx[group_idx], self._cur_w[group_idx]
+
+    def current_retrieved_chunk(self, group_idx: int = 0):
+        """Gathered (chunk_k (N, K, S, dim), chunk_v, weights (N, 1, K)) like the reference
+        (``model/DRT.py:139-140``); materialised on demand."""
+        idx, w = self._cur_idx[group_idx], self._cur_w[group_idx]
+        if idx is None:
+            return None, None, None
+        k, v = self.retrieve_chunks(idx)
+        return k, v, w
+
+    # ------------------------------------------------------------------ lower hidden-state staging
+    @property
+    def lower_hidden_states(self):
+        return self._current_hidden_states
+
+    def clear_lower_hidden_states(self) -> None:
+        self._current_hidden_states = None
+
+    def cache_lower_hidden_states(self, hidden_states: torch.Tensor) -> None:
+        if self._current_hidden_states is None:
+            self._current_hidden_states = hidden_states
+        else:
+            self._current_hidden_states = torch.cat([self._current_hidden_states, hidden_states], dim=1)

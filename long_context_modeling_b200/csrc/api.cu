@@ -1,0 +1,206 @@
+// extern "C" entry points of libgca_b200.so: argument validation on the host, kernel
+// selection, launches on the caller's stream.  Nothing here allocates device memory.
+#include <cstdlib>
+#include <cstring>
+
+#include "gca_common.cuh"
+
+namespace gca {
+int launch_decode(const GcaFwdArgs& a, cudaStream_t stream);
+int launch_lmk_score_topk(const LmkTopkArgs& a, void* scratch, cudaStream_t stream);
+int launch_lmk_merge(const LmkMergeArgs& a, cudaStream_t stream);
+size_t lmk_topk_workspace_bytes_impl(const LmkTopkArgs& a);
+bool bwd_tc_available();
+int launch_cache_append(const CacheAppendArgs& a, cudaStream_t stream);
+}  // namespace gca
+
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int esize_of(int dtype) { return dtype == GCA_BF16 ? 2 : dtype == GCA_F32 ? 4 : 0; }
+
+// Strides of the four outer axes must keep every row 16-byte aligned.
+int check_strides(const int64_t s[4], int esize, const int32_t dims[4]) {
+  for (int i = 0; i < 4; ++i) {
+    if (dims[i] > 1 || i == 3) {
+      if (s[i] < 0) return GCA_ERR_STRIDE;
+      if (((long long)s[i] * esize) % 16 != 0) return GCA_ERR_STRIDE;
+    }
+  }
+  return 0;
+}
+
+int check_common(const void* q, const void* k, const void* v, const int32_t* idx, const float* w, int dtype, int N,
+                 int J, int Hq, int Hkv, int S, int L, int D, int K, int C) {
+  if (!q || !k || !v || !idx || !w) return GCA_ERR_NULL;
+  if (esize_of(dtype) == 0) return GCA_ERR_DTYPE;
+  if (N < 0 || J < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return GCA_ERR_SHAPE;
+  if (L != 64 || D != 64 || S < 1 || S > 64 || K < 1 || K > 32 || C < 1) return GCA_ERR_SHAPE;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v)) return GCA_ERR_ALIGN;
+  return 0;
+}
+
+int check_fwd(const GcaFwdArgs* a) {
+  if (!a) return GCA_ERR_NULL;
+  int rc = check_common(a->q, a->k_cache, a->v_cache, a->indices, a->weights, a->dtype, a->N, a->J, a->Hq, a->Hkv,
+                        a->S, a->L, a->D, a->K, a->C);
+  if (rc) return rc;
+  if (!a->out) return GCA_ERR_NULL;
+  if (!aligned16(a->out)) return GCA_ERR_ALIGN;
+  if (!(a->sm_scale > 0.f) || a->off_by_one < 0.f) return GCA_ERR_SHAPE;
+  const int es = esize_of(a->dtype);
+  const int32_t qd[4] = {a->N, a->J, a->Hq, a->S};
+  const int32_t kd[4] = {a->N, a->C, a->L, a->Hkv};
+  if ((rc = check_strides(a->q_stride, es, qd))) return rc;
+  if ((rc = check_strides(a->o_stride, es, qd))) return rc;
+  if ((rc = check_strides(a->k_stride, es, kd))) return rc;
+  if ((rc = check_strides(a->v_stride, es, kd))) return rc;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int gca_abi_version(void) { return GCA_ABI_VERSION; }
+
+const char* gca_strerror(int code) {
+  switch (code) {
+    case GCA_OK: return "ok";
+    case GCA_ERR_NULL: return "a required pointer is NULL";
+    case GCA_ERR_DTYPE: return "unsupported dtype";
+    case GCA_ERR_SHAPE: return "dimension outside the supported envelope (L = D = 64, 1 <= S <= 64, 1 <= K <= 32, Hq % Hkv == 0)";
+    case GCA_ERR_STRIDE: return "stride not usable: rows must stay 16-byte aligned";
+    case GCA_ERR_ALIGN: return "base pointer not 16-byte aligned";
+    case GCA_ERR_WORKSPACE: return "workspace missing or too small";
+    case GCA_ERR_ALGO: return "requested kernel variant cannot run this problem";
+    case GCA_ERR_TMA: return "tensor-map encoding rejected by the driver";
+    case GCA_ERR_TOO_LARGE: return "size exceeds a fixed built-in limit";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString((cudaError_t)code);
+  return "unknown error";
+}
+
+int gca_fwd(const GcaFwdArgs* a, void* stream) {
+  int rc = check_fwd(a);
+  if (rc) return rc;
+  if (a->N == 0 || a->J == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  int algo = a->algo;
+  const bool tc_ok = a->dtype == GCA_BF16 && a->S == 64;
+  if (algo == GCA_ALGO_AUTO) algo = tc_ok ? GCA_ALGO_TC : GCA_ALGO_SIMT;
+  if (algo == GCA_ALGO_TC) return tc_ok ? gca::launch_fwd_tc(*a, s) : GCA_ERR_ALGO;
+  if (algo == GCA_ALGO_SIMT) return gca::launch_fwd_simt(*a, s);
+  return GCA_ERR_ALGO;
+}
+
+int gca_decode(const GcaFwdArgs* a, void* stream) {
+  int rc = check_fwd(a);
+  if (rc) return rc;
+  if (a->S > 16) return GCA_ERR_SHAPE;
+  if (a->N == 0 || a->J == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (a->algo != GCA_ALGO_SIMT && a->dtype == GCA_BF16 && (a->Hq / a->Hkv) * a->S <= 16) return gca::launch_decode(*a, s);
+  if (a->algo == GCA_ALGO_TC) return GCA_ERR_ALGO;
+  GcaFwdArgs b = *a;
+  b.lse = nullptr;
+  return gca::launch_fwd_simt(b, s);
+}
+
+static size_t dw_part_bytes(const GcaBwdArgs* a) {
+  return gca::align_up((size_t)a->N * a->J * a->Hq * a->K * sizeof(float), 256);
+}
+
+size_t gca_bwd_workspace_bytes(const GcaBwdArgs* a) {
+  if (!a) return 0;
+  return gca::csr_workspace_bytes(a->N, a->J, a->K, a->C) + dw_part_bytes(a);
+}
+
+int gca_bwd(const GcaBwdArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  int rc = check_common(a->q, a->k_cache, a->v_cache, a->indices, a->weights, a->dtype, a->N, a->J, a->Hq, a->Hkv,
+                        a->S, a->L, a->D, a->K, a->C);
+  if (rc) return rc;
+  if (!a->dout || !a->lse || !a->dq || !a->dk_cache || !a->dv_cache || !a->dw) return GCA_ERR_NULL;
+  if (!aligned16(a->dout) || !aligned16(a->dq) || !aligned16(a->dk_cache) || !aligned16(a->dv_cache)) return GCA_ERR_ALIGN;
+  if (!(a->sm_scale > 0.f) || a->off_by_one < 0.f) return GCA_ERR_SHAPE;
+  const int es = esize_of(a->dtype);
+  const int32_t qd[4] = {a->N, a->J, a->Hq, a->S};
+  const int32_t kd[4] = {a->N, a->C, a->L, a->Hkv};
+  if ((rc = check_strides(a->q_stride, es, qd))) return rc;
+  if ((rc = check_strides(a->do_stride, es, qd))) return rc;
+  if ((rc = check_strides(a->dq_stride, es, qd))) return rc;
+  if ((rc = check_strides(a->k_stride, es, kd))) return rc;
+  if ((rc = check_strides(a->v_stride, es, kd))) return rc;
+  if ((rc = check_strides(a->dk_stride, es, kd))) return rc;
+  if ((rc = check_strides(a->dv_stride, es, kd))) return rc;
+  if (a->N == 0) return 0;
+  if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u)) return GCA_ERR_WORKSPACE;
+  if (a->workspace_bytes < gca_bwd_workspace_bytes(a)) return GCA_ERR_WORKSPACE;
+  cudaStream_t s = (cudaStream_t)stream;
+  gca::Csr csr;
+  size_t used = 0;
+  rc = gca::build_csr(a->indices, a->N, a->J, a->K, a->C, a->workspace, a->workspace_bytes, &csr, &used, s);
+  if (rc) return rc;
+  float* dw_part = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + used);
+  int algo = a->algo;
+  const bool tc_ok = a->dtype == GCA_BF16 && a->S == 64;
+  if (algo == GCA_ALGO_AUTO) algo = (tc_ok && gca::bwd_tc_available()) ? GCA_ALGO_TC : GCA_ALGO_SIMT;
+  if (algo == GCA_ALGO_TC) rc = tc_ok ? gca::launch_bwd_tc(*a, csr, dw_part, s) : GCA_ERR_ALGO;
+  else if (algo == GCA_ALGO_SIMT) rc = gca::launch_bwd_simt(*a, csr, dw_part, s);
+  else rc = GCA_ERR_ALGO;
+  if (rc) return rc;
+  return gca::launch_dw_reduce(dw_part, a->dw, a->N * a->J, a->Hq, a->K, s);
+}
+
+static int check_topk(const LmkTopkArgs* a) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->lmk_q || !a->lmk_k || !a->out_keys) return GCA_ERR_NULL;
+  if (a->N < 0 || a->Cq < 0 || a->E < 0) return GCA_ERR_SHAPE;
+  if (a->D < 8 || a->D % 8 != 0 || a->D > 1024 || a->K < 1 || a->K > 32) return GCA_ERR_SHAPE;
+  if (a->head_dim != 0 && (a->head_dim != 64 || a->D % 64 != 0 || a->noise)) return GCA_ERR_SHAPE;
+  if (!aligned16(a->lmk_q) || !aligned16(a->lmk_k)) return GCA_ERR_ALIGN;
+  if (a->q_row_stride % 8 || a->k_row_stride % 8 || a->q_batch_stride % 8 || a->k_batch_stride % 8) return GCA_ERR_STRIDE;
+  if (a->e_base < 0 || a->e_base + a->E >= 0xffffffffll) return GCA_ERR_TOO_LARGE;
+  if (a->splits < 0) return GCA_ERR_SHAPE;
+  return 0;
+}
+
+size_t lmk_topk_workspace_bytes(const LmkTopkArgs* a) {
+  if (check_topk(a)) return 0;
+  return gca::lmk_topk_workspace_bytes_impl(*a);
+}
+
+int lmk_score_topk(const LmkTopkArgs* a, void* stream) {
+  int rc = check_topk(a);
+  if (rc) return rc;
+  if (a->N == 0 || a->Cq == 0) return 0;
+  const size_t need = gca::lmk_topk_workspace_bytes_impl(*a);
+  if (!a->workspace || a->workspace_bytes < need) return GCA_ERR_WORKSPACE;
+  return gca::launch_lmk_score_topk(*a, a->workspace, (cudaStream_t)stream);
+}
+
+int lmk_topk_merge(const LmkMergeArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->keys || !a->out_keys) return GCA_ERR_NULL;
+  if (a->R < 0 || a->P < 1 || a->K < 1 || a->K > 32) return GCA_ERR_SHAPE;
+  return gca::launch_lmk_merge(*a, (cudaStream_t)stream);
+}
+
+int gca_cache_append(const CacheAppendArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->new_k || !a->new_v || !a->k_cache || !a->v_cache) return GCA_ERR_NULL;
+  const int es = esize_of(a->dtype);
+  if (es == 0) return GCA_ERR_DTYPE;
+  if (a->N < 0 || a->count < 0 || a->pos < 0 || a->L < 1 || a->HD < 1) return GCA_ERR_SHAPE;
+  if ((a->HD * es) % 16 != 0 || (a->new_lmk && (a->Dm * es) % 16 != 0)) return GCA_ERR_SHAPE;
+  if ((a->new_batch_stride * es) % 16 || (a->cache_batch_stride * es) % 16) return GCA_ERR_STRIDE;
+  if (a->new_lmk && ((a->new_lmk_batch_stride * es) % 16 || (a->lmk_cache_batch_stride * es) % 16)) return GCA_ERR_STRIDE;
+  if (!aligned16(a->new_k) || !aligned16(a->new_v) || !aligned16(a->k_cache) || !aligned16(a->v_cache)) return GCA_ERR_ALIGN;
+  if (a->new_lmk && (!aligned16(a->new_lmk) || !a->lmk_cache || !aligned16(a->lmk_cache))) return GCA_ERR_ALIGN;
+  return gca::launch_cache_append(*a, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,67 @@
+// Shared declarations for the GCA kernels: argument views, dtype helpers, error checks.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gca_b200.h"
+
+#define GCA_LOG2E 1.4426950408889634f
+
+#define GCA_CUDA_CHECK(expr)                         \
+  do {                                               \
+    cudaError_t _e = (expr);                         \
+    if (_e != cudaSuccess) return (int)_e;           \
+  } while (0)
+
+namespace gca {
+
+// Element-typed load/store that always computes in float.
+template <typename T> __device__ __forceinline__ float ld_f(const T* p);
+template <> __device__ __forceinline__ float ld_f<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ld_f<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+template <typename T> __device__ __forceinline__ void st_f(T* p, float v);
+template <> __device__ __forceinline__ void st_f<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void st_f<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16_rn(v);
+}
+
+// Problem geometry shared by forward and backward kernels (passed by value).
+struct Geom {
+  int N, J, Hq, Hkv, S, L, D, K, C, G;
+  long long qs[4];   // q   strides n, j, h, s
+  long long os[4];   // out / dq strides
+  long long ks[4];   // k   strides n, c, l, h
+  long long vs[4];   // v   strides n, c, l, h
+  float sm_scale;
+  float off_by_one;
+};
+
+// Inverse retrieval index: for every cache chunk (n, c) the sorted list of (j*K + k)
+// entries that retrieved it.  `offsets` has N*C + 1 entries into `sorted_keys`, whose low
+// 32 bits hold the entry.
+struct Csr {
+  const int* offsets;
+  const unsigned long long* sorted_keys;
+};
+
+int build_csr(const int32_t* indices, int N, int J, int K, int C, void* workspace, size_t workspace_bytes,
+              Csr* out, size_t* used_bytes, cudaStream_t stream);
+size_t csr_workspace_bytes(int N, int J, int K, int C);
+
+// SIMT (CUDA-core, fp32 accumulate) kernels: every dtype, S <= 64, L = D = 64.
+int launch_fwd_simt(const GcaFwdArgs& a, cudaStream_t stream);
+int launch_bwd_simt(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream);
+
+// tcgen05 / TMEM / TMA kernels: bf16, S = L = D = 64.
+int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream);
+int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream);
+
+int launch_dw_reduce(const float* dw_part, float* dw, int ZJ, int Hq, int K, cudaStream_t stream);
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace gca

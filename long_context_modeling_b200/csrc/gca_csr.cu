@@ -1,0 +1,82 @@
+// Inverse retrieval index for the kv-major backward pass.
+//
+// For every cache chunk (n, c) the backward needs the list of (query chunk j, slot k)
+// pairs that retrieved it, in a fixed order so that float32 accumulation is reproducible.
+// Each valid entry becomes the 64-bit key  (n*C + c) << 32 | (j*K + k); a radix sort
+// of the keys gives the lists back to back, and a binary search per chunk finds where
+// each list starts.  Padding slots (index < 0) and out-of-range indices sort to the end.
+#include <cub/device/device_radix_sort.cuh>
+
+#include "gca_common.cuh"
+
+namespace gca {
+
+namespace {
+
+__global__ void csr_keys_kernel(const int32_t* __restrict__ indices, unsigned long long* __restrict__ keys,
+                                int N, int JK, int C) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)N * JK) return;
+  const int n = (int)(i / JK);
+  const int t = (int)(i % JK);
+  const int idx = indices[i];
+  keys[i] = (idx < 0 || idx >= C) ? ~0ull
+                                  : (((unsigned long long)((long long)n * C + idx)) << 32) | (unsigned)t;
+}
+
+__global__ void csr_offsets_kernel(const unsigned long long* __restrict__ sorted, int* __restrict__ offsets,
+                                   long long total, long long NC) {
+  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c > NC) return;
+  const unsigned long long target = (unsigned long long)c << 32;   // first key of chunk c (or end)
+  long long lo = 0, hi = total;
+  while (lo < hi) {
+    const long long mid = (lo + hi) >> 1;
+    if (sorted[mid] < target) lo = mid + 1; else hi = mid;
+  }
+  offsets[c] = (int)lo;
+}
+
+size_t cub_temp_bytes(long long total) {
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortKeys(nullptr, bytes, (const unsigned long long*)nullptr,
+                                 (unsigned long long*)nullptr, (int)total);
+  return bytes;
+}
+
+}  // namespace
+
+size_t csr_workspace_bytes(int N, int J, int K, int C) {
+  const long long total = (long long)N * J * K;
+  const long long NC = (long long)N * C;
+  return align_up(total * 8, 256) * 2 + align_up((NC + 1) * 4, 256) + align_up(cub_temp_bytes(total), 256);
+}
+
+int build_csr(const int32_t* indices, int N, int J, int K, int C, void* workspace, size_t workspace_bytes,
+              Csr* out, size_t* used_bytes, cudaStream_t stream) {
+  const long long total = (long long)N * J * K;
+  const long long NC = (long long)N * C;
+  if (total >= (1ll << 31) || NC >= (1ll << 31)) return GCA_ERR_TOO_LARGE;
+  const size_t need = csr_workspace_bytes(N, J, K, C);
+  if (!workspace || workspace_bytes < need) return GCA_ERR_WORKSPACE;
+  char* p = (char*)workspace;
+  unsigned long long* keys_in = (unsigned long long*)p;  p += align_up(total * 8, 256);
+  unsigned long long* keys_out = (unsigned long long*)p; p += align_up(total * 8, 256);
+  int* offsets = (int*)p;                                p += align_up((NC + 1) * 4, 256);
+  size_t temp = cub_temp_bytes(total);
+  void* temp_ptr = p;
+  if (total > 0) {
+    csr_keys_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(indices, keys_in, N, J * K, C);
+    GCA_CUDA_CHECK(cudaGetLastError());
+    // keys of valid entries use at most 32 + ceil(log2(N*C)) bits; invalid ones are all-ones
+    GCA_CUDA_CHECK(cub::DeviceRadixSort::SortKeys(temp_ptr, temp, keys_in, keys_out, (int)total, 0, 64, stream));
+  }
+  csr_offsets_kernel<<<(unsigned)((NC + 1 + 255) / 256), 256, 0, stream>>>(keys_out, offsets, total, NC);
+  GCA_CUDA_CHECK(cudaGetLastError());
+  out->offsets = offsets;
+  out->sorted_keys = keys_out;
+  *used_bytes = need;
+  return 0;
+}
+
+}  // namespace gca

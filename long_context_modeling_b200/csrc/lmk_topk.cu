@@ -1,0 +1,374 @@
+// Landmark scoring + causal chunk mask + top-k + retrieval weights.
+//
+// The cached landmarks (E rows of D bf16 values) are streamed once.  One warp scores one
+// landmark row at a time: the row is cut in 8-element (16-byte) pieces, lane l owns pieces
+// l, l+32, l+64, ... so every load instruction of the warp covers 512 contiguous bytes.
+// The float32 dot product is accumulated in a FIXED order (pieces in increasing order inside
+// a lane, then a butterfly over the lanes), which makes every score -- and therefore every
+// selected index -- independent of grid size, split count and GPU count.
+//
+// Candidates are 64-bit keys  orderable(score) << 32 | (0xFFFFFFFF - global_index):  a
+// larger key is a better candidate, equal scores resolve to the lower index, and merging
+// lists from warps, blocks or GPUs is a plain integer top-k.  Key 0 means "empty".
+//
+// Each warp keeps its running top-K per query row as a sorted list spread over its lanes
+// (lane i holds the i-th best).  Blocks write their lists to a scratch buffer; a second,
+// tiny kernel merges the lists of all blocks of a row and emits indices, noise-free scores,
+// softmax weights and the number of valid slots.
+#include "gca_common.cuh"
+
+namespace gca {
+
+namespace {
+
+constexpr int SCAN_WARPS = 8;
+constexpr int MAXK = 32;
+
+__device__ __forceinline__ unsigned orderable(float s) {
+  const unsigned u = __float_as_uint(s);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float from_orderable(unsigned o) {
+  return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
+}
+__device__ __forceinline__ unsigned long long make_key(float score, unsigned gidx) {
+  return ((unsigned long long)orderable(score) << 32) | (unsigned long long)(0xffffffffu - gidx);
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// Insert `key` into the descending list held one element per lane.  Warp-uniform call.
+__device__ __forceinline__ void list_insert(unsigned long long& mine, unsigned long long key, int lane) {
+  const bool lower = mine < key;
+  const unsigned long long up = __shfl_up_sync(0xffffffffu, mine, 1);
+  const int lower_prev = __shfl_up_sync(0xffffffffu, (int)lower, 1);
+  if (lower) mine = (lane > 0 && lower_prev) ? up : key;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float f[8]) {
+  f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+  f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+  f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+  f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+struct ScanParams {
+  const __nv_bfloat16* lq;
+  const __nv_bfloat16* lk;
+  const float* noise;
+  unsigned long long* part;     // (rows, splits, K)
+  long long qbs, qrs, kbs, krs;
+  long long q_pos0, e_base;
+  int N, Cq, E, D, K, H;
+  int splits, e_per_split;
+  int score_round;
+  float scale;
+};
+
+// NP: pieces per lane (D <= 256*NP).  TQ: query rows per block (per-sequence mode).
+// PER_HEAD: head_dim == 64, one list per head, TQ must be 1.
+template <int NP, int TQ, bool PER_HEAD>
+__global__ void __launch_bounds__(SCAN_WARPS * 32)
+lmk_scan_kernel(ScanParams p) {
+  constexpr int NL = PER_HEAD ? NP * 4 : TQ;
+  __shared__ unsigned long long sL[SCAN_WARPS][NL][MAXK];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, t0 = blockIdx.y * TQ, n = blockIdx.z;
+  const int pieces = p.D >> 3;
+
+  float qf[TQ][NP][8];
+#pragma unroll
+  for (int t = 0; t < TQ; ++t)
+#pragma unroll
+    for (int pp = 0; pp < NP; ++pp) {
+      const int c = lane + 32 * pp;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (c < pieces && t0 + t < p.Cq)
+        v = *reinterpret_cast<const uint4*>(p.lq + n * p.qbs + (long long)(t0 + t) * p.qrs + c * 8);
+      unpack8(v, qf[t][pp]);
+    }
+
+  unsigned long long mine[NL], thr[NL];
+#pragma unroll
+  for (int l = 0; l < NL; ++l) { mine[l] = 0ull; thr[l] = 0ull; }
+
+  const int e_lo = split * p.e_per_split;
+  const int e_hi = min(p.E, e_lo + p.e_per_split);
+  const __nv_bfloat16* kb = p.lk + n * p.kbs;
+  // the last query row of the tile sees the most chunks: rows past that limit are skipped
+  const long long tile_limit = p.q_pos0 + min(t0 + TQ, p.Cq) - 1;
+
+  for (int e = e_lo + warp; e < e_hi; e += 2 * SCAN_WARPS) {
+    uint4 kv[2][NP];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int eu = e + u * SCAN_WARPS;
+#pragma unroll
+      for (int pp = 0; pp < NP; ++pp) {
+        const int c = lane + 32 * pp;
+        kv[u][pp] = make_uint4(0, 0, 0, 0);
+        if (eu < e_hi && c < pieces && p.e_base + eu < tile_limit)
+          kv[u][pp] = *reinterpret_cast<const uint4*>(kb + (long long)eu * p.krs + c * 8);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int eu = e + u * SCAN_WARPS;
+      const long long eg = p.e_base + eu;
+      if (eu >= e_hi || eg >= tile_limit) continue;     // warp-uniform
+      float kf[NP][8];
+#pragma unroll
+      for (int pp = 0; pp < NP; ++pp) unpack8(kv[u][pp], kf[pp]);
+      if (!PER_HEAD) {
+#pragma unroll
+        for (int t = 0; t < TQ; ++t) {
+          float acc = 0.f;
+#pragma unroll
+          for (int pp = 0; pp < NP; ++pp)
+            if (lane + 32 * pp < pieces) {
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) acc = fmaf(qf[t][pp][jj], kf[pp][jj], acc);
+            }
+#pragma unroll
+          for (int of = 16; of > 0; of >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, of);
+          float s = p.score_round ? round_bf16(round_bf16(acc) * p.scale) : acc * p.scale;
+          const int row = t0 + t;
+          const bool vis = row < p.Cq && eg < p.q_pos0 + row;
+          if (p.noise && vis) s += p.noise[((long long)n * p.Cq + row) * p.E + eu];
+          const unsigned long long key = make_key(s, (unsigned)eg);
+          if (vis && key > thr[t]) {
+            list_insert(mine[t], key, lane);
+            thr[t] = __shfl_sync(0xffffffffu, mine[t], p.K - 1);
+          }
+        }
+      } else {
+        const bool vis = eg < p.q_pos0 + t0;
+#pragma unroll
+        for (int pp = 0; pp < NP; ++pp) {
+          float acc = 0.f;
+          if (lane + 32 * pp < pieces) {
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) acc = fmaf(qf[0][pp][jj], kf[pp][jj], acc);
+          }
+#pragma unroll
+          for (int of = 4; of > 0; of >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, of);
+#pragma unroll
+          for (int hg = 0; hg < 4; ++hg) {
+            const int l = pp * 4 + hg;
+            const float raw = __shfl_sync(0xffffffffu, acc, hg * 8);
+            const float s = p.score_round ? round_bf16(round_bf16(raw) * p.scale) : raw * p.scale;
+            const unsigned long long key = make_key(s, (unsigned)eg);
+            if (vis && l < p.H && key > thr[l]) {
+              list_insert(mine[l], key, lane);
+              thr[l] = __shfl_sync(0xffffffffu, mine[l], p.K - 1);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // merge the 8 per-warp lists of every row of the tile; list l is merged by warp l % 8
+#pragma unroll
+  for (int l = 0; l < NL; ++l)
+    if (lane < p.K) sL[warp][l][lane] = mine[l];
+  __syncthreads();
+#pragma unroll
+  for (int l = 0; l < NL; ++l) {
+    if ((l % SCAN_WARPS) != warp) continue;
+    long long row;
+    if (PER_HEAD) { if (l >= p.H) continue; row = ((long long)n * p.Cq + t0) * p.H + l; }
+    else          { if (t0 + l >= p.Cq) continue; row = (long long)n * p.Cq + t0 + l; }
+    unsigned long long m = 0ull, th = 0ull;
+    for (int w = 0; w < SCAN_WARPS; ++w)
+      for (int i = 0; i < p.K; ++i) {
+        const unsigned long long key = sL[w][l][i];
+        if (key <= th) break;                              // lists are descending
+        list_insert(m, key, lane);
+        th = __shfl_sync(0xffffffffu, m, p.K - 1);
+      }
+    if (lane < p.K) p.part[(row * p.splits + split) * p.K + lane] = m;
+  }
+}
+
+struct FinalParams {
+  const unsigned long long* keys;   // (R, P)
+  unsigned long long* out_keys;
+  int32_t* out_indices;
+  float* out_scores;
+  float* out_weights;
+  int32_t* out_nvalid;
+  // optional recompute of noise-free scores (per-sequence mode with noise)
+  const __nv_bfloat16* lq;
+  const __nv_bfloat16* lk;
+  long long qbs, qrs, kbs, krs, e_base;
+  int Cq, D, score_round;
+  float scale;
+  int R, P, K;
+};
+
+constexpr int FIN_WARPS = 8;
+
+__global__ void __launch_bounds__(FIN_WARPS * 32)
+lmk_finalize_kernel(FinalParams p) {
+  __shared__ unsigned long long sL[FIN_WARPS][MAXK];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = blockIdx.x;
+  const unsigned long long* src = p.keys + row * p.P;
+  // each warp merges a contiguous share of the candidates
+  const int per = (p.P + FIN_WARPS - 1) / FIN_WARPS;
+  const int lo = warp * per, hi = min(p.P, lo + per);
+  unsigned long long m = 0ull, th = 0ull;
+  for (int i0 = lo; i0 < hi; i0 += 32) {
+    const unsigned long long mykey = (i0 + lane < hi) ? src[i0 + lane] : 0ull;
+    unsigned pending = __ballot_sync(0xffffffffu, mykey > th);
+    while (pending) {
+      const int srcl = __ffs(pending) - 1;
+      pending &= pending - 1;
+      const unsigned long long key = __shfl_sync(0xffffffffu, mykey, srcl);
+      if (key > th) {
+        list_insert(m, key, lane);
+        th = __shfl_sync(0xffffffffu, m, p.K - 1);
+      }
+    }
+  }
+  if (lane < p.K) sL[warp][lane] = m;
+  __syncthreads();
+  if (warp != 0) return;
+  m = 0ull; th = 0ull;
+  for (int w = 0; w < FIN_WARPS; ++w)
+    for (int i = 0; i < p.K; ++i) {
+      const unsigned long long key = sL[w][i];
+      if (key <= th) break;
+      list_insert(m, key, lane);
+      th = __shfl_sync(0xffffffffu, m, p.K - 1);
+    }
+  const bool valid = lane < p.K && m != 0ull;
+  const int idx = valid ? (int)(0xffffffffu - (unsigned)(m & 0xffffffffull)) : -1;
+  float score = valid ? from_orderable((unsigned)(m >> 32)) : -INFINITY;
+  if (p.lq) {
+    // selection used noisy scores: recompute the noise-free score of every winner in the
+    // same fixed order as the scan
+    const long long n = row / p.Cq, r = row % p.Cq;
+    const int pieces = p.D >> 3;
+    for (int i = 0; i < p.K; ++i) {
+      const int wi = __shfl_sync(0xffffffffu, idx, i);
+      if (wi < 0) continue;
+      float acc = 0.f;
+      for (int c = lane; c < pieces; c += 32) {
+        const uint4 a = *reinterpret_cast<const uint4*>(p.lq + n * p.qbs + r * p.qrs + c * 8);
+        const uint4 b = *reinterpret_cast<const uint4*>(p.lk + n * p.kbs + (wi - p.e_base) * p.krs + c * 8);
+        float af[8], bf[8];
+        unpack8(a, af); unpack8(b, bf);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) acc = fmaf(af[jj], bf[jj], acc);
+      }
+#pragma unroll
+      for (int of = 16; of > 0; of >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, of);
+      const float s = p.score_round ? round_bf16(round_bf16(acc) * p.scale) : acc * p.scale;
+      if (lane == i) score = s;
+    }
+  }
+  // softmax over the valid slots
+  float mx = valid ? score : -INFINITY;
+#pragma unroll
+  for (int of = 16; of > 0; of >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, of));
+  float ex = valid ? expf(score - mx) : 0.f;
+  float sum = ex;
+#pragma unroll
+  for (int of = 16; of > 0; of >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, of);
+  const float wgt = (valid && sum > 0.f) ? ex / sum : 0.f;
+  const unsigned nv = __popc(__ballot_sync(0xffffffffu, valid));
+  if (lane < p.K) {
+    const long long o = row * p.K + lane;
+    if (p.out_keys) p.out_keys[o] = m;
+    if (p.out_indices) p.out_indices[o] = idx;
+    if (p.out_scores) p.out_scores[o] = score;
+    if (p.out_weights) p.out_weights[o] = wgt;
+  }
+  if (lane == 0 && p.out_nvalid) p.out_nvalid[row] = (int)nv;
+}
+
+int choose_splits(const LmkTopkArgs& a, int tq) {
+  if (a.splits > 0) return a.splits;
+  const long long blocks = (long long)a.N * ((a.Cq + tq - 1) / tq);
+  long long s = (2 * 148 + blocks - 1) / blocks;
+  const long long max_s = (a.E + 255) / 256;              // keep at least 256 rows per split
+  if (s > max_s) s = max_s;
+  if (s < 1) s = 1;
+  return (int)s;
+}
+
+int pick_tq(const LmkTopkArgs& a) { return (a.head_dim > 0 || a.Cq < 4) ? 1 : 4; }
+
+template <int NP>
+void launch_scan(const ScanParams& sp, int tq, bool per_head, dim3 grid, cudaStream_t stream) {
+  if (per_head) lmk_scan_kernel<NP, 1, true><<<grid, SCAN_WARPS * 32, 0, stream>>>(sp);
+  else if (tq == 1) lmk_scan_kernel<NP, 1, false><<<grid, SCAN_WARPS * 32, 0, stream>>>(sp);
+  else lmk_scan_kernel<NP, 4, false><<<grid, SCAN_WARPS * 32, 0, stream>>>(sp);
+}
+
+}  // namespace
+
+size_t lmk_topk_rows(const LmkTopkArgs& a) {
+  const int H = a.head_dim > 0 ? a.D / a.head_dim : 1;
+  return (size_t)a.N * a.Cq * H;
+}
+
+size_t lmk_topk_workspace_bytes_impl(const LmkTopkArgs& a) {
+  const int splits = choose_splits(a, pick_tq(a));
+  return align_up(lmk_topk_rows(a) * (size_t)splits * a.K * sizeof(unsigned long long), 256);
+}
+
+// Scan + finalize on caller-provided scratch.  `scratch` must hold
+// lmk_topk_workspace_bytes_impl(a) bytes.
+int launch_lmk_score_topk(const LmkTopkArgs& a, void* scratch, cudaStream_t stream) {
+  const bool per_head = a.head_dim > 0;
+  const int H = per_head ? a.D / a.head_dim : 1;
+  const int tq = pick_tq(a);
+  const int splits = choose_splits(a, tq);
+  ScanParams sp;
+  sp.lq = (const __nv_bfloat16*)a.lmk_q; sp.lk = (const __nv_bfloat16*)a.lmk_k; sp.noise = a.noise;
+  sp.part = (unsigned long long*)scratch;
+  sp.qbs = a.q_batch_stride; sp.qrs = a.q_row_stride; sp.kbs = a.k_batch_stride; sp.krs = a.k_row_stride;
+  sp.q_pos0 = a.q_pos0; sp.e_base = a.e_base;
+  sp.N = a.N; sp.Cq = a.Cq; sp.E = a.E; sp.D = a.D; sp.K = a.K; sp.H = H;
+  sp.splits = splits; sp.e_per_split = (a.E + splits - 1) / splits;
+  sp.score_round = a.score_round;
+  sp.scale = (float)(1.0 / sqrt((double)(per_head ? a.head_dim : a.D)));
+  const size_t rows = lmk_topk_rows(a);
+  if (rows == 0) return 0;
+  dim3 grid((unsigned)splits, (unsigned)((a.Cq + tq - 1) / tq), (unsigned)a.N);
+  const int np = (a.D + 255) / 256;
+  switch (np) {
+    case 1: launch_scan<1>(sp, tq, per_head, grid, stream); break;
+    case 2: launch_scan<2>(sp, tq, per_head, grid, stream); break;
+    case 3: launch_scan<3>(sp, tq, per_head, grid, stream); break;
+    case 4: launch_scan<4>(sp, tq, per_head, grid, stream); break;
+    default: return GCA_ERR_SHAPE;
+  }
+  GCA_CUDA_CHECK(cudaGetLastError());
+  FinalParams fp;
+  fp.keys = sp.part; fp.out_keys = (unsigned long long*)a.out_keys; fp.out_indices = a.out_indices; fp.out_scores = a.out_scores;
+  fp.out_weights = a.out_weights; fp.out_nvalid = a.out_nvalid;
+  const bool recompute = a.noise != nullptr && !per_head;
+  fp.lq = recompute ? sp.lq : nullptr; fp.lk = sp.lk;
+  fp.qbs = sp.qbs; fp.qrs = sp.qrs; fp.kbs = sp.kbs; fp.krs = sp.krs; fp.e_base = a.e_base;
+  fp.Cq = a.Cq; fp.D = a.D; fp.score_round = a.score_round; fp.scale = sp.scale;
+  fp.R = (int)rows; fp.P = splits * a.K; fp.K = a.K;
+  lmk_finalize_kernel<<<(unsigned)rows, FIN_WARPS * 32, 0, stream>>>(fp);
+  return (int)cudaGetLastError();
+}
+
+int launch_lmk_merge(const LmkMergeArgs& a, cudaStream_t stream) {
+  if (a.R == 0) return 0;
+  FinalParams fp;
+  fp.keys = (const unsigned long long*)a.keys; fp.out_keys = (unsigned long long*)a.out_keys; fp.out_indices = a.out_indices; fp.out_scores = a.out_scores;
+  fp.out_weights = a.out_weights; fp.out_nvalid = a.out_nvalid;
+  fp.lq = nullptr; fp.lk = nullptr; fp.qbs = fp.qrs = fp.kbs = fp.krs = fp.e_base = 0;
+  fp.Cq = 1; fp.D = 0; fp.score_round = 0; fp.scale = 1.f;
+  fp.R = a.R; fp.P = a.P; fp.K = a.K;
+  lmk_finalize_kernel<<<(unsigned)a.R, FIN_WARPS * 32, 0, stream>>>(fp);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace gca

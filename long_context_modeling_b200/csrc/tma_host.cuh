@@ -1,0 +1,54 @@
+// Host-side construction of TMA tensor maps for 64 x 64 bf16 tiles with 128-byte swizzle.
+// The driver entry point is resolved through the runtime so the library does not link
+// against libcuda directly.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gca_b200.h"
+
+namespace gca {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    if (q != cudaDriverEntryPointSuccess) return nullptr;
+    return (EncodeTiledFn)f;
+  }();
+  return fn;
+}
+
+// A bf16 tensor viewed as (d0 = 64 contiguous, d1, d2, d3, d4) with element strides s1..s4;
+// every copy moves one (64 x 64 x 1 x 1 x 1) box, i.e. 64 rows of 128 bytes, swizzled.
+inline int make_tile_map_5d(CUtensorMap* map, const void* base, int d0, int d1, int d2, int d3, int d4,
+                            long long s1, long long s2, long long s3, long long s4) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return GCA_ERR_TMA;
+  const long long dims_in[5] = {d0, d1, d2, d3, d4};
+  long long str_in[4] = {s1, s2, s3, s4};
+  cuuint64_t dims[5];
+  cuuint64_t strides[4];
+  for (int i = 0; i < 5; ++i) dims[i] = (cuuint64_t)dims_in[i];
+  for (int i = 0; i < 4; ++i) {
+    // a dimension of extent 1 never advances: any legal stride will do
+    if (dims_in[i + 1] == 1 && (str_in[i] <= 0 || (str_in[i] % 8) != 0)) str_in[i] = 64;
+    if (str_in[i] <= 0 || (str_in[i] % 8) != 0) return GCA_ERR_STRIDE;
+    strides[i] = (cuuint64_t)str_in[i] * 2;
+  }
+  const cuuint32_t box[5] = {64, 64, 1, 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : GCA_ERR_TMA;
+}
+
+}  // namespace gca

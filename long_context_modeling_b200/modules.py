@@ -1,0 +1,125 @@
+"""The GCA sub-layer as an ``nn.Module``: mirror of ``TritonGroupCrossAttention``
+(``model/DRT.py:304-398``) with the same parameter names (``pre_norm``, ``q_proj``,
+``o_proj``) so reference checkpoints load.
+
+``forward`` keeps the reference's argument meaning (pre-gathered chunks).  ``forward_indexed``
+is the fast path: the query is handed to the kernel as a strided view of the projection
+output and K/V are read from the chunk cache by retrieved index, so neither the gather
+(``model/DRT.py:198-199``) nor the two layout copies (``:328-332``, ``:372-378``) happen.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+
+from . import gca
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, hidden_size: int, eps: float = 1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        dt = x.dtype
+        x = x.float()
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps)
+        return (x * self.weight.float()).to(dt)
+
+
+def preprocess_chunk_kv_cache(chunk_k: torch.Tensor, chunk_v: torch.Tensor, weights: torch.Tensor, num_heads: int):
+    """``TritonGroupCrossAttention.preprocess_chunk_kv_cache`` (``model/DRT.py:320-332``):
+    chunk_k/v (N, D*K, S, h*d), weights (N, D, K) -> k, v (N*D, h, K, S, d), weights (N*D, K)."""
+    n, dk, s, hd = chunk_k.shape
+    kk = weights.shape[-1]
+    d = dk // kk
+    hdim = hd // num_heads
+
+    def split(t):
+        return t.reshape(n, d, kk, s, num_heads, hdim).permute(0, 1, 4, 2, 3, 5).reshape(n * d, num_heads, kk, s, hdim).contiguous()
+
+    return split(chunk_k), split(chunk_v), weights.reshape(n * d, kk)
+
+
+class TritonGroupCrossAttention(nn.Module):
+    def __init__(self, hidden_size: int, num_heads: int, enc_chunk_size: int = 63, chunk_topk: int = 8,
+                 rms_norm_eps: float = 1e-5, attention_bias: bool = False, enable_softmax_one: bool = False):
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.num_heads = num_heads
+        self.head_dim = hidden_size // num_heads
+        self.enc_chunk_size = enc_chunk_size
+        self.topK = chunk_topk
+        self.pre_norm = RMSNorm(hidden_size, eps=rms_norm_eps)
+        self.q_proj = nn.Linear(hidden_size, num_heads * self.head_dim, bias=attention_bias)
+        self.o_proj = nn.Linear(hidden_size, num_heads * self.head_dim, bias=attention_bias)
+        self.enable_softmax_one = enable_softmax_one
+        self.sm_n = 1.0 if enable_softmax_one else 0.0          # model/DRT.py:317-318
+
+    @classmethod
+    def from_config(cls, config):
+        return cls(config.hidden_size, config.num_attention_heads, config.enc_chunk_size, config.chunk_topk,
+                   getattr(config, "rms_norm_eps", 1e-5), getattr(config, "attention_bias", False),
+                   getattr(config, "enable_softmax_one", False))
+
+    preprocess_chunk_kv_cache = staticmethod(preprocess_chunk_kv_cache)
+
+    def _zeros(self, hidden_states):
+        return torch.zeros((hidden_states.shape[0], hidden_states.shape[1] * hidden_states.shape[2],
+                            hidden_states.shape[-1]), dtype=hidden_states.dtype, device=hidden_states.device)
+
+    def _pad_first_chunk(self, hidden_states, o):
+        """The first chunk has nothing to retrieve: its rows are zeros (model/DRT.py:387-394)."""
+        ret = torch.zeros((hidden_states.shape[0], hidden_states.shape[1] * hidden_states.shape[2],
+                           hidden_states.shape[-1]), dtype=o.dtype, device=o.device)
+        ret[:, -o.shape[1]:, :] = o
+        return ret
+
+    def forward(self, hidden_states: torch.Tensor, chunk_k: torch.Tensor, chunk_v: torch.Tensor,
+                weights: torch.Tensor) -> torch.Tensor:
+        """hidden_states (N, D, S, dim); chunk_k/v (N*D', h, K, S, d); weights (N*D', K) with
+        D' = D-1 when D > 1 (the first chunk is skipped) -- ``model/DRT.py:345-398``."""
+        hs = self.pre_norm(hidden_states)
+        chunk_size = hs.shape[1]
+        q = self.q_proj(hs)
+        n, dd, s, _ = q.shape
+        q = q.view(n, dd, s, self.num_heads, self.head_dim).permute(0, 1, 3, 2, 4)   # N D h S d (view)
+        if weights.shape[0] * weights.shape[1] == 0:
+            return self._zeros(hidden_states)
+        if chunk_size > 1:
+            q = q[:, 1:]
+        q = q.reshape(-1, self.num_heads, s, self.head_dim).contiguous()
+        scale = 1.0 / math.sqrt(self.head_dim)
+        if chunk_size > 1 and self.training:
+            vals = gca.attention(q, chunk_k, chunk_v, weights, scale, self.sm_n)
+        else:
+            vals = gca.gca_kv_cache(q, chunk_k, chunk_v, weights, scale, self.sm_n)
+        vals = vals.view(n, -1, self.num_heads, s, self.head_dim).permute(0, 1, 3, 2, 4).reshape(n, -1, self.hidden_size)
+        o = self.o_proj(vals)
+        return self._pad_first_chunk(hidden_states, o) if chunk_size > 1 else o
+
+    def forward_indexed(self, hidden_states: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                        indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """hidden_states (N, D, S, dim); caches (N, C, L, h*d); indices / weights (N, D', K)
+        where D' = D-1 for D > 1 (query chunk j uses the retrieval made by chunk j-1) and
+        D' = D = 1 while decoding."""
+        hs = self.pre_norm(hidden_states)
+        chunk_size = hs.shape[1]
+        q = self.q_proj(hs)
+        n, dd, s, _ = q.shape
+        if indices.shape[1] * indices.shape[2] == 0:
+            return self._zeros(hidden_states)
+        q5 = q.view(n, dd, s, self.num_heads, self.head_dim).permute(0, 1, 3, 2, 4)  # strided view, no copy
+        if chunk_size > 1:
+            q5 = q5[:, 1:]
+        scale = 1.0 / math.sqrt(self.head_dim)
+        if torch.is_grad_enabled() and (q5.requires_grad or k_cache.requires_grad or weights.requires_grad):
+            vals = gca.gca_indexed(q5, k_cache, v_cache, indices, weights, scale, self.sm_n, token_major_out=True)
+        else:
+            vals = gca.gca_indexed_nograd(q5, k_cache, v_cache, indices, weights, scale, self.sm_n)
+        vals = vals.permute(0, 1, 3, 2, 4).reshape(n, -1, self.hidden_size)
+        o = self.o_proj(vals)
+        return self._pad_first_chunk(hidden_states, o) if chunk_size > 1 else o
