@@ -1,0 +1,305 @@
+#!/usr/bin/env python
+"""Benchmark of the GCA hot path: forward + backward of Grouped Cross-Attention read
+straight from the chunk cache, at the DRT-16K shape (8 sequences x 16,384 positions per GPU,
+12 heads x 64, chunk 64, top-k 8, bf16).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  `value` = algorithmic TFLOP/s with inputs resident in HBM;
+`e2e` = the same through the public Python API from pinned host buffers (H2D + D2H inside
+the timed region); `roofline` = the forward tensor-core kernel against the measured dense
+bf16 peak; `cpu_baseline` = the PyTorch einsum formulation the reference uses as its ground
+truth (ltriton/gca.py:912-921 behind the gather of model/DRT.py:193-199) on the host cores.
+Data are synthetic (seeded N(0,1) tensors, uniform causal retrieved ids) and stand in for the
+PG19 / arXiv-math token data of the reference, which is not available offline.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+
+N_SEQ, CHUNKS, HEADS, TOPK, HEAD_DIM, CHUNK = 8, 256, 12, 8, 64, 64
+FWD_FLOP_PER_SLOT = 4 * CHUNK * CHUNK * HEAD_DIM          # QK^T + PV for one (query chunk, head, slot)
+FWD_BWD_FACTOR = 3.5                                      # backward counted as 2.5 x forward (ltriton/gca.py:1091-1092)
+
+
+def valid_slots(chunks: int, topk: int) -> int:
+    return sum(min(topk, j - 1) for j in range(1, chunks))
+
+
+def workload_flops(n_seq: int) -> float:
+    return float(n_seq * HEADS * valid_slots(CHUNKS, TOPK)) * FWD_FLOP_PER_SLOT
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def make_inputs(seed: int, n_seq: int, dtype=torch.bfloat16):
+    """CPU tensors in the fixed order q, k_cache, v_cache, indices/scores, dout."""
+    import cases
+    return cases.gca_indexed_case(seed, n_seq, CHUNKS, HEADS, TOPK, dtype=dtype, zero_landmark=True)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def stop(self):
+        self._stop.set()
+        self.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+# --------------------------------------------------------------------------------------------
+# CPU arms (the oracle is only ever the thing measured here as the *baseline*, never the product)
+# --------------------------------------------------------------------------------------------
+def cpu_reference_step(sample):
+    from oracle import gca_oracle as G
+    q, kc, vc, idx, w, dout = sample
+    G.gca_indexed_grads(q, kc, vc, idx, w, 1.0 / 8.0, dout, work_dtype=torch.float32)
+
+
+def run_cpu(steps: int, warmup: int, n_seq_sample: int):
+    torch.set_num_threads(os.cpu_count() or 1)
+    sample = tuple(t.float() if t.is_floating_point() else t for t in make_inputs(0, n_seq_sample, torch.float32))
+    for _ in range(warmup):
+        cpu_reference_step(sample)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_reference_step(sample)
+    dt = (time.perf_counter() - t0) / steps
+    return workload_flops(n_seq_sample) * FWD_BWD_FACTOR / dt / 1e12, dt
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    tflops, dt = run_cpu(steps, warmup, 1)
+    cores = os.cpu_count() or 1
+    sample = f"1 of the {N_SEQ} sequences per step (256 chunks x 12 heads x top-8, fp32), {steps} steps"
+    line = {"impl": "reference", "metric": "gca_fwd_bwd_tflops", "value": tflops, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_dict(),
+            "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def config_dict():
+    return {"workload": "GCA fwd+bwd at the DRT-16K shape: 8 sequences x 256 chunks x 64 positions per GPU, "
+                        "12 heads x 64, top-k 8, chunk cache read by retrieved index, bf16 (BASELINE configs[1] "
+                        "hot path == configs[2] point L=16K, K=8, BxH=96)",
+            "n_seq_per_gpu": N_SEQ, "chunks": CHUNKS, "heads": HEADS, "head_dim": HEAD_DIM, "topk": TOPK,
+            "valid_slots_per_seq_head": valid_slots(CHUNKS, TOPK),
+            "cache_policy": "inputs (q, caches, dout: ~0.8 GB per step) exceed the 126 MB L2; two input sets alternate",
+            "parallelism": "one process per GPU, sequences sharded over ranks, no data-path collective"}
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+def gpu_arm(args):
+    import torch.distributed as dist
+    import long_context_modeling_b200 as lcm
+    from long_context_modeling_b200 import gca as gmod
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the GCA path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    scale = 1.0 / 8.0
+
+    # two alternating input sets (different seeds per rank: independent sequences, weak scaling)
+    host_sets = []
+    for s in range(2):
+        q, kc, vc, idx, w, dout = make_inputs(1000 * rank + s, N_SEQ)
+        host_sets.append(tuple(t.pin_memory() for t in (q, kc, vc, idx.to(torch.int32), w, dout)))
+    dev_sets = [tuple(t.to(dev) for t in hs) for hs in host_sets]
+
+    def device_step(ds):
+        q, kc, vc, idx, w, dout = ds
+        q = q.detach().requires_grad_()
+        kc = kc.detach().requires_grad_()
+        vc = vc.detach().requires_grad_()
+        w = w.detach().requires_grad_()
+        o = lcm.gca_indexed(q, kc, vc, idx, w, scale)
+        o.backward(dout)
+        return o, q.grad, kc.grad, vc.grad, w.grad
+
+    pinned_out = None
+
+    def e2e_step(hs):
+        nonlocal pinned_out
+        ds = tuple(t.to(dev, non_blocking=True) for t in hs)
+        outs = device_step(ds)
+        if pinned_out is None:
+            pinned_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for p, o in zip(pinned_out, outs):
+            p.copy_(o, non_blocking=True)
+        return outs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, sets, steps, warmup):
+        for i in range(warmup):
+            fn(sets[i % 2])
+        barrier()
+        sampler = ClockSampler(physical_gpu_index(local))
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(sets[i % 2])
+        e1.record()
+        barrier()
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, clocks
+
+    steps, warmup = args.steps, max(3, args.warmup)
+    ms_dev, clocks = timed(device_step, dev_sets, steps, warmup)
+    ms_e2e, _ = timed(e2e_step, host_sets, max(3, steps // 4), 3)
+
+    # forward kernel alone (one launch per call): the roofline numerator
+    q, kc, vc, idx, w, dout = dev_sets[0]
+    for _ in range(3):
+        gmod.gca_forward_with_lse(q, kc, vc, idx, w, scale)
+    torch.cuda.synchronize()
+    reps = max(10, steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        qq, kk, vv, ii, ww, _ = dev_sets[i % 2]
+        gmod.gca_forward_with_lse(qq, kk, vv, ii, ww, scale)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_fwd = e0.elapsed_time(e1) / reps
+    status = lcm.read_status()
+
+    flops_fwd = workload_flops(N_SEQ)
+    flops_step = flops_fwd * FWD_BWD_FACTOR
+    value = flops_step * world / (ms_dev * 1e-3) / 1e12
+    e2e_val = flops_step * world / (ms_e2e * 1e-3) / 1e12
+    h2d = sum(t.numel() * t.element_size() for t in host_sets[0])
+    d2h = sum(p.numel() * p.element_size() for p in pinned_out)
+    achieved = flops_fwd / (ms_fwd * 1e-3) / 1e12
+    line = {
+        "metric": "gca_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": config_dict(), "clocks": clocks,
+        "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e},
+        "gpu_launches": 6 * steps,
+        "kernels": {"fwd_ms": ms_fwd, "fwd_bwd_ms": ms_dev, "bwd_ms_by_difference": ms_dev - ms_fwd},
+        "roofline": {"kernel": "gca forward (fwd_tc_kernel)", "bound": "tensor", "achieved": achieved,
+                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                     "peak_source": peaks["source"] + " burst dense bf16", "traffic": None,
+                     "algorithmic_flops_per_launch": flops_fwd,
+                     "pct_of_tensor_peak_fwd_bwd": 100.0 * value / world / peaks["bf16_tflops"]},
+        "device_status": status,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        tf, dt = run_cpu(2, 1, 1)
+        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                "sample": "1 of the 8 sequences (256 chunks x 12 heads x top-8), fp32 einsum + "
+                                          "gather + autograd, 2 timed steps"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

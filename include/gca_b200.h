@@ -249,6 +249,10 @@ int gca_cache_append(const CacheAppendArgs* args, void* stream);
 
 const char* gca_strerror(int code);
 int gca_abi_version(void);
+/* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,
+ * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs): lets a foreign-language binding verify
+ * its struct layout before the first call. */
+size_t gca_sizeof(int which);
 
 #ifdef __cplusplus
 }

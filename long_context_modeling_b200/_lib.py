@@ -90,6 +90,7 @@ EXPORTS = {
     "gca_cache_append": (C.c_int, [C.POINTER(CacheAppendArgs), C.c_void_p]),
     "gca_strerror": (C.c_char_p, [C.c_int]),
     "gca_abi_version": (C.c_int, []),
+    "gca_sizeof": (C.c_size_t, [C.c_int]),
 }
 
 _lib: Optional[C.CDLL] = None
@@ -110,6 +111,10 @@ def lib() -> C.CDLL:
             fn.argtypes = argtypes
         if handle.gca_abi_version() != 1:
             raise RuntimeError("libgca_b200.so has an unexpected ABI version")
+        for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs)):
+            if handle.gca_sizeof(which) != C.sizeof(struct):
+                raise RuntimeError(f"struct layout mismatch for {struct.__name__}: "
+                                   f"library {handle.gca_sizeof(which)} vs binding {C.sizeof(struct)}")
         _lib = handle
     return _lib
 

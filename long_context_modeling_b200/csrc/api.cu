@@ -20,6 +20,12 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 int esize_of(int dtype) { return dtype == GCA_BF16 ? 2 : dtype == GCA_F32 ? 4 : 0; }
 
+// Debug knob: GCA_DEFAULT_ALGO=simt makes GCA_ALGO_AUTO pick the CUDA-core kernels.
+bool prefer_simt() {
+  const char* e = getenv("GCA_DEFAULT_ALGO");
+  return e && strcmp(e, "simt") == 0;
+}
+
 // Strides of the four outer axes must keep every row 16-byte aligned.
 int check_strides(const int64_t s[4], int esize, const int32_t dims[4]) {
   for (int i = 0; i < 4; ++i) {
@@ -65,6 +71,17 @@ extern "C" {
 
 int gca_abi_version(void) { return GCA_ABI_VERSION; }
 
+size_t gca_sizeof(int which) {
+  switch (which) {
+    case 0: return sizeof(GcaFwdArgs);
+    case 1: return sizeof(GcaBwdArgs);
+    case 2: return sizeof(LmkTopkArgs);
+    case 3: return sizeof(LmkMergeArgs);
+    case 4: return sizeof(CacheAppendArgs);
+    default: return 0;
+  }
+}
+
 const char* gca_strerror(int code) {
   switch (code) {
     case GCA_OK: return "ok";
@@ -90,7 +107,7 @@ int gca_fwd(const GcaFwdArgs* a, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   int algo = a->algo;
   const bool tc_ok = a->dtype == GCA_BF16 && a->S == 64;
-  if (algo == GCA_ALGO_AUTO) algo = tc_ok ? GCA_ALGO_TC : GCA_ALGO_SIMT;
+  if (algo == GCA_ALGO_AUTO) algo = (tc_ok && !prefer_simt()) ? GCA_ALGO_TC : GCA_ALGO_SIMT;
   if (algo == GCA_ALGO_TC) return tc_ok ? gca::launch_fwd_tc(*a, s) : GCA_ERR_ALGO;
   if (algo == GCA_ALGO_SIMT) return gca::launch_fwd_simt(*a, s);
   return GCA_ERR_ALGO;
@@ -148,6 +165,7 @@ int gca_bwd(const GcaBwdArgs* a, void* stream) {
   int algo = a->algo;
   const bool tc_ok = a->dtype == GCA_BF16 && a->S == 64;
   if (algo == GCA_ALGO_AUTO) algo = (tc_ok && gca::bwd_tc_available()) ? GCA_ALGO_TC : GCA_ALGO_SIMT;
+  if (algo == GCA_ALGO_TC && !gca::bwd_tc_available()) algo = GCA_ALGO_SIMT;   // until the tensor-core backward lands
   if (algo == GCA_ALGO_TC) rc = tc_ok ? gca::launch_bwd_tc(*a, csr, dw_part, s) : GCA_ERR_ALGO;
   else if (algo == GCA_ALGO_SIMT) rc = gca::launch_bwd_simt(*a, csr, dw_part, s);
   else rc = GCA_ERR_ALGO;

@@ -42,7 +42,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after `limit` polls or as soon as *abort_flag is set (by another
 // role that already gave up).  Returns false on give-up; the caller must then unwind.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  uint32_t limit = (1u << 24)) {
+                                                  uint32_t limit = (1u << 22)) {
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *abort_flag) return false;

@@ -1,0 +1,144 @@
+"""Chunk-range-sharded landmark retrieval and GCA decode for very long contexts.
+
+The reference never shards retrieval (it parks the chunk cache on the host instead,
+``model/DRT.py:87-128`` and ``eval/slidewin_eval.py:115``).  Here rank ``r`` of ``g`` owns
+the contiguous chunk range ``shard_range(E, g, r)`` of the landmark and K/V cache.  A
+retrieval step is
+
+1. local: fused score + top-k over the local landmarks, reporting GLOBAL chunk ids
+   (``lmk_score_topk(..., e_base=lo)``),
+2. exchange: ONE all-gather of the ``K`` packed 64-bit candidates per row (NCCL over
+   NVLink; 64 B per row per rank for K = 8),
+3. merge: every rank selects the same global top-k from the ``g*K`` candidates (integer
+   order on the packed keys, so the result is identical everywhere).
+
+GCA over the winners is owner-computes: each rank attends over the winners it holds, with
+the globally normalised weights, and the (tiny) outputs are summed with an all-reduce.
+
+Failures are detected on the host: every payload carries a header (rank, rows, K, range)
+that is checked after the exchange; a rank that never joins ends the collective with the
+process group's timeout.  Both surface as ``ShardExchangeError``.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .retrieval import Retrieval, lmk_score_topk, merge_topk
+
+HEADER = 6          # rank, rows, K, lo, hi, magic
+MAGIC = 0x6C6D6B31  # "lmk1"
+
+
+class ShardExchangeError(RuntimeError):
+    pass
+
+
+def shard_range(e_total: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous, balanced chunk range [lo, hi) owned by ``rank``."""
+    base, rem = divmod(e_total, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def _decode_scores(keys: torch.Tensor) -> torch.Tensor:
+    """Float32 scores of packed keys held in a CPU int64 tensor (host-side check only)."""
+    import numpy as np
+    k = keys.contiguous().numpy().view(np.uint64)
+    o = (k >> np.uint64(32)).astype(np.uint32)
+    neg = (o >> np.uint32(31)) == 0
+    bits = np.where(neg, ~o, o & np.uint32(0x7FFFFFFF)).astype(np.uint32)
+    return torch.from_numpy(bits.view(np.float32).copy())
+
+
+def validate_payloads(payloads, world: int, rows: int, topk: int, e_total: int) -> None:
+    """Check what the exchange delivered; raises ShardExchangeError naming the first fault."""
+    if len(payloads) != world:
+        raise ShardExchangeError(f"expected {world} payloads, got {len(payloads)}")
+    for r, p in enumerate(payloads):
+        p = p.cpu()
+        if p.numel() != HEADER + rows * topk:
+            raise ShardExchangeError(f"rank {r}: payload has {p.numel()} words, expected {HEADER + rows * topk}")
+        h = p[:HEADER].tolist()
+        if h[5] != MAGIC:
+            raise ShardExchangeError(f"rank {r}: payload missing or corrupt (bad magic)")
+        if h[0] != r:
+            raise ShardExchangeError(f"rank {r}: payload claims to come from rank {h[0]}")
+        if h[1] != rows or h[2] != topk:
+            raise ShardExchangeError(f"rank {r}: rows/k mismatch ({h[1]}, {h[2]}) vs ({rows}, {topk})")
+        lo, hi = shard_range(e_total, world, r)
+        if (h[3], h[4]) != (lo, hi):
+            raise ShardExchangeError(f"rank {r}: owns [{h[3]}, {h[4]}) but the plan says [{lo}, {hi})")
+        keys = p[HEADER:]
+        live = keys != 0
+        idx = 0xFFFFFFFF - (keys & 0xFFFFFFFF)
+        if bool(((idx < lo) | (idx >= hi))[live].any()):
+            raise ShardExchangeError(f"rank {r}: candidate outside its chunk range [{lo}, {hi})")
+        scores = _decode_scores(keys[live])
+        if bool(torch.isnan(scores).any()):
+            raise ShardExchangeError(f"rank {r}: NaN score among the candidates")
+
+
+def sharded_lmk_topk(lmk_q: torch.Tensor, lmk_k_local: torch.Tensor, topk: int, *, e_total: int,
+                     group=None, head_dim: int = 0, q_pos0: Optional[int] = None, validate: bool = True,
+                     score_fn: Callable = lmk_score_topk, merge_fn: Callable = merge_topk,
+                     _tamper: Optional[Callable] = None) -> Retrieval:
+    """Global top-k over a landmark cache sharded by chunk range.
+
+    lmk_q (N, Cq, D) replicated on every rank; lmk_k_local (N, hi-lo, D) this rank's range.
+    ``q_pos0`` defaults to ``e_total - Cq`` (the reference's causal mask over the whole
+    cache).  ``score_fn`` / ``merge_fn`` default to the CUDA kernels; tests running CPU
+    ranks inject checkers.  ``_tamper`` lets a test corrupt this rank's payload.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    lo, hi = shard_range(e_total, world, rank)
+    if lmk_k_local.shape[1] != hi - lo:
+        raise ValueError(f"rank {rank} must hold chunks [{lo}, {hi}), got {lmk_k_local.shape[1]} landmarks")
+    cq = lmk_q.shape[1]
+    q_pos0 = (e_total - cq) if q_pos0 is None else q_pos0
+    local = score_fn(lmk_q, lmk_k_local, topk, q_pos0=q_pos0, e_base=lo, head_dim=head_dim)
+    rows_shape = tuple(local.keys.shape[:-1])
+    rows = 1
+    for s in rows_shape:
+        rows *= s
+    header = torch.tensor([rank, rows, topk, lo, hi, MAGIC], dtype=torch.int64, device=local.keys.device)
+    payload = torch.cat([header, local.keys.reshape(-1)])
+    if _tamper is not None:
+        payload = _tamper(payload)
+    gathered = [torch.empty(HEADER + rows * topk, dtype=torch.int64, device=payload.device) for _ in range(world)]
+    try:
+        if payload.numel() != HEADER + rows * topk:
+            # a malformed local payload would make the collective itself undefined: send a
+            # well-sized poison record instead so every rank fails the same check
+            payload = torch.zeros(HEADER + rows * topk, dtype=torch.int64, device=payload.device)
+        dist.all_gather(gathered, payload.contiguous(), group=group)
+    except RuntimeError as exc:          # a rank never joined / left: the group timed out
+        raise ShardExchangeError(f"candidate exchange failed: {exc}") from exc
+    if validate:
+        validate_payloads(gathered, world, rows, topk, e_total)
+    keys = torch.stack([g[HEADER:].view(rows, topk) for g in gathered], dim=1).reshape(rows_shape + (world * topk,))
+    return merge_fn(keys, topk)
+
+
+def sharded_gca_decode(q: torch.Tensor, k_cache_local: torch.Tensor, v_cache_local: torch.Tensor,
+                       indices: torch.Tensor, weights: torch.Tensor, sm_scale: float, *, e_total: int,
+                       group=None, gca_fn: Optional[Callable] = None) -> torch.Tensor:
+    """Owner-computes GCA over a K/V cache sharded by chunk range.
+
+    q (N, 1, Hq, Sq, D) replicated; caches hold this rank's chunks [lo, hi); indices are
+    GLOBAL chunk ids (N, 1, K) with -1 padding and weights the globally normalised
+    retrieval weights.  Every rank attends over the winners it owns (the others become
+    padding slots), then the partial outputs are summed across ranks."""
+    if gca_fn is None:
+        from .gca import gca_indexed_nograd as gca_fn
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    lo, hi = shard_range(e_total, world, rank)
+    mine = (indices >= lo) & (indices < hi)
+    local_idx = torch.where(mine, indices - lo, torch.full_like(indices, -1))
+    part = gca_fn(q, k_cache_local, v_cache_local, local_idx, weights, sm_scale).float()
+    dist.all_reduce(part, group=group)
+    return part.to(q.dtype)
