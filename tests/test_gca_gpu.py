@@ -45,7 +45,7 @@ def run_indexed(lcm, q, kc, vc, idx, w, scale, dout=None, algo=0, **kw):
     return o, qd.grad, kd.grad, vd.grad, wd.grad
 
 
-ALGOS = [pytest.param(1, id="simt"), pytest.param(2, id="tc")]
+ALGOS = [pytest.param(1, id="cudacore"), pytest.param(2, id="tensorcore")]
 
 
 @pytest.mark.parametrize("algo", ALGOS)
