@@ -222,7 +222,7 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
   for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
     const Unit t = decode_unit(p, u);
     const int h = t.h0 + tile;
-    const bool live = h < p.Hq;
+    const bool live = (tile == 0 || t.two) && h < p.Hq;
     int my_idx; bool bad;
     const unsigned mask = slot_mask(p, t.zj, lane, &my_idx, &bad);
     if (bad && p.status && warp == 0 && lane == 0) atomicOr(p.status, GCA_STATUS_BAD_INDEX);
