@@ -41,7 +41,8 @@ enum GcaError {
   GCA_ERR_WORKSPACE = -6,   /* workspace missing or too small */
   GCA_ERR_ALGO = -7,        /* requested kernel variant cannot run this problem */
   GCA_ERR_TMA = -8,         /* the driver rejected a tensor-map encoding */
-  GCA_ERR_TOO_LARGE = -9    /* a size exceeds a fixed built-in limit */
+  GCA_ERR_TOO_LARGE = -9,   /* a size exceeds a fixed built-in limit */
+  GCA_ERR_STATIC_SCRATCH = -10 /* lmk_score_topk_static: the problem needs more than the built-in scratch */
 };
 
 /* kernel variants (GcaFwdArgs.algo / GcaBwdArgs.algo) */
@@ -204,6 +205,27 @@ typedef struct LmkTopkArgs {
 
 int lmk_score_topk(const LmkTopkArgs* args, void* stream);
 size_t lmk_topk_workspace_bytes(const LmkTopkArgs* args);
+
+/*
+ * lmk_score_topk for callers that cannot provide device scratch.  (No counterpart in the
+ * reference: it exists for hosts that must not allocate device memory around the call -- a
+ * server that handed all HBM to its own pools, a plugin inside someone else's allocator, a
+ * loop that cannot afford an allocator call.)
+ *
+ * Same arguments, same results, bit for bit; args->workspace / workspace_bytes are ignored.
+ * The per-block candidate lists go into an array compiled into the library
+ * (LMK_STATIC_SCRATCH_BYTES of device memory on every GPU that loads it, held until exit).
+ * Limit: lmk_topk_workspace_bytes(args) must not exceed LMK_STATIC_SCRATCH_BYTES, i.e.
+ * rows * splits * K * 8 bytes <= 1 MiB (rows = N*Cq, times D/64 in per-head mode); a larger
+ * problem is refused with GCA_ERR_STATIC_SCRATCH and nothing is launched.  Passing
+ * args->splits lets the caller shrink the need.
+ * The call allocates nothing, on the host or on the device.  Its first use on a device looks
+ * up the array's address; make that first call outside of any stream capture.  All calls
+ * on one GPU share the array (contents left over from the previous call are never read), so
+ * calls that could overlap on the same GPU must be serialised by the caller.
+ */
+#define LMK_STATIC_SCRATCH_BYTES (1 << 20)
+int lmk_score_topk_static(const LmkTopkArgs* args, void* stream);
 
 /*
  * Merge of candidate lists (the exchange step of the chunk-range-sharded cache; no

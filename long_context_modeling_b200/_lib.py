@@ -86,6 +86,7 @@ EXPORTS = {
     "gca_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(GcaBwdArgs)]),
     "lmk_score_topk": (C.c_int, [C.POINTER(LmkTopkArgs), C.c_void_p]),
     "lmk_topk_workspace_bytes": (C.c_size_t, [C.POINTER(LmkTopkArgs)]),
+    "lmk_score_topk_static": (C.c_int, [C.POINTER(LmkTopkArgs), C.c_void_p]),
     "lmk_topk_merge": (C.c_int, [C.POINTER(LmkMergeArgs), C.c_void_p]),
     "gca_cache_append": (C.c_int, [C.POINTER(CacheAppendArgs), C.c_void_p]),
     "gca_strerror": (C.c_char_p, [C.c_int]),

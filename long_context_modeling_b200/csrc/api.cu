@@ -94,6 +94,9 @@ const char* gca_strerror(int code) {
     case GCA_ERR_ALGO: return "requested kernel variant cannot run this problem";
     case GCA_ERR_TMA: return "tensor-map encoding rejected by the driver";
     case GCA_ERR_TOO_LARGE: return "size exceeds a fixed built-in limit";
+    case GCA_ERR_STATIC_SCRATCH:
+      return "lmk_score_topk_static: rows * splits * K * 8 bytes exceeds the 1 MiB built-in scratch "
+             "(lower args->splits or use lmk_score_topk with a workspace)";
     default: break;
   }
   if (code > 0) return cudaGetErrorString((cudaError_t)code);

@@ -372,3 +372,74 @@ int launch_lmk_merge(const LmkMergeArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace gca
+
+// ---------------------------------------------------------------------------------------------
+// lmk_score_topk_static: the same scan + finalize, for callers that cannot hand us scratch.
+//
+// Who needs this: a host that must not (or cannot) allocate device memory around the call --
+// for example a serving process that gave all of HBM to its own pools at start-up, a plugin
+// living inside another framework whose allocator it may not touch, or a latency-critical loop
+// where an allocator call (and the device-wide synchronisation it can imply) is not acceptable.
+// Such a caller still passes its inputs and outputs, but the per-block candidate lists go into
+// a fixed array that lives in the library image.
+//
+// The array is file-scope device memory: every GPU that loads this library carries it
+// (LMK_STATIC_SCRATCH_BYTES = 1 MiB) until the process exits.  In host code its name is only a
+// stand-in for the symbol, not a device address, so the address is looked up with
+// cudaGetSymbolAddress -- once per device, with that device current, on the first call made on
+// that device -- and only that looked-up pointer is handed to the kernels.  Because of that
+// look-up, make the first call on each device before starting any stream capture.
+//
+// All calls on one GPU share the array.  It keeps whatever the previous call left in it; that
+// is harmless here because a call writes every (row, split) list it later reads, so nothing
+// needs to start at zero.  Two calls that overlap on the same GPU (different streams, or
+// different host threads) would overwrite each other's lists: serialise them.
+// ---------------------------------------------------------------------------------------------
+#include <mutex>
+
+namespace gca {
+namespace {
+
+static __device__ __align__(256) unsigned long long g_lmk_static_scratch[LMK_STATIC_SCRATCH_BYTES / 8];
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[MAX_DEVICES] = {};
+
+// Device address of the static scratch on the current device (resolved once per device).
+int static_scratch_ptr(void** out) {
+  int dev = 0;
+  GCA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) return GCA_ERR_TOO_LARGE;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    GCA_CUDA_CHECK(cudaGetSymbolAddress(&p, g_lmk_static_scratch));
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+}  // namespace gca
+
+extern "C" int lmk_score_topk_static(const LmkTopkArgs* a, void* stream) {
+  // same argument rules as lmk_score_topk; `workspace` / `workspace_bytes` are ignored
+  if (!a) return GCA_ERR_NULL;
+  if (!a->lmk_q || !a->lmk_k || !a->out_keys) return GCA_ERR_NULL;
+  if (a->N < 0 || a->Cq < 0 || a->E < 0) return GCA_ERR_SHAPE;
+  if (a->D < 8 || a->D % 8 != 0 || a->D > 1024 || a->K < 1 || a->K > 32) return GCA_ERR_SHAPE;
+  if (a->head_dim != 0 && (a->head_dim != 64 || a->D % 64 != 0 || a->noise)) return GCA_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(a->lmk_q) & 15u) || (reinterpret_cast<uintptr_t>(a->lmk_k) & 15u)) return GCA_ERR_ALIGN;
+  if (a->q_row_stride % 8 || a->k_row_stride % 8 || a->q_batch_stride % 8 || a->k_batch_stride % 8) return GCA_ERR_STRIDE;
+  if (a->e_base < 0 || a->e_base + a->E >= 0xffffffffll) return GCA_ERR_TOO_LARGE;
+  if (a->splits < 0) return GCA_ERR_SHAPE;
+  if (a->N == 0 || a->Cq == 0) return 0;
+  // rows x splits x K candidate keys of 8 bytes must fit the built-in array
+  if (gca::lmk_topk_workspace_bytes_impl(*a) > (size_t)LMK_STATIC_SCRATCH_BYTES) return GCA_ERR_STATIC_SCRATCH;
+  void* scratch = nullptr;
+  int rc = gca::static_scratch_ptr(&scratch);
+  if (rc) return rc;
+  return gca::launch_lmk_score_topk(*a, scratch, (cudaStream_t)stream);
+}
