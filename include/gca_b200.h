@@ -269,6 +269,13 @@ typedef struct CacheAppendArgs {
 
 int gca_cache_append(const CacheAppendArgs* args, void* stream);
 
+/*
+ * Development aid: when given a device buffer of 36 int64 words, block 0 of the tensor-core
+ * forward kernel records the cycles its three roles (softmax warp, MMA issuer, TMA producer;
+ * 12 words each) spend in each phase of the pipeline.  NULL switches it off (default).
+ */
+int gca_debug_profile_buffer(void* device_ptr);
+
 const char* gca_strerror(int code);
 int gca_abi_version(void);
 /* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,

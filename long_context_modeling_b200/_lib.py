@@ -89,6 +89,7 @@ EXPORTS = {
     "lmk_score_topk_static": (C.c_int, [C.POINTER(LmkTopkArgs), C.c_void_p]),
     "lmk_topk_merge": (C.c_int, [C.POINTER(LmkMergeArgs), C.c_void_p]),
     "gca_cache_append": (C.c_int, [C.POINTER(CacheAppendArgs), C.c_void_p]),
+    "gca_debug_profile_buffer": (C.c_int, [C.c_void_p]),
     "gca_strerror": (C.c_char_p, [C.c_int]),
     "gca_abi_version": (C.c_int, []),
     "gca_sizeof": (C.c_size_t, [C.c_int]),

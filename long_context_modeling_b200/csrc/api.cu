@@ -11,6 +11,7 @@ int launch_lmk_score_topk(const LmkTopkArgs& a, void* scratch, cudaStream_t stre
 int launch_lmk_merge(const LmkMergeArgs& a, cudaStream_t stream);
 size_t lmk_topk_workspace_bytes_impl(const LmkTopkArgs& a);
 bool bwd_tc_available();
+void set_fwd_profile_buffer(void* device_ptr);
 int launch_cache_append(const CacheAppendArgs& a, cudaStream_t stream);
 }  // namespace gca
 
@@ -70,6 +71,11 @@ int check_fwd(const GcaFwdArgs* a) {
 extern "C" {
 
 int gca_abi_version(void) { return GCA_ABI_VERSION; }
+
+int gca_debug_profile_buffer(void* device_ptr) {
+  gca::set_fwd_profile_buffer(device_ptr);
+  return 0;
+}
 
 size_t gca_sizeof(int which) {
   switch (which) {

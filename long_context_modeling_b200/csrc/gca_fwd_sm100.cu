@@ -1,23 +1,35 @@
 // GCA forward on the 5th-generation tensor cores (tcgen05 + TMEM), bf16, S = L = D = 64.
 //
-// Work unit: one (sequence n, query chunk j, PAIR of q heads).  A 64-row MMA writes only
-// 16 of the 32 TMEM lanes of each lane quarter, so two 64-row tiles are interleaved
-// (head A in lanes 0-15, head B in lanes 16-31 of every quarter): each of the 128 softmax
-// threads then owns one complete row of one head, and row max / row sum need no shuffles.
+// Work unit: one (sequence n, query chunk j, PAIR of q heads A, B).  The two heads are
+// stacked along M so every MMA is a full 128-row instruction:
 //
-// Per retrieved slot k (padding slots are skipped):
-//   S   = Q K_k^T             tcgen05.mma  M=64 N=64 K=64, Q and K_k K-major in smem
-//   P   = w_k * softmax(S)    one thread per row: tcgen05.ld, exp2, scale by w_k / l, bf16
-//   O  += P V_k               tcgen05.mma  with V_k as MN-major B operand; the K slots
-//                             accumulate in ONE TMEM tile, which fuses the weighted merge
-// K_k / V_k tiles are fetched straight from the chunk cache by TMA with the retrieved chunk
-// index as a tensor coordinate (no gathered copy exists).  Softmax of a slot needs only
-// that slot's 64 keys, so there is no running rescale.
+//   S  = [Q_A; Q_B] [K_A; K_B]^T   M=128, N=128, K=64: the diagonal 64x64 blocks are the two
+//                                  heads' scores (rows 0-63 x cols 0-63, rows 64-127 x cols
+//                                  64-127); the off-diagonal blocks are computed and ignored
+//   O += [P_A; P_B] [V_A | V_B]    same shape, V as MN-major B operand spanning both heads
 //
-// CTA = 6 warps: warps 0-3 softmax + epilogue, warp 4 TMA producer, warp 5 MMA issuer.
-// CTAs are persistent and walk the units in (n, j, head pair) order so that concurrently
-// running CTAs touch the cache of few sequences (L2 reuse of chunks retrieved many times).
-// Every mbarrier wait is bounded; on expiry the CTA flags GCA_STATUS_TIMEOUT and unwinds.
+// Issuing one tcgen05.mma costs the issuing thread ~70-100 cycles whatever its shape
+// (measured), and a 64x64x16 instruction is only 32 cycles of tensor work, so with these tiny
+// tiles the instruction count -- not the FLOP count -- is what must be minimised: stacking
+// the heads halves it, and the discarded off-diagonal half of the result is free.  With GQA,
+// when both q heads share one kv head, N is 64 and nothing is discarded.
+//
+// Per retrieved slot k (padding slots are skipped):  S -> one thread per row computes
+// P = (w_k / l) * exp2(S c - m) in bf16 (no running rescale: a slot's softmax spans exactly
+// one key tile) -> O accumulates over all K slots in ONE TMEM tile (fused weighted merge).
+// K_k / V_k tiles for both heads arrive with ONE TMA copy each, straight from the chunk
+// cache with the retrieved chunk index as a tensor coordinate (no gathered copy exists).
+//
+// CTA = 12 warps.  Warps 0-7: two softmax warpgroups taking alternate slots (thread =
+// TMEM lane = row).  Warp 8: TMA producer for Q and K, warp 9: TMA producer for V (separate
+// rings, K is released as soon as S is done).  Warp 10 issues the S MMAs, warp 11 the PV
+// MMAs.  The four single-lane roles are kept to a few dozen instructions per slot (a lone
+// warp retires one dependent instruction every ~5 cycles, so bookkeeping there is as
+// expensive as the MMAs): units are decoded incrementally, stage releases are relayed by the
+// softmax warps with plain mbarrier arrives.  CTAs are persistent and walk the units in
+// (n, j, head pair) order so that concurrently running CTAs touch the cache of few sequences
+// (L2 reuse of chunks retrieved many times).  Every mbarrier wait is bounded; on expiry the
+// CTA flags GCA_STATUS_TIMEOUT, drains its copies and unwinds.
 #include <cstdlib>
 
 #include "gca_common.cuh"
@@ -31,286 +43,390 @@ namespace {
 using namespace sm100;
 
 constexpr int TILE_BYTES = 64 * 64 * 2;
-constexpr int NSTAGE = 3;
-constexpr int NTHREADS = 192;
-constexpr int TMEM_COLS = 256;          // S0 | S1 | O0 | O1, 64 columns each
+constexpr int PAIR_BYTES = 2 * TILE_BYTES;
+constexpr int NK = 4, NV = 4;               // ring depths (16 KB per stage each)
+constexpr int NTHREADS = 384;
+constexpr int KPROD_WARP = 8, VPROD_WARP = 9, SMMA_WARP = 10, PVMMA_WARP = 11;
+constexpr int TMEM_COLS = 512;              // S0 | S1 | O0 | O1, 128 columns each
 
-constexpr int OFF_Q = 0;                              // [2 bufs][2 tiles]
-constexpr int OFF_KV = OFF_Q + 4 * TILE_BYTES;        // [NSTAGE][Ka Kb Va Vb]
-constexpr int OFF_P = OFF_KV + NSTAGE * 4 * TILE_BYTES;   // [2 bufs][2 tiles]
-constexpr int OFF_BAR = OFF_P + 4 * TILE_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;      // + alignment slack
+constexpr int OFF_Q = 0;                              // [2 bufs][A B]
+constexpr int OFF_K = OFF_Q + 2 * PAIR_BYTES;         // [NK][A B]
+constexpr int OFF_V = OFF_K + NK * PAIR_BYTES;        // [NV][A B]
+constexpr int OFF_P = OFF_V + NV * PAIR_BYTES;        // [2 bufs][A B]
+constexpr int OFF_BAR = OFF_P + 2 * PAIR_BYTES;
+constexpr int OFF_IDX = OFF_BAR + 512;                // 2 producers x 32 retrieved indices
+constexpr int SMEM_BYTES = OFF_IDX + 256 + 1024;      // + alignment slack
 
-enum Bar { Q_FULL = 0, Q_EMPTY = 2, KV_FULL = 4, KV_EMPTY = 4 + NSTAGE, S_FULL = 4 + 2 * NSTAGE,
-           S_EMPTY = S_FULL + 2, P_FULL = S_EMPTY + 2, P_EMPTY = P_FULL + 2, O_FULL = P_EMPTY + 2,
-           O_EMPTY = O_FULL + 2, NUM_BARS = O_EMPTY + 2 };
-
-constexpr uint32_t IDESC_S = umma_idesc_bf16(64, 64, 0, 0);
-constexpr uint32_t IDESC_PV = umma_idesc_bf16(64, 64, 0, 1);
+enum Bar { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + NK, V_FULL = K_EMPTY + NK, V_EMPTY = V_FULL + NV,
+           S_FULL = V_EMPTY + NV, S_EMPTY = S_FULL + 2, P_FULL = S_EMPTY + 2, P_EMPTY = P_FULL + 2,
+           O_FULL = P_EMPTY + 2, O_EMPTY = O_FULL + 2, NUM_BARS = O_EMPTY + 2 };
 
 struct FwdTcParams {
-  CUtensorMap tm_q, tm_k, tm_v;
+  CUtensorMap tm_q, tm_k2, tm_v2, tm_k1, tm_v1;   // *2: both heads of a pair per copy, *1: one head
   const int32_t* indices;
   const float* weights;
   __nv_bfloat16* out;
   float* lse;
   int32_t* status;
+  long long* prof;          // optional cycle counters of block 0 (debug), or nullptr
   long long os[4];
-  long long units;
+  int units;
   int N, J, Hq, Hkv, G, K, C, HP;
   int pair;                 // 1: a unit is a pair of q heads; 0: a single head (debug knob)
   float c2;
   float off_by_one;
 };
 
-struct Unit {
-  int zj, n, j, h0, two, hk0, hk1, share;
+// Debug profiling (compiled in only with -DGCA_PROFILE): cycles per phase of one lane.
+#ifdef GCA_PROFILE
+struct Prof {
+  long long acc[12];
+  long long t;
+  bool on;
+  __device__ __forceinline__ void init(bool enable) { on = enable; for (int i = 0; i < 12; ++i) acc[i] = 0; if (on) t = clock64(); }
+  __device__ __forceinline__ void lap(int i) { if (on) { const long long n = clock64(); acc[i] += n - t; t = n; } }
+  __device__ __forceinline__ void dump(long long* dst) { if (on) for (int i = 0; i < 12; ++i) dst[i] = acc[i]; }
 };
-__device__ __forceinline__ Unit decode_unit(const FwdTcParams& p, long long u) {
-  Unit t;
-  t.zj = (int)(u / p.HP);
-  const int hp = (int)(u % p.HP);
-  t.n = t.zj / p.J; t.j = t.zj % p.J;
+#else
+struct Prof {
+  __device__ __forceinline__ void init(bool) {}
+  __device__ __forceinline__ void lap(int) {}
+  __device__ __forceinline__ void dump(long long*) {}
+};
+#endif
+
+// Incremental walk over this CTA's units u = blockIdx.x, +gridDim.x, ...: unit u is
+// (zj, hp) = (u / HP, u % HP); no division after the first step.
+struct UnitCursor {
+  int u, zj, hp, dzj, dhp;
+  __device__ __forceinline__ void init(const FwdTcParams& p) {
+    u = blockIdx.x; zj = u / p.HP; hp = u - zj * p.HP;
+    dzj = gridDim.x / p.HP; dhp = gridDim.x - dzj * p.HP;
+  }
+  __device__ __forceinline__ void advance(const FwdTcParams& p) {
+    u += gridDim.x; zj += dzj; hp += dhp;
+    if (hp >= p.HP) { hp -= p.HP; ++zj; }
+  }
+  __device__ __forceinline__ int next_zj(const FwdTcParams& p) const { return zj + dzj + ((hp + dhp >= p.HP) ? 1 : 0); }
+};
+struct UnitInfo { int h0, hk0; bool two, share; };
+__device__ __forceinline__ UnitInfo unit_info(const FwdTcParams& p, int hp) {
+  UnitInfo t;
   t.h0 = p.pair ? 2 * hp : hp;
   t.two = p.pair && (t.h0 + 1) < p.Hq;
-  t.hk0 = t.h0 / p.G;
-  t.hk1 = t.two ? (t.h0 + 1) / p.G : t.hk0;
-  t.share = t.two && (t.hk1 == t.hk0);
+  if (p.G == 1) { t.hk0 = t.h0; t.share = false; }
+  else { t.hk0 = t.h0 / p.G; t.share = t.two && ((t.h0 + 1) / p.G == t.hk0); }
   return t;
 }
-// bit k set when slot k of (zj) holds a usable chunk index; also returns this lane's index
-__device__ __forceinline__ unsigned slot_mask(const FwdTcParams& p, int zj, int lane, int* my_idx, bool* bad) {
-  int idx = -1;
-  if (lane < p.K) idx = p.indices[(long long)zj * p.K + lane];
-  *my_idx = idx;
-  *bad = __any_sync(0xffffffffu, idx >= p.C);
+// Lane-parallel read of one row of retrieved indices; every role prefetches the next row.
+__device__ __forceinline__ int load_index_row(const FwdTcParams& p, int u, int zj, int lane) {
+  if (u >= p.units || lane >= p.K) return -1;
+  return p.indices[(long long)zj * p.K + lane];
+}
+__device__ __forceinline__ unsigned valid_mask(const FwdTcParams& p, int idx) {
   return __ballot_sync(0xffffffffu, idx >= 0 && idx < p.C);
 }
 
-// ----------------------------------------------------------------------------- producer
+// Running slot counters of a ring / double buffer (no div or mod in the slot loops).
+struct Ring {
+  uint32_t st, ph;
+  int depth;
+  __device__ __forceinline__ void init(int d) { st = 0; ph = 0; depth = d; }
+  __device__ __forceinline__ void next() { if (++st == (uint32_t)depth) { st = 0; ph ^= 1; } }
+};
+
+// ----------------------------------------------------------------------------- producers
+// mode 0: Q (per unit) + K (per slot);  mode 1: V (per slot)
+template <int MODE>
 __device__ void producer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane) {
-  uint32_t qcnt = 0, kvcnt = 0;
+  int* sidx = reinterpret_cast<int*>(smem + OFF_IDX) + MODE * 32;
+  constexpr int FULL = MODE == 0 ? K_FULL : V_FULL, EMPTY = MODE == 0 ? K_EMPTY : V_EMPTY;
+  constexpr int DEPTH = MODE == 0 ? NK : NV, OFF = MODE == 0 ? OFF_K : OFF_V;
+  UnitCursor c;
+  c.init(p);
+  Ring ring; ring.init(DEPTH);
+  uint32_t ucnt = 0, issued = 0;
   bool ok = true;
-  for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-    const Unit t = decode_unit(p, u);
-    int my_idx; bool bad;
-    const unsigned mask = slot_mask(p, t.zj, lane, &my_idx, &bad);
+  int next_idx = load_index_row(p, c.u, c.zj, lane);
+  for (; c.u < p.units; c.advance(p)) {
+    const int my_idx = next_idx;
+    next_idx = load_index_row(p, c.u + gridDim.x, c.next_zj(p), lane);
+    const unsigned mask = valid_mask(p, my_idx);
     if (mask == 0) continue;
-    const uint32_t qb = qcnt & 1;
-    if (lane == 0) {
-      ok = mbar_wait_bounded(&bars[Q_EMPTY + qb], ((qcnt >> 1) & 1) ^ 1, abort_flag);
-      if (ok) {
-        mbar_arrive_expect_tx(&bars[Q_FULL + qb], t.two ? 2 * TILE_BYTES : TILE_BYTES);
-        tma_load_5d(smem + OFF_Q + qb * 2 * TILE_BYTES, &p.tm_q, &bars[Q_FULL + qb], 0, 0, t.h0, t.j, t.n);
-        if (t.two)
-          tma_load_5d(smem + OFF_Q + qb * 2 * TILE_BYTES + TILE_BYTES, &p.tm_q, &bars[Q_FULL + qb], 0, 0, t.h0 + 1, t.j, t.n);
-      }
+    __syncwarp();
+    sidx[lane] = my_idx;
+    __syncwarp();
+    const uint32_t un = ucnt++;
+    if (lane != 0 || !ok) continue;
+    const UnitInfo t = unit_info(p, c.hp);
+    const int n = c.zj / p.J, j = c.zj - n * p.J;
+    if (MODE == 0) {
+      const uint32_t qb = un & 1;
+      ok = mbar_wait_bounded(&bars[Q_EMPTY + qb], ((un >> 1) & 1) ^ 1, abort_flag);
+      if (!ok) continue;
+      mbar_arrive_expect_tx(&bars[Q_FULL + qb], PAIR_BYTES);
+      tma_load_5d(smem + OFF_Q + qb * PAIR_BYTES, &p.tm_q, &bars[Q_FULL + qb], 0, 0, t.h0, j, n);
     }
-    ++qcnt;
-    unsigned m = mask;
-    while (m && ok) {
+    const CUtensorMap* tm = MODE == 0 ? (t.share ? &p.tm_k1 : &p.tm_k2) : (t.share ? &p.tm_v1 : &p.tm_v2);
+    const uint32_t bytes = t.share ? TILE_BYTES : PAIR_BYTES;
+    for (unsigned m = mask; m; m &= m - 1) {
       const int k = __ffs(m) - 1;
-      m &= m - 1;
-      const int idx = __shfl_sync(0xffffffffu, my_idx, k);
-      const uint32_t st = kvcnt % NSTAGE;
-      if (lane == 0) {
-        ok = mbar_wait_bounded(&bars[KV_EMPTY + st], ((kvcnt / NSTAGE) & 1) ^ 1, abort_flag);
-        if (ok) {
-          const bool both = t.two && !t.share;
-          uint8_t* base = smem + OFF_KV + st * 4 * TILE_BYTES;
-          mbar_arrive_expect_tx(&bars[KV_FULL + st], both ? 4 * TILE_BYTES : 2 * TILE_BYTES);
-          tma_load_5d(base, &p.tm_k, &bars[KV_FULL + st], 0, 0, t.hk0, idx, t.n);
-          tma_load_5d(base + 2 * TILE_BYTES, &p.tm_v, &bars[KV_FULL + st], 0, 0, t.hk0, idx, t.n);
-          if (both) {
-            tma_load_5d(base + TILE_BYTES, &p.tm_k, &bars[KV_FULL + st], 0, 0, t.hk1, idx, t.n);
-            tma_load_5d(base + 3 * TILE_BYTES, &p.tm_v, &bars[KV_FULL + st], 0, 0, t.hk1, idx, t.n);
-          }
-        }
-      }
-      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-      ++kvcnt;
+      ok = mbar_wait_bounded(&bars[EMPTY + ring.st], ring.ph ^ 1, abort_flag);
+      if (!ok) break;
+      mbar_arrive_expect_tx(&bars[FULL + ring.st], bytes);
+      tma_load_5d(smem + OFF + ring.st * PAIR_BYTES, tm, &bars[FULL + ring.st], 0, 0, t.hk0, sidx[k], n);
+      ring.next();
+      ++issued;
     }
-    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
   }
   // If anybody gave up, wait (bounded) for the copies this lane still has in flight so no
   // bulk copy can land in shared memory after the CTA has exited.
   if (lane == 0 && *abort_flag) {
-    for (uint32_t back = 0; back < NSTAGE && back < kvcnt; ++back) {
-      const uint32_t g = kvcnt - 1 - back;
+    for (uint32_t back = 0; back < (uint32_t)DEPTH && back < issued; ++back) {
+      const uint32_t g = issued - 1 - back;
       for (int i = 0; i < (1 << 20); ++i)
-        if (mbar_try_wait(&bars[KV_FULL + g % NSTAGE], (g / NSTAGE) & 1)) break;
+        if (mbar_try_wait(&bars[FULL + g % DEPTH], (g / DEPTH) & 1)) break;
     }
-    for (uint32_t back = 0; back < 2 && back < qcnt; ++back) {
-      const uint32_t g = qcnt - 1 - back;
-      for (int i = 0; i < (1 << 20); ++i)
-        if (mbar_try_wait(&bars[Q_FULL + (g & 1)], (g >> 1) & 1)) break;
-    }
+    if (MODE == 0)
+      for (uint32_t back = 0; back < 2 && back < ucnt; ++back) {
+        const uint32_t g = ucnt - 1 - back;
+        for (int i = 0; i < (1 << 20); ++i)
+          if (mbar_try_wait(&bars[Q_FULL + (g & 1)], (g >> 1) & 1)) break;
+      }
   }
 }
 
-// ----------------------------------------------------------------------------- MMA issuer
-__device__ void mma_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
-                         uint32_t tmem_base) {
-  uint32_t qcnt = 0, gcnt = 0, ocnt = 0;
+// ----------------------------------------------------------------------------- MMA issuers
+// mode 0: S = Q K^T per slot;  mode 1: O += P V per slot
+template <int MODE>
+__device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
+                            uint32_t tmem_base) {
+  const uint64_t dQ = umma_desc_sw128(smem_u32(smem + OFF_Q)), dK = umma_desc_sw128(smem_u32(smem + OFF_K));
+  const uint64_t dP = umma_desc_sw128(smem_u32(smem + OFF_P));
+  const uint64_t dV = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_V), TILE_BYTES);
+  constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
+  UnitCursor c;
+  c.init(p);
+  Ring ring; ring.init(MODE == 0 ? NK : NV);
+  uint32_t ucnt = 0, sb = 0, sph = 0;         // S/P double buffer index and phase
   bool ok = true;
-  const uint32_t sQ = smem_u32(smem + OFF_Q), sKV = smem_u32(smem + OFF_KV), sP = smem_u32(smem + OFF_P);
-  for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-    const Unit t = decode_unit(p, u);
-    int my_idx; bool bad;
-    const unsigned mask = slot_mask(p, t.zj, lane, &my_idx, &bad);
+  Prof pf;
+  pf.init(p.prof != nullptr && blockIdx.x == 0 && lane == 0);
+  int next_idx = load_index_row(p, c.u, c.zj, lane);
+  for (; c.u < p.units; c.advance(p)) {
+    const int my_idx = next_idx;
+    next_idx = load_index_row(p, c.u + gridDim.x, c.next_zj(p), lane);
+    const unsigned mask = valid_mask(p, my_idx);
+    if (mask == 0) continue;
+    const uint32_t un = ucnt++;
+    if (lane != 0 || !ok) continue;
     const int nv = __popc(mask);
-    if (nv == 0) continue;
-    if (lane == 0) {
-      const uint32_t qb = qcnt & 1, ob = ocnt & 1;
-      const int ntile = t.two ? 2 : 1;
-      const uint32_t b_off = (t.two && !t.share) ? TILE_BYTES : 0;   // where tile B's K/V sit
-      ok = mbar_wait_bounded(&bars[Q_FULL + qb], (qcnt >> 1) & 1, abort_flag) &&
-           mbar_wait_bounded(&bars[O_EMPTY + ob], ((ocnt >> 1) & 1) ^ 1, abort_flag);
-
-      auto issue_s = [&](uint32_t g) -> bool {
-        const uint32_t st = g % NSTAGE, sb = g & 1;
-        if (!mbar_wait_bounded(&bars[KV_FULL + st], (g / NSTAGE) & 1, abort_flag)) return false;
-        if (!mbar_wait_bounded(&bars[S_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag)) return false;
+    const UnitInfo t = unit_info(p, c.hp);
+    const uint32_t ub = un & 1, uph = (un >> 1) & 1;
+    const uint32_t idesc = umma_idesc_bf16(128, t.share ? 64 : 128, 0, MODE);
+    pf.lap(7);
+    if (MODE == 0) ok = mbar_wait_bounded(&bars[Q_FULL + ub], uph, abort_flag);
+    else ok = mbar_wait_bounded(&bars[O_EMPTY + ub], uph ^ 1, abort_flag);
+    pf.lap(0);
+    for (int i = 0; i < nv && ok; ++i) {
+      if (MODE == 0) {
+        ok = mbar_wait_bounded(&bars[K_FULL + ring.st], ring.ph, abort_flag);
+        pf.lap(1);
+        if (ok) ok = mbar_wait_bounded(&bars[S_EMPTY + sb], sph ^ 1, abort_flag);
+        pf.lap(2);
+        if (!ok) break;
         tc_fence_after();
-        for (int tl = 0; tl < ntile; ++tl) {
-          const uint64_t a = umma_desc_sw128(sQ + qb * 2 * TILE_BYTES + tl * TILE_BYTES);
-          const uint64_t b = umma_desc_sw128(sKV + st * 4 * TILE_BYTES + (tl ? b_off : 0));
-          const uint32_t d = tmem_base + sb * 64 + (tl ? (16u << 16) : 0u);
+        const uint64_t a = dQ + ub * PAIR16, b = dK + ring.st * PAIR16;
+        const uint32_t dt = tmem_base + sb * 128;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(d, a + kk * 2, b + kk * 2, IDESC_S, kk > 0);
-        }
+        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(dt, a + kk * 2, b + kk * 2, idesc, kk > 0);
         umma_commit(&bars[S_FULL + sb]);
-        return true;
-      };
-
-      if (ok) ok = issue_s(gcnt);
-      for (int i = 0; i < nv && ok; ++i) {
-        const uint32_t g = gcnt + i;
-        if (i + 1 < nv) ok = issue_s(g + 1);
-        else umma_commit(&bars[Q_EMPTY + qb]);      // every S MMA of the unit has been issued
-        if (!ok) break;
-        const uint32_t st = g % NSTAGE, sb = g & 1;
-        ok = mbar_wait_bounded(&bars[P_FULL + sb], (g >> 1) & 1, abort_flag);
+      } else {
+        ok = mbar_wait_bounded(&bars[V_FULL + ring.st], ring.ph, abort_flag);
+        pf.lap(1);
+        if (ok) ok = mbar_wait_bounded(&bars[P_FULL + sb], sph, abort_flag);
+        pf.lap(2);
         if (!ok) break;
         tc_fence_after();
-        for (int tl = 0; tl < ntile; ++tl) {
-          const uint64_t a = umma_desc_sw128(sP + sb * 2 * TILE_BYTES + tl * TILE_BYTES);
-          const uint64_t b = umma_desc_sw128(sKV + st * 4 * TILE_BYTES + 2 * TILE_BYTES + (tl ? b_off : 0));
-          const uint32_t d = tmem_base + 128 + ob * 64 + (tl ? (16u << 16) : 0u);
+        const uint64_t a = dP + sb * PAIR16, b = dV + ring.st * PAIR16;
+        const uint32_t dt = tmem_base + 256 + ub * 128;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(d, a + kk * 2, b + kk * 128, IDESC_PV, (i > 0 || kk > 0));
-        }
+        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(dt, a + kk * 2, b + kk * 128, idesc, (i > 0 || kk > 0));
         umma_commit(&bars[P_EMPTY + sb]);
-        umma_commit(&bars[KV_EMPTY + st]);
+        if (i == nv - 1) umma_commit(&bars[O_FULL + ub]);
       }
-      if (ok) umma_commit(&bars[O_FULL + ob]);
+      pf.lap(3);
+      ring.next();
+      sb ^= 1; if (sb == 0) sph ^= 1;
     }
-    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-    ++qcnt; ++ocnt; gcnt += nv;
   }
+  pf.dump(p.prof + 12 + 12 * MODE);
 }
 
 // ----------------------------------------------------------------------------- softmax + epilogue
-__device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int warp,
-                             int lane, uint32_t tmem_base) {
-  const int tile = lane >> 4;
-  const int row = warp * 16 + (lane & 15);
-  const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+__device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
+                             int quad, int lane, uint32_t tmem_base) {
+  const int tile = quad >> 1;                       // TMEM lanes 0-63: head A, 64-127: head B
+  const int row = (quad & 1) * 32 + lane;           // query row inside the head
+  const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
+  const bool elected = quad == 0 && lane == 0;      // relays stage releases for its warpgroup
   uint8_t* sP = smem + OFF_P;
-  uint32_t gcnt = 0, ocnt = 0;
+  UnitCursor c;
+  c.init(p);
+  uint32_t ucnt = 0, g = 0;
   bool ok = true;
-  for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-    const Unit t = decode_unit(p, u);
+  Prof pf;
+  pf.init(p.prof != nullptr && blockIdx.x == 0 && wg == 0 && elected);
+  int next_idx = load_index_row(p, c.u, c.zj, lane);
+  float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.zj * p.K + lane] : 0.f;
+
+  for (; c.u < p.units && ok; c.advance(p)) {
+    const int my_idx = next_idx;
+    const float my_w = next_w;
+    {
+      const int nzj = c.next_zj(p);
+      next_idx = load_index_row(p, c.u + gridDim.x, nzj, lane);
+      next_w = (c.u + gridDim.x < p.units && lane < p.K) ? p.weights[(long long)nzj * p.K + lane] : 0.f;
+    }
+    const unsigned mask = valid_mask(p, my_idx);
+    const UnitInfo t = unit_info(p, c.hp);
     const int h = t.h0 + tile;
     const bool live = (tile == 0 || t.two) && h < p.Hq;
-    int my_idx; bool bad;
-    const unsigned mask = slot_mask(p, t.zj, lane, &my_idx, &bad);
-    if (bad && p.status && warp == 0 && lane == 0) atomicOr(p.status, GCA_STATUS_BAD_INDEX);
-    const float my_w = lane < p.K ? p.weights[(long long)t.zj * p.K + lane] : 0.f;
-    float* lse_base = p.lse ? p.lse + ((long long)t.zj * p.Hq + h) * p.K * 64 + row : nullptr;
-    if (lse_base && live)
-      for (int k = 0; k < p.K; ++k)
-        if (!((mask >> k) & 1)) lse_base[k * 64] = 0.f;
-    __nv_bfloat16* orow = p.out + t.n * p.os[0] + t.j * p.os[1] + h * p.os[2] + row * p.os[3];
-    if (mask == 0) {
-      if (live) {
+    const uint32_t coff = t.share ? 0u : (uint32_t)tile * 64u;
+    const int n = c.zj / p.J, j = c.zj - n * p.J;
+    float* lse_base = p.lse ? p.lse + ((long long)c.zj * p.Hq + h) * p.K * 64 + row : nullptr;
+    __nv_bfloat16* orow = p.out + n * p.os[0] + j * p.os[1] + h * p.os[2] + row * p.os[3];
+    if (wg == 0) {
+      const bool bad = __any_sync(0xffffffffu, my_idx >= p.C);
+      if (bad && p.status && elected) atomicOr(p.status, GCA_STATUS_BAD_INDEX);
+      if (lse_base && live && mask != ((p.K >= 32) ? 0xffffffffu : ((1u << p.K) - 1u)))
+        for (int k = 0; k < p.K; ++k)
+          if (!((mask >> k) & 1)) lse_base[k * 64] = 0.f;
+      if (mask == 0 && live) {
         const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
+        for (int cc = 0; cc < 8; ++cc) reinterpret_cast<uint4*>(orow)[cc] = z;
       }
-      continue;
     }
-    const uint32_t ob = ocnt & 1;
-    unsigned m = mask;
-    while (m) {
+    if (mask == 0) continue;
+    const uint32_t un = ucnt++;
+    const uint32_t ob = un & 1;
+    for (unsigned m = mask; m; m &= m - 1, ++g) {
+      if ((int)(g & 1) != wg) continue;              // the other warpgroup's slot
       const int k = __ffs(m) - 1;
-      m &= m - 1;
-      const float w = __shfl_sync(0xffffffffu, my_w, k);
-      const uint32_t g = gcnt, sb = g & 1;
+      const bool last = (m & (m - 1)) == 0;
+      const float wk = __shfl_sync(0xffffffffu, my_w, k);
+      const uint32_t sb = g & 1;
+      pf.lap(7);
       ok = mbar_wait_bounded(&bars[S_FULL + sb], (g >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      pf.lap(0);
+      if (elected) {                                   // S is done: its K stage (and Q) can be refilled
+        mbar_arrive(&bars[K_EMPTY + g % NK]);
+        if (last) mbar_arrive(&bars[Q_EMPTY + ob]);
+      }
       tc_fence_after();
       uint32_t x[64];
-      tmem_ld_32x32b_x32(tlane + sb * 64, x);
-      tmem_ld_32x32b_x32(tlane + sb * 64 + 32, x + 32);
+      tmem_ld_32x32b_x32(tlane + sb * 128 + coff, x);
+      tmem_ld_32x32b_x32(tlane + sb * 128 + coff + 32, x + 32);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&bars[S_EMPTY + sb]);
+      pf.lap(1);
 
-      float mx = -INFINITY;
+      // row max: four independent chains of 3-input max
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(x[c]));
-      float mm = mx * p.c2;
-      if (p.off_by_one > 0.f) mm = fmaxf(mm, 0.f);
-      float l = 0.f;
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float e = ex2_approx(fmaf(__uint_as_float(x[c]), p.c2, -mm));
-        x[c] = __float_as_uint(e);
-        l += e;
+      for (int cc = 0; cc < 64; cc += 8) {
+        m0 = fmax3(m0, __uint_as_float(x[cc + 0]), __uint_as_float(x[cc + 1]));
+        m1 = fmax3(m1, __uint_as_float(x[cc + 2]), __uint_as_float(x[cc + 3]));
+        m2 = fmax3(m2, __uint_as_float(x[cc + 4]), __uint_as_float(x[cc + 5]));
+        m3 = fmax3(m3, __uint_as_float(x[cc + 6]), __uint_as_float(x[cc + 7]));
       }
+      float mm = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.c2;
+      if (p.off_by_one > 0.f) mm = fmaxf(mm, 0.f);
+      // p = exp2(x * c2 - mm): packed FMA, MUFU exp2, four packed partial sums
+      const float2 c2v = make_float2(p.c2, p.c2), nmm = make_float2(-mm, -mm);
+      float2 s0 = make_float2(0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;
+#pragma unroll
+      for (int cc = 0; cc < 64; cc += 8) {
+        float2 a0 = __ffma2_rn(make_float2(__uint_as_float(x[cc + 0]), __uint_as_float(x[cc + 1])), c2v, nmm);
+        float2 a1 = __ffma2_rn(make_float2(__uint_as_float(x[cc + 2]), __uint_as_float(x[cc + 3])), c2v, nmm);
+        float2 a2 = __ffma2_rn(make_float2(__uint_as_float(x[cc + 4]), __uint_as_float(x[cc + 5])), c2v, nmm);
+        float2 a3 = __ffma2_rn(make_float2(__uint_as_float(x[cc + 6]), __uint_as_float(x[cc + 7])), c2v, nmm);
+        a0.x = ex2_approx(a0.x); a0.y = ex2_approx(a0.y);
+        a1.x = ex2_approx(a1.x); a1.y = ex2_approx(a1.y);
+        a2.x = ex2_approx(a2.x); a2.y = ex2_approx(a2.y);
+        a3.x = ex2_approx(a3.x); a3.y = ex2_approx(a3.y);
+        s0 = __fadd2_rn(s0, a0); s1 = __fadd2_rn(s1, a1); s2 = __fadd2_rn(s2, a2); s3 = __fadd2_rn(s3, a3);
+        x[cc + 0] = __float_as_uint(a0.x); x[cc + 1] = __float_as_uint(a0.y);
+        x[cc + 2] = __float_as_uint(a1.x); x[cc + 3] = __float_as_uint(a1.y);
+        x[cc + 4] = __float_as_uint(a2.x); x[cc + 5] = __float_as_uint(a2.y);
+        x[cc + 6] = __float_as_uint(a3.x); x[cc + 7] = __float_as_uint(a3.y);
+      }
+      const float2 st2 = __fadd2_rn(__fadd2_rn(s0, s1), __fadd2_rn(s2, s3));
+      float l = st2.x + st2.y;
       if (p.off_by_one > 0.f) l += p.off_by_one * ex2_approx(-mm);
       if (lse_base && live) lse_base[k * 64] = mm + __log2f(l);
-      const float f = w / l;
-      uint32_t pk[32];
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        pk[c] = pack_bf16x2(__uint_as_float(x[2 * c]) * f, __uint_as_float(x[2 * c + 1]) * f);
+      const float f = __fdividef(wk, l);
+      const float2 fv = make_float2(f, f);
 
+      pf.lap(2);
       ok = mbar_wait_bounded(&bars[P_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-      uint8_t* prow = sP + sb * 2 * TILE_BYTES + tile * TILE_BYTES + row * 128;
+      pf.lap(3);
+      // PV of slot g-2 (same P buffer) is done: its V stage can be refilled
+      if (elected && g >= 2) mbar_arrive(&bars[V_EMPTY + (g - 2) % NV]);
+      uint8_t* prow = sP + sb * PAIR_BYTES + tile * TILE_BYTES + row * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      for (int cc = 0; cc < 8; ++cc) {
+        const float2 q0 = __fmul2_rn(make_float2(__uint_as_float(x[8 * cc + 0]), __uint_as_float(x[8 * cc + 1])), fv);
+        const float2 q1 = __fmul2_rn(make_float2(__uint_as_float(x[8 * cc + 2]), __uint_as_float(x[8 * cc + 3])), fv);
+        const float2 q2 = __fmul2_rn(make_float2(__uint_as_float(x[8 * cc + 4]), __uint_as_float(x[8 * cc + 5])), fv);
+        const float2 q3 = __fmul2_rn(make_float2(__uint_as_float(x[8 * cc + 6]), __uint_as_float(x[8 * cc + 7])), fv);
+        *reinterpret_cast<uint4*>(prow + ((cc ^ (row & 7)) << 4)) =
+            make_uint4(pack_bf16x2(q0.x, q0.y), pack_bf16x2(q1.x, q1.y), pack_bf16x2(q2.x, q2.y), pack_bf16x2(q3.x, q3.y));
+      }
       fence_proxy_async_smem();
       mbar_arrive(&bars[P_FULL + sb]);
-      ++gcnt;
+      pf.lap(4);
     }
     if (!ok) break;
-    // epilogue: O tile -> bf16 -> global, one 128-byte row per thread
-    ok = mbar_wait_bounded(&bars[O_FULL + ob], (ocnt >> 1) & 1, abort_flag);
-    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-    tc_fence_after();
-    uint32_t o[64];
-    tmem_ld_32x32b_x32(tlane + 128 + ob * 64, o);
-    tmem_ld_32x32b_x32(tlane + 128 + ob * 64 + 32, o + 32);
-    tmem_ld_wait();
-    tc_fence_before();
-    mbar_arrive(&bars[O_EMPTY + ob]);
-    if (live) {
+    // epilogue by the warpgroup that owns this unit's accumulator: O tile -> bf16 -> global
+    if ((int)ob == wg) {
+      pf.lap(7);
+      ok = mbar_wait_bounded(&bars[O_FULL + ob], (un >> 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      pf.lap(5);
+      tc_fence_after();
+      uint32_t o[64];
+      tmem_ld_32x32b_x32(tlane + 256 + ob * 128 + coff, o);
+      tmem_ld_32x32b_x32(tlane + 256 + ob * 128 + coff + 32, o + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[O_EMPTY + ob]);
+      if (live) {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint4 v;
-        v.x = pack_bf16x2(__uint_as_float(o[8 * c + 0]), __uint_as_float(o[8 * c + 1]));
-        v.y = pack_bf16x2(__uint_as_float(o[8 * c + 2]), __uint_as_float(o[8 * c + 3]));
-        v.z = pack_bf16x2(__uint_as_float(o[8 * c + 4]), __uint_as_float(o[8 * c + 5]));
-        v.w = pack_bf16x2(__uint_as_float(o[8 * c + 6]), __uint_as_float(o[8 * c + 7]));
-        reinterpret_cast<uint4*>(orow)[c] = v;
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(o[8 * cc + 0]), __uint_as_float(o[8 * cc + 1]));
+          v.y = pack_bf16x2(__uint_as_float(o[8 * cc + 2]), __uint_as_float(o[8 * cc + 3]));
+          v.z = pack_bf16x2(__uint_as_float(o[8 * cc + 4]), __uint_as_float(o[8 * cc + 5]));
+          v.w = pack_bf16x2(__uint_as_float(o[8 * cc + 6]), __uint_as_float(o[8 * cc + 7]));
+          reinterpret_cast<uint4*>(orow)[cc] = v;
+        }
       }
+      pf.lap(6);
     }
-    ++ocnt;
   }
+  pf.lap(7);
+  pf.dump(p.prof);
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -329,48 +445,60 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams p) {
       mbar_init(&bars[P_FULL + i], 128); mbar_init(&bars[P_EMPTY + i], 1);
       mbar_init(&bars[O_FULL + i], 1); mbar_init(&bars[O_EMPTY + i], 128);
     }
-    for (int i = 0; i < NSTAGE; ++i) { mbar_init(&bars[KV_FULL + i], 1); mbar_init(&bars[KV_EMPTY + i], 1); }
+    for (int i = 0; i < NK; ++i) { mbar_init(&bars[K_FULL + i], 1); mbar_init(&bars[K_EMPTY + i], 1); }
+    for (int i = 0; i < NV; ++i) { mbar_init(&bars[V_FULL + i], 1); mbar_init(&bars[V_EMPTY + i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-  if (warp == 4 && lane == 0) { tma_prefetch_desc(&p.tm_q); tma_prefetch_desc(&p.tm_k); tma_prefetch_desc(&p.tm_v); }
+  if (warp == SMMA_WARP) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  if (warp == KPROD_WARP && lane == 0) { tma_prefetch_desc(&p.tm_q); tma_prefetch_desc(&p.tm_k2); tma_prefetch_desc(&p.tm_k1); }
+  if (warp == VPROD_WARP && lane == 0) { tma_prefetch_desc(&p.tm_v2); tma_prefetch_desc(&p.tm_v1); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 4) softmax_role(p, smem, bars, abort_flag, warp, lane, tmem_base);
-  else if (warp == 4) producer_role(p, smem, bars, abort_flag, lane);
-  else mma_role(p, smem, bars, abort_flag, lane, tmem_base);
+  if (warp < 8) softmax_role(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
+  else if (warp == KPROD_WARP) producer_role<0>(p, smem, bars, abort_flag, lane);
+  else if (warp == VPROD_WARP) producer_role<1>(p, smem, bars, abort_flag, lane);
+  else if (warp == SMMA_WARP) issuer_role<0>(p, smem, bars, abort_flag, lane, tmem_base);
+  else issuer_role<1>(p, smem, bars, abort_flag, lane, tmem_base);
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == SMMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
 }
 
+long long* g_profile_buffer = nullptr;
+
 }  // namespace
+
+void set_fwd_profile_buffer(void* device_ptr) { g_profile_buffer = static_cast<long long*>(device_ptr); }
 
 int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;
   FwdTcParams p;
-  // q viewed as (d, s, h, j, n); caches as (d, l, h, c, n): box = one 64 x 64 tile
-  int rc = make_tile_map_5d(&p.tm_q, a.q, 64, 64, a.Hq, a.J, a.N, a.q_stride[3], a.q_stride[2], a.q_stride[1], a.q_stride[0]);
-  if (rc) return rc;
-  rc = make_tile_map_5d(&p.tm_k, a.k_cache, 64, 64, a.Hkv, a.C, a.N, a.k_stride[2], a.k_stride[3], a.k_stride[1], a.k_stride[0]);
-  if (rc) return rc;
-  rc = make_tile_map_5d(&p.tm_v, a.v_cache, 64, 64, a.Hkv, a.C, a.N, a.v_stride[2], a.v_stride[3], a.v_stride[1], a.v_stride[0]);
-  if (rc) return rc;
+  // q viewed as (d, s, h, j, n); caches as (d, l, h, c, n).  One copy moves a 64 x 64 tile of
+  // each of two consecutive heads (box extent 2 on the head axis), or of one head (tm_*1).
+  int rc;
+  if ((rc = make_tile_map_5d(&p.tm_q, a.q, 64, 64, a.Hq, a.J, a.N, a.q_stride[3], a.q_stride[2], a.q_stride[1], a.q_stride[0], 2))) return rc;
+  if ((rc = make_tile_map_5d(&p.tm_k2, a.k_cache, 64, 64, a.Hkv, a.C, a.N, a.k_stride[2], a.k_stride[3], a.k_stride[1], a.k_stride[0], 2))) return rc;
+  if ((rc = make_tile_map_5d(&p.tm_v2, a.v_cache, 64, 64, a.Hkv, a.C, a.N, a.v_stride[2], a.v_stride[3], a.v_stride[1], a.v_stride[0], 2))) return rc;
+  if ((rc = make_tile_map_5d(&p.tm_k1, a.k_cache, 64, 64, a.Hkv, a.C, a.N, a.k_stride[2], a.k_stride[3], a.k_stride[1], a.k_stride[0], 1))) return rc;
+  if ((rc = make_tile_map_5d(&p.tm_v1, a.v_cache, 64, 64, a.Hkv, a.C, a.N, a.v_stride[2], a.v_stride[3], a.v_stride[1], a.v_stride[0], 1))) return rc;
   p.indices = a.indices; p.weights = a.weights; p.out = (__nv_bfloat16*)a.out; p.lse = a.lse; p.status = a.status;
   for (int i = 0; i < 4; ++i) p.os[i] = a.o_stride[i];
   p.N = a.N; p.J = a.J; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = a.Hq / a.Hkv; p.K = a.K; p.C = a.C;
   const char* pair_env = getenv("GCA_TC_PAIR");
   p.pair = (pair_env && pair_env[0] == '0') ? 0 : 1;
   p.HP = p.pair ? (a.Hq + 1) / 2 : a.Hq;
-  p.units = (long long)a.N * a.J * p.HP;
+  const long long units = (long long)a.N * a.J * p.HP;
+  if (units >= (1ll << 31) - 65536) return GCA_ERR_TOO_LARGE;
+  p.units = (int)units;
   p.c2 = a.sm_scale * GCA_LOG2E;
   p.off_by_one = a.off_by_one;
+  p.prof = g_profile_buffer;
   if (p.units == 0) return 0;
   int dev = 0, sms = 0;
   GCA_CUDA_CHECK(cudaGetDevice(&dev));

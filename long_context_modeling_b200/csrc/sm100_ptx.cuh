@@ -118,6 +118,18 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// Same, for an MN-major operand that spans several 64-wide blocks of its M/N axis: the blocks
+// (each a 64-row x 128-byte tile) sit `block_bytes` apart (the leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn_blocks(uint32_t smem_addr, uint32_t block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)((block_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16 with bf16 inputs and float32 accumulation.
 //   c_format=F32 [4,6), a_format=BF16 [7,10), b_format=BF16 [10,13), a_major [15], b_major [16]
 //   (0 = K-major, 1 = MN-major), N>>3 [17,23), M>>4 [24,29).
