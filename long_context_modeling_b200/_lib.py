@@ -11,7 +11,7 @@ import os
 from typing import Optional
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libgca_b200.so")
+LIB_PATH = os.environ.get("GCA_B200_LIB") or os.path.join(_HERE, "libgca_b200.so")
 
 BF16, F32 = 0, 1
 ALGO_AUTO, ALGO_SIMT, ALGO_TC = 0, 1, 2

@@ -10,17 +10,25 @@
 //    forward: dQ += dS K_k accumulated over the K slots in TMEM, and the per-head part of
 //    dw_k = sum_rows <dO, O_k> = sum_rows rowsum(P * dP).
 //
-// Per (query tile, key tile) both kernels recompute  S = Q K^T  and  dP = dO V^T  with two
-// 64x64x64 MMAs, then one thread per query row forms  P = exp2(S c - LSE),
-// Di = rowsum(P*dP),  dS = w P (dP - Di)  and stages bf16 tiles for the follow-up MMAs.
-// Transposed operands (P^T, dS^T, and dO / Q / K as the N-contiguous B operand) are read
-// through MN-major shared-memory descriptors, so nothing is transposed in software.
-// As in the forward, two 64-row tiles are interleaved in the TMEM lanes (lanes 0-15 /
-// 16-31 of every quarter) so all 128 worker threads own a full row.
+// Per (query tile, key tile) both kernels recompute  S = Q K^T  and  dP = dO V^T, then one
+// thread per query row forms  P = exp2(S c - LSE),  Di = rowsum(P*dP),  dS = w P (dP - Di)
+// and stages bf16 tiles for the follow-up MMAs.  As in the forward, the two heads of a pair
+// are stacked so that every tcgen05.mma is a 128-row instruction whose diagonal 64x64
+// blocks are the two heads' results (the issue cost of an MMA does not depend on its shape,
+// so fewer, larger instructions win).  Transposed operands (P^T, dS^T, and dO / Q / K as the
+// N-contiguous B operand) are read through MN-major shared-memory descriptors spanning both
+// heads' tiles, so nothing is transposed in software.
+//
+// CTA = 12 warps: two worker warpgroups (thread = TMEM lane = row) taking alternate
+// iterations, two TMA producers, two MMA issuers (recompute products / gradient products).
+// S and dP live in a single TMEM buffer each (a worker group drains it into registers at
+// once), the accumulators take the rest of TMEM.  Stage releases are relayed by the workers
+// with plain mbarrier arrives.  Every wait is bounded (GCA_STATUS_TIMEOUT on expiry).
 #include <cstdlib>
 
 #include "gca_common.cuh"
 #include "sm100_ptx.cuh"
+#include "tc_common.cuh"
 #include "tma_host.cuh"
 
 namespace gca {
@@ -30,71 +38,65 @@ namespace {
 using namespace sm100;
 
 constexpr int TILE_BYTES = 64 * 64 * 2;
-constexpr int NSTAGE = 3;
-constexpr int NTHREADS = 192;
+constexpr int PAIR_BYTES = 2 * TILE_BYTES;
+constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
+constexpr int NTHREADS = 384;
+constexpr int PROD_A = 8, PROD_B = 9, ISSUE_A = 10, ISSUE_B = 11;
 constexpr int TMEM_COLS = 512;
-constexpr uint32_t LANE16 = 16u << 16;
+constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC = 256;
 
-constexpr uint32_t IDESC_KK = umma_idesc_bf16(64, 64, 0, 0);   // A K-major, B K-major   (S, dP)
-constexpr uint32_t IDESC_KM = umma_idesc_bf16(64, 64, 0, 1);   // A K-major, B MN-major  (dQ)
-constexpr uint32_t IDESC_MM = umma_idesc_bf16(64, 64, 1, 1);   // A MN-major, B MN-major (dV, dK)
-
-__device__ __forceinline__ void named_barrier_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-// four K steps of one 64x64x64 product
-__device__ __forceinline__ void mma_tile(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, int a_step, int b_step,
-                                         bool accumulate_first) {
+// Four K steps of one stacked product.  a_step / b_step: descriptor advance per K step of 16.
+constexpr int STEP_K = 2;      // K-major operand: +32 bytes (>> 4)
+constexpr int STEP_MN = 128;   // MN-major operand: +2048 bytes (>> 4)
+__device__ __forceinline__ void mma4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, int a_step, int b_step,
+                                     bool accumulate_first) {
 #pragma unroll
   for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(d, a + kk * a_step, b + kk * b_step, idesc, (accumulate_first || kk > 0));
 }
-constexpr int STEP_K = 2;      // K-major operand: +32 bytes per K step (>> 4)
-constexpr int STEP_MN = 128;   // MN-major operand: +2048 bytes per K step (>> 4)
 
-// One thread, one query row: P, Di, dS from the S and dP rows.  Writes (w P) and/or dS as
-// bf16 into swizzled K-major tiles.  Returns Di (unweighted).
-__device__ __forceinline__ float row_backward(const uint32_t* s, const uint32_t* dp, float lse, float c2, float w,
+// One thread, one query row.  s: raw scores (overwritten by P), dp: raw dP.  Writes dS
+// (and w*P when pw_row != nullptr) as bf16 into swizzled [row][key] tiles; returns Di.
+__device__ __forceinline__ float row_backward(uint32_t* s, const uint32_t* dp, float lse, float c2, float w,
                                               uint8_t* pw_row, uint8_t* ds_row, int row) {
-  float p[64];
-  float di = 0.f;
+  const float2 c2v = make_float2(c2, c2), nl = make_float2(-lse, -lse);
+  float2 d0 = make_float2(0.f, 0.f), d1 = d0, d2 = d0, d3 = d0;
 #pragma unroll
-  for (int c = 0; c < 64; ++c) {
-    p[c] = ex2_approx(fmaf(__uint_as_float(s[c]), c2, -lse));
-    di = fmaf(p[c], __uint_as_float(dp[c]), di);
+  for (int c = 0; c < 64; c += 8) {
+    float2 a0 = __ffma2_rn(f2(s[c + 0], s[c + 1]), c2v, nl), a1 = __ffma2_rn(f2(s[c + 2], s[c + 3]), c2v, nl);
+    float2 a2 = __ffma2_rn(f2(s[c + 4], s[c + 5]), c2v, nl), a3 = __ffma2_rn(f2(s[c + 6], s[c + 7]), c2v, nl);
+    a0.x = ex2_approx(a0.x); a0.y = ex2_approx(a0.y); a1.x = ex2_approx(a1.x); a1.y = ex2_approx(a1.y);
+    a2.x = ex2_approx(a2.x); a2.y = ex2_approx(a2.y); a3.x = ex2_approx(a3.x); a3.y = ex2_approx(a3.y);
+    d0 = __ffma2_rn(a0, f2(dp[c + 0], dp[c + 1]), d0); d1 = __ffma2_rn(a1, f2(dp[c + 2], dp[c + 3]), d1);
+    d2 = __ffma2_rn(a2, f2(dp[c + 4], dp[c + 5]), d2); d3 = __ffma2_rn(a3, f2(dp[c + 6], dp[c + 7]), d3);
+    s[c + 0] = __float_as_uint(a0.x); s[c + 1] = __float_as_uint(a0.y); s[c + 2] = __float_as_uint(a1.x); s[c + 3] = __float_as_uint(a1.y);
+    s[c + 4] = __float_as_uint(a2.x); s[c + 5] = __float_as_uint(a2.y); s[c + 6] = __float_as_uint(a3.x); s[c + 7] = __float_as_uint(a3.y);
   }
+  const float2 dsum = __fadd2_rn(__fadd2_rn(d0, d1), __fadd2_rn(d2, d3));
+  const float di = dsum.x + dsum.y;
+  const float2 wv = make_float2(w, w), ndi = make_float2(-di, -di);
   const int sw = row & 7;
-  if (pw_row) {
-#pragma unroll
-    for (int c8 = 0; c8 < 8; ++c8) {
-      uint4 v;
-      v.x = pack_bf16x2(p[8 * c8 + 0] * w, p[8 * c8 + 1] * w);
-      v.y = pack_bf16x2(p[8 * c8 + 2] * w, p[8 * c8 + 3] * w);
-      v.z = pack_bf16x2(p[8 * c8 + 4] * w, p[8 * c8 + 5] * w);
-      v.w = pack_bf16x2(p[8 * c8 + 6] * w, p[8 * c8 + 7] * w);
-      *reinterpret_cast<uint4*>(pw_row + ((c8 ^ sw) << 4)) = v;
-    }
-  }
 #pragma unroll
   for (int c8 = 0; c8 < 8; ++c8) {
-    float e[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) e[i] = p[8 * c8 + i] * w * (__uint_as_float(dp[8 * c8 + i]) - di);
-    uint4 v;
-    v.x = pack_bf16x2(e[0], e[1]); v.y = pack_bf16x2(e[2], e[3]);
-    v.z = pack_bf16x2(e[4], e[5]); v.w = pack_bf16x2(e[6], e[7]);
-    *reinterpret_cast<uint4*>(ds_row + ((c8 ^ sw) << 4)) = v;
+    const float2 p0 = __fmul2_rn(f2(s[8 * c8 + 0], s[8 * c8 + 1]), wv), p1 = __fmul2_rn(f2(s[8 * c8 + 2], s[8 * c8 + 3]), wv);
+    const float2 p2 = __fmul2_rn(f2(s[8 * c8 + 4], s[8 * c8 + 5]), wv), p3 = __fmul2_rn(f2(s[8 * c8 + 6], s[8 * c8 + 7]), wv);
+    if (pw_row)
+      *reinterpret_cast<uint4*>(pw_row + ((c8 ^ sw) << 4)) =
+          make_uint4(pack_bf16x2(p0.x, p0.y), pack_bf16x2(p1.x, p1.y), pack_bf16x2(p2.x, p2.y), pack_bf16x2(p3.x, p3.y));
+    const float2 e0 = __fmul2_rn(p0, __fadd2_rn(f2(dp[8 * c8 + 0], dp[8 * c8 + 1]), ndi));
+    const float2 e1 = __fmul2_rn(p1, __fadd2_rn(f2(dp[8 * c8 + 2], dp[8 * c8 + 3]), ndi));
+    const float2 e2 = __fmul2_rn(p2, __fadd2_rn(f2(dp[8 * c8 + 4], dp[8 * c8 + 5]), ndi));
+    const float2 e3 = __fmul2_rn(p3, __fadd2_rn(f2(dp[8 * c8 + 6], dp[8 * c8 + 7]), ndi));
+    *reinterpret_cast<uint4*>(ds_row + ((c8 ^ sw) << 4)) =
+        make_uint4(pack_bf16x2(e0.x, e0.y), pack_bf16x2(e1.x, e1.y), pack_bf16x2(e2.x, e2.y), pack_bf16x2(e3.x, e3.y));
   }
   return di;
 }
 
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_t* acc, float scale) {
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    uint4 v;
-    v.x = pack_bf16x2(__uint_as_float(acc[8 * c + 0]) * scale, __uint_as_float(acc[8 * c + 1]) * scale);
-    v.y = pack_bf16x2(__uint_as_float(acc[8 * c + 2]) * scale, __uint_as_float(acc[8 * c + 3]) * scale);
-    v.z = pack_bf16x2(__uint_as_float(acc[8 * c + 4]) * scale, __uint_as_float(acc[8 * c + 5]) * scale);
-    v.w = pack_bf16x2(__uint_as_float(acc[8 * c + 6]) * scale, __uint_as_float(acc[8 * c + 7]) * scale);
-    reinterpret_cast<uint4*>(dst)[c] = v;
+__device__ __forceinline__ void drain(uint64_t* bars, int full0, uint32_t issued, int depth) {
+  for (uint32_t back = 0; back < (uint32_t)depth && back < issued; ++back) {
+    const uint32_t g = issued - 1 - back;
+    for (int i = 0; i < (1 << 20); ++i)
+      if (mbar_try_wait(&bars[full0 + g % depth], (g / depth) & 1)) break;
   }
 }
 
@@ -102,262 +104,288 @@ __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_
 // q-major kernel: dQ, dw
 // =============================================================================================
 namespace qk {
-constexpr int OFF_QDO = 0;                                   // [2 bufs][Qa Qb dOa dOb]
-constexpr int OFF_KV = OFF_QDO + 2 * 4 * TILE_BYTES;         // [NSTAGE][Ka Kb Va Vb]
-constexpr int OFF_DS = OFF_KV + NSTAGE * 4 * TILE_BYTES;     // [2 bufs][dSa dSb]
-constexpr int OFF_DW = OFF_DS + 2 * 2 * TILE_BYTES;          // float [2 units][32 slots][2 tiles][4 warps]
-constexpr int OFF_BAR = OFF_DW + 2 * 32 * 2 * 4 * 4;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-enum Bar { QDO_FULL = 0, QDO_EMPTY = 2, KV_FULL = 4, KV_EMPTY = 4 + NSTAGE, SP_FULL = 4 + 2 * NSTAGE,
-           SP_EMPTY = SP_FULL + 2, DS_FULL = SP_EMPTY + 2, DS_EMPTY = DS_FULL + 2, DQ_FULL = DS_EMPTY + 2,
-           DQ_EMPTY = DQ_FULL + 2, NUM_BARS = DQ_EMPTY + 2 };
-constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 256;
+constexpr int NKS = 4, NVS = 3;
+constexpr int OFF_QDO = 0;                                   // [2 bufs][Q pair | dO pair]
+constexpr int OFF_K = OFF_QDO + 2 * 2 * PAIR_BYTES;          // [NKS][K pair]
+constexpr int OFF_V = OFF_K + NKS * PAIR_BYTES;              // [NVS][V pair]
+constexpr int OFF_DS = OFF_V + NVS * PAIR_BYTES;             // [2 bufs][dS pair]
+constexpr int OFF_DW = OFF_DS + 2 * PAIR_BYTES;              // float [2 units][32 slots][2 tiles][2 warps]
+constexpr int OFF_BAR = OFF_DW + 2 * 32 * 2 * 2 * 4;
+constexpr int OFF_IDX = OFF_BAR + 512;
+constexpr int SMEM_BYTES = OFF_IDX + 256 + 1024;
+enum Bar { QDO_FULL = 0, QDO_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + NKS, V_FULL = K_EMPTY + NKS,
+           V_EMPTY = V_FULL + NVS, SP_FULL = V_EMPTY + NVS, SP_EMPTY = SP_FULL + 2, DS_FULL = SP_EMPTY + 1,
+           DS_EMPTY = DS_FULL + 2, DQ_FULL = DS_EMPTY + 2, DQ_EMPTY = DQ_FULL + 2, DW_BAR = DQ_EMPTY + 2, NUM_BARS = DW_BAR + 1 };
 }  // namespace qk
 
 struct BwdQParams {
-  CUtensorMap tm_q, tm_do, tm_k, tm_v;
+  CUtensorMap tm_q, tm_do, tm_k2, tm_v2, tm_k1, tm_v1;
   const int32_t* indices;
   const float* weights;
   const float* lse;
   __nv_bfloat16* dq;
   float* dw_part;
   int32_t* status;
+  long long* prof;
   long long dqs[4];
-  long long units;
+  int units;
   int N, J, Hq, Hkv, G, K, C, HP;
   float c2, sm_scale;
 };
 
-struct QUnit { int zj, n, j, h0, two, hk0, hk1, share; };
-__device__ __forceinline__ QUnit decode_qunit(const BwdQParams& p, long long u) {
-  QUnit t;
-  t.zj = (int)(u / p.HP);
-  const int hp = (int)(u % p.HP);
-  t.n = t.zj / p.J; t.j = t.zj % p.J;
+struct QInfo { int h0, hk0; bool two, share; };
+__device__ __forceinline__ QInfo q_info(const BwdQParams& p, int hp) {
+  QInfo t;
   t.h0 = 2 * hp;
   t.two = (t.h0 + 1) < p.Hq;
-  t.hk0 = t.h0 / p.G;
-  t.hk1 = t.two ? (t.h0 + 1) / p.G : t.hk0;
-  t.share = t.two && (t.hk1 == t.hk0);
+  if (p.G == 1) { t.hk0 = t.h0; t.share = false; }
+  else { t.hk0 = t.h0 / p.G; t.share = t.two && ((t.h0 + 1) / p.G == t.hk0); }
   return t;
 }
-__device__ __forceinline__ unsigned q_slot_mask(const BwdQParams& p, int zj, int lane, int* my_idx) {
-  int idx = -1;
-  if (lane < p.K) idx = p.indices[(long long)zj * p.K + lane];
-  *my_idx = idx;
+__device__ __forceinline__ int q_load_row(const BwdQParams& p, int u, int zj, int lane) {
+  if (u >= p.units || lane >= p.K) return -1;
+  return p.indices[(long long)zj * p.K + lane];
+}
+__device__ __forceinline__ unsigned q_valid(const BwdQParams& p, int idx) {
   return __ballot_sync(0xffffffffu, idx >= 0 && idx < p.C);
 }
 
+// mode 0: Q + dO per unit, K per slot;  mode 1: V per slot
+template <int MODE>
 __device__ void q_producer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane) {
   using namespace qk;
-  uint32_t ucnt = 0, kvcnt = 0;
+  int* sidx = reinterpret_cast<int*>(smem + OFF_IDX) + MODE * 32;
+  constexpr int FULL = MODE == 0 ? K_FULL : V_FULL, EMPTY = MODE == 0 ? K_EMPTY : V_EMPTY;
+  constexpr int DEPTH = MODE == 0 ? NKS : NVS, OFF = MODE == 0 ? OFF_K : OFF_V;
+  PairCursor c;
+  c.init(p.HP);
+  Ring ring; ring.init(DEPTH);
+  uint32_t ucnt = 0, issued = 0;
   bool ok = true;
-  for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-    const QUnit t = decode_qunit(p, u);
-    int my_idx;
-    const unsigned mask = q_slot_mask(p, t.zj, lane, &my_idx);
+  int next_idx = q_load_row(p, c.u, c.outer, lane);
+  for (; c.u < p.units; c.advance()) {
+    const int my_idx = next_idx;
+    next_idx = q_load_row(p, c.u + gridDim.x, c.next_outer(), lane);
+    const unsigned mask = q_valid(p, my_idx);
     if (mask == 0) continue;
-    const uint32_t qb = ucnt & 1;
-    if (lane == 0) {
-      ok = mbar_wait_bounded(&bars[QDO_EMPTY + qb], ((ucnt >> 1) & 1) ^ 1, abort_flag);
-      if (ok) {
-        uint8_t* base = smem + OFF_QDO + qb * 4 * TILE_BYTES;
-        mbar_arrive_expect_tx(&bars[QDO_FULL + qb], (t.two ? 4 : 2) * TILE_BYTES);
-        tma_load_5d(base, &p.tm_q, &bars[QDO_FULL + qb], 0, 0, t.h0, t.j, t.n);
-        tma_load_5d(base + 2 * TILE_BYTES, &p.tm_do, &bars[QDO_FULL + qb], 0, 0, t.h0, t.j, t.n);
-        if (t.two) {
-          tma_load_5d(base + TILE_BYTES, &p.tm_q, &bars[QDO_FULL + qb], 0, 0, t.h0 + 1, t.j, t.n);
-          tma_load_5d(base + 3 * TILE_BYTES, &p.tm_do, &bars[QDO_FULL + qb], 0, 0, t.h0 + 1, t.j, t.n);
-        }
-      }
+    __syncwarp();
+    sidx[lane] = my_idx;
+    __syncwarp();
+    const uint32_t un = ucnt++;
+    if (lane != 0 || !ok) continue;
+    const QInfo t = q_info(p, c.inner);
+    const int n = c.outer / p.J, j = c.outer - n * p.J;
+    if (MODE == 0) {
+      const uint32_t ub = un & 1;
+      ok = mbar_wait_bounded(&bars[QDO_EMPTY + ub], ((un >> 1) & 1) ^ 1, abort_flag);
+      if (!ok) continue;
+      uint8_t* base = smem + OFF_QDO + ub * 2 * PAIR_BYTES;
+      mbar_arrive_expect_tx(&bars[QDO_FULL + ub], 2 * PAIR_BYTES);
+      tma_load_5d(base, &p.tm_q, &bars[QDO_FULL + ub], 0, 0, t.h0, j, n);
+      tma_load_5d(base + PAIR_BYTES, &p.tm_do, &bars[QDO_FULL + ub], 0, 0, t.h0, j, n);
     }
-    ++ucnt;
-    unsigned m = mask;
-    while (m && ok) {
+    const CUtensorMap* tm = MODE == 0 ? (t.share ? &p.tm_k1 : &p.tm_k2) : (t.share ? &p.tm_v1 : &p.tm_v2);
+    const uint32_t bytes = t.share ? TILE_BYTES : PAIR_BYTES;
+    for (unsigned m = mask; m; m &= m - 1) {
       const int k = __ffs(m) - 1;
-      m &= m - 1;
-      const int idx = __shfl_sync(0xffffffffu, my_idx, k);
-      const uint32_t st = kvcnt % NSTAGE;
-      if (lane == 0) {
-        ok = mbar_wait_bounded(&bars[KV_EMPTY + st], ((kvcnt / NSTAGE) & 1) ^ 1, abort_flag);
-        if (ok) {
-          const bool both = t.two && !t.share;
-          uint8_t* base = smem + OFF_KV + st * 4 * TILE_BYTES;
-          mbar_arrive_expect_tx(&bars[KV_FULL + st], (both ? 4 : 2) * TILE_BYTES);
-          tma_load_5d(base, &p.tm_k, &bars[KV_FULL + st], 0, 0, t.hk0, idx, t.n);
-          tma_load_5d(base + 2 * TILE_BYTES, &p.tm_v, &bars[KV_FULL + st], 0, 0, t.hk0, idx, t.n);
-          if (both) {
-            tma_load_5d(base + TILE_BYTES, &p.tm_k, &bars[KV_FULL + st], 0, 0, t.hk1, idx, t.n);
-            tma_load_5d(base + 3 * TILE_BYTES, &p.tm_v, &bars[KV_FULL + st], 0, 0, t.hk1, idx, t.n);
-          }
-        }
-      }
-      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-      ++kvcnt;
+      ok = mbar_wait_bounded(&bars[EMPTY + ring.st], ring.ph ^ 1, abort_flag);
+      if (!ok) break;
+      mbar_arrive_expect_tx(&bars[FULL + ring.st], bytes);
+      tma_load_5d(smem + OFF + ring.st * PAIR_BYTES, tm, &bars[FULL + ring.st], 0, 0, t.hk0, sidx[k], n);
+      ring.next();
+      ++issued;
     }
-    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
   }
-  if (lane == 0 && *abort_flag) {      // drain this lane's copies in flight (bounded)
-    for (uint32_t back = 0; back < NSTAGE && back < kvcnt; ++back) {
-      const uint32_t g = kvcnt - 1 - back;
-      for (int i = 0; i < (1 << 20); ++i)
-        if (mbar_try_wait(&bars[KV_FULL + g % NSTAGE], (g / NSTAGE) & 1)) break;
-    }
-    for (uint32_t back = 0; back < 2 && back < ucnt; ++back) {
-      const uint32_t g = ucnt - 1 - back;
-      for (int i = 0; i < (1 << 20); ++i)
-        if (mbar_try_wait(&bars[QDO_FULL + (g & 1)], (g >> 1) & 1)) break;
-    }
+  if (lane == 0 && *abort_flag) {
+    drain(bars, FULL, issued, DEPTH);
+    if (MODE == 0) drain(bars, QDO_FULL, ucnt, 2);
   }
 }
 
-__device__ void q_mma(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
-                      uint32_t tmem_base) {
+// mode 0: S and dP per slot;  mode 1: dQ += dS K per slot
+template <int MODE>
+__device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
+                         uint32_t tmem_base) {
   using namespace qk;
-  uint32_t ucnt = 0, gcnt = 0;
+  const uint64_t dQDO = umma_desc_sw128(smem_u32(smem + OFF_QDO));
+  const uint64_t dK = umma_desc_sw128(smem_u32(smem + OFF_K)), dV = umma_desc_sw128(smem_u32(smem + OFF_V));
+  const uint64_t dKmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_K), TILE_BYTES);
+  const uint64_t dDS = umma_desc_sw128(smem_u32(smem + OFF_DS));
+  PairCursor c;
+  c.init(p.HP);
+  Ring rk, rv; rk.init(NKS); rv.init(NVS);
+  uint32_t ucnt = 0, g = 0;
   bool ok = true;
-  const uint32_t sQDO = smem_u32(smem + OFF_QDO), sKV = smem_u32(smem + OFF_KV), sDS = smem_u32(smem + OFF_DS);
-  for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-    const QUnit t = decode_qunit(p, u);
-    int my_idx;
-    const int nv = __popc(q_slot_mask(p, t.zj, lane, &my_idx));
-    if (nv == 0) continue;
-    if (lane == 0) {
-      const uint32_t qb = ucnt & 1, ob = ucnt & 1;
-      const int ntile = t.two ? 2 : 1;
-      const uint32_t b_off = (t.two && !t.share) ? TILE_BYTES : 0;
-      ok = mbar_wait_bounded(&bars[QDO_FULL + qb], (ucnt >> 1) & 1, abort_flag) &&
-           mbar_wait_bounded(&bars[DQ_EMPTY + ob], ((ucnt >> 1) & 1) ^ 1, abort_flag);
-      auto issue_sp = [&](uint32_t g) -> bool {
-        const uint32_t st = g % NSTAGE, sb = g & 1;
-        if (!mbar_wait_bounded(&bars[KV_FULL + st], (g / NSTAGE) & 1, abort_flag)) return false;
-        if (!mbar_wait_bounded(&bars[SP_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag)) return false;
-        tc_fence_after();
-        for (int tl = 0; tl < ntile; ++tl) {
-          const uint32_t lane_off = tl ? LANE16 : 0u;
-          const uint32_t qbase = sQDO + qb * 4 * TILE_BYTES + tl * TILE_BYTES;
-          const uint32_t kbase = sKV + st * 4 * TILE_BYTES + (tl ? b_off : 0);
-          mma_tile(tmem_base + COL_S + sb * 64 + lane_off, umma_desc_sw128(qbase), umma_desc_sw128(kbase), IDESC_KK,
-                   STEP_K, STEP_K, false);
-          mma_tile(tmem_base + COL_DP + sb * 64 + lane_off, umma_desc_sw128(qbase + 2 * TILE_BYTES),
-                   umma_desc_sw128(kbase + 2 * TILE_BYTES), IDESC_KK, STEP_K, STEP_K, false);
-        }
-        umma_commit(&bars[SP_FULL + sb]);
-        return true;
-      };
-      if (ok) ok = issue_sp(gcnt);
-      for (int i = 0; i < nv && ok; ++i) {
-        const uint32_t g = gcnt + i;
-        if (i + 1 < nv) ok = issue_sp(g + 1);
-        else umma_commit(&bars[QDO_EMPTY + qb]);
+  PhaseTimer pf;
+  pf.init(p.prof != nullptr && blockIdx.x == 0 && lane == 0);
+  int next_idx = q_load_row(p, c.u, c.outer, lane);
+  for (; c.u < p.units; c.advance()) {
+    const int my_idx = next_idx;
+    next_idx = q_load_row(p, c.u + gridDim.x, c.next_outer(), lane);
+    const unsigned mask = q_valid(p, my_idx);
+    if (mask == 0) continue;
+    const uint32_t un = ucnt++;
+    if (lane != 0 || !ok) continue;
+    pf.lap(7);
+    const int nv = __popc(mask);
+    const QInfo t = q_info(p, c.inner);
+    const uint32_t ub = un & 1, uph = (un >> 1) & 1;
+    const int ncol = t.share ? 64 : 128;
+    if (MODE == 0) ok = mbar_wait_bounded(&bars[QDO_FULL + ub], uph, abort_flag);
+    else ok = mbar_wait_bounded(&bars[DQ_EMPTY + ub], uph ^ 1, abort_flag);
+    pf.lap(0);
+    for (int i = 0; i < nv && ok; ++i, ++g) {
+      if (MODE == 0) {
+        ok = mbar_wait_bounded(&bars[K_FULL + rk.st], rk.ph, abort_flag) &&
+             mbar_wait_bounded(&bars[V_FULL + rv.st], rv.ph, abort_flag);
+        pf.lap(1);
+        ok = ok && mbar_wait_bounded(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag);
+        pf.lap(2);
         if (!ok) break;
-        const uint32_t st = g % NSTAGE, sb = g & 1;
+        tc_fence_after();
+        const uint32_t idesc = umma_idesc_bf16(128, ncol, 0, 0);
+        const uint64_t q = dQDO + ub * 2 * PAIR16;
+        mma4(tmem_base + COL_S, q, dK + rk.st * PAIR16, idesc, STEP_K, STEP_K, false);
+        mma4(tmem_base + COL_DP, q + PAIR16, dV + rv.st * PAIR16, idesc, STEP_K, STEP_K, false);
+        umma_commit(&bars[SP_FULL + (g & 1)]);   // one barrier per worker group: a waiter never lags a barrier by two phases
+        rv.next();
+      } else {
+        const uint32_t sb = g & 1;
         ok = mbar_wait_bounded(&bars[DS_FULL + sb], (g >> 1) & 1, abort_flag);
+        pf.lap(1);
         if (!ok) break;
         tc_fence_after();
-        for (int tl = 0; tl < ntile; ++tl)     // dQ += dS K_k : A = dS (K-major), B = K_k (MN-major)
-          mma_tile(tmem_base + COL_DQ + ob * 64 + (tl ? LANE16 : 0u),
-                   umma_desc_sw128(sDS + sb * 2 * TILE_BYTES + tl * TILE_BYTES),
-                   umma_desc_sw128(sKV + st * 4 * TILE_BYTES + (tl ? b_off : 0)), IDESC_KM, STEP_K, STEP_MN, i > 0);
+        // dQ += dS K_k : A = dS (K-major), B = K_k (MN-major, both heads' tiles)
+        mma4(tmem_base + COL_ACC + ub * 128, dDS + sb * PAIR16, dKmn + rk.st * PAIR16, umma_idesc_bf16(128, ncol, 0, 1),
+             STEP_K, STEP_MN, i > 0);
         umma_commit(&bars[DS_EMPTY + sb]);
-        umma_commit(&bars[KV_EMPTY + st]);
+        if (i == nv - 1) umma_commit(&bars[DQ_FULL + ub]);
       }
-      if (ok) umma_commit(&bars[DQ_FULL + ob]);
+      pf.lap(3);
+      rk.next();
     }
-    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-    ++ucnt; gcnt += nv;
   }
+  pf.dump(p.prof + 36 + 12 + 12 * MODE);
 }
 
-__device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int warp,
-                         int lane, uint32_t tmem_base) {
+__device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
+                         int quad, int lane, uint32_t tmem_base) {
   using namespace qk;
-  const int tile = lane >> 4;
-  const int row = warp * 16 + (lane & 15);
-  const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const int tile = quad >> 1;
+  const int row = (quad & 1) * 32 + lane;
+  const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
+  const bool elected = quad == 0 && lane == 0;
+  const int tid = (wg * 4 + quad) * 32 + lane;                  // 0..255 over both worker groups
   float* dws = reinterpret_cast<float*>(smem + OFF_DW);
-  uint32_t ucnt = 0, gcnt = 0;
+  PairCursor c;
+  c.init(p.HP);
+  uint32_t ucnt = 0, g = 0;
   bool ok = true;
-  for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-    const QUnit t = decode_qunit(p, u);
+  PhaseTimer pf;
+  pf.init(p.prof != nullptr && blockIdx.x == 0 && wg == 0 && elected);
+  int next_idx = q_load_row(p, c.u, c.outer, lane);
+  float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.outer * p.K + lane] : 0.f;
+  for (; c.u < p.units && ok; c.advance()) {
+    const int my_idx = next_idx;
+    const float my_w = next_w;
+    {
+      const int nzj = c.next_outer();
+      next_idx = q_load_row(p, c.u + gridDim.x, nzj, lane);
+      next_w = (c.u + gridDim.x < p.units && lane < p.K) ? p.weights[(long long)nzj * p.K + lane] : 0.f;
+    }
+    const unsigned mask = q_valid(p, my_idx);
+    const QInfo t = q_info(p, c.inner);
     const int h = t.h0 + tile;
-    const bool live = h < p.Hq;
-    int my_idx;
-    const unsigned mask = q_slot_mask(p, t.zj, lane, &my_idx);
-    const float my_w = lane < p.K ? p.weights[(long long)t.zj * p.K + lane] : 0.f;
-    __nv_bfloat16* dq_row = p.dq + t.n * p.dqs[0] + t.j * p.dqs[1] + h * p.dqs[2] + row * p.dqs[3];
-    float* dwp = p.dw_part + ((long long)t.zj * p.Hq + t.h0) * p.K;          // [tile][k] via + tile*K
+    const bool live = (tile == 0 || t.two) && h < p.Hq;
+    const uint32_t coff = t.share ? 0u : (uint32_t)tile * 64u;
+    const int n = c.outer / p.J, j = c.outer - n * p.J;
+    __nv_bfloat16* dq_row = p.dq + n * p.dqs[0] + j * p.dqs[1] + h * p.dqs[2] + row * p.dqs[3];
+    float* dwp = p.dw_part + ((long long)c.outer * p.Hq + t.h0) * p.K;     // [tile][k]
     if (mask == 0) {
-      if (live) {
+      if (wg == 0 && live) {
         const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(dq_row)[c] = z;
+        for (int cc = 0; cc < 8; ++cc) reinterpret_cast<uint4*>(dq_row)[cc] = z;
       }
-      const int tid = warp * 32 + lane;
       if (tid < 2 * p.K && (t.h0 + tid / p.K) < p.Hq) dwp[tid] = 0.f;
       continue;
     }
-    const uint32_t ob = ucnt & 1;
-    float* dws_u = dws + (ucnt & 1) * (32 * 2 * 4);
-    const float* lse_base = p.lse + ((long long)t.zj * p.Hq + (live ? h : t.h0)) * p.K * 64 + row;
-    unsigned m = mask;
-    while (m) {
+    const uint32_t un = ucnt++;
+    const uint32_t ub = un & 1;
+    float* dws_u = dws + ub * (32 * 2 * 2);
+    const float* lse_base = p.lse + ((long long)c.outer * p.Hq + (live ? h : t.h0)) * p.K * 64 + row;
+    for (unsigned m = mask; m; m &= m - 1, ++g) {
+      if ((int)(g & 1) != wg) continue;
       const int k = __ffs(m) - 1;
-      m &= m - 1;
+      const bool last = (m & (m - 1)) == 0;
       const float w = __shfl_sync(0xffffffffu, my_w, k);
       const float lse = lse_base[k * 64];
-      const uint32_t g = gcnt, sb = g & 1;
-      ok = mbar_wait_bounded(&bars[SP_FULL + sb], (g >> 1) & 1, abort_flag);
+      const uint32_t sb = g & 1;
+      pf.lap(7);
+      ok = mbar_wait_bounded(&bars[SP_FULL + (g & 1)], (g >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      pf.lap(0);
+      if (elected) {                         // S/dP done: the V stage (and at the end Q/dO) can be refilled
+        mbar_arrive(&bars[V_EMPTY + g % NVS]);
+        if (last) mbar_arrive(&bars[QDO_EMPTY + ub]);
+      }
       tc_fence_after();
       uint32_t s[64], dp[64];
-      tmem_ld_32x32b_x32(tlane + COL_S + sb * 64, s);
-      tmem_ld_32x32b_x32(tlane + COL_S + sb * 64 + 32, s + 32);
-      tmem_ld_32x32b_x32(tlane + COL_DP + sb * 64, dp);
-      tmem_ld_32x32b_x32(tlane + COL_DP + sb * 64 + 32, dp + 32);
+      tmem_ld_32x32b_x32(tlane + COL_S + coff, s);
+      tmem_ld_32x32b_x32(tlane + COL_S + coff + 32, s + 32);
+      tmem_ld_32x32b_x32(tlane + COL_DP + coff, dp);
+      tmem_ld_32x32b_x32(tlane + COL_DP + coff + 32, dp + 32);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&bars[SP_EMPTY + sb]);
+      mbar_arrive(&bars[SP_EMPTY]);
+      pf.lap(1);
       ok = mbar_wait_bounded(&bars[DS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-      uint8_t* ds_row = smem + OFF_DS + sb * 2 * TILE_BYTES + tile * TILE_BYTES + row * 128;
+      pf.lap(2);
+      if (elected && g >= 2) mbar_arrive(&bars[K_EMPTY + (g - 2) % NKS]);   // dQ MMA of slot g-2 is done
+      uint8_t* ds_row = smem + OFF_DS + sb * PAIR_BYTES + tile * TILE_BYTES + row * 128;
       float di = row_backward(s, dp, lse, p.c2, w, nullptr, ds_row, row);
       fence_proxy_async_smem();
       mbar_arrive(&bars[DS_FULL + sb]);
-      // dw: sum of Di over the 16 rows this warp holds of each tile
+      pf.lap(3);
+      // dw: sum of Di over the 32 rows this warp holds of its tile
 #pragma unroll
-      for (int of = 8; of > 0; of >>= 1) di += __shfl_xor_sync(0xffffffffu, di, of);
-      if ((lane & 15) == 0) dws_u[(k * 2 + tile) * 4 + warp] = di;
-      ++gcnt;
+      for (int of = 16; of > 0; of >>= 1) di += __shfl_xor_sync(0xffffffffu, di, of);
+      if (lane == 0) dws_u[(k * 2 + tile) * 2 + (quad & 1)] = di;
+      pf.lap(4);
     }
     if (!ok) break;
-    named_barrier_128();
-    {
-      const int tid = warp * 32 + lane;
-      if (tid < 2 * p.K) {
-        const int tl = tid / p.K, k = tid % p.K;
-        if (t.h0 + tl < p.Hq) {
-          float v = 0.f;
-          if ((mask >> k) & 1) {
-            const float* src = dws_u + (k * 2 + tl) * 4;
-            v = ((src[0] + src[1]) + src[2]) + src[3];
-          }
-          dwp[tl * p.K + k] = v;
-        }
+    pf.lap(7);
+    // both worker groups have written their dw partials (bounded rendezvous of the 256 workers)
+    mbar_arrive(&bars[DW_BAR]);
+    ok = mbar_wait_bounded(&bars[DW_BAR], un & 1, abort_flag);
+    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+    if (tid < 2 * p.K) {
+      const int tl = tid / p.K, k = tid - tl * p.K;
+      if (t.h0 + tl < p.Hq) {
+        float v = 0.f;
+        if ((mask >> k) & 1) v = dws_u[(k * 2 + tl) * 2] + dws_u[(k * 2 + tl) * 2 + 1];
+        dwp[tl * p.K + k] = v;
       }
     }
-    ok = mbar_wait_bounded(&bars[DQ_FULL + ob], (ucnt >> 1) & 1, abort_flag);
-    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-    tc_fence_after();
-    uint32_t acc[64];
-    tmem_ld_32x32b_x32(tlane + COL_DQ + ob * 64, acc);
-    tmem_ld_32x32b_x32(tlane + COL_DQ + ob * 64 + 32, acc + 32);
-    tmem_ld_wait();
-    tc_fence_before();
-    mbar_arrive(&bars[DQ_EMPTY + ob]);
-    if (live) store_row_bf16(dq_row, acc, p.sm_scale);
-    ++ucnt;
+    pf.lap(4);
+    if ((int)ub == wg) {
+      ok = mbar_wait_bounded(&bars[DQ_FULL + ub], (un >> 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      pf.lap(5);
+      tc_fence_after();
+      uint32_t acc[64];
+      tmem_ld_32x32b_x32(tlane + COL_ACC + ub * 128 + coff, acc);
+      tmem_ld_32x32b_x32(tlane + COL_ACC + ub * 128 + coff + 32, acc + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[DQ_EMPTY + ub]);
+      if (live) store_row_bf16(dq_row, acc, p.sm_scale);
+      pf.lap(6);
+    }
   }
+  pf.lap(7);
+  pf.dump(p.prof + 36);
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -372,28 +400,31 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[QDO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1);
-      mbar_init(&bars[SP_FULL + i], 1); mbar_init(&bars[SP_EMPTY + i], 128);
       mbar_init(&bars[DS_FULL + i], 128); mbar_init(&bars[DS_EMPTY + i], 1);
       mbar_init(&bars[DQ_FULL + i], 1); mbar_init(&bars[DQ_EMPTY + i], 128);
     }
-    for (int i = 0; i < NSTAGE; ++i) { mbar_init(&bars[KV_FULL + i], 1); mbar_init(&bars[KV_EMPTY + i], 1); }
+    mbar_init(&bars[SP_FULL], 1); mbar_init(&bars[SP_FULL + 1], 1); mbar_init(&bars[SP_EMPTY], 128);
+    mbar_init(&bars[DW_BAR], 256);
+    for (int i = 0; i < NKS; ++i) { mbar_init(&bars[K_FULL + i], 1); mbar_init(&bars[K_EMPTY + i], 1); }
+    for (int i = 0; i < NVS; ++i) { mbar_init(&bars[V_FULL + i], 1); mbar_init(&bars[V_EMPTY + i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-  if (warp == 4 && lane == 0) {
-    tma_prefetch_desc(&p.tm_q); tma_prefetch_desc(&p.tm_do); tma_prefetch_desc(&p.tm_k); tma_prefetch_desc(&p.tm_v);
-  }
+  if (warp == ISSUE_A) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  if (warp == PROD_A && lane == 0) { tma_prefetch_desc(&p.tm_q); tma_prefetch_desc(&p.tm_do); tma_prefetch_desc(&p.tm_k2); }
+  if (warp == PROD_B && lane == 0) { tma_prefetch_desc(&p.tm_v2); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (warp < 4) q_worker(p, smem, bars, abort_flag, warp, lane, tmem_base);
-  else if (warp == 4) q_producer(p, smem, bars, abort_flag, lane);
-  else q_mma(p, smem, bars, abort_flag, lane, tmem_base);
+  if (warp < 8) q_worker(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
+  else if (warp == PROD_A) q_producer<0>(p, smem, bars, abort_flag, lane);
+  else if (warp == PROD_B) q_producer<1>(p, smem, bars, abort_flag, lane);
+  else if (warp == ISSUE_A) q_issuer<0>(p, smem, bars, abort_flag, lane, tmem_base);
+  else q_issuer<1>(p, smem, bars, abort_flag, lane, tmem_base);
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == ISSUE_A) tmem_dealloc(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
 }
 
@@ -401,19 +432,21 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
 // kv-major kernel: dK, dV
 // =============================================================================================
 namespace kv {
-constexpr int OFF_KV = 0;                                    // [2 bufs][Ka Kb Va Vb]
-constexpr int OFF_QDO = OFF_KV + 2 * 4 * TILE_BYTES;         // [NSTAGE][Qa Qb dOa dOb]
-constexpr int OFF_PDS = OFF_QDO + NSTAGE * 4 * TILE_BYTES;   // [2 bufs][Pwa Pwb dSa dSb]
-constexpr int OFF_BAR = OFF_PDS + 2 * 4 * TILE_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-enum Bar { KV_FULL = 0, KV_EMPTY = 2, QDO_FULL = 4, QDO_EMPTY = 4 + NSTAGE, SP_FULL = 4 + 2 * NSTAGE,
-           SP_EMPTY = SP_FULL + 2, PDS_FULL = SP_EMPTY + 2, PDS_EMPTY = PDS_FULL + 2, ACC_FULL = PDS_EMPTY + 2,
-           ACC_EMPTY = ACC_FULL + 2, NUM_BARS = ACC_EMPTY + 2 };
-constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DK = 256, COL_DV = 384;   // each double-buffered, 64 columns
+constexpr int NQ = 3;
+constexpr int OFF_KV = 0;                                    // [2 bufs][K pair | V pair]
+constexpr int OFF_Q = OFF_KV + 2 * 2 * PAIR_BYTES;           // [NQ][Q pair]
+constexpr int OFF_DO = OFF_Q + NQ * PAIR_BYTES;              // [NQ][dO pair]
+constexpr int OFF_PDS = OFF_DO + NQ * PAIR_BYTES;            // [2 bufs][Pw pair | dS pair]
+constexpr int OFF_BAR = OFF_PDS + 2 * 2 * PAIR_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
+enum Bar { KV_FULL = 0, KV_EMPTY = 2, Q_FULL = 4, DO_FULL = Q_FULL + NQ, QDO_EMPTY = DO_FULL + NQ,
+           SP_FULL = QDO_EMPTY + NQ, SP_EMPTY = SP_FULL + 2, PDS_FULL = SP_EMPTY + 1, PDS_EMPTY = PDS_FULL + 2,
+           ACC_FULL = PDS_EMPTY + 2, ACC_EMPTY = ACC_FULL + 2, NUM_BARS = ACC_EMPTY + 1 };
+constexpr uint32_t COL_DK = 256, COL_DV = 384;
 }  // namespace kv
 
 struct BwdKvParams {
-  CUtensorMap tm_q, tm_do, tm_k, tm_v;
+  CUtensorMap tm_q2, tm_do2, tm_q1, tm_do1, tm_k2, tm_v2;
   const float* weights;
   const float* lse;
   const int* offsets;
@@ -421,209 +454,236 @@ struct BwdKvParams {
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
   int32_t* status;
+  long long* prof;
   long long dks[4], dvs[4];
-  long long units;
+  int units;
   int N, J, Hq, Hkv, G, K, C, HP;
   float c2, sm_scale;
 };
 
-struct KvUnit { int nc, n, c, hk0, two, beg, end; };
-__device__ __forceinline__ KvUnit decode_kvunit(const BwdKvParams& p, long long u) {
-  KvUnit t;
-  t.nc = (int)(u / p.HP);
-  const int hp = (int)(u % p.HP);
-  t.n = t.nc / p.C; t.c = t.nc % p.C;
-  t.hk0 = 2 * hp;
-  t.two = (t.hk0 + 1) < p.Hkv;
-  t.beg = p.offsets[t.nc];
-  t.end = p.offsets[t.nc + 1];
-  return t;
-}
-
+// mode 0: K + V per unit and Q per iteration;  mode 1: dO per iteration
+template <int MODE>
 __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
   using namespace kv;
-  uint32_t ucnt = 0, icnt = 0;
+  PairCursor c;
+  c.init(p.HP);
+  Ring ring; ring.init(NQ);
+  uint32_t ucnt = 0, issued = 0;
   bool ok = true;
-  for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-    const KvUnit t = decode_kvunit(p, u);
-    if (t.end == t.beg) continue;
-    const uint32_t kb = ucnt & 1;
-    ok = mbar_wait_bounded(&bars[KV_EMPTY + kb], ((ucnt >> 1) & 1) ^ 1, abort_flag);
-    if (!ok) break;
-    {
-      uint8_t* base = smem + OFF_KV + kb * 4 * TILE_BYTES;
-      mbar_arrive_expect_tx(&bars[KV_FULL + kb], (t.two ? 4 : 2) * TILE_BYTES);
-      tma_load_5d(base, &p.tm_k, &bars[KV_FULL + kb], 0, 0, t.hk0, t.c, t.n);
-      tma_load_5d(base + 2 * TILE_BYTES, &p.tm_v, &bars[KV_FULL + kb], 0, 0, t.hk0, t.c, t.n);
-      if (t.two) {
-        tma_load_5d(base + TILE_BYTES, &p.tm_k, &bars[KV_FULL + kb], 0, 0, t.hk0 + 1, t.c, t.n);
-        tma_load_5d(base + 3 * TILE_BYTES, &p.tm_v, &bars[KV_FULL + kb], 0, 0, t.hk0 + 1, t.c, t.n);
-      }
+  int nbeg = c.u < p.units ? p.offsets[c.outer] : 0, nend = c.u < p.units ? p.offsets[c.outer + 1] : 0;
+  for (; c.u < p.units && ok; c.advance()) {
+    const int beg = nbeg, end = nend;
+    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nbeg = p.offsets[no]; nend = p.offsets[no + 1]; }
+    if (end == beg) continue;
+    const uint32_t un = ucnt++;
+    const int hk0 = 2 * c.inner;
+    const bool two = hk0 + 1 < p.Hkv;
+    const int n = c.outer / p.C, ch = c.outer - n * p.C;
+    if (MODE == 0) {
+      const uint32_t kb = un & 1;
+      ok = mbar_wait_bounded(&bars[KV_EMPTY + kb], ((un >> 1) & 1) ^ 1, abort_flag);
+      if (!ok) break;
+      uint8_t* base = smem + OFF_KV + kb * 2 * PAIR_BYTES;
+      mbar_arrive_expect_tx(&bars[KV_FULL + kb], 2 * PAIR_BYTES);
+      tma_load_5d(base, &p.tm_k2, &bars[KV_FULL + kb], 0, 0, hk0, ch, n);
+      tma_load_5d(base + PAIR_BYTES, &p.tm_v2, &bars[KV_FULL + kb], 0, 0, hk0, ch, n);
     }
-    ++ucnt;
-    for (int e = t.beg; e < t.end && ok; ++e) {
+    const int FULL = MODE == 0 ? Q_FULL : DO_FULL;
+    const int OFF = MODE == 0 ? OFF_Q : OFF_DO;
+    for (int e = beg; e < end && ok; ++e) {
       const int entry = (int)(p.sorted_keys[e] & 0xffffffffull);
       const int j = entry / p.K;
-      for (int gi = 0; gi < p.G && ok; ++gi) {
-        const uint32_t st = icnt % NSTAGE;
-        ok = mbar_wait_bounded(&bars[QDO_EMPTY + st], ((icnt / NSTAGE) & 1) ^ 1, abort_flag);
+      for (int gi = 0; gi < p.G; ++gi) {
+        ok = mbar_wait_bounded(&bars[QDO_EMPTY + ring.st], ring.ph ^ 1, abort_flag);
         if (!ok) break;
-        uint8_t* base = smem + OFF_QDO + st * 4 * TILE_BYTES;
-        const int ha = t.hk0 * p.G + gi, hb = (t.hk0 + 1) * p.G + gi;
-        mbar_arrive_expect_tx(&bars[QDO_FULL + st], (t.two ? 4 : 2) * TILE_BYTES);
-        tma_load_5d(base, &p.tm_q, &bars[QDO_FULL + st], 0, 0, ha, j, t.n);
-        tma_load_5d(base + 2 * TILE_BYTES, &p.tm_do, &bars[QDO_FULL + st], 0, 0, ha, j, t.n);
-        if (t.two) {
-          tma_load_5d(base + TILE_BYTES, &p.tm_q, &bars[QDO_FULL + st], 0, 0, hb, j, t.n);
-          tma_load_5d(base + 3 * TILE_BYTES, &p.tm_do, &bars[QDO_FULL + st], 0, 0, hb, j, t.n);
+        uint8_t* dst = smem + OFF + ring.st * PAIR_BYTES;
+        mbar_arrive_expect_tx(&bars[FULL + ring.st], PAIR_BYTES);
+        if (p.G == 1) {
+          tma_load_5d(dst, MODE == 0 ? &p.tm_q2 : &p.tm_do2, &bars[FULL + ring.st], 0, 0, hk0, j, n);
+        } else {      // the two q heads of the pair are G apart: one copy per head
+          const CUtensorMap* tm = MODE == 0 ? &p.tm_q1 : &p.tm_do1;
+          const int hb = two ? (hk0 + 1) * p.G + gi : hk0 * p.G + gi;
+          tma_load_5d(dst, tm, &bars[FULL + ring.st], 0, 0, hk0 * p.G + gi, j, n);
+          tma_load_5d(dst + TILE_BYTES, tm, &bars[FULL + ring.st], 0, 0, hb, j, n);
         }
-        ++icnt;
+        ring.next();
+        ++issued;
       }
     }
   }
   if (*abort_flag) {
-    for (uint32_t back = 0; back < NSTAGE && back < icnt; ++back) {
-      const uint32_t g = icnt - 1 - back;
-      for (int i = 0; i < (1 << 20); ++i)
-        if (mbar_try_wait(&bars[QDO_FULL + g % NSTAGE], (g / NSTAGE) & 1)) break;
-    }
-    for (uint32_t back = 0; back < 2 && back < ucnt; ++back) {
-      const uint32_t g = ucnt - 1 - back;
-      for (int i = 0; i < (1 << 20); ++i)
-        if (mbar_try_wait(&bars[KV_FULL + (g & 1)], (g >> 1) & 1)) break;
-    }
+    drain(bars, MODE == 0 ? Q_FULL : DO_FULL, issued, NQ);
+    if (MODE == 0) drain(bars, KV_FULL, ucnt, 2);
   }
 }
 
-__device__ void kv_mma(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag,
-                       uint32_t tmem_base) {
+// mode 0: S and dP per iteration;  mode 1: dV and dK per iteration
+template <int MODE>
+__device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag,
+                          uint32_t tmem_base) {
   using namespace kv;
-  uint32_t ucnt = 0, icnt = 0;
+  const uint64_t dKV = umma_desc_sw128(smem_u32(smem + OFF_KV));
+  const uint64_t dQ = umma_desc_sw128(smem_u32(smem + OFF_Q)), dDO = umma_desc_sw128(smem_u32(smem + OFF_DO));
+  const uint64_t dQmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_Q), TILE_BYTES);
+  const uint64_t dDOmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_DO), TILE_BYTES);
+  const uint64_t dPDSmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_PDS), TILE_BYTES);
+  constexpr uint32_t IDESC_KK = umma_idesc_bf16(128, 128, 0, 0), IDESC_MM = umma_idesc_bf16(128, 128, 1, 1);
+  PairCursor c;
+  c.init(p.HP);
+  Ring ring; ring.init(NQ);
+  uint32_t ucnt = 0, g = 0;
   bool ok = true;
-  const uint32_t sKV = smem_u32(smem + OFF_KV), sQDO = smem_u32(smem + OFF_QDO), sPDS = smem_u32(smem + OFF_PDS);
-  for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-    const KvUnit t = decode_kvunit(p, u);
-    const int niter = (t.end - t.beg) * p.G;
+  PhaseTimer pf;
+  pf.init(p.prof != nullptr && blockIdx.x == 0);
+  int nbeg = c.u < p.units ? p.offsets[c.outer] : 0, nend = c.u < p.units ? p.offsets[c.outer + 1] : 0;
+  for (; c.u < p.units && ok; c.advance()) {
+    const int beg = nbeg, end = nend;
+    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nbeg = p.offsets[no]; nend = p.offsets[no + 1]; }
+    const int niter = (end - beg) * p.G;
     if (niter == 0) continue;
-    const uint32_t kb = ucnt & 1, ob = ucnt & 1;
-    const int ntile = t.two ? 2 : 1;
-    ok = mbar_wait_bounded(&bars[KV_FULL + kb], (ucnt >> 1) & 1, abort_flag) &&
-         mbar_wait_bounded(&bars[ACC_EMPTY + ob], ((ucnt >> 1) & 1) ^ 1, abort_flag);
-    auto issue_sp = [&](uint32_t g) -> bool {
-      const uint32_t st = g % NSTAGE, sb = g & 1;
-      if (!mbar_wait_bounded(&bars[QDO_FULL + st], (g / NSTAGE) & 1, abort_flag)) return false;
-      if (!mbar_wait_bounded(&bars[SP_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag)) return false;
-      tc_fence_after();
-      for (int tl = 0; tl < ntile; ++tl) {
-        const uint32_t lane_off = tl ? LANE16 : 0u;
-        const uint32_t qbase = sQDO + st * 4 * TILE_BYTES + tl * TILE_BYTES;
-        const uint32_t kbase = sKV + kb * 4 * TILE_BYTES + tl * TILE_BYTES;
-        mma_tile(tmem_base + COL_S + sb * 64 + lane_off, umma_desc_sw128(qbase), umma_desc_sw128(kbase), IDESC_KK,
-                 STEP_K, STEP_K, false);
-        mma_tile(tmem_base + COL_DP + sb * 64 + lane_off, umma_desc_sw128(qbase + 2 * TILE_BYTES),
-                 umma_desc_sw128(kbase + 2 * TILE_BYTES), IDESC_KK, STEP_K, STEP_K, false);
-      }
-      umma_commit(&bars[SP_FULL + sb]);
-      return true;
-    };
-    if (ok) ok = issue_sp(icnt);
-    for (int i = 0; i < niter && ok; ++i) {
-      const uint32_t g = icnt + i;
-      if (i + 1 < niter) ok = issue_sp(g + 1);
-      else umma_commit(&bars[KV_EMPTY + kb]);
-      if (!ok) break;
-      const uint32_t st = g % NSTAGE, sb = g & 1;
-      ok = mbar_wait_bounded(&bars[PDS_FULL + sb], (g >> 1) & 1, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      for (int tl = 0; tl < ntile; ++tl) {
-        const uint32_t lane_off = tl ? LANE16 : 0u;
-        const uint32_t pbase = sPDS + sb * 4 * TILE_BYTES + tl * TILE_BYTES;
-        const uint32_t qbase = sQDO + st * 4 * TILE_BYTES + tl * TILE_BYTES;
+    pf.lap(7);
+    const uint32_t un = ucnt++;
+    const uint32_t kb = un & 1;
+    if (MODE == 0) ok = mbar_wait_bounded(&bars[KV_FULL + kb], (un >> 1) & 1, abort_flag);
+    else ok = mbar_wait_bounded(&bars[ACC_EMPTY], (un & 1) ^ 1, abort_flag);
+    pf.lap(0);
+    for (int i = 0; i < niter && ok; ++i, ++g) {
+      if (MODE == 0) {
+        ok = mbar_wait_bounded(&bars[Q_FULL + ring.st], ring.ph, abort_flag) &&
+             mbar_wait_bounded(&bars[DO_FULL + ring.st], ring.ph, abort_flag);
+        pf.lap(1);
+        ok = ok && mbar_wait_bounded(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag);
+        pf.lap(2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t kd = dKV + kb * 2 * PAIR16;
+        mma4(tmem_base + COL_S, dQ + ring.st * PAIR16, kd, IDESC_KK, STEP_K, STEP_K, false);
+        mma4(tmem_base + COL_DP, dDO + ring.st * PAIR16, kd + PAIR16, IDESC_KK, STEP_K, STEP_K, false);
+        umma_commit(&bars[SP_FULL + (g & 1)]);
+      } else {
+        const uint32_t sb = g & 1;
+        ok = mbar_wait_bounded(&bars[PDS_FULL + sb], (g >> 1) & 1, abort_flag);
+        pf.lap(1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t pd = dPDSmn + sb * 2 * PAIR16;
         // dV += (w P)^T dO : A = Pw read transposed (MN-major), B = dO (MN-major)
-        mma_tile(tmem_base + COL_DV + ob * 64 + lane_off, umma_desc_sw128(pbase),
-                 umma_desc_sw128(qbase + 2 * TILE_BYTES), IDESC_MM, STEP_MN, STEP_MN, i > 0);
+        mma4(tmem_base + COL_DV, pd, dDOmn + ring.st * PAIR16, IDESC_MM, STEP_MN, STEP_MN, i > 0);
         // dK += dS^T Q
-        mma_tile(tmem_base + COL_DK + ob * 64 + lane_off, umma_desc_sw128(pbase + 2 * TILE_BYTES),
-                 umma_desc_sw128(qbase), IDESC_MM, STEP_MN, STEP_MN, i > 0);
+        mma4(tmem_base + COL_DK, pd + PAIR16, dQmn + ring.st * PAIR16, IDESC_MM, STEP_MN, STEP_MN, i > 0);
+        umma_commit(&bars[PDS_EMPTY + sb]);
+        if (i == niter - 1) umma_commit(&bars[ACC_FULL + (un & 1)]);
       }
-      umma_commit(&bars[PDS_EMPTY + sb]);
-      umma_commit(&bars[QDO_EMPTY + st]);
+      pf.lap(3);
+      ring.next();
     }
-    if (ok) umma_commit(&bars[ACC_FULL + ob]);
-    ++ucnt; icnt += niter;
   }
+  pf.dump(p.prof + 72 + 12 + 12 * MODE);
 }
 
-__device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int warp,
-                          int lane, uint32_t tmem_base) {
+__device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
+                          int quad, int lane, uint32_t tmem_base) {
   using namespace kv;
-  const int tile = lane >> 4;
-  const int row = warp * 16 + (lane & 15);
-  const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
-  uint32_t ucnt = 0, icnt = 0;
+  const int tile = quad >> 1;
+  const int row = (quad & 1) * 32 + lane;
+  const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
+  const uint32_t coff = (uint32_t)tile * 64u;
+  const bool elected = quad == 0 && lane == 0;
+  PairCursor c;
+  c.init(p.HP);
+  uint32_t ucnt = 0, g = 0;
   bool ok = true;
-  for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-    const KvUnit t = decode_kvunit(p, u);
-    const int hk = t.hk0 + tile;
+  PhaseTimer pf;
+  pf.init(p.prof != nullptr && blockIdx.x == 0 && wg == 0 && elected);
+  int nbeg = c.u < p.units ? p.offsets[c.outer] : 0, nend = c.u < p.units ? p.offsets[c.outer + 1] : 0;
+  for (; c.u < p.units && ok; c.advance()) {
+    const int beg = nbeg, end = nend;
+    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nbeg = p.offsets[no]; nend = p.offsets[no + 1]; }
+    const int hk = 2 * c.inner + tile;
     const bool live = hk < p.Hkv;
-    __nv_bfloat16* dk_row = p.dk + t.n * p.dks[0] + t.c * p.dks[1] + row * p.dks[2] + hk * p.dks[3];
-    __nv_bfloat16* dv_row = p.dv + t.n * p.dvs[0] + t.c * p.dvs[1] + row * p.dvs[2] + hk * p.dvs[3];
-    if (t.end == t.beg) {
-      if (live) {
+    const int n = c.outer / p.C, ch = c.outer - n * p.C;
+    __nv_bfloat16* dk_row = p.dk + n * p.dks[0] + ch * p.dks[1] + row * p.dks[2] + hk * p.dks[3];
+    __nv_bfloat16* dv_row = p.dv + n * p.dvs[0] + ch * p.dvs[1] + row * p.dvs[2] + hk * p.dvs[3];
+    if (end == beg) {
+      if (wg == 0 && live) {
         const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) { reinterpret_cast<uint4*>(dk_row)[c] = z; reinterpret_cast<uint4*>(dv_row)[c] = z; }
+        for (int cc = 0; cc < 8; ++cc) { reinterpret_cast<uint4*>(dk_row)[cc] = z; reinterpret_cast<uint4*>(dv_row)[cc] = z; }
       }
       continue;
     }
-    const uint32_t ob = ucnt & 1;
-    for (int e = t.beg; e < t.end && ok; ++e) {
-      const int entry = (int)(p.sorted_keys[e] & 0xffffffffull);
-      const int j = entry / p.K, k = entry % p.K;
-      const long long zj = (long long)t.n * p.J + j;
-      const float w = p.weights[zj * p.K + k];
-      for (int gi = 0; gi < p.G; ++gi) {
-        const int h = (live ? hk : t.hk0) * p.G + gi;
+    const uint32_t un = ucnt++;
+    const uint32_t kb = un & 1;
+    const int hk_safe = live ? hk : 2 * c.inner;
+    for (int e = beg; e < end && ok; ++e) {
+      float w = 0.f;
+      long long zj = 0;
+      int k = 0;
+      // every thread needs (zj, k, w) of an entry only for its own iterations; fetch lazily
+      bool fetched = false;
+      for (int gi = 0; gi < p.G; ++gi, ++g) {
+        if ((int)(g & 1) != wg) continue;
+        if (!fetched) {
+          const int entry = (int)(p.sorted_keys[e] & 0xffffffffull);
+          const int j = entry / p.K;
+          k = entry - j * p.K;
+          zj = (long long)n * p.J + j;
+          w = p.weights[zj * p.K + k];
+          fetched = true;
+        }
+        const bool last = (e == end - 1) && (gi == p.G - 1);
+        const int h = hk_safe * p.G + gi;
         const float lse = p.lse[((zj * p.Hq + h) * p.K + k) * 64 + row];
-        const uint32_t g = icnt, sb = g & 1;
-        ok = mbar_wait_bounded(&bars[SP_FULL + sb], (g >> 1) & 1, abort_flag);
+        const uint32_t sb = g & 1;
+        pf.lap(7);
+        ok = mbar_wait_bounded(&bars[SP_FULL + (g & 1)], (g >> 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        pf.lap(0);
+        if (elected && last) mbar_arrive(&bars[KV_EMPTY + kb]);     // the unit's K/V tiles are no longer needed
         tc_fence_after();
         uint32_t s[64], dp[64];
-        tmem_ld_32x32b_x32(tlane + COL_S + sb * 64, s);
-        tmem_ld_32x32b_x32(tlane + COL_S + sb * 64 + 32, s + 32);
-        tmem_ld_32x32b_x32(tlane + COL_DP + sb * 64, dp);
-        tmem_ld_32x32b_x32(tlane + COL_DP + sb * 64 + 32, dp + 32);
+        tmem_ld_32x32b_x32(tlane + COL_S + coff, s);
+        tmem_ld_32x32b_x32(tlane + COL_S + coff + 32, s + 32);
+        tmem_ld_32x32b_x32(tlane + COL_DP + coff, dp);
+        tmem_ld_32x32b_x32(tlane + COL_DP + coff + 32, dp + 32);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(&bars[SP_EMPTY + sb]);
+        mbar_arrive(&bars[SP_EMPTY]);
+        pf.lap(1);
         ok = mbar_wait_bounded(&bars[PDS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-        uint8_t* base = smem + OFF_PDS + sb * 4 * TILE_BYTES + tile * TILE_BYTES + row * 128;
-        row_backward(s, dp, lse, p.c2, w, base, base + 2 * TILE_BYTES, row);
+        pf.lap(2);
+        if (elected && g >= 2) mbar_arrive(&bars[QDO_EMPTY + (g - 2) % NQ]);   // dV/dK MMAs of iteration g-2 are done
+        uint8_t* base = smem + OFF_PDS + sb * 2 * PAIR_BYTES + tile * TILE_BYTES + row * 128;
+        row_backward(s, dp, lse, p.c2, w, base, base + PAIR_BYTES, row);
         fence_proxy_async_smem();
         mbar_arrive(&bars[PDS_FULL + sb]);
-        ++icnt;
+        pf.lap(3);
       }
     }
     if (!ok) break;
-    ok = mbar_wait_bounded(&bars[ACC_FULL + ob], (ucnt >> 1) & 1, abort_flag);
-    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-    tc_fence_after();
-    uint32_t acc[64];
-    tmem_ld_32x32b_x32(tlane + COL_DK + ob * 64, acc);
-    tmem_ld_32x32b_x32(tlane + COL_DK + ob * 64 + 32, acc + 32);
-    tmem_ld_wait();
-    if (live) store_row_bf16(dk_row, acc, p.sm_scale);
-    tmem_ld_32x32b_x32(tlane + COL_DV + ob * 64, acc);
-    tmem_ld_32x32b_x32(tlane + COL_DV + ob * 64 + 32, acc + 32);
-    tmem_ld_wait();
-    tc_fence_before();
-    mbar_arrive(&bars[ACC_EMPTY + ob]);
-    if (live) store_row_bf16(dv_row, acc, 1.0f);
-    ++ucnt;
+    pf.lap(7);
+    if ((int)(un & 1) == wg) {
+      ok = mbar_wait_bounded(&bars[ACC_FULL + (un & 1)], (un >> 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      pf.lap(5);
+      tc_fence_after();
+      uint32_t acc[64];
+      tmem_ld_32x32b_x32(tlane + COL_DK + coff, acc);
+      tmem_ld_32x32b_x32(tlane + COL_DK + coff + 32, acc + 32);
+      tmem_ld_wait();
+      if (live) store_row_bf16(dk_row, acc, p.sm_scale);
+      tmem_ld_32x32b_x32(tlane + COL_DV + coff, acc);
+      tmem_ld_32x32b_x32(tlane + COL_DV + coff + 32, acc + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[ACC_EMPTY]);
+      if (live) store_row_bf16(dv_row, acc, 1.0f);
+      pf.lap(6);
+    }
   }
+  pf.lap(7);
+  pf.dump(p.prof + 72);
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -638,56 +698,65 @@ bwd_kv_tc_kernel(const __grid_constant__ BwdKvParams p) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[KV_FULL + i], 1); mbar_init(&bars[KV_EMPTY + i], 1);
-      mbar_init(&bars[SP_FULL + i], 1); mbar_init(&bars[SP_EMPTY + i], 128);
       mbar_init(&bars[PDS_FULL + i], 128); mbar_init(&bars[PDS_EMPTY + i], 1);
-      mbar_init(&bars[ACC_FULL + i], 1); mbar_init(&bars[ACC_EMPTY + i], 128);
     }
-    for (int i = 0; i < NSTAGE; ++i) { mbar_init(&bars[QDO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1); }
+    mbar_init(&bars[SP_FULL], 1); mbar_init(&bars[SP_FULL + 1], 1); mbar_init(&bars[SP_EMPTY], 128);
+    mbar_init(&bars[ACC_FULL], 1); mbar_init(&bars[ACC_FULL + 1], 1); mbar_init(&bars[ACC_EMPTY], 128);
+    for (int i = 0; i < NQ; ++i) { mbar_init(&bars[Q_FULL + i], 1); mbar_init(&bars[DO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-  if (warp == 4 && lane == 0) {
-    tma_prefetch_desc(&p.tm_q); tma_prefetch_desc(&p.tm_do); tma_prefetch_desc(&p.tm_k); tma_prefetch_desc(&p.tm_v);
-  }
+  if (warp == ISSUE_A) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  if (warp == PROD_A && lane == 0) { tma_prefetch_desc(&p.tm_q2); tma_prefetch_desc(&p.tm_k2); tma_prefetch_desc(&p.tm_v2); }
+  if (warp == PROD_B && lane == 0) { tma_prefetch_desc(&p.tm_do2); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (warp < 4) kv_worker(p, smem, bars, abort_flag, warp, lane, tmem_base);
-  else if (warp == 4) { if (lane == 0) kv_producer(p, smem, bars, abort_flag); }
-  else { if (lane == 0) kv_mma(p, smem, bars, abort_flag, tmem_base); }
+  if (warp < 8) kv_worker(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
+  else if (warp == PROD_A) { if (lane == 0) kv_producer<0>(p, smem, bars, abort_flag); }
+  else if (warp == PROD_B) { if (lane == 0) kv_producer<1>(p, smem, bars, abort_flag); }
+  else if (warp == ISSUE_A) { if (lane == 0) kv_issuer<0>(p, smem, bars, abort_flag, tmem_base); }
+  else { if (lane == 0) kv_issuer<1>(p, smem, bars, abort_flag, tmem_base); }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == ISSUE_A) tmem_dealloc(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
 }
 
 }  // namespace
 
 bool bwd_tc_available() { return true; }
+long long* profile_buffer();
 
 int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;
   int dev = 0, sms = 0;
   GCA_CUDA_CHECK(cudaGetDevice(&dev));
   GCA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  CUtensorMap tm_q, tm_do, tm_k, tm_v;
-  int rc;
-  if ((rc = make_tile_map_5d(&tm_q, a.q, 64, 64, a.Hq, a.J, a.N, a.q_stride[3], a.q_stride[2], a.q_stride[1], a.q_stride[0]))) return rc;
-  if ((rc = make_tile_map_5d(&tm_do, a.dout, 64, 64, a.Hq, a.J, a.N, a.do_stride[3], a.do_stride[2], a.do_stride[1], a.do_stride[0]))) return rc;
-  if ((rc = make_tile_map_5d(&tm_k, a.k_cache, 64, 64, a.Hkv, a.C, a.N, a.k_stride[2], a.k_stride[3], a.k_stride[1], a.k_stride[0]))) return rc;
-  if ((rc = make_tile_map_5d(&tm_v, a.v_cache, 64, 64, a.Hkv, a.C, a.N, a.v_stride[2], a.v_stride[3], a.v_stride[1], a.v_stride[0]))) return rc;
   const float c2 = a.sm_scale * GCA_LOG2E;
+  int rc;
+  auto qmap = [&](CUtensorMap* m, const void* base, const int64_t* st, int box) {
+    return make_tile_map_5d(m, base, 64, 64, a.Hq, a.J, a.N, st[3], st[2], st[1], st[0], box);
+  };
+  auto kmap = [&](CUtensorMap* m, const void* base, const int64_t* st, int box) {
+    return make_tile_map_5d(m, base, 64, 64, a.Hkv, a.C, a.N, st[2], st[3], st[1], st[0], box);
+  };
   {
     BwdKvParams p;
-    p.tm_q = tm_q; p.tm_do = tm_do; p.tm_k = tm_k; p.tm_v = tm_v;
+    if ((rc = qmap(&p.tm_q2, a.q, a.q_stride, 2)) || (rc = qmap(&p.tm_do2, a.dout, a.do_stride, 2)) ||
+        (rc = qmap(&p.tm_q1, a.q, a.q_stride, 1)) || (rc = qmap(&p.tm_do1, a.dout, a.do_stride, 1)) ||
+        (rc = kmap(&p.tm_k2, a.k_cache, a.k_stride, 2)) || (rc = kmap(&p.tm_v2, a.v_cache, a.v_stride, 2)))
+      return rc;
     p.weights = a.weights; p.lse = a.lse; p.offsets = csr.offsets; p.sorted_keys = csr.sorted_keys;
     p.dk = (__nv_bfloat16*)a.dk_cache; p.dv = (__nv_bfloat16*)a.dv_cache; p.status = a.status;
+    p.prof = profile_buffer();
     for (int i = 0; i < 4; ++i) { p.dks[i] = a.dk_stride[i]; p.dvs[i] = a.dv_stride[i]; }
     p.N = a.N; p.J = a.J; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = a.Hq / a.Hkv; p.K = a.K; p.C = a.C;
     p.HP = (a.Hkv + 1) / 2;
-    p.units = (long long)a.N * a.C * p.HP;
+    const long long units = (long long)a.N * a.C * p.HP;
+    if (units >= (1ll << 31) - 65536) return GCA_ERR_TOO_LARGE;
+    p.units = (int)units;
     p.c2 = c2; p.sm_scale = a.sm_scale;
     if (p.units > 0) {
       GCA_CUDA_CHECK(cudaFuncSetAttribute(bwd_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kv::SMEM_BYTES));
@@ -698,13 +767,19 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
   }
   {
     BwdQParams p;
-    p.tm_q = tm_q; p.tm_do = tm_do; p.tm_k = tm_k; p.tm_v = tm_v;
+    if ((rc = qmap(&p.tm_q, a.q, a.q_stride, 2)) || (rc = qmap(&p.tm_do, a.dout, a.do_stride, 2)) ||
+        (rc = kmap(&p.tm_k2, a.k_cache, a.k_stride, 2)) || (rc = kmap(&p.tm_v2, a.v_cache, a.v_stride, 2)) ||
+        (rc = kmap(&p.tm_k1, a.k_cache, a.k_stride, 1)) || (rc = kmap(&p.tm_v1, a.v_cache, a.v_stride, 1)))
+      return rc;
     p.indices = a.indices; p.weights = a.weights; p.lse = a.lse;
     p.dq = (__nv_bfloat16*)a.dq; p.dw_part = dw_part; p.status = a.status;
+    p.prof = profile_buffer();
     for (int i = 0; i < 4; ++i) p.dqs[i] = a.dq_stride[i];
     p.N = a.N; p.J = a.J; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = a.Hq / a.Hkv; p.K = a.K; p.C = a.C;
     p.HP = (a.Hq + 1) / 2;
-    p.units = (long long)a.N * a.J * p.HP;
+    const long long units = (long long)a.N * a.J * p.HP;
+    if (units >= (1ll << 31) - 65536) return GCA_ERR_TOO_LARGE;
+    p.units = (int)units;
     p.c2 = c2; p.sm_scale = a.sm_scale;
     if (p.units > 0) {
       GCA_CUDA_CHECK(cudaFuncSetAttribute(bwd_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, qk::SMEM_BYTES));

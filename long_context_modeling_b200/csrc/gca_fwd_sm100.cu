@@ -475,6 +475,7 @@ long long* g_profile_buffer = nullptr;
 }  // namespace
 
 void set_fwd_profile_buffer(void* device_ptr) { g_profile_buffer = static_cast<long long*>(device_ptr); }
+long long* profile_buffer() { return g_profile_buffer; }
 
 int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;
