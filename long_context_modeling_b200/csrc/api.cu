@@ -136,7 +136,7 @@ int gca_decode(const GcaFwdArgs* a, void* stream) {
 }
 
 static size_t dw_part_bytes(const GcaBwdArgs* a) {
-  return gca::align_up((size_t)a->N * a->J * a->Hq * a->K * sizeof(float), 256);
+  return gca::align_up((size_t)2 * a->N * a->J * a->Hq * a->K * sizeof(float), 256);   // two partials per (row block, head, slot)
 }
 
 size_t gca_bwd_workspace_bytes(const GcaBwdArgs* a) {
@@ -179,7 +179,7 @@ int gca_bwd(const GcaBwdArgs* a, void* stream) {
   else if (algo == GCA_ALGO_SIMT) rc = gca::launch_bwd_simt(*a, csr, dw_part, s);
   else rc = GCA_ERR_ALGO;
   if (rc) return rc;
-  return gca::launch_dw_reduce(dw_part, a->dw, a->N * a->J, a->Hq, a->K, s);
+  return gca::launch_dw_reduce(dw_part, a->dw, a->N * a->J, a->Hq, a->K, algo == GCA_ALGO_TC ? 2 : 1, s);
 }
 
 static int check_topk(const LmkTopkArgs* a) {

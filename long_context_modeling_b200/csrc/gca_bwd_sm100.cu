@@ -20,10 +20,10 @@
 // heads' tiles, so nothing is transposed in software.
 //
 // CTA = 12 warps: two worker warpgroups (thread = TMEM lane = row) taking alternate
-// iterations, two TMA producers, two MMA issuers (recompute products / gradient products).
-// S and dP live in a single TMEM buffer each (a worker group drains it into registers at
-// once), the accumulators take the rest of TMEM.  Stage releases are relayed by the workers
-// with plain mbarrier arrives.  Every wait is bounded (GCA_STATUS_TIMEOUT on expiry).
+// iterations, one TMA producer, and THREE MMA issuers: S, dP and the gradient products each
+// have their own warp, because S and dP share one TMEM buffer each (the accumulators take
+// the rest of TMEM) and their issue latency therefore sits on the critical path of every
+// iteration.  Every wait is bounded (GCA_STATUS_TIMEOUT on expiry).
 #include <cstdlib>
 
 #include "gca_common.cuh"
@@ -33,6 +33,8 @@
 
 namespace gca {
 
+long long* profile_buffer();
+
 namespace {
 
 using namespace sm100;
@@ -41,7 +43,7 @@ constexpr int TILE_BYTES = 64 * 64 * 2;
 constexpr int PAIR_BYTES = 2 * TILE_BYTES;
 constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
 constexpr int NTHREADS = 384;
-constexpr int PROD_A = 8, PROD_B = 9, ISSUE_A = 10, ISSUE_B = 11;
+constexpr int PROD_WARP = 8, ISSUE_S = 9, ISSUE_DP = 10, ISSUE_G = 11;
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC = 256;
 
@@ -109,13 +111,12 @@ constexpr int OFF_QDO = 0;                                   // [2 bufs][Q pair 
 constexpr int OFF_K = OFF_QDO + 2 * 2 * PAIR_BYTES;          // [NKS][K pair]
 constexpr int OFF_V = OFF_K + NKS * PAIR_BYTES;              // [NVS][V pair]
 constexpr int OFF_DS = OFF_V + NVS * PAIR_BYTES;             // [2 bufs][dS pair]
-constexpr int OFF_DW = OFF_DS + 2 * PAIR_BYTES;              // float [2 units][32 slots][2 tiles][2 warps]
-constexpr int OFF_BAR = OFF_DW + 2 * 32 * 2 * 2 * 4;
+constexpr int OFF_BAR = OFF_DS + 2 * PAIR_BYTES;
 constexpr int OFF_IDX = OFF_BAR + 512;
 constexpr int SMEM_BYTES = OFF_IDX + 256 + 1024;
 enum Bar { QDO_FULL = 0, QDO_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + NKS, V_FULL = K_EMPTY + NKS,
            V_EMPTY = V_FULL + NVS, SP_FULL = V_EMPTY + NVS, SP_EMPTY = SP_FULL + 2, DS_FULL = SP_EMPTY + 1,
-           DS_EMPTY = DS_FULL + 2, DQ_FULL = DS_EMPTY + 2, DQ_EMPTY = DQ_FULL + 2, DW_BAR = DQ_EMPTY + 2, NUM_BARS = DW_BAR + 1 };
+           DS_EMPTY = DS_FULL + 2, DQ_FULL = DS_EMPTY + 2, DQ_EMPTY = DQ_FULL + 2, NUM_BARS = DQ_EMPTY + 2 };
 }  // namespace qk
 
 struct BwdQParams {
@@ -124,7 +125,7 @@ struct BwdQParams {
   const float* weights;
   const float* lse;
   __nv_bfloat16* dq;
-  float* dw_part;
+  float* dw_part;           // (N*J, Hq, K, 2): two half-tile partials per (row block, head, slot)
   int32_t* status;
   long long* prof;
   long long dqs[4];
@@ -150,16 +151,13 @@ __device__ __forceinline__ unsigned q_valid(const BwdQParams& p, int idx) {
   return __ballot_sync(0xffffffffu, idx >= 0 && idx < p.C);
 }
 
-// mode 0: Q + dO per unit, K per slot;  mode 1: V per slot
-template <int MODE>
+// One lane: Q + dO per unit, K and V per slot.
 __device__ void q_producer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane) {
   using namespace qk;
-  int* sidx = reinterpret_cast<int*>(smem + OFF_IDX) + MODE * 32;
-  constexpr int FULL = MODE == 0 ? K_FULL : V_FULL, EMPTY = MODE == 0 ? K_EMPTY : V_EMPTY;
-  constexpr int DEPTH = MODE == 0 ? NKS : NVS, OFF = MODE == 0 ? OFF_K : OFF_V;
+  int* sidx = reinterpret_cast<int*>(smem + OFF_IDX);
   PairCursor c;
   c.init(p.HP);
-  Ring ring; ring.init(DEPTH);
+  Ring rk, rv; rk.init(NKS); rv.init(NVS);
   uint32_t ucnt = 0, issued = 0;
   bool ok = true;
   int next_idx = q_load_row(p, c.u, c.outer, lane);
@@ -175,7 +173,7 @@ __device__ void q_producer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, v
     if (lane != 0 || !ok) continue;
     const QInfo t = q_info(p, c.inner);
     const int n = c.outer / p.J, j = c.outer - n * p.J;
-    if (MODE == 0) {
+    {
       const uint32_t ub = un & 1;
       ok = mbar_wait_bounded(&bars[QDO_EMPTY + ub], ((un >> 1) & 1) ^ 1, abort_flag);
       if (!ok) continue;
@@ -184,26 +182,33 @@ __device__ void q_producer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, v
       tma_load_5d(base, &p.tm_q, &bars[QDO_FULL + ub], 0, 0, t.h0, j, n);
       tma_load_5d(base + PAIR_BYTES, &p.tm_do, &bars[QDO_FULL + ub], 0, 0, t.h0, j, n);
     }
-    const CUtensorMap* tm = MODE == 0 ? (t.share ? &p.tm_k1 : &p.tm_k2) : (t.share ? &p.tm_v1 : &p.tm_v2);
+    const CUtensorMap* tmk = t.share ? &p.tm_k1 : &p.tm_k2;
+    const CUtensorMap* tmv = t.share ? &p.tm_v1 : &p.tm_v2;
     const uint32_t bytes = t.share ? TILE_BYTES : PAIR_BYTES;
     for (unsigned m = mask; m; m &= m - 1) {
-      const int k = __ffs(m) - 1;
-      ok = mbar_wait_bounded(&bars[EMPTY + ring.st], ring.ph ^ 1, abort_flag);
+      const int idx = sidx[__ffs(m) - 1];
+      ok = mbar_wait_bounded(&bars[K_EMPTY + rk.st], rk.ph ^ 1, abort_flag);
       if (!ok) break;
-      mbar_arrive_expect_tx(&bars[FULL + ring.st], bytes);
-      tma_load_5d(smem + OFF + ring.st * PAIR_BYTES, tm, &bars[FULL + ring.st], 0, 0, t.hk0, sidx[k], n);
-      ring.next();
+      mbar_arrive_expect_tx(&bars[K_FULL + rk.st], bytes);
+      tma_load_5d(smem + OFF_K + rk.st * PAIR_BYTES, tmk, &bars[K_FULL + rk.st], 0, 0, t.hk0, idx, n);
+      rk.next();
+      ok = mbar_wait_bounded(&bars[V_EMPTY + rv.st], rv.ph ^ 1, abort_flag);
+      if (!ok) break;
+      mbar_arrive_expect_tx(&bars[V_FULL + rv.st], bytes);
+      tma_load_5d(smem + OFF_V + rv.st * PAIR_BYTES, tmv, &bars[V_FULL + rv.st], 0, 0, t.hk0, idx, n);
+      rv.next();
       ++issued;
     }
   }
   if (lane == 0 && *abort_flag) {
-    drain(bars, FULL, issued, DEPTH);
-    if (MODE == 0) drain(bars, QDO_FULL, ucnt, 2);
+    drain(bars, K_FULL, issued, NKS);
+    drain(bars, V_FULL, issued, NVS);
+    drain(bars, QDO_FULL, ucnt, 2);
   }
 }
 
-// mode 0: S and dP per slot;  mode 1: dQ += dS K per slot
-template <int MODE>
+// role 0: S per slot;  role 1: dP per slot;  role 2: dQ += dS K per slot
+template <int ROLE>
 __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
                          uint32_t tmem_base) {
   using namespace qk;
@@ -213,7 +218,7 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
   const uint64_t dDS = umma_desc_sw128(smem_u32(smem + OFF_DS));
   PairCursor c;
   c.init(p.HP);
-  Ring rk, rv; rk.init(NKS); rv.init(NVS);
+  Ring ring; ring.init(ROLE == 1 ? NVS : NKS);
   uint32_t ucnt = 0, g = 0;
   bool ok = true;
   PhaseTimer pf;
@@ -231,13 +236,12 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     const QInfo t = q_info(p, c.inner);
     const uint32_t ub = un & 1, uph = (un >> 1) & 1;
     const int ncol = t.share ? 64 : 128;
-    if (MODE == 0) ok = mbar_wait_bounded(&bars[QDO_FULL + ub], uph, abort_flag);
+    if (ROLE != 2) ok = mbar_wait_bounded(&bars[QDO_FULL + ub], uph, abort_flag);
     else ok = mbar_wait_bounded(&bars[DQ_EMPTY + ub], uph ^ 1, abort_flag);
     pf.lap(0);
     for (int i = 0; i < nv && ok; ++i, ++g) {
-      if (MODE == 0) {
-        ok = mbar_wait_bounded(&bars[K_FULL + rk.st], rk.ph, abort_flag) &&
-             mbar_wait_bounded(&bars[V_FULL + rv.st], rv.ph, abort_flag);
+      if (ROLE != 2) {
+        ok = mbar_wait_bounded(&bars[(ROLE == 0 ? K_FULL : V_FULL) + ring.st], ring.ph, abort_flag);
         pf.lap(1);
         ok = ok && mbar_wait_bounded(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag);
         pf.lap(2);
@@ -245,10 +249,9 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
         tc_fence_after();
         const uint32_t idesc = umma_idesc_bf16(128, ncol, 0, 0);
         const uint64_t q = dQDO + ub * 2 * PAIR16;
-        mma4(tmem_base + COL_S, q, dK + rk.st * PAIR16, idesc, STEP_K, STEP_K, false);
-        mma4(tmem_base + COL_DP, q + PAIR16, dV + rv.st * PAIR16, idesc, STEP_K, STEP_K, false);
-        umma_commit(&bars[SP_FULL + (g & 1)]);   // one barrier per worker group: a waiter never lags a barrier by two phases
-        rv.next();
+        if (ROLE == 0) mma4(tmem_base + COL_S, q, dK + ring.st * PAIR16, idesc, STEP_K, STEP_K, false);
+        else mma4(tmem_base + COL_DP, q + PAIR16, dV + ring.st * PAIR16, idesc, STEP_K, STEP_K, false);
+        umma_commit(&bars[SP_FULL + (g & 1)]);    // the barrier expects both the S and the dP commit
       } else {
         const uint32_t sb = g & 1;
         ok = mbar_wait_bounded(&bars[DS_FULL + sb], (g >> 1) & 1, abort_flag);
@@ -256,16 +259,17 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
         if (!ok) break;
         tc_fence_after();
         // dQ += dS K_k : A = dS (K-major), B = K_k (MN-major, both heads' tiles)
-        mma4(tmem_base + COL_ACC + ub * 128, dDS + sb * PAIR16, dKmn + rk.st * PAIR16, umma_idesc_bf16(128, ncol, 0, 1),
+        mma4(tmem_base + COL_ACC + ub * 128, dDS + sb * PAIR16, dKmn + ring.st * PAIR16, umma_idesc_bf16(128, ncol, 0, 1),
              STEP_K, STEP_MN, i > 0);
         umma_commit(&bars[DS_EMPTY + sb]);
+        umma_commit(&bars[K_EMPTY + ring.st]);     // the K tiles of this slot are free once dQ is done
         if (i == nv - 1) umma_commit(&bars[DQ_FULL + ub]);
       }
       pf.lap(3);
-      rk.next();
+      ring.next();
     }
   }
-  pf.dump(p.prof + 36 + 12 + 12 * MODE);
+  pf.dump(p.prof + 36 + 12 + 12 * ROLE);
 }
 
 __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
@@ -275,8 +279,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
   const int row = (quad & 1) * 32 + lane;
   const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
   const bool elected = quad == 0 && lane == 0;
-  const int tid = (wg * 4 + quad) * 32 + lane;                  // 0..255 over both worker groups
-  float* dws = reinterpret_cast<float*>(smem + OFF_DW);
+  const int tid = quad * 32 + lane;                             // 0..127 inside the worker group
   PairCursor c;
   c.init(p.HP);
   uint32_t ucnt = 0, g = 0;
@@ -300,19 +303,24 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     const uint32_t coff = t.share ? 0u : (uint32_t)tile * 64u;
     const int n = c.outer / p.J, j = c.outer - n * p.J;
     __nv_bfloat16* dq_row = p.dq + n * p.dqs[0] + j * p.dqs[1] + h * p.dqs[2] + row * p.dqs[3];
-    float* dwp = p.dw_part + ((long long)c.outer * p.Hq + t.h0) * p.K;     // [tile][k]
-    if (mask == 0) {
-      if (wg == 0 && live) {
+    float* dwp = p.dw_part + ((long long)c.outer * p.Hq + t.h0) * p.K * 2;     // [tile][k][half]
+    if (wg == 0) {
+      // padding slots (and whole units without valid slots): zero dw partials, zero dQ rows
+      const unsigned full = (p.K >= 32) ? 0xffffffffu : ((1u << p.K) - 1u);
+      if (mask != full)
+        for (int i = tid; i < 4 * p.K; i += 128) {
+          const int tl = i / (2 * p.K), k = (i - tl * 2 * p.K) >> 1;
+          if (!((mask >> k) & 1) && t.h0 + tl < p.Hq) dwp[i] = 0.f;
+        }
+      if (mask == 0 && live) {
         const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) reinterpret_cast<uint4*>(dq_row)[cc] = z;
       }
-      if (tid < 2 * p.K && (t.h0 + tid / p.K) < p.Hq) dwp[tid] = 0.f;
-      continue;
     }
+    if (mask == 0) continue;
     const uint32_t un = ucnt++;
     const uint32_t ub = un & 1;
-    float* dws_u = dws + ub * (32 * 2 * 2);
     const float* lse_base = p.lse + ((long long)c.outer * p.Hq + (live ? h : t.h0)) * p.K * 64 + row;
     for (unsigned m = mask; m; m &= m - 1, ++g) {
       if ((int)(g & 1) != wg) continue;
@@ -322,7 +330,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       const float lse = lse_base[k * 64];
       const uint32_t sb = g & 1;
       pf.lap(7);
-      ok = mbar_wait_bounded(&bars[SP_FULL + (g & 1)], (g >> 1) & 1, abort_flag);
+      ok = mbar_wait_bounded(&bars[SP_FULL + sb], (g >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(0);
       if (elected) {                         // S/dP done: the V stage (and at the end Q/dO) can be refilled
@@ -342,34 +350,20 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       ok = mbar_wait_bounded(&bars[DS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(2);
-      if (elected && g >= 2) mbar_arrive(&bars[K_EMPTY + (g - 2) % NKS]);   // dQ MMA of slot g-2 is done
       uint8_t* ds_row = smem + OFF_DS + sb * PAIR_BYTES + tile * TILE_BYTES + row * 128;
       float di = row_backward(s, dp, lse, p.c2, w, nullptr, ds_row, row);
       fence_proxy_async_smem();
       mbar_arrive(&bars[DS_FULL + sb]);
       pf.lap(3);
-      // dw: sum of Di over the 32 rows this warp holds of its tile
+      // dw: sum of Di over the 32 rows this warp holds of its tile -> one partial per warp
 #pragma unroll
       for (int of = 16; of > 0; of >>= 1) di += __shfl_xor_sync(0xffffffffu, di, of);
-      if (lane == 0) dws_u[(k * 2 + tile) * 2 + (quad & 1)] = di;
+      if (lane == 0 && live) dwp[(tile * p.K + k) * 2 + (quad & 1)] = di;
       pf.lap(4);
     }
     if (!ok) break;
-    pf.lap(7);
-    // both worker groups have written their dw partials (bounded rendezvous of the 256 workers)
-    mbar_arrive(&bars[DW_BAR]);
-    ok = mbar_wait_bounded(&bars[DW_BAR], un & 1, abort_flag);
-    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-    if (tid < 2 * p.K) {
-      const int tl = tid / p.K, k = tid - tl * p.K;
-      if (t.h0 + tl < p.Hq) {
-        float v = 0.f;
-        if ((mask >> k) & 1) v = dws_u[(k * 2 + tl) * 2] + dws_u[(k * 2 + tl) * 2 + 1];
-        dwp[tl * p.K + k] = v;
-      }
-    }
-    pf.lap(4);
     if ((int)ub == wg) {
+      pf.lap(7);
       ok = mbar_wait_bounded(&bars[DQ_FULL + ub], (un >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(5);
@@ -400,31 +394,32 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[QDO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1);
+      mbar_init(&bars[SP_FULL + i], 2);                              // S commit + dP commit
       mbar_init(&bars[DS_FULL + i], 128); mbar_init(&bars[DS_EMPTY + i], 1);
       mbar_init(&bars[DQ_FULL + i], 1); mbar_init(&bars[DQ_EMPTY + i], 128);
     }
-    mbar_init(&bars[SP_FULL], 1); mbar_init(&bars[SP_FULL + 1], 1); mbar_init(&bars[SP_EMPTY], 128);
-    mbar_init(&bars[DW_BAR], 256);
+    mbar_init(&bars[SP_EMPTY], 128);
     for (int i = 0; i < NKS; ++i) { mbar_init(&bars[K_FULL + i], 1); mbar_init(&bars[K_EMPTY + i], 1); }
     for (int i = 0; i < NVS; ++i) { mbar_init(&bars[V_FULL + i], 1); mbar_init(&bars[V_EMPTY + i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == ISSUE_A) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-  if (warp == PROD_A && lane == 0) { tma_prefetch_desc(&p.tm_q); tma_prefetch_desc(&p.tm_do); tma_prefetch_desc(&p.tm_k2); }
-  if (warp == PROD_B && lane == 0) { tma_prefetch_desc(&p.tm_v2); }
+  if (warp == ISSUE_S) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  if (warp == PROD_WARP && lane == 0) {
+    tma_prefetch_desc(&p.tm_q); tma_prefetch_desc(&p.tm_do); tma_prefetch_desc(&p.tm_k2); tma_prefetch_desc(&p.tm_v2);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (warp < 8) q_worker(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
-  else if (warp == PROD_A) q_producer<0>(p, smem, bars, abort_flag, lane);
-  else if (warp == PROD_B) q_producer<1>(p, smem, bars, abort_flag, lane);
-  else if (warp == ISSUE_A) q_issuer<0>(p, smem, bars, abort_flag, lane, tmem_base);
-  else q_issuer<1>(p, smem, bars, abort_flag, lane, tmem_base);
+  else if (warp == PROD_WARP) q_producer(p, smem, bars, abort_flag, lane);
+  else if (warp == ISSUE_S) q_issuer<0>(p, smem, bars, abort_flag, lane, tmem_base);
+  else if (warp == ISSUE_DP) q_issuer<1>(p, smem, bars, abort_flag, lane, tmem_base);
+  else q_issuer<2>(p, smem, bars, abort_flag, lane, tmem_base);
   tc_fence_before();
   __syncthreads();
-  if (warp == ISSUE_A) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == ISSUE_S) tmem_dealloc(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
 }
 
@@ -434,14 +429,13 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
 namespace kv {
 constexpr int NQ = 3;
 constexpr int OFF_KV = 0;                                    // [2 bufs][K pair | V pair]
-constexpr int OFF_Q = OFF_KV + 2 * 2 * PAIR_BYTES;           // [NQ][Q pair]
-constexpr int OFF_DO = OFF_Q + NQ * PAIR_BYTES;              // [NQ][dO pair]
-constexpr int OFF_PDS = OFF_DO + NQ * PAIR_BYTES;            // [2 bufs][Pw pair | dS pair]
+constexpr int OFF_QDO = OFF_KV + 2 * 2 * PAIR_BYTES;         // [NQ][Q pair | dO pair]
+constexpr int OFF_PDS = OFF_QDO + NQ * 2 * PAIR_BYTES;       // [2 bufs][Pw pair | dS pair]
 constexpr int OFF_BAR = OFF_PDS + 2 * 2 * PAIR_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
-enum Bar { KV_FULL = 0, KV_EMPTY = 2, Q_FULL = 4, DO_FULL = Q_FULL + NQ, QDO_EMPTY = DO_FULL + NQ,
-           SP_FULL = QDO_EMPTY + NQ, SP_EMPTY = SP_FULL + 2, PDS_FULL = SP_EMPTY + 1, PDS_EMPTY = PDS_FULL + 2,
-           ACC_FULL = PDS_EMPTY + 2, ACC_EMPTY = ACC_FULL + 2, NUM_BARS = ACC_EMPTY + 1 };
+enum Bar { KV_FULL = 0, KV_EMPTY = 2, QDO_FULL = 4, QDO_EMPTY = QDO_FULL + NQ, SP_FULL = QDO_EMPTY + NQ,
+           SP_EMPTY = SP_FULL + 2, PDS_FULL = SP_EMPTY + 1, PDS_EMPTY = PDS_FULL + 2, ACC_FULL = PDS_EMPTY + 2,
+           ACC_EMPTY = ACC_FULL + 2, NUM_BARS = ACC_EMPTY + 1 };
 constexpr uint32_t COL_DK = 256, COL_DV = 384;
 }  // namespace kv
 
@@ -461,8 +455,7 @@ struct BwdKvParams {
   float c2, sm_scale;
 };
 
-// mode 0: K + V per unit and Q per iteration;  mode 1: dO per iteration
-template <int MODE>
+// One lane: K + V per unit, Q + dO per iteration.
 __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
   using namespace kv;
   PairCursor c;
@@ -479,7 +472,7 @@ __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars,
     const int hk0 = 2 * c.inner;
     const bool two = hk0 + 1 < p.Hkv;
     const int n = c.outer / p.C, ch = c.outer - n * p.C;
-    if (MODE == 0) {
+    {
       const uint32_t kb = un & 1;
       ok = mbar_wait_bounded(&bars[KV_EMPTY + kb], ((un >> 1) & 1) ^ 1, abort_flag);
       if (!ok) break;
@@ -488,23 +481,23 @@ __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars,
       tma_load_5d(base, &p.tm_k2, &bars[KV_FULL + kb], 0, 0, hk0, ch, n);
       tma_load_5d(base + PAIR_BYTES, &p.tm_v2, &bars[KV_FULL + kb], 0, 0, hk0, ch, n);
     }
-    const int FULL = MODE == 0 ? Q_FULL : DO_FULL;
-    const int OFF = MODE == 0 ? OFF_Q : OFF_DO;
     for (int e = beg; e < end && ok; ++e) {
       const int entry = (int)(p.sorted_keys[e] & 0xffffffffull);
       const int j = entry / p.K;
       for (int gi = 0; gi < p.G; ++gi) {
         ok = mbar_wait_bounded(&bars[QDO_EMPTY + ring.st], ring.ph ^ 1, abort_flag);
         if (!ok) break;
-        uint8_t* dst = smem + OFF + ring.st * PAIR_BYTES;
-        mbar_arrive_expect_tx(&bars[FULL + ring.st], PAIR_BYTES);
+        uint8_t* dst = smem + OFF_QDO + ring.st * 2 * PAIR_BYTES;
+        mbar_arrive_expect_tx(&bars[QDO_FULL + ring.st], 2 * PAIR_BYTES);
         if (p.G == 1) {
-          tma_load_5d(dst, MODE == 0 ? &p.tm_q2 : &p.tm_do2, &bars[FULL + ring.st], 0, 0, hk0, j, n);
+          tma_load_5d(dst, &p.tm_q2, &bars[QDO_FULL + ring.st], 0, 0, hk0, j, n);
+          tma_load_5d(dst + PAIR_BYTES, &p.tm_do2, &bars[QDO_FULL + ring.st], 0, 0, hk0, j, n);
         } else {      // the two q heads of the pair are G apart: one copy per head
-          const CUtensorMap* tm = MODE == 0 ? &p.tm_q1 : &p.tm_do1;
-          const int hb = two ? (hk0 + 1) * p.G + gi : hk0 * p.G + gi;
-          tma_load_5d(dst, tm, &bars[FULL + ring.st], 0, 0, hk0 * p.G + gi, j, n);
-          tma_load_5d(dst + TILE_BYTES, tm, &bars[FULL + ring.st], 0, 0, hb, j, n);
+          const int ha = hk0 * p.G + gi, hb = two ? (hk0 + 1) * p.G + gi : ha;
+          tma_load_5d(dst, &p.tm_q1, &bars[QDO_FULL + ring.st], 0, 0, ha, j, n);
+          tma_load_5d(dst + TILE_BYTES, &p.tm_q1, &bars[QDO_FULL + ring.st], 0, 0, hb, j, n);
+          tma_load_5d(dst + PAIR_BYTES, &p.tm_do1, &bars[QDO_FULL + ring.st], 0, 0, ha, j, n);
+          tma_load_5d(dst + PAIR_BYTES + TILE_BYTES, &p.tm_do1, &bars[QDO_FULL + ring.st], 0, 0, hb, j, n);
         }
         ring.next();
         ++issued;
@@ -512,20 +505,19 @@ __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars,
     }
   }
   if (*abort_flag) {
-    drain(bars, MODE == 0 ? Q_FULL : DO_FULL, issued, NQ);
-    if (MODE == 0) drain(bars, KV_FULL, ucnt, 2);
+    drain(bars, QDO_FULL, issued, NQ);
+    drain(bars, KV_FULL, ucnt, 2);
   }
 }
 
-// mode 0: S and dP per iteration;  mode 1: dV and dK per iteration
-template <int MODE>
+// role 0: S per iteration;  role 1: dP per iteration;  role 2: dV and dK per iteration
+template <int ROLE>
 __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag,
                           uint32_t tmem_base) {
   using namespace kv;
   const uint64_t dKV = umma_desc_sw128(smem_u32(smem + OFF_KV));
-  const uint64_t dQ = umma_desc_sw128(smem_u32(smem + OFF_Q)), dDO = umma_desc_sw128(smem_u32(smem + OFF_DO));
-  const uint64_t dQmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_Q), TILE_BYTES);
-  const uint64_t dDOmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_DO), TILE_BYTES);
+  const uint64_t dQDO = umma_desc_sw128(smem_u32(smem + OFF_QDO));
+  const uint64_t dQDOmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_QDO), TILE_BYTES);
   const uint64_t dPDSmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_PDS), TILE_BYTES);
   constexpr uint32_t IDESC_KK = umma_idesc_bf16(128, 128, 0, 0), IDESC_MM = umma_idesc_bf16(128, 128, 1, 1);
   PairCursor c;
@@ -544,21 +536,21 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
     pf.lap(7);
     const uint32_t un = ucnt++;
     const uint32_t kb = un & 1;
-    if (MODE == 0) ok = mbar_wait_bounded(&bars[KV_FULL + kb], (un >> 1) & 1, abort_flag);
+    if (ROLE != 2) ok = mbar_wait_bounded(&bars[KV_FULL + kb], (un >> 1) & 1, abort_flag);
     else ok = mbar_wait_bounded(&bars[ACC_EMPTY], (un & 1) ^ 1, abort_flag);
     pf.lap(0);
     for (int i = 0; i < niter && ok; ++i, ++g) {
-      if (MODE == 0) {
-        ok = mbar_wait_bounded(&bars[Q_FULL + ring.st], ring.ph, abort_flag) &&
-             mbar_wait_bounded(&bars[DO_FULL + ring.st], ring.ph, abort_flag);
+      const uint64_t stage = ring.st * 2 * PAIR16;
+      if (ROLE != 2) {
+        ok = mbar_wait_bounded(&bars[QDO_FULL + ring.st], ring.ph, abort_flag);
         pf.lap(1);
         ok = ok && mbar_wait_bounded(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag);
         pf.lap(2);
         if (!ok) break;
         tc_fence_after();
         const uint64_t kd = dKV + kb * 2 * PAIR16;
-        mma4(tmem_base + COL_S, dQ + ring.st * PAIR16, kd, IDESC_KK, STEP_K, STEP_K, false);
-        mma4(tmem_base + COL_DP, dDO + ring.st * PAIR16, kd + PAIR16, IDESC_KK, STEP_K, STEP_K, false);
+        if (ROLE == 0) mma4(tmem_base + COL_S, dQDO + stage, kd, IDESC_KK, STEP_K, STEP_K, false);
+        else mma4(tmem_base + COL_DP, dQDO + stage + PAIR16, kd + PAIR16, IDESC_KK, STEP_K, STEP_K, false);
         umma_commit(&bars[SP_FULL + (g & 1)]);
       } else {
         const uint32_t sb = g & 1;
@@ -568,17 +560,18 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         tc_fence_after();
         const uint64_t pd = dPDSmn + sb * 2 * PAIR16;
         // dV += (w P)^T dO : A = Pw read transposed (MN-major), B = dO (MN-major)
-        mma4(tmem_base + COL_DV, pd, dDOmn + ring.st * PAIR16, IDESC_MM, STEP_MN, STEP_MN, i > 0);
+        mma4(tmem_base + COL_DV, pd, dQDOmn + stage + PAIR16, IDESC_MM, STEP_MN, STEP_MN, i > 0);
         // dK += dS^T Q
-        mma4(tmem_base + COL_DK, pd + PAIR16, dQmn + ring.st * PAIR16, IDESC_MM, STEP_MN, STEP_MN, i > 0);
+        mma4(tmem_base + COL_DK, pd + PAIR16, dQDOmn + stage, IDESC_MM, STEP_MN, STEP_MN, i > 0);
         umma_commit(&bars[PDS_EMPTY + sb]);
+        umma_commit(&bars[QDO_EMPTY + ring.st]);   // Q / dO of this iteration are free once dV, dK are done
         if (i == niter - 1) umma_commit(&bars[ACC_FULL + (un & 1)]);
       }
       pf.lap(3);
       ring.next();
     }
   }
-  pf.dump(p.prof + 72 + 12 + 12 * MODE);
+  pf.dump(p.prof + 72 + 12 + 12 * ROLE);
 }
 
 __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
@@ -619,8 +612,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       float w = 0.f;
       long long zj = 0;
       int k = 0;
-      // every thread needs (zj, k, w) of an entry only for its own iterations; fetch lazily
-      bool fetched = false;
+      bool fetched = false;            // (zj, k, w) of an entry are needed only for this group's iterations
       for (int gi = 0; gi < p.G; ++gi, ++g) {
         if ((int)(g & 1) != wg) continue;
         if (!fetched) {
@@ -636,7 +628,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         const float lse = p.lse[((zj * p.Hq + h) * p.K + k) * 64 + row];
         const uint32_t sb = g & 1;
         pf.lap(7);
-        ok = mbar_wait_bounded(&bars[SP_FULL + (g & 1)], (g >> 1) & 1, abort_flag);
+        ok = mbar_wait_bounded(&bars[SP_FULL + sb], (g >> 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
         pf.lap(0);
         if (elected && last) mbar_arrive(&bars[KV_EMPTY + kb]);     // the unit's K/V tiles are no longer needed
@@ -653,7 +645,6 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         ok = mbar_wait_bounded(&bars[PDS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
         pf.lap(2);
-        if (elected && g >= 2) mbar_arrive(&bars[QDO_EMPTY + (g - 2) % NQ]);   // dV/dK MMAs of iteration g-2 are done
         uint8_t* base = smem + OFF_PDS + sb * 2 * PAIR_BYTES + tile * TILE_BYTES + row * 128;
         row_backward(s, dp, lse, p.c2, w, base, base + PAIR_BYTES, row);
         fence_proxy_async_smem();
@@ -662,8 +653,8 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       }
     }
     if (!ok) break;
-    pf.lap(7);
     if ((int)(un & 1) == wg) {
+      pf.lap(7);
       ok = mbar_wait_bounded(&bars[ACC_FULL + (un & 1)], (un >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(5);
@@ -698,36 +689,38 @@ bwd_kv_tc_kernel(const __grid_constant__ BwdKvParams p) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[KV_FULL + i], 1); mbar_init(&bars[KV_EMPTY + i], 1);
+      mbar_init(&bars[SP_FULL + i], 2);                              // S commit + dP commit
       mbar_init(&bars[PDS_FULL + i], 128); mbar_init(&bars[PDS_EMPTY + i], 1);
+      mbar_init(&bars[ACC_FULL + i], 1);
     }
-    mbar_init(&bars[SP_FULL], 1); mbar_init(&bars[SP_FULL + 1], 1); mbar_init(&bars[SP_EMPTY], 128);
-    mbar_init(&bars[ACC_FULL], 1); mbar_init(&bars[ACC_FULL + 1], 1); mbar_init(&bars[ACC_EMPTY], 128);
-    for (int i = 0; i < NQ; ++i) { mbar_init(&bars[Q_FULL + i], 1); mbar_init(&bars[DO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1); }
+    mbar_init(&bars[SP_EMPTY], 128);
+    mbar_init(&bars[ACC_EMPTY], 128);
+    for (int i = 0; i < NQ; ++i) { mbar_init(&bars[QDO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == ISSUE_A) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-  if (warp == PROD_A && lane == 0) { tma_prefetch_desc(&p.tm_q2); tma_prefetch_desc(&p.tm_k2); tma_prefetch_desc(&p.tm_v2); }
-  if (warp == PROD_B && lane == 0) { tma_prefetch_desc(&p.tm_do2); }
+  if (warp == ISSUE_S) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  if (warp == PROD_WARP && lane == 0) {
+    tma_prefetch_desc(&p.tm_q2); tma_prefetch_desc(&p.tm_do2); tma_prefetch_desc(&p.tm_k2); tma_prefetch_desc(&p.tm_v2);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (warp < 8) kv_worker(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
-  else if (warp == PROD_A) { if (lane == 0) kv_producer<0>(p, smem, bars, abort_flag); }
-  else if (warp == PROD_B) { if (lane == 0) kv_producer<1>(p, smem, bars, abort_flag); }
-  else if (warp == ISSUE_A) { if (lane == 0) kv_issuer<0>(p, smem, bars, abort_flag, tmem_base); }
-  else { if (lane == 0) kv_issuer<1>(p, smem, bars, abort_flag, tmem_base); }
+  else if (warp == PROD_WARP) { if (lane == 0) kv_producer(p, smem, bars, abort_flag); }
+  else if (warp == ISSUE_S) { if (lane == 0) kv_issuer<0>(p, smem, bars, abort_flag, tmem_base); }
+  else if (warp == ISSUE_DP) { if (lane == 0) kv_issuer<1>(p, smem, bars, abort_flag, tmem_base); }
+  else { if (lane == 0) kv_issuer<2>(p, smem, bars, abort_flag, tmem_base); }
   tc_fence_before();
   __syncthreads();
-  if (warp == ISSUE_A) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == ISSUE_S) tmem_dealloc(tmem_base, TMEM_COLS);
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
 }
 
 }  // namespace
 
 bool bwd_tc_available() { return true; }
-long long* profile_buffer();
 
 int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;

@@ -60,7 +60,8 @@ int launch_bwd_simt(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStr
 int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream);
 int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream);
 
-int launch_dw_reduce(const float* dw_part, float* dw, int ZJ, int Hq, int K, cudaStream_t stream);
+// dw[zj, k] = sum over heads and `parts` partials of dw_part[zj, h, k, part], in a fixed order
+int launch_dw_reduce(const float* dw_part, float* dw, int ZJ, int Hq, int K, int parts, cudaStream_t stream);
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 

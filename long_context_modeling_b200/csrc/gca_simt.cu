@@ -335,13 +335,15 @@ bwd_q_simt_kernel(const E* __restrict__ q, const E* __restrict__ kc, const E* __
   }
 }
 
-__global__ void dw_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int ZJ, int Hq, int K) {
+__global__ void dw_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int ZJ, int Hq, int K,
+                                 int parts) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)ZJ * K) return;
   const long long zj = i / K;
   const int k = (int)(i % K);
   float t = 0.f;
-  for (int h = 0; h < Hq; ++h) t += part[(zj * Hq + h) * K + k];
+  for (int h = 0; h < Hq; ++h)
+    for (int q = 0; q < parts; ++q) t += part[((zj * Hq + h) * K + k) * parts + q];
   dw[i] = t;
 }
 
@@ -408,10 +410,10 @@ int launch_bwd_simt(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStr
   return GCA_ERR_DTYPE;
 }
 
-int launch_dw_reduce(const float* dw_part, float* dw, int ZJ, int Hq, int K, cudaStream_t stream) {
+int launch_dw_reduce(const float* dw_part, float* dw, int ZJ, int Hq, int K, int parts, cudaStream_t stream) {
   const long long total = (long long)ZJ * K;
   if (total == 0) return 0;
-  dw_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(dw_part, dw, ZJ, Hq, K);
+  dw_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(dw_part, dw, ZJ, Hq, K, parts);
   return (int)cudaGetLastError();
 }
 
