@@ -289,6 +289,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
   int next_idx = q_load_row(p, c.u, c.outer, lane);
   float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.outer * p.K + lane] : 0.f;
   for (; c.u < p.units && ok; c.advance()) {
+    pf.lap(8);
     const int my_idx = next_idx;
     const float my_w = next_w;
     {
@@ -297,6 +298,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       next_w = (c.u + gridDim.x < p.units && lane < p.K) ? p.weights[(long long)nzj * p.K + lane] : 0.f;
     }
     const unsigned mask = q_valid(p, my_idx);
+    pf.lap(9);
     const QInfo t = q_info(p, c.inner);
     const int h = t.h0 + tile;
     const bool live = (tile == 0 || t.two) && h < p.Hq;
@@ -322,8 +324,10 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     const uint32_t un = ucnt++;
     const uint32_t ub = un & 1;
     const float* lse_base = p.lse + ((long long)c.outer * p.Hq + (live ? h : t.h0)) * p.K * 64 + row;
+    pf.lap(10);
     for (unsigned m = mask; m; m &= m - 1, ++g) {
       if ((int)(g & 1) != wg) continue;
+      pf.lap(11);
       const int k = __ffs(m) - 1;
       const bool last = (m & (m - 1)) == 0;
       const float w = __shfl_sync(0xffffffffu, my_w, k);

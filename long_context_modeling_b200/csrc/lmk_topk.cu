@@ -88,19 +88,26 @@ lmk_scan_kernel(ScanParams p) {
     }
 
   unsigned long long mine[NL], thr[NL];
+  // Cheap pre-filter: a candidate can only enter a full list if its score beats the list's
+  // K-th score (rows arrive in increasing index order inside a warp, so an equal score loses
+  // the tie).  NaN while the list is not full: "!(s <= NaN)" lets everything through.
+  float thr_s[PER_HEAD ? NP : TQ];
 #pragma unroll
   for (int l = 0; l < NL; ++l) { mine[l] = 0ull; thr[l] = 0ull; }
+#pragma unroll
+  for (int l = 0; l < (PER_HEAD ? NP : TQ); ++l) thr_s[l] = __int_as_float(0x7fc00000);
 
   const int e_lo = split * p.e_per_split;
   const int e_hi = min(p.E, e_lo + p.e_per_split);
   const __nv_bfloat16* kb = p.lk + n * p.kbs;
   // the last query row of the tile sees the most chunks: rows past that limit are skipped
   const long long tile_limit = p.q_pos0 + min(t0 + TQ, p.Cq) - 1;
+  constexpr int U = (TQ == 1) ? 4 : 2;          // landmark rows in flight per warp iteration
 
-  for (int e = e_lo + warp; e < e_hi; e += 2 * SCAN_WARPS) {
-    uint4 kv[2][NP];
+  for (int e = e_lo + warp; e < e_hi; e += U * SCAN_WARPS) {
+    uint4 kv[U][NP];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int eu = e + u * SCAN_WARPS;
 #pragma unroll
       for (int pp = 0; pp < NP; ++pp) {
@@ -111,7 +118,7 @@ lmk_scan_kernel(ScanParams p) {
       }
     }
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int eu = e + u * SCAN_WARPS;
       const long long eg = p.e_base + eu;
       if (eu >= e_hi || eg >= tile_limit) continue;     // warp-uniform
@@ -134,10 +141,13 @@ lmk_scan_kernel(ScanParams p) {
           const int row = t0 + t;
           const bool vis = row < p.Cq && eg < p.q_pos0 + row;
           if (p.noise && vis) s += p.noise[((long long)n * p.Cq + row) * p.E + eu];
-          const unsigned long long key = make_key(s, (unsigned)eg);
-          if (vis && key > thr[t]) {
-            list_insert(mine[t], key, lane);
-            thr[t] = __shfl_sync(0xffffffffu, mine[t], p.K - 1);
+          if (vis && !(s <= thr_s[t])) {
+            const unsigned long long key = make_key(s, (unsigned)eg);
+            if (key > thr[t]) {
+              list_insert(mine[t], key, lane);
+              thr[t] = __shfl_sync(0xffffffffu, mine[t], p.K - 1);
+              if (thr[t] != 0ull) thr_s[t] = from_orderable((unsigned)(thr[t] >> 32));
+            }
           }
         }
       } else {
@@ -151,15 +161,22 @@ lmk_scan_kernel(ScanParams p) {
           }
 #pragma unroll
           for (int of = 4; of > 0; of >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, of);
+          // lanes 8g..8g+7 now hold the score of head 4*pp + g; each lane group tests it against
+          // its own head's threshold, and only rows with a candidate take the uniform path
+          const float s_loc = p.score_round ? round_bf16(round_bf16(acc) * p.scale) : acc * p.scale;
+          const unsigned cand = __ballot_sync(0xffffffffu, vis && !(s_loc <= thr_s[pp]));
+          if (cand == 0) continue;
 #pragma unroll
           for (int hg = 0; hg < 4; ++hg) {
+            if (!((cand >> (8 * hg)) & 1u)) continue;
             const int l = pp * 4 + hg;
-            const float raw = __shfl_sync(0xffffffffu, acc, hg * 8);
-            const float s = p.score_round ? round_bf16(round_bf16(raw) * p.scale) : raw * p.scale;
+            if (l >= p.H) continue;
+            const float s = __shfl_sync(0xffffffffu, s_loc, hg * 8);
             const unsigned long long key = make_key(s, (unsigned)eg);
-            if (vis && l < p.H && key > thr[l]) {
+            if (key > thr[l]) {
               list_insert(mine[l], key, lane);
               thr[l] = __shfl_sync(0xffffffffu, mine[l], p.K - 1);
+              if (thr[l] != 0ull && (lane >> 3) == hg) thr_s[pp] = from_orderable((unsigned)(thr[l] >> 32));
             }
           }
         }

@@ -32,7 +32,8 @@ inline EncodeTiledFn encode_tiled_fn() {
 // heads of a pair: two 64 x 64 tiles land back to back in shared memory); entries past the
 // end of the axis are filled with zeros.
 inline int make_tile_map_5d(CUtensorMap* map, const void* base, int d0, int d1, int d2, int d3, int d4,
-                            long long s1, long long s2, long long s3, long long s4, int box_d2 = 1) {
+                            long long s1, long long s2, long long s3, long long s4, int box_d2 = 1,
+                            bool swizzle128 = true) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return GCA_ERR_TMA;
   const long long dims_in[5] = {d0, d1, d2, d3, d4};
@@ -49,7 +50,8 @@ inline int make_tile_map_5d(CUtensorMap* map, const void* base, int d0, int d1, 
   const cuuint32_t box[5] = {64, 64, (cuuint32_t)box_d2, 1, 1};
   const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : GCA_ERR_TMA;
 }
