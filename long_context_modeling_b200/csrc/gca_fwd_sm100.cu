@@ -20,16 +20,21 @@
 // K_k / V_k tiles for both heads arrive with ONE TMA copy each, straight from the chunk
 // cache with the retrieved chunk index as a tensor coordinate (no gathered copy exists).
 //
-// CTA = 12 warps.  Warps 0-7: two softmax warpgroups taking alternate slots (thread =
-// TMEM lane = row).  Warp 8: TMA producer for Q and K, warp 9: TMA producer for V (separate
-// rings, K is released as soon as S is done).  Warp 10 issues the S MMAs, warp 11 the PV
-// MMAs.  The four single-lane roles are kept to a few dozen instructions per slot (a lone
-// warp retires one dependent instruction every ~5 cycles, so bookkeeping there is as
-// expensive as the MMAs): units are decoded incrementally, stage releases are relayed by the
-// softmax warps with plain mbarrier arrives.  CTAs are persistent and walk the units in
-// (n, j, head pair) order so that concurrently running CTAs touch the cache of few sequences
-// (L2 reuse of chunks retrieved many times).  Every mbarrier wait is bounded; on expiry the
-// CTA flags GCA_STATUS_TIMEOUT, drains its copies and unwinds.
+// CTA = 16 warps.
+//   warps 0-11  three softmax warpgroups taking the slots round-robin (thread = TMEM lane =
+//               row); each owns one S accumulator and one P buffer, so one group's chain
+//               S -> TMEM read -> exp2 -> P -> PV overlaps the other two groups' chains
+//   warp  12    TMA producer for Q and K;  warp 13: TMA producer for V (separate rings; K is
+//               released as soon as S is done)
+//   warp  14    issues the S MMAs;  warp 15 the PV MMAs (one O accumulator, slots in order, so
+//               the result does not depend on timing)
+// A warp can issue one tcgen05.mma per ~100 cycles when it runs converged with warp-uniform
+// operands and only the instruction itself is predicated on elect.sync (~150 inside a
+// divergent `if (lane == 0)` region), so the issuing warps run all lanes.  Ring stages are
+// released by tcgen05.commit straight onto the producers' barriers.  CTAs are persistent and
+// walk the units in (n, j, head pair) order so that concurrently running CTAs touch the cache
+// of few sequences (L2 reuse of chunks retrieved many times).  Every mbarrier wait is bounded;
+// on expiry the CTA flags GCA_STATUS_TIMEOUT, drains its copies and unwinds.
 #include <cstdlib>
 
 #include "gca_common.cuh"
@@ -45,21 +50,28 @@ using namespace sm100;
 constexpr int TILE_BYTES = 64 * 64 * 2;
 constexpr int PAIR_BYTES = 2 * TILE_BYTES;
 constexpr int NK = 4, NV = 4;               // ring depths (16 KB per stage each)
-constexpr int NTHREADS = 384;
-constexpr int KPROD_WARP = 8, VPROD_WARP = 9, SMMA_WARP = 10, PVMMA_WARP = 11;
-constexpr int TMEM_COLS = 512;              // S0 | S1 | O0 | O1, 128 columns each
+constexpr int NWG = 3;                      // softmax warpgroups
+constexpr int NTHREADS = (4 * NWG + 4) * 32;
+constexpr int KPROD_WARP = 4 * NWG, VPROD_WARP = KPROD_WARP + 1, SMMA_WARP = KPROD_WARP + 2;   // last warp: PV issuer
+constexpr int TMEM_COLS = 512;              // S0 | S1 | S2 | O, 128 columns each
+constexpr int TMEM_O = NWG * 128;
 
 constexpr int OFF_Q = 0;                              // [2 bufs][A B]
 constexpr int OFF_K = OFF_Q + 2 * PAIR_BYTES;         // [NK][A B]
 constexpr int OFF_V = OFF_K + NK * PAIR_BYTES;        // [NV][A B]
-constexpr int OFF_P = OFF_V + NV * PAIR_BYTES;        // [2 bufs][A B]
-constexpr int OFF_BAR = OFF_P + 2 * PAIR_BYTES;
+constexpr int OFF_P = OFF_V + NV * PAIR_BYTES;        // [NWG bufs][A B]
+constexpr int OFF_BAR = OFF_P + NWG * PAIR_BYTES;
 constexpr int OFF_IDX = OFF_BAR + 512;                // 2 producers x 32 retrieved indices
 constexpr int SMEM_BYTES = OFF_IDX + 256 + 1024;      // + alignment slack
 
 enum Bar { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + NK, V_FULL = K_EMPTY + NK, V_EMPTY = V_FULL + NV,
-           S_FULL = V_EMPTY + NV, S_EMPTY = S_FULL + 2, P_FULL = S_EMPTY + 2, P_EMPTY = P_FULL + 2,
-           O_FULL = P_EMPTY + 2, O_EMPTY = O_FULL + 2, NUM_BARS = O_EMPTY + 2 };
+           S_FULL = V_EMPTY + NV, S_EMPTY = S_FULL + NWG, P_FULL = S_EMPTY + NWG, P_EMPTY = P_FULL + NWG,
+           O_FULL = P_EMPTY + NWG, O_EMPTY = O_FULL + NWG, NUM_BARS = O_EMPTY + 1 };
+// Every barrier has ONE waiting party that waits for each of its phases in turn (a waiter that
+// skipped a phase would mistake an older completion for the one it wants): hence one O_FULL
+// barrier per warpgroup although there is a single O accumulator.
+static_assert(NUM_BARS * 8 + 16 <= 512, "barrier block");
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 
 struct FwdTcParams {
   CUtensorMap tm_q, tm_k2, tm_v2, tm_k1, tm_v1;   // *2: both heads of a pair per copy, *1: one head
@@ -73,26 +85,24 @@ struct FwdTcParams {
   int units;
   int N, J, Hq, Hkv, G, K, C, HP;
   int pair;                 // 1: a unit is a pair of q heads; 0: a single head (debug knob)
+  int dbg;                  // profile builds only: bit mask of work to skip (timing experiments)
   float c2;
   float off_by_one;
 };
 
-// Debug profiling (compiled in only with -DGCA_PROFILE): cycles per phase of one lane.
+// Debug tracing (compiled in only with -DGCA_PROFILE).
 #ifdef GCA_PROFILE
-struct Prof {
-  long long acc[12];
-  long long t;
-  bool on;
-  __device__ __forceinline__ void init(bool enable) { on = enable; for (int i = 0; i < 12; ++i) acc[i] = 0; if (on) t = clock64(); }
-  __device__ __forceinline__ void lap(int i) { if (on) { const long long n = clock64(); acc[i] += n - t; t = n; } }
-  __device__ __forceinline__ void dump(long long* dst) { if (on) for (int i = 0; i < 12; ++i) dst[i] = acc[i]; }
-};
+// event trace of block 0: prof[64 + event * 256 + slot] = clock of that event for that slot
+#define GCA_TRACE(ev, slot) do { if (p.prof != nullptr && blockIdx.x == 0 && (slot) < 256u) p.prof[64 + (ev) * 256 + (slot)] = clock64(); } while (0)
 #else
-struct Prof {
-  __device__ __forceinline__ void init(bool) {}
-  __device__ __forceinline__ void lap(int) {}
-  __device__ __forceinline__ void dump(long long*) {}
-};
+#define GCA_TRACE(ev, slot) do { } while (0)
+#endif
+
+// Timing experiments (compiled in only with -DGCA_DBGKNOBS): skip parts of the work.
+#ifdef GCA_DBGKNOBS
+#define GCA_DBG(bit) ((p.dbg >> (bit)) & 1)
+#else
+#define GCA_DBG(bit) 0
 #endif
 
 // Incremental walk over this CTA's units u = blockIdx.x, +gridDim.x, ...: unit u is
@@ -174,6 +184,7 @@ __device__ void producer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bar
       ok = mbar_wait_bounded(&bars[EMPTY + ring.st], ring.ph ^ 1, abort_flag);
       if (!ok) break;
       mbar_arrive_expect_tx(&bars[FULL + ring.st], bytes);
+      GCA_TRACE(MODE, issued);
       tma_load_5d(smem + OFF + ring.st * PAIR_BYTES, tm, &bars[FULL + ring.st], 0, 0, t.hk0, sidx[k], n);
       ring.next();
       ++issued;
@@ -197,70 +208,57 @@ __device__ void producer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bar
 }
 
 // ----------------------------------------------------------------------------- MMA issuers
-// mode 0: S = Q K^T per slot;  mode 1: O += P V per slot
+// mode 0: S_b = Q K^T;  mode 1: O += P_b V  (b = slot number mod NWG).  All 32 lanes run this
+// code; elect.sync inside the MMA / commit wrappers picks the issuing lane.
 template <int MODE>
 __device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
                             uint32_t tmem_base) {
-  const uint64_t dQ = umma_desc_sw128(smem_u32(smem + OFF_Q)), dK = umma_desc_sw128(smem_u32(smem + OFF_K));
-  const uint64_t dP = umma_desc_sw128(smem_u32(smem + OFF_P));
-  const uint64_t dV = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_V), TILE_BYTES);
   constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
+  constexpr uint32_t FULL = MODE == 0 ? K_FULL : V_FULL, EMPTY = MODE == 0 ? K_EMPTY : V_EMPTY;
+  constexpr uint32_t DEPTH = MODE == 0 ? NK : NV;
+  const uint64_t dA = MODE == 0 ? umma_desc_sw128(smem_u32(smem + OFF_Q)) : umma_desc_sw128(smem_u32(smem + OFF_P));
+  const uint64_t dB = MODE == 0 ? umma_desc_sw128(smem_u32(smem + OFF_K))
+                                : umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_V), TILE_BYTES);
   UnitCursor c;
   c.init(p);
-  Ring ring; ring.init(MODE == 0 ? NK : NV);
-  uint32_t ucnt = 0, sb = 0, sph = 0;         // S/P double buffer index and phase
+  uint32_t ucnt = 0, g = 0;                   // units with work; running slot number
+  uint32_t sb = 0, sph = 0;                   // S/P buffer (= owning warpgroup) and its phase
+  uint32_t um = 0;                            // unit counter modulo NWG (who writes the output)
   bool ok = true;
-  Prof pf;
-  pf.init(p.prof != nullptr && blockIdx.x == 0 && lane == 0);
   int next_idx = load_index_row(p, c.u, c.zj, lane);
-  for (; c.u < p.units; c.advance(p)) {
+  for (; c.u < p.units && ok; c.advance(p)) {
     const int my_idx = next_idx;
     next_idx = load_index_row(p, c.u + gridDim.x, c.next_zj(p), lane);
     const unsigned mask = valid_mask(p, my_idx);
     if (mask == 0) continue;
     const uint32_t un = ucnt++;
-    if (lane != 0 || !ok) continue;
     const int nv = __popc(mask);
     const UnitInfo t = unit_info(p, c.hp);
-    const uint32_t ub = un & 1, uph = (un >> 1) & 1;
+    const uint32_t ub = un & 1;
     const uint32_t idesc = umma_idesc_bf16(128, t.share ? 64 : 128, 0, MODE);
-    pf.lap(7);
-    if (MODE == 0) ok = mbar_wait_bounded(&bars[Q_FULL + ub], uph, abort_flag);
-    else ok = mbar_wait_bounded(&bars[O_EMPTY + ub], uph ^ 1, abort_flag);
-    pf.lap(0);
-    for (int i = 0; i < nv && ok; ++i) {
-      if (MODE == 0) {
-        ok = mbar_wait_bounded(&bars[K_FULL + ring.st], ring.ph, abort_flag);
-        pf.lap(1);
-        if (ok) ok = mbar_wait_bounded(&bars[S_EMPTY + sb], sph ^ 1, abort_flag);
-        pf.lap(2);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t a = dQ + ub * PAIR16, b = dK + ring.st * PAIR16;
-        const uint32_t dt = tmem_base + sb * 128;
+    if (MODE == 0) ok = mbar_wait_warp(&bars[Q_FULL + ub], (un >> 1) & 1, abort_flag, lane);
+    else ok = mbar_wait_warp(&bars[O_EMPTY], (un & 1) ^ 1, abort_flag, lane);
+    for (int i = 0; i < nv && ok; ++i, ++g) {
+      const uint32_t st = g % DEPTH, ph = (g / DEPTH) & 1u;
+      ok = mbar_wait_warp(&bars[FULL + st], ph, abort_flag, lane);
+      if (lane == 0) GCA_TRACE(2 + 3 * MODE, g);
+      if (ok) ok = mbar_wait_warp(&bars[(MODE == 0 ? S_EMPTY : P_FULL) + sb], MODE == 0 ? (sph ^ 1u) : sph, abort_flag, lane);
+      if (lane == 0) GCA_TRACE(3 + 3 * MODE, g);
+      if (!ok) break;
+      tc_fence_after();
+      const uint64_t a = MODE == 0 ? dA + ub * PAIR16 : dA + sb * PAIR16, b = dB + st * PAIR16;
+      const uint32_t dt = tmem_base + (MODE == 0 ? sb * 128 : TMEM_O);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(dt, a + kk * 2, b + kk * 2, idesc, kk > 0);
-        umma_commit(&bars[S_FULL + sb]);
-      } else {
-        ok = mbar_wait_bounded(&bars[V_FULL + ring.st], ring.ph, abort_flag);
-        pf.lap(1);
-        if (ok) ok = mbar_wait_bounded(&bars[P_FULL + sb], sph, abort_flag);
-        pf.lap(2);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t a = dP + sb * PAIR16, b = dV + ring.st * PAIR16;
-        const uint32_t dt = tmem_base + 256 + ub * 128;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(dt, a + kk * 2, b + kk * 128, idesc, (i > 0 || kk > 0));
-        umma_commit(&bars[P_EMPTY + sb]);
-        if (i == nv - 1) umma_commit(&bars[O_FULL + ub]);
-      }
-      pf.lap(3);
-      ring.next();
-      sb ^= 1; if (sb == 0) sph ^= 1;
+      for (int kk = 0; kk < 4; ++kk)
+        umma_bf16_ss_elect(dt, a + kk * 2, b + kk * (MODE == 0 ? 2 : 128), idesc, MODE == 0 ? (uint32_t)(kk > 0) : (uint32_t)(i > 0 || kk > 0));
+      umma_commit_elect(&bars[(MODE == 0 ? S_FULL : P_EMPTY) + sb]);
+      umma_commit_elect(&bars[EMPTY + st]);
+      if (i == nv - 1) umma_commit_elect(&bars[MODE == 0 ? Q_EMPTY + ub : O_FULL + um]);
+      if (lane == 0) GCA_TRACE(4 + 3 * MODE, g);
+      if (++sb == NWG) { sb = 0; sph ^= 1; }
     }
+    if (++um == NWG) um = 0;
   }
-  pf.dump(p.prof + 12 + 12 * MODE);
 }
 
 // ----------------------------------------------------------------------------- softmax + epilogue
@@ -275,14 +273,14 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
   const int tile = quad >> 1;                       // TMEM lanes 0-63: head A, 64-127: head B
   const int row = (quad & 1) * 32 + lane;           // query row inside the head
   const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
-  const bool elected = quad == 0 && lane == 0;      // relays stage releases for its warpgroup
-  uint8_t* sP = smem + OFF_P;
+  const bool elected = quad == 0 && lane == 0;
+  uint8_t* sP = smem + OFF_P + wg * PAIR_BYTES;      // this warpgroup's P buffer
+  const uint32_t tS = tlane + (uint32_t)wg * 128;    // and its S accumulator
   UnitCursor c;
   c.init(p);
-  uint32_t ucnt = 0, g = 0;
+  uint32_t ucnt = 0, own = 0, epi = 0, g = 0;        // units with work; own slots / outputs done; running slot
+  int gm = 0, um = 0;                                // slot and unit counters modulo NWG
   bool ok = true;
-  Prof pf;
-  pf.init(p.prof != nullptr && blockIdx.x == 0 && wg == 0 && elected);
   int next_idx = load_index_row(p, c.u, c.zj, lane);
   float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.zj * p.K + lane] : 0.f;
 
@@ -315,33 +313,35 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
       }
     }
     if (mask == 0) continue;
-    const uint32_t un = ucnt++;
-    const uint32_t ob = un & 1;
+    ++ucnt;
+    const bool my_unit = um == wg;                   // this group writes the unit's output
+    if (++um == NWG) um = 0;
     for (unsigned m = mask; m; m &= m - 1, ++g) {
-      if ((int)(g & 1) != wg) continue;              // the other warpgroup's slot
+      const bool mine = gm == wg;
+      if (++gm == NWG) gm = 0;
+      if (!mine) continue;                           // another warpgroup's slot
       const int k = __ffs(m) - 1;
-      const bool last = (m & (m - 1)) == 0;
       const float wk = __shfl_sync(0xffffffffu, my_w, k);
-      const uint32_t sb = g & 1;
-      pf.lap(7);
-      ok = mbar_wait_bounded(&bars[S_FULL + sb], (g >> 1) & 1, abort_flag);
-      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-      pf.lap(0);
-      if (elected) {                                   // S is done: its K stage (and Q) can be refilled
-        mbar_arrive(&bars[K_EMPTY + g % NK]);
-        if (last) mbar_arrive(&bars[Q_EMPTY + ob]);
-      }
+      const uint32_t oph = own & 1;
+      const uint32_t gt = g;                         // (trace builds only)
+      (void)gt;
+      ++own;
+      ok = mbar_wait_warp(&bars[S_FULL + wg], oph, abort_flag, lane);
+      if (!ok) break;
+      if (elected) GCA_TRACE(8, gt);
       tc_fence_after();
       uint32_t x[64];
-      tmem_ld_32x32b_x32(tlane + sb * 128 + coff, x);
-      tmem_ld_32x32b_x32(tlane + sb * 128 + coff + 32, x + 32);
+      tmem_ld_32x32b_x32(tS + coff, x);
+      tmem_ld_32x32b_x32(tS + coff + 32, x + 32);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&bars[S_EMPTY + sb]);
-      pf.lap(1);
+      mbar_arrive_warp(&bars[S_EMPTY + wg], lane);
+      if (elected) GCA_TRACE(9, gt);
 
       // row max: four independent chains of 3-input max
       float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      if (GCA_DBG(1)) m0 = __uint_as_float(x[0]);
+      else
 #pragma unroll
       for (int cc = 0; cc < 64; cc += 8) {
         m0 = fmax3(m0, __uint_as_float(x[cc + 0]), __uint_as_float(x[cc + 1]));
@@ -360,10 +360,12 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
         float2 a1 = __ffma2_rn(make_float2(__uint_as_float(x[cc + 2]), __uint_as_float(x[cc + 3])), c2v, nmm);
         float2 a2 = __ffma2_rn(make_float2(__uint_as_float(x[cc + 4]), __uint_as_float(x[cc + 5])), c2v, nmm);
         float2 a3 = __ffma2_rn(make_float2(__uint_as_float(x[cc + 6]), __uint_as_float(x[cc + 7])), c2v, nmm);
+        if (!GCA_DBG(0)) {
         a0.x = ex2_approx(a0.x); a0.y = ex2_approx(a0.y);
         a1.x = ex2_approx(a1.x); a1.y = ex2_approx(a1.y);
         a2.x = ex2_approx(a2.x); a2.y = ex2_approx(a2.y);
         a3.x = ex2_approx(a3.x); a3.y = ex2_approx(a3.y);
+        }
         s0 = __fadd2_rn(s0, a0); s1 = __fadd2_rn(s1, a1); s2 = __fadd2_rn(s2, a2); s3 = __fadd2_rn(s3, a3);
         x[cc + 0] = __float_as_uint(a0.x); x[cc + 1] = __float_as_uint(a0.y);
         x[cc + 2] = __float_as_uint(a1.x); x[cc + 3] = __float_as_uint(a1.y);
@@ -373,17 +375,16 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
       const float2 st2 = __fadd2_rn(__fadd2_rn(s0, s1), __fadd2_rn(s2, s3));
       float l = st2.x + st2.y;
       if (p.off_by_one > 0.f) l += p.off_by_one * ex2_approx(-mm);
-      if (lse_base && live) lse_base[k * 64] = mm + __log2f(l);
+      if (lse_base && live && !GCA_DBG(3)) lse_base[k * 64] = mm + __log2f(l);
       const float f = __fdividef(wk, l);
       const float2 fv = make_float2(f, f);
 
-      pf.lap(2);
-      ok = mbar_wait_bounded(&bars[P_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
-      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-      pf.lap(3);
-      // PV of slot g-2 (same P buffer) is done: its V stage can be refilled
-      if (elected && g >= 2) mbar_arrive(&bars[V_EMPTY + (g - 2) % NV]);
-      uint8_t* prow = sP + sb * PAIR_BYTES + tile * TILE_BYTES + row * 128;
+      if (elected) GCA_TRACE(10, gt);
+      ok = mbar_wait_warp(&bars[P_EMPTY + wg], oph ^ 1, abort_flag, lane);   // PV of this group's previous slot
+      if (!ok) break;
+      if (elected) GCA_TRACE(11, gt);
+      uint8_t* prow = sP + tile * TILE_BYTES + row * 128;
+      if (!GCA_DBG(2))
 #pragma unroll
       for (int cc = 0; cc < 8; ++cc) {
         const float2 q0 = __fmul2_rn(make_float2(__uint_as_float(x[8 * cc + 0]), __uint_as_float(x[8 * cc + 1])), fv);
@@ -394,23 +395,22 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
             make_uint4(pack_bf16x2(q0.x, q0.y), pack_bf16x2(q1.x, q1.y), pack_bf16x2(q2.x, q2.y), pack_bf16x2(q3.x, q3.y));
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bars[P_FULL + sb]);
-      pf.lap(4);
+      mbar_arrive_warp(&bars[P_FULL + wg], lane);
+      if (elected) GCA_TRACE(12, gt);
     }
     if (!ok) break;
-    // epilogue by the warpgroup that owns this unit's accumulator: O tile -> bf16 -> global
-    if ((int)ob == wg) {
-      pf.lap(7);
-      ok = mbar_wait_bounded(&bars[O_FULL + ob], (un >> 1) & 1, abort_flag);
-      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-      pf.lap(5);
+    // epilogue, the warpgroups taking turns: O tile -> bf16 -> global
+    if (my_unit) {
+      ok = mbar_wait_warp(&bars[O_FULL + wg], epi & 1, abort_flag, lane);
+      ++epi;
+      if (!ok) break;
       tc_fence_after();
       uint32_t o[64];
-      tmem_ld_32x32b_x32(tlane + 256 + ob * 128 + coff, o);
-      tmem_ld_32x32b_x32(tlane + 256 + ob * 128 + coff + 32, o + 32);
+      tmem_ld_32x32b_x32(tlane + TMEM_O + coff, o);
+      tmem_ld_32x32b_x32(tlane + TMEM_O + coff + 32, o + 32);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&bars[O_EMPTY + ob]);
+      mbar_arrive_warp(&bars[O_EMPTY], lane);
       if (live) {
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
@@ -422,11 +422,8 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
           reinterpret_cast<uint4*>(orow)[cc] = v;
         }
       }
-      pf.lap(6);
     }
   }
-  pf.lap(7);
-  pf.dump(p.prof);
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -439,12 +436,13 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars[Q_FULL + i], 1); mbar_init(&bars[Q_EMPTY + i], 1);
-      mbar_init(&bars[S_FULL + i], 1); mbar_init(&bars[S_EMPTY + i], 128);
-      mbar_init(&bars[P_FULL + i], 128); mbar_init(&bars[P_EMPTY + i], 1);
-      mbar_init(&bars[O_FULL + i], 1); mbar_init(&bars[O_EMPTY + i], 128);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars[Q_FULL + i], 1); mbar_init(&bars[Q_EMPTY + i], 1); }
+    for (int i = 0; i < NWG; ++i) {
+      mbar_init(&bars[S_FULL + i], 1); mbar_init(&bars[S_EMPTY + i], 4);     // counts in warps
+      mbar_init(&bars[P_FULL + i], 4); mbar_init(&bars[P_EMPTY + i], 1);
     }
+    for (int i = 0; i < NWG; ++i) mbar_init(&bars[O_FULL + i], 1);
+    mbar_init(&bars[O_EMPTY], 4);
     for (int i = 0; i < NK; ++i) { mbar_init(&bars[K_FULL + i], 1); mbar_init(&bars[K_EMPTY + i], 1); }
     for (int i = 0; i < NV; ++i) { mbar_init(&bars[V_FULL + i], 1); mbar_init(&bars[V_EMPTY + i], 1); }
     *abort_flag = 0;
@@ -458,7 +456,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams p) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 8) softmax_role(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
+  if (warp < 4 * NWG) softmax_role(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
   else if (warp == KPROD_WARP) producer_role<0>(p, smem, bars, abort_flag, lane);
   else if (warp == VPROD_WARP) producer_role<1>(p, smem, bars, abort_flag, lane);
   else if (warp == SMMA_WARP) issuer_role<0>(p, smem, bars, abort_flag, lane, tmem_base);
@@ -493,6 +491,8 @@ int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream) {
   p.N = a.N; p.J = a.J; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = a.Hq / a.Hkv; p.K = a.K; p.C = a.C;
   const char* pair_env = getenv("GCA_TC_PAIR");
   p.pair = (pair_env && pair_env[0] == '0') ? 0 : 1;
+  const char* dbg_env = getenv("GCA_DBG");
+  p.dbg = dbg_env ? atoi(dbg_env) : 0;
   p.HP = p.pair ? (a.Hq + 1) / 2 : a.Hq;
   const long long units = (long long)a.N * a.J * p.HP;
   if (units >= (1ll << 31) - 65536) return GCA_ERR_TOO_LARGE;

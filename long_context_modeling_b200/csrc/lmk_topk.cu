@@ -87,13 +87,13 @@ lmk_scan_kernel(ScanParams p) {
       unpack8(v, qf[t][pp]);
     }
 
-  unsigned long long mine[NL], thr[NL];
-  // Cheap pre-filter: a candidate can only enter a full list if its score beats the list's
-  // K-th score (rows arrive in increasing index order inside a warp, so an equal score loses
-  // the tie).  NaN while the list is not full: "!(s <= NaN)" lets everything through.
+  unsigned long long mine[NL];
+  // Admission test: a candidate enters a full list only if its score beats the list's K-th
+  // score (rows arrive in increasing index order inside a warp, so an equal score loses the
+  // tie; scores are never -0).  NaN while the list is not full: "!(s <= NaN)" admits everything.
   float thr_s[PER_HEAD ? NP : TQ];
 #pragma unroll
-  for (int l = 0; l < NL; ++l) { mine[l] = 0ull; thr[l] = 0ull; }
+  for (int l = 0; l < NL; ++l) mine[l] = 0ull;
 #pragma unroll
   for (int l = 0; l < (PER_HEAD ? NP : TQ); ++l) thr_s[l] = __int_as_float(0x7fc00000);
 
@@ -102,7 +102,7 @@ lmk_scan_kernel(ScanParams p) {
   const __nv_bfloat16* kb = p.lk + n * p.kbs;
   // the last query row of the tile sees the most chunks: rows past that limit are skipped
   const long long tile_limit = p.q_pos0 + min(t0 + TQ, p.Cq) - 1;
-  constexpr int U = (TQ == 1) ? 4 : 2;          // landmark rows in flight per warp iteration
+  constexpr int U = (TQ == 1 && !PER_HEAD) ? 4 : 2;   // landmark rows in flight per warp iteration
 
   for (int e = e_lo + warp; e < e_hi; e += U * SCAN_WARPS) {
     uint4 kv[U][NP];
@@ -142,12 +142,9 @@ lmk_scan_kernel(ScanParams p) {
           const bool vis = row < p.Cq && eg < p.q_pos0 + row;
           if (p.noise && vis) s += p.noise[((long long)n * p.Cq + row) * p.E + eu];
           if (vis && !(s <= thr_s[t])) {
-            const unsigned long long key = make_key(s, (unsigned)eg);
-            if (key > thr[t]) {
-              list_insert(mine[t], key, lane);
-              thr[t] = __shfl_sync(0xffffffffu, mine[t], p.K - 1);
-              if (thr[t] != 0ull) thr_s[t] = from_orderable((unsigned)(thr[t] >> 32));
-            }
+            list_insert(mine[t], make_key(s, (unsigned)eg), lane);
+            const unsigned long long kth = __shfl_sync(0xffffffffu, mine[t], p.K - 1);
+            if (kth != 0ull) thr_s[t] = from_orderable((unsigned)(kth >> 32));
           }
         }
       } else {
@@ -172,12 +169,9 @@ lmk_scan_kernel(ScanParams p) {
             const int l = pp * 4 + hg;
             if (l >= p.H) continue;
             const float s = __shfl_sync(0xffffffffu, s_loc, hg * 8);
-            const unsigned long long key = make_key(s, (unsigned)eg);
-            if (key > thr[l]) {
-              list_insert(mine[l], key, lane);
-              thr[l] = __shfl_sync(0xffffffffu, mine[l], p.K - 1);
-              if (thr[l] != 0ull && (lane >> 3) == hg) thr_s[pp] = from_orderable((unsigned)(thr[l] >> 32));
-            }
+            list_insert(mine[l], make_key(s, (unsigned)eg), lane);
+            const unsigned long long kth = __shfl_sync(0xffffffffu, mine[l], p.K - 1);
+            if (kth != 0ull && (lane >> 3) == hg) thr_s[pp] = from_orderable((unsigned)(kth >> 32));
           }
         }
       }

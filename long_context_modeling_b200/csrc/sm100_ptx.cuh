@@ -32,10 +32,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
+#ifdef GCA_WAIT_HINT_NS
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
+#ifdef GCA_WAIT_HINT_NS
+        , "r"((uint32_t)GCA_WAIT_HINT_NS)
+#endif
       : "memory");
   return ok != 0;
 }
@@ -45,10 +52,36 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
                                                   uint32_t limit = (1u << 22)) {
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef GCA_WAIT_SLEEP_NS
+    __nanosleep(GCA_WAIT_SLEEP_NS);
+#endif
     if ((i & 255u) == 255u && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
+}
+
+// Warp-level forms.  An mbarrier is one shared-memory word: 128 threads arriving on it, or 128
+// threads polling it, are 128 serialised shared-memory operations that also crowd the queue the
+// exp2 unit is fed from.  So a warp waits with ONE polling lane and arrives ONCE, after
+// __syncwarp() has ordered the other lanes' accesses (each lane issues its own proxy / tcgen05
+// fence before calling mbar_arrive_warp); barrier counts are then in warps, not threads.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
+#ifdef GCA_POLL_ONE_LANE
+  bool ok = true;
+  if (lane == 0) ok = mbar_wait_bounded(bar, parity, abort_flag);
+#else
+  // every lane polls (measured: a single polling lane with the others parked at the vote makes
+  // each barrier hop several times slower)
+  const bool ok = mbar_wait_bounded(bar, parity, abort_flag);
+#endif
+  // a vote, not a shuffle: its result is warp-uniform by construction, which keeps the code
+  // that follows (tcgen05.mma issue in particular) on the uniform path
+  return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
 }
 
 // ---------------------------------------------------------------- fences
@@ -152,6 +185,28 @@ __device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, u
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
+}
+
+// The same two, for a warp that runs the issuing code with ALL lanes (uniform control flow and
+// warp-uniform operands): the instruction itself is predicated on elect.sync, so one lane
+// issues it.  Measured: ~100 cycles per MMA for the issuing warp, against ~150 when the code
+// sits inside a divergent `if (lane == 0)` region.  Every lane of the warp must call these.
+__device__ __forceinline__ void umma_bf16_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
+      : "memory");
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {
