@@ -43,17 +43,19 @@ constexpr int TILE_BYTES = 64 * 64 * 2;
 constexpr int PAIR_BYTES = 2 * TILE_BYTES;
 constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
 constexpr int NTHREADS = 384;
-constexpr int PROD_WARP = 8, ISSUE_S = 9, ISSUE_DP = 10, ISSUE_G = 11;
+constexpr int PROD_WARP = 8, ISSUE_S = 9, ISSUE_DP = 10;   // warp 11: gradient-product issuer
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC = 256;
 
 // Four K steps of one stacked product.  a_step / b_step: descriptor advance per K step of 16.
+// Called by ALL lanes of the issuing warp (converged, warp-uniform operands); elect.sync picks
+// the lane that issues: ~100 cycles per instruction instead of ~150 inside an `if (lane == 0)`.
 constexpr int STEP_K = 2;      // K-major operand: +32 bytes (>> 4)
 constexpr int STEP_MN = 128;   // MN-major operand: +2048 bytes (>> 4)
 __device__ __forceinline__ void mma4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, int a_step, int b_step,
                                      bool accumulate_first) {
 #pragma unroll
-  for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(d, a + kk * a_step, b + kk * b_step, idesc, (accumulate_first || kk > 0));
+  for (int kk = 0; kk < 4; ++kk) umma_bf16_ss_elect(d, a + kk * a_step, b + kk * b_step, idesc, (uint32_t)(accumulate_first || kk > 0));
 }
 
 // One thread, one query row.  s: raw scores (overwritten by P), dp: raw dP.  Writes dS
@@ -221,55 +223,45 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
   Ring ring; ring.init(ROLE == 1 ? NVS : NKS);
   uint32_t ucnt = 0, g = 0;
   bool ok = true;
-  PhaseTimer pf;
-  pf.init(p.prof != nullptr && blockIdx.x == 0 && lane == 0);
   int next_idx = q_load_row(p, c.u, c.outer, lane);
-  for (; c.u < p.units; c.advance()) {
+  for (; c.u < p.units && ok; c.advance()) {
     const int my_idx = next_idx;
     next_idx = q_load_row(p, c.u + gridDim.x, c.next_outer(), lane);
     const unsigned mask = q_valid(p, my_idx);
     if (mask == 0) continue;
     const uint32_t un = ucnt++;
-    if (lane != 0 || !ok) continue;
-    pf.lap(7);
     const int nv = __popc(mask);
     const QInfo t = q_info(p, c.inner);
     const uint32_t ub = un & 1, uph = (un >> 1) & 1;
     const int ncol = t.share ? 64 : 128;
-    if (ROLE != 2) ok = mbar_wait_bounded(&bars[QDO_FULL + ub], uph, abort_flag);
-    else ok = mbar_wait_bounded(&bars[DQ_EMPTY + ub], uph ^ 1, abort_flag);
-    pf.lap(0);
+    if (ROLE != 2) ok = mbar_wait_warp(&bars[QDO_FULL + ub], uph, abort_flag, lane);
+    else ok = mbar_wait_warp(&bars[DQ_EMPTY + ub], uph ^ 1, abort_flag, lane);
     for (int i = 0; i < nv && ok; ++i, ++g) {
       if (ROLE != 2) {
-        ok = mbar_wait_bounded(&bars[(ROLE == 0 ? K_FULL : V_FULL) + ring.st], ring.ph, abort_flag);
-        pf.lap(1);
-        ok = ok && mbar_wait_bounded(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag);
-        pf.lap(2);
+        ok = mbar_wait_warp(&bars[(ROLE == 0 ? K_FULL : V_FULL) + ring.st], ring.ph, abort_flag, lane);
+        if (ok) ok = mbar_wait_warp(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag, lane);
         if (!ok) break;
         tc_fence_after();
         const uint32_t idesc = umma_idesc_bf16(128, ncol, 0, 0);
         const uint64_t q = dQDO + ub * 2 * PAIR16;
         if (ROLE == 0) mma4(tmem_base + COL_S, q, dK + ring.st * PAIR16, idesc, STEP_K, STEP_K, false);
         else mma4(tmem_base + COL_DP, q + PAIR16, dV + ring.st * PAIR16, idesc, STEP_K, STEP_K, false);
-        umma_commit(&bars[SP_FULL + (g & 1)]);    // the barrier expects both the S and the dP commit
+        umma_commit_elect(&bars[SP_FULL + (g & 1)]);    // the barrier expects both the S and the dP commit
       } else {
         const uint32_t sb = g & 1;
-        ok = mbar_wait_bounded(&bars[DS_FULL + sb], (g >> 1) & 1, abort_flag);
-        pf.lap(1);
+        ok = mbar_wait_warp(&bars[DS_FULL + sb], (g >> 1) & 1, abort_flag, lane);
         if (!ok) break;
         tc_fence_after();
         // dQ += dS K_k : A = dS (K-major), B = K_k (MN-major, both heads' tiles)
         mma4(tmem_base + COL_ACC + ub * 128, dDS + sb * PAIR16, dKmn + ring.st * PAIR16, umma_idesc_bf16(128, ncol, 0, 1),
              STEP_K, STEP_MN, i > 0);
-        umma_commit(&bars[DS_EMPTY + sb]);
-        umma_commit(&bars[K_EMPTY + ring.st]);     // the K tiles of this slot are free once dQ is done
-        if (i == nv - 1) umma_commit(&bars[DQ_FULL + ub]);
+        umma_commit_elect(&bars[DS_EMPTY + sb]);
+        umma_commit_elect(&bars[K_EMPTY + ring.st]);     // the K tiles of this slot are free once dQ is done
+        if (i == nv - 1) umma_commit_elect(&bars[DQ_FULL + ub]);
       }
-      pf.lap(3);
       ring.next();
     }
   }
-  pf.dump(p.prof + 36 + 12 + 12 * ROLE);
 }
 
 __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
@@ -516,7 +508,7 @@ __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars,
 
 // role 0: S per iteration;  role 1: dP per iteration;  role 2: dV and dK per iteration
 template <int ROLE>
-__device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag,
+__device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
                           uint32_t tmem_base) {
   using namespace kv;
   const uint64_t dKV = umma_desc_sw128(smem_u32(smem + OFF_KV));
@@ -529,37 +521,30 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
   Ring ring; ring.init(NQ);
   uint32_t ucnt = 0, g = 0;
   bool ok = true;
-  PhaseTimer pf;
-  pf.init(p.prof != nullptr && blockIdx.x == 0);
   int nbeg = c.u < p.units ? p.offsets[c.outer] : 0, nend = c.u < p.units ? p.offsets[c.outer + 1] : 0;
   for (; c.u < p.units && ok; c.advance()) {
     const int beg = nbeg, end = nend;
     if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nbeg = p.offsets[no]; nend = p.offsets[no + 1]; }
     const int niter = (end - beg) * p.G;
     if (niter == 0) continue;
-    pf.lap(7);
     const uint32_t un = ucnt++;
     const uint32_t kb = un & 1;
-    if (ROLE != 2) ok = mbar_wait_bounded(&bars[KV_FULL + kb], (un >> 1) & 1, abort_flag);
-    else ok = mbar_wait_bounded(&bars[ACC_EMPTY], (un & 1) ^ 1, abort_flag);
-    pf.lap(0);
+    if (ROLE != 2) ok = mbar_wait_warp(&bars[KV_FULL + kb], (un >> 1) & 1, abort_flag, lane);
+    else ok = mbar_wait_warp(&bars[ACC_EMPTY], (un & 1) ^ 1, abort_flag, lane);
     for (int i = 0; i < niter && ok; ++i, ++g) {
       const uint64_t stage = ring.st * 2 * PAIR16;
       if (ROLE != 2) {
-        ok = mbar_wait_bounded(&bars[QDO_FULL + ring.st], ring.ph, abort_flag);
-        pf.lap(1);
-        ok = ok && mbar_wait_bounded(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag);
-        pf.lap(2);
+        ok = mbar_wait_warp(&bars[QDO_FULL + ring.st], ring.ph, abort_flag, lane);
+        if (ok) ok = mbar_wait_warp(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag, lane);
         if (!ok) break;
         tc_fence_after();
         const uint64_t kd = dKV + kb * 2 * PAIR16;
         if (ROLE == 0) mma4(tmem_base + COL_S, dQDO + stage, kd, IDESC_KK, STEP_K, STEP_K, false);
         else mma4(tmem_base + COL_DP, dQDO + stage + PAIR16, kd + PAIR16, IDESC_KK, STEP_K, STEP_K, false);
-        umma_commit(&bars[SP_FULL + (g & 1)]);
+        umma_commit_elect(&bars[SP_FULL + (g & 1)]);
       } else {
         const uint32_t sb = g & 1;
-        ok = mbar_wait_bounded(&bars[PDS_FULL + sb], (g >> 1) & 1, abort_flag);
-        pf.lap(1);
+        ok = mbar_wait_warp(&bars[PDS_FULL + sb], (g >> 1) & 1, abort_flag, lane);
         if (!ok) break;
         tc_fence_after();
         const uint64_t pd = dPDSmn + sb * 2 * PAIR16;
@@ -567,15 +552,13 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         mma4(tmem_base + COL_DV, pd, dQDOmn + stage + PAIR16, IDESC_MM, STEP_MN, STEP_MN, i > 0);
         // dK += dS^T Q
         mma4(tmem_base + COL_DK, pd + PAIR16, dQDOmn + stage, IDESC_MM, STEP_MN, STEP_MN, i > 0);
-        umma_commit(&bars[PDS_EMPTY + sb]);
-        umma_commit(&bars[QDO_EMPTY + ring.st]);   // Q / dO of this iteration are free once dV, dK are done
-        if (i == niter - 1) umma_commit(&bars[ACC_FULL + (un & 1)]);
+        umma_commit_elect(&bars[PDS_EMPTY + sb]);
+        umma_commit_elect(&bars[QDO_EMPTY + ring.st]);   // Q / dO of this iteration are free once dV, dK are done
+        if (i == niter - 1) umma_commit_elect(&bars[ACC_FULL + (un & 1)]);
       }
-      pf.lap(3);
       ring.next();
     }
   }
-  pf.dump(p.prof + 72 + 12 + 12 * ROLE);
 }
 
 __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
@@ -713,9 +696,9 @@ bwd_kv_tc_kernel(const __grid_constant__ BwdKvParams p) {
   const uint32_t tmem_base = *tmem_slot;
   if (warp < 8) kv_worker(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
   else if (warp == PROD_WARP) { if (lane == 0) kv_producer(p, smem, bars, abort_flag); }
-  else if (warp == ISSUE_S) { if (lane == 0) kv_issuer<0>(p, smem, bars, abort_flag, tmem_base); }
-  else if (warp == ISSUE_DP) { if (lane == 0) kv_issuer<1>(p, smem, bars, abort_flag, tmem_base); }
-  else { if (lane == 0) kv_issuer<2>(p, smem, bars, abort_flag, tmem_base); }
+  else if (warp == ISSUE_S) kv_issuer<0>(p, smem, bars, abort_flag, lane, tmem_base);
+  else if (warp == ISSUE_DP) kv_issuer<1>(p, smem, bars, abort_flag, lane, tmem_base);
+  else kv_issuer<2>(p, smem, bars, abort_flag, lane, tmem_base);
   tc_fence_before();
   __syncthreads();
   if (warp == ISSUE_S) tmem_dealloc(tmem_base, TMEM_COLS);
