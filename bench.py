@@ -6,9 +6,10 @@ straight from the chunk cache, at the DRT-16K shape (8 sequences x 16,384 positi
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 Prints ONE JSON line (rank 0).  `value` = algorithmic TFLOP/s with inputs resident in HBM;
-`e2e` = the same through the public Python API from pinned host buffers (H2D + D2H inside
-the timed region); `roofline` = the forward tensor-core kernel against the measured dense
-bf16 peak; `cpu_baseline` = the PyTorch einsum formulation the reference uses as its ground
+`e2e` = the same through the public Python API from pinned host buffers (every step's H2D and
+D2H inside the timed region, overlapped across steps by `HostGcaPipeline`); `roofline` = the
+slowest of the three tensor-core kernels against the measured dense bf16 peak (all three are
+listed under `kernels`); `cpu_baseline` = the PyTorch einsum formulation the reference uses as its ground
 truth (ltriton/gca.py:912-921 behind the gather of model/DRT.py:193-199) on the host cores.
 Data are synthetic (seeded N(0,1) tensors, uniform causal retrieved ids) and stand in for the
 PG19 / arXiv-math token data of the reference, which is not available offline.
@@ -32,6 +33,8 @@ sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
 N_SEQ, CHUNKS, HEADS, TOPK, HEAD_DIM, CHUNK = 8, 256, 12, 8, 64, 64
 FWD_FLOP_PER_SLOT = 4 * CHUNK * CHUNK * HEAD_DIM          # QK^T + PV for one (query chunk, head, slot)
 FWD_BWD_FACTOR = 3.5                                      # backward counted as 2.5 x forward (ltriton/gca.py:1091-1092)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, ncu capture of `--n-seq 2` (see profiles/)
+TRAFFIC_2SEQ = {"fwd": 139.3e6 + 45.3e6, "bwd_kv": 215.9e6 + 68.3e6, "bwd_q": 204.7e6 + 41.3e6}
 
 
 def valid_slots(chunks: int, topk: int) -> int:
@@ -197,26 +200,24 @@ def gpu_arm(args):
         o.backward(dout)
         return o, q.grad, kc.grad, vc.grad, w.grad
 
-    pinned_out = None
+    pipe = lcm.HostGcaPipeline(dev, scale, depth=3)
+    e2e_check = [0.0]
 
     def e2e_step(hs):
-        nonlocal pinned_out
-        ds = tuple(t.to(dev, non_blocking=True) for t in hs)
-        outs = device_step(ds)
-        if pinned_out is None:
-            pinned_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
-        for p, o in zip(pinned_out, outs):
-            p.copy_(o, non_blocking=True)
-        return outs
+        done = pipe.submit(hs)
+        if done is not None:
+            e2e_check[0] += float(done[4][0, 1, 0])          # the host reads the finished step's result
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, sets, steps, warmup):
+    def timed(fn, sets, steps, warmup, finish=None):
         for i in range(warmup):
             fn(sets[i % 2])
+        if finish:
+            finish()
         barrier()
         sampler = ClockSampler(physical_gpu_index(local))
         sampler.start()
@@ -224,6 +225,8 @@ def gpu_arm(args):
         e0.record()
         for i in range(steps):
             fn(sets[i % 2])
+        if finish:
+            finish()                      # waits for the last downloads: they are part of the timed region
         e1.record()
         barrier()
         clocks = sampler.stop()
@@ -236,44 +239,71 @@ def gpu_arm(args):
 
     steps, warmup = args.steps, max(3, args.warmup)
     ms_dev, clocks = timed(device_step, dev_sets, steps, warmup)
-    ms_e2e, _ = timed(e2e_step, host_sets, max(3, steps // 4), 3)
+    ms_e2e, _ = timed(e2e_step, host_sets, max(6, steps // 2), 4, finish=pipe.drain)
 
-    # forward kernel alone (one launch per call): the roofline numerator
-    q, kc, vc, idx, w, dout = dev_sets[0]
-    for _ in range(3):
-        gmod.gca_forward_with_lse(q, kc, vc, idx, w, scale)
-    torch.cuda.synchronize()
+    # the three tensor-core kernels one at a time (one launch per call), for the roofline
+    def time_calls(fn, reps):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
     reps = max(10, steps)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(reps):
-        qq, kk, vv, ii, ww, _ = dev_sets[i % 2]
-        gmod.gca_forward_with_lse(qq, kk, vv, ii, ww, scale)
-    e1.record()
-    torch.cuda.synchronize()
-    ms_fwd = e0.elapsed_time(e1) / reps
+    fwd_out = [gmod.gca_forward_with_lse(*ds[:5], scale) for ds in dev_sets]
+    ms_fwd = time_calls(lambda i: gmod.gca_forward_with_lse(*dev_sets[i % 2][:5], scale), reps)
+    bufs = []
+    for ds, (_, lse) in zip(dev_sets, fwd_out):          # inverse index once per input set, then the stages alone
+        bufs.append(gmod.gca_backward_stages(*ds[:5], ds[5], lse, scale, stages=gmod.BWD_STAGE_INDEX))
+
+    def stage(i, which):
+        ds = dev_sets[i % 2]
+        gmod.gca_backward_stages(*ds[:5], ds[5], fwd_out[i % 2][1], scale, stages=which, bufs=bufs[i % 2])
+
+    ms_idx = time_calls(lambda i: stage(i, gmod.BWD_STAGE_INDEX), reps)
+    ms_kv = time_calls(lambda i: stage(i, gmod.BWD_STAGE_KV), reps)
+    ms_q = time_calls(lambda i: stage(i, gmod.BWD_STAGE_Q), reps)
     status = lcm.read_status()
 
     flops_fwd = workload_flops(N_SEQ)
     flops_step = flops_fwd * FWD_BWD_FACTOR
     value = flops_step * world / (ms_dev * 1e-3) / 1e12
     e2e_val = flops_step * world / (ms_e2e * 1e-3) / 1e12
-    h2d = sum(t.numel() * t.element_size() for t in host_sets[0])
-    d2h = sum(p.numel() * p.element_size() for p in pinned_out)
-    achieved = flops_fwd / (ms_fwd * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"]
+    # Algorithmic work per kernel, in units of the forward's two products (S = QK^T, O = PV):
+    # dK/dV kernel = dV + dK (its recomputed S and dP are overhead, not counted), dQ kernel =
+    # S + dP + dQ, so that forward + both = 3.5 x forward, the convention of the headline metric.
+    # DRAM traffic per launch: dram__bytes_read + dram__bytes_write of one ncu capture of the
+    # 2-sequence case (profiles/), scaled by the number of sequences (traffic grows with units).
+    kernels = {}
+    for name, ms, work, traffic_2seq in (("fwd_tc_kernel", ms_fwd, 1.0, TRAFFIC_2SEQ["fwd"]),
+                                         ("bwd_kv_tc_kernel", ms_kv, 1.0, TRAFFIC_2SEQ["bwd_kv"]),
+                                         ("bwd_q_tc_kernel (+ dw reduction)", ms_q, 1.5, TRAFFIC_2SEQ["bwd_q"])):
+        ach = flops_fwd * work / (ms * 1e-3) / 1e12
+        kernels[name] = {"ms": ms, "algorithmic_flops_per_launch": flops_fwd * work, "achieved_tflops": ach,
+                         "frac_of_peak": ach / peak, "dram_traffic_bytes_per_launch": traffic_2seq * N_SEQ / 2}
+    kernels["inverse index (CUB radix sort + 2 kernels)"] = {"ms": ms_idx}
+    top = max((k for k in kernels if "ms" in kernels[k] and "achieved_tflops" in kernels[k]), key=lambda k: kernels[k]["ms"])
     line = {
         "metric": "gca_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "config": config_dict(), "clocks": clocks,
-        "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e},
+        "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": pipe.h2d_bytes,
+                "d2h_bytes_per_step": pipe.d2h_bytes, "ms_per_step": ms_e2e,
+                "how": "HostGcaPipeline, 3 steps in flight: upload, kernels and download of consecutive steps overlap"},
         "gpu_launches": 6 * steps,
-        "kernels": {"fwd_ms": ms_fwd, "fwd_bwd_ms": ms_dev, "bwd_ms_by_difference": ms_dev - ms_fwd},
-        "roofline": {"kernel": "gca forward (fwd_tc_kernel)", "bound": "tensor", "achieved": achieved,
-                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                     "peak_source": peaks["source"] + " burst dense bf16", "traffic": None,
-                     "algorithmic_flops_per_launch": flops_fwd,
-                     "pct_of_tensor_peak_fwd_bwd": 100.0 * value / world / peaks["bf16_tflops"]},
+        "kernels": kernels,
+        "roofline": {"kernel": top, "bound": "tensor", "achieved": kernels[top]["achieved_tflops"],
+                     "peak": peak, "unit": "TFLOP/s", "frac": kernels[top]["frac_of_peak"],
+                     "peak_source": peaks["source"] + " burst dense bf16",
+                     "traffic": kernels[top]["dram_traffic_bytes_per_launch"],
+                     "algorithmic_flops_per_launch": kernels[top]["algorithmic_flops_per_launch"],
+                     "pct_of_tensor_peak_fwd_bwd": 100.0 * value / world / peak},
         "device_status": status,
     }
     if rank == 0 and world == 1 and not args.no_cpu:

@@ -156,6 +156,20 @@ int gca_bwd(const GcaBwdArgs* args, void* stream);
 size_t gca_bwd_workspace_bytes(const GcaBwdArgs* args);
 
 /*
+ * The same backward, one stage at a time (gca_bwd == all three, in this order, on one stream).
+ * The reference runs its two backward kernels back to back inside `_attention.backward`
+ * (ltriton/gca.py:786-838); the stages exist here so that a caller can put the dK/dV and the
+ * dQ/dw kernels on two streams (both only read the inverse index) and time them separately.
+ *   GCA_BWD_STAGE_INDEX  build the inverse retrieval index (chunk -> retrieving slots) in
+ *                        `workspace`; must have completed before the other two stages run
+ *   GCA_BWD_STAGE_KV     dk_cache, dv_cache
+ *   GCA_BWD_STAGE_Q      dq, dw
+ * All calls of one backward pass the same argument block (same workspace).
+ */
+enum { GCA_BWD_STAGE_INDEX = 1, GCA_BWD_STAGE_KV = 2, GCA_BWD_STAGE_Q = 4, GCA_BWD_STAGE_ALL = 7 };
+int gca_bwd_stages(const GcaBwdArgs* args, unsigned stages, void* stream);
+
+/*
  * Landmark scoring + causal chunk mask + top-k + retrieval weights, fused.  Stands in for
  * the tensor program of `DRT._perform_batch_retrieval` (model/DRT.py:612-627: einsum,
  * masked_fill with `_enc_dec_score_mask` :590-607, optional Gumbel noise, topk, softmax,

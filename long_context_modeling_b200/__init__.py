@@ -7,4 +7,5 @@ from .gca import attention, gca_kv_cache, gca_indexed, gca_indexed_nograd, read_
 from .retrieval import (lmk_score_topk, merge_topk, retrieve, perform_batch_retrieval,  # noqa: F401
                         decode_retrieval, differentiable_weights, Retrieval)
 from .chunk_cache import ChunkKVManager  # noqa: F401
+from .host_pipeline import HostGcaPipeline  # noqa: F401
 from .modules import TritonGroupCrossAttention, preprocess_chunk_kv_cache  # noqa: F401

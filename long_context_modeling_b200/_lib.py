@@ -84,6 +84,7 @@ EXPORTS = {
     "gca_decode": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
     "gca_bwd": (C.c_int, [C.POINTER(GcaBwdArgs), C.c_void_p]),
     "gca_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(GcaBwdArgs)]),
+    "gca_bwd_stages": (C.c_int, [C.POINTER(GcaBwdArgs), C.c_uint, C.c_void_p]),
     "lmk_score_topk": (C.c_int, [C.POINTER(LmkTopkArgs), C.c_void_p]),
     "lmk_topk_workspace_bytes": (C.c_size_t, [C.POINTER(LmkTopkArgs)]),
     "lmk_score_topk_static": (C.c_int, [C.POINTER(LmkTopkArgs), C.c_void_p]),

@@ -144,8 +144,11 @@ size_t gca_bwd_workspace_bytes(const GcaBwdArgs* a) {
   return gca::csr_workspace_bytes(a->N, a->J, a->K, a->C) + dw_part_bytes(a);
 }
 
-int gca_bwd(const GcaBwdArgs* a, void* stream) {
+int gca_bwd(const GcaBwdArgs* a, void* stream) { return gca_bwd_stages(a, GCA_BWD_STAGE_ALL, stream); }
+
+int gca_bwd_stages(const GcaBwdArgs* a, unsigned stages, void* stream) {
   if (!a) return GCA_ERR_NULL;
+  if (stages == 0 || (stages & ~(unsigned)GCA_BWD_STAGE_ALL)) return GCA_ERR_SHAPE;
   int rc = check_common(a->q, a->k_cache, a->v_cache, a->indices, a->weights, a->dtype, a->N, a->J, a->Hq, a->Hkv,
                         a->S, a->L, a->D, a->K, a->C);
   if (rc) return rc;
@@ -168,17 +171,20 @@ int gca_bwd(const GcaBwdArgs* a, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   gca::Csr csr;
   size_t used = 0;
-  rc = gca::build_csr(a->indices, a->N, a->J, a->K, a->C, a->workspace, a->workspace_bytes, &csr, &used, s);
+  rc = gca::build_csr(a->indices, a->N, a->J, a->K, a->C, a->workspace, a->workspace_bytes, &csr, &used, s,
+                      (stages & GCA_BWD_STAGE_INDEX) != 0);
   if (rc) return rc;
+  if (!(stages & (GCA_BWD_STAGE_KV | GCA_BWD_STAGE_Q))) return 0;
   float* dw_part = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + used);
   int algo = a->algo;
   const bool tc_ok = a->dtype == GCA_BF16 && a->S == 64;
   if (algo == GCA_ALGO_AUTO) algo = (tc_ok && gca::bwd_tc_available()) ? GCA_ALGO_TC : GCA_ALGO_SIMT;
   if (algo == GCA_ALGO_TC && !gca::bwd_tc_available()) algo = GCA_ALGO_SIMT;   // until the tensor-core backward lands
-  if (algo == GCA_ALGO_TC) rc = tc_ok ? gca::launch_bwd_tc(*a, csr, dw_part, s) : GCA_ERR_ALGO;
-  else if (algo == GCA_ALGO_SIMT) rc = gca::launch_bwd_simt(*a, csr, dw_part, s);
+  if (algo == GCA_ALGO_TC) rc = tc_ok ? gca::launch_bwd_tc(*a, csr, dw_part, s, stages) : GCA_ERR_ALGO;
+  else if (algo == GCA_ALGO_SIMT) rc = gca::launch_bwd_simt(*a, csr, dw_part, s, stages);
   else rc = GCA_ERR_ALGO;
   if (rc) return rc;
+  if (!(stages & GCA_BWD_STAGE_Q)) return 0;
   return gca::launch_dw_reduce(dw_part, a->dw, a->N * a->J, a->Hq, a->K, algo == GCA_ALGO_TC ? 2 : 1, s);
 }
 

@@ -709,7 +709,7 @@ bwd_kv_tc_kernel(const __grid_constant__ BwdKvParams p) {
 
 bool bwd_tc_available() { return true; }
 
-int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream) {
+int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream, unsigned stages) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;
   int dev = 0, sms = 0;
   GCA_CUDA_CHECK(cudaGetDevice(&dev));
@@ -722,7 +722,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
   auto kmap = [&](CUtensorMap* m, const void* base, const int64_t* st, int box) {
     return make_tile_map_5d(m, base, 64, 64, a.Hkv, a.C, a.N, st[2], st[3], st[1], st[0], box);
   };
-  {
+  if (stages & GCA_BWD_STAGE_KV) {
     BwdKvParams p;
     if ((rc = qmap(&p.tm_q2, a.q, a.q_stride, 2)) || (rc = qmap(&p.tm_do2, a.dout, a.do_stride, 2)) ||
         (rc = qmap(&p.tm_q1, a.q, a.q_stride, 1)) || (rc = qmap(&p.tm_do1, a.dout, a.do_stride, 1)) ||
@@ -745,7 +745,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
       GCA_CUDA_CHECK(cudaGetLastError());
     }
   }
-  {
+  if (stages & GCA_BWD_STAGE_Q) {
     BwdQParams p;
     if ((rc = qmap(&p.tm_q, a.q, a.q_stride, 2)) || (rc = qmap(&p.tm_do, a.dout, a.do_stride, 2)) ||
         (rc = kmap(&p.tm_k2, a.k_cache, a.k_stride, 2)) || (rc = kmap(&p.tm_v2, a.v_cache, a.v_stride, 2)) ||

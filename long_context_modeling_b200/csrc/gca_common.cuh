@@ -48,17 +48,19 @@ struct Csr {
   const unsigned long long* sorted_keys;
 };
 
+// launch == false: only lay the index out in `workspace` (it was built by an earlier call)
 int build_csr(const int32_t* indices, int N, int J, int K, int C, void* workspace, size_t workspace_bytes,
-              Csr* out, size_t* used_bytes, cudaStream_t stream);
+              Csr* out, size_t* used_bytes, cudaStream_t stream, bool launch = true);
 size_t csr_workspace_bytes(int N, int J, int K, int C);
 
 // SIMT (CUDA-core, fp32 accumulate) kernels: every dtype, S <= 64, L = D = 64.
 int launch_fwd_simt(const GcaFwdArgs& a, cudaStream_t stream);
-int launch_bwd_simt(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream);
+// stages: GCA_BWD_STAGE_KV and / or GCA_BWD_STAGE_Q
+int launch_bwd_simt(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream, unsigned stages);
 
 // tcgen05 / TMEM / TMA kernels: bf16, S = L = D = 64.
 int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream);
-int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream);
+int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream, unsigned stages);
 
 // dw[zj, k] = sum over heads and `parts` partials of dw_part[zj, h, k, part], in a fixed order
 int launch_dw_reduce(const float* dw_part, float* dw, int ZJ, int Hq, int K, int parts, cudaStream_t stream);

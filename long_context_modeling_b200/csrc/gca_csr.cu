@@ -2,9 +2,9 @@
 //
 // For every cache chunk (n, c) the backward needs the list of (query chunk j, slot k)
 // pairs that retrieved it, in a fixed order so that float32 accumulation is reproducible.
-// Each valid entry becomes the 64-bit key  (n*C + c) << 32 | (j*K + k); a radix sort
-// of the keys gives the lists back to back, and a binary search per chunk finds where
-// each list starts.  Padding slots (index < 0) and out-of-range indices sort to the end.
+// Each valid entry becomes the 64-bit key  (n*C + c) << 32 | (j*K + k); a stable radix sort
+// on the chunk field gives the lists back to back (two 8-bit passes at N*C = 2048 instead of
+// the eight of a full 64-bit sort), and a binary search per chunk finds where each list starts.  Padding slots (index < 0) and out-of-range indices sort to the end.
 #include <cub/device/device_radix_sort.cuh>
 
 #include "gca_common.cuh"
@@ -53,7 +53,7 @@ size_t csr_workspace_bytes(int N, int J, int K, int C) {
 }
 
 int build_csr(const int32_t* indices, int N, int J, int K, int C, void* workspace, size_t workspace_bytes,
-              Csr* out, size_t* used_bytes, cudaStream_t stream) {
+              Csr* out, size_t* used_bytes, cudaStream_t stream, bool launch) {
   const long long total = (long long)N * J * K;
   const long long NC = (long long)N * C;
   if (total >= (1ll << 31) || NC >= (1ll << 31)) return GCA_ERR_TOO_LARGE;
@@ -65,14 +65,21 @@ int build_csr(const int32_t* indices, int N, int J, int K, int C, void* workspac
   int* offsets = (int*)p;                                p += align_up((NC + 1) * 4, 256);
   size_t temp = cub_temp_bytes(total);
   void* temp_ptr = p;
-  if (total > 0) {
+  if (launch && total > 0) {
     csr_keys_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(indices, keys_in, N, J * K, C);
     GCA_CUDA_CHECK(cudaGetLastError());
-    // keys of valid entries use at most 32 + ceil(log2(N*C)) bits; invalid ones are all-ones
-    GCA_CUDA_CHECK(cub::DeviceRadixSort::SortKeys(temp_ptr, temp, keys_in, keys_out, (int)total, 0, 64, stream));
+    // The keys are generated in increasing (j*K + k) order inside a sequence, and the radix sort
+    // is stable, so sorting on the chunk field alone is a full sort.  Valid chunk ids are < N*C
+    // <= 2^b; the all-ones key of an invalid entry has bit b set and sorts behind them.
+    int b = 0;
+    while ((1ll << b) < NC) ++b;
+    const int end_bit = 32 + b + 1 > 64 ? 64 : 32 + b + 1;
+    GCA_CUDA_CHECK(cub::DeviceRadixSort::SortKeys(temp_ptr, temp, keys_in, keys_out, (int)total, 32, end_bit, stream));
   }
-  csr_offsets_kernel<<<(unsigned)((NC + 1 + 255) / 256), 256, 0, stream>>>(keys_out, offsets, total, NC);
-  GCA_CUDA_CHECK(cudaGetLastError());
+  if (launch) {
+    csr_offsets_kernel<<<(unsigned)((NC + 1 + 255) / 256), 256, 0, stream>>>(keys_out, offsets, total, NC);
+    GCA_CUDA_CHECK(cudaGetLastError());
+  }
   out->offsets = offsets;
   out->sorted_keys = keys_out;
   *used_bytes = need;

@@ -376,12 +376,13 @@ int fwd_simt_typed(const GcaFwdArgs& a, cudaStream_t stream) {
 }
 
 template <typename E>
-int bwd_simt_typed(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream) {
+int bwd_simt_typed(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream, unsigned stages) {
   const size_t smem = 6 * T * LD * sizeof(float);
   GCA_CUDA_CHECK(cudaFuncSetAttribute(bwd_kv_simt_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   GCA_CUDA_CHECK(cudaFuncSetAttribute(bwd_q_simt_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   Geom g = make_geom(a);
   dim3 gkv((unsigned)(a.N * a.C), (unsigned)a.Hkv);
+  if (stages & GCA_BWD_STAGE_KV)
   bwd_kv_simt_kernel<E><<<gkv, NTHREADS, smem, stream>>>(
       (const E*)a.q, (const E*)a.k_cache, (const E*)a.v_cache, a.weights, (const E*)a.dout, a.lse,
       (E*)a.dk_cache, (E*)a.dv_cache, csr, g,
@@ -390,6 +391,7 @@ int bwd_simt_typed(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStre
       a.dv_stride[0], a.dv_stride[1], a.dv_stride[2], a.dv_stride[3]);
   GCA_CUDA_CHECK(cudaGetLastError());
   dim3 gq((unsigned)(a.N * a.J), (unsigned)a.Hq);
+  if (stages & GCA_BWD_STAGE_Q)
   bwd_q_simt_kernel<E><<<gq, NTHREADS, smem, stream>>>(
       (const E*)a.q, (const E*)a.k_cache, (const E*)a.v_cache, a.indices, a.weights, (const E*)a.dout, a.lse,
       (E*)a.dq, dw_part, g, a.do_stride[0], a.do_stride[1], a.do_stride[2], a.do_stride[3]);
@@ -404,9 +406,9 @@ int launch_fwd_simt(const GcaFwdArgs& a, cudaStream_t stream) {
   return GCA_ERR_DTYPE;
 }
 
-int launch_bwd_simt(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream) {
-  if (a.dtype == GCA_BF16) return bwd_simt_typed<__nv_bfloat16>(a, csr, dw_part, stream);
-  if (a.dtype == GCA_F32) return bwd_simt_typed<float>(a, csr, dw_part, stream);
+int launch_bwd_simt(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream, unsigned stages) {
+  if (a.dtype == GCA_BF16) return bwd_simt_typed<__nv_bfloat16>(a, csr, dw_part, stream, stages);
+  if (a.dtype == GCA_F32) return bwd_simt_typed<float>(a, csr, dw_part, stream, stages);
   return GCA_ERR_DTYPE;
 }
 

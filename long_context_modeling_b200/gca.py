@@ -130,22 +130,42 @@ class _GcaIndexed(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         q5, kc5, vc5, idx32, w32, lse = ctx.saved_tensors
-        dout = _inner_contiguous(dout)
-        n, j, hq, s, d = q5.shape
-        _, c, l, hkv, _ = kc5.shape
-        k = idx32.shape[-1]
-        dq = torch.empty_like(q5)
-        if dq.stride(-1) != 1:
-            dq = torch.empty((n, j, hq, s, d), dtype=q5.dtype, device=q5.device)
-        dk = torch.empty_like(kc5)
-        dv = torch.empty_like(vc5)
-        if dk.stride(-1) != 1 or dv.stride(-1) != 1:
-            dk = torch.empty(kc5.shape, dtype=kc5.dtype, device=kc5.device)
-            dv = torch.empty(vc5.shape, dtype=vc5.dtype, device=vc5.device)
-        dw = torch.empty((n, j, k), dtype=torch.float32, device=q5.device)
-        a = _lib.GcaBwdArgs()
-        a.q, a.k_cache, a.v_cache = q5.data_ptr(), kc5.data_ptr(), vc5.data_ptr()
-        a.indices, a.weights, a.dout, a.lse = idx32.data_ptr(), w32.data_ptr(), dout.data_ptr(), lse.data_ptr()
+        dq, dk, dv, dw = _backward_call(q5, kc5, vc5, idx32, w32, dout, lse, ctx.sm_scale, ctx.off_by_one, ctx.algo)
+        return dq, dk, dv, None, dw, None, None, None, None
+
+
+BWD_STAGE_INDEX, BWD_STAGE_KV, BWD_STAGE_Q, BWD_STAGE_ALL = 1, 2, 4, 7
+
+
+def _backward_call(q5, kc5, vc5, idx32, w32, dout, lse, sm_scale, off_by_one, algo, stages=BWD_STAGE_ALL, bufs=None):
+    """One `gca_bwd_stages` call.  `bufs` = (dq, dk, dv, dw, workspace) from an earlier call of the
+    same backward (the stages of one backward share their outputs and the inverse index)."""
+    dout = _inner_contiguous(dout)
+    n, j, hq, s, d = q5.shape
+    _, c, l, hkv, _ = kc5.shape
+    k = idx32.shape[-1]
+    a = _lib.GcaBwdArgs()
+    a.q, a.k_cache, a.v_cache = q5.data_ptr(), kc5.data_ptr(), vc5.data_ptr()
+    a.indices, a.weights, a.dout, a.lse = idx32.data_ptr(), w32.data_ptr(), dout.data_ptr(), lse.data_ptr()
+    a.N, a.J, a.Hq, a.Hkv, a.S, a.L, a.D, a.K, a.C = n, j, hq, hkv, s, l, d, k, c
+    a.dtype = _dtype_code(q5)
+    a.algo = algo
+    a.sm_scale, a.off_by_one = float(sm_scale), float(off_by_one)
+    with torch.cuda.device(q5.device):
+        if bufs is None:
+            dq = torch.empty_like(q5)
+            if dq.stride(-1) != 1:
+                dq = torch.empty((n, j, hq, s, d), dtype=q5.dtype, device=q5.device)
+            dk = torch.empty_like(kc5)
+            dv = torch.empty_like(vc5)
+            if dk.stride(-1) != 1 or dv.stride(-1) != 1:
+                dk = torch.empty(kc5.shape, dtype=kc5.dtype, device=kc5.device)
+                dv = torch.empty(vc5.shape, dtype=vc5.dtype, device=vc5.device)
+            dw = torch.empty((n, j, k), dtype=torch.float32, device=q5.device)
+            nbytes = _lib.lib().gca_bwd_workspace_bytes(C.byref(a))
+            ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=q5.device)
+        else:
+            dq, dk, dv, dw, ws = bufs
         a.dq, a.dk_cache, a.dv_cache, a.dw = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dw.data_ptr()
         a.status = _status(q5.device).data_ptr()
         a.q_stride = _lib.strides4(*q5.stride()[:4])
@@ -155,18 +175,30 @@ class _GcaIndexed(torch.autograd.Function):
         a.v_stride = _lib.strides4(*vc5.stride()[:4])
         a.dk_stride = _lib.strides4(*dk.stride()[:4])
         a.dv_stride = _lib.strides4(*dv.stride()[:4])
-        a.N, a.J, a.Hq, a.Hkv, a.S, a.L, a.D, a.K, a.C = n, j, hq, hkv, s, l, d, k, c
-        a.dtype = _dtype_code(q5)
-        a.algo = ctx.algo
-        a.sm_scale, a.off_by_one = float(ctx.sm_scale), float(ctx.off_by_one)
-        with torch.cuda.device(q5.device):
-            nbytes = _lib.lib().gca_bwd_workspace_bytes(C.byref(a))
-            ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=q5.device)
-            base = ws.data_ptr()
-            a.workspace = (base + 255) // 256 * 256
-            a.workspace_bytes = nbytes
-            _lib.check(_lib.lib().gca_bwd(C.byref(a), _stream()), "gca_bwd")
-        return dq, dk, dv, None, dw, None, None, None, None
+        a.workspace = (ws.data_ptr() + 255) // 256 * 256
+        a.workspace_bytes = ws.numel() - 256
+        _lib.check(_lib.lib().gca_bwd_stages(C.byref(a), stages, _stream()), "gca_bwd_stages")
+    if bufs is None and stages != BWD_STAGE_ALL:
+        return dq, dk, dv, dw, ws
+    return dq, dk, dv, dw
+
+
+def gca_backward_stages(q, k_cache, v_cache, indices, weights, dout, lse, sm_scale, *, stages=BWD_STAGE_ALL,
+                        bufs=None, softmax_off_by_one=False, algo: int = ALGO_AUTO):
+    """The backward of `gca_indexed` without autograd, optionally one stage at a time
+    (BWD_STAGE_INDEX, then BWD_STAGE_KV and BWD_STAGE_Q in any order or on two streams).
+
+    q (N, J, Hq, S, D); caches (N, C, L, Hkv*D); dout like q; lse as returned by
+    `gca_forward_with_lse`.  A partial call returns (dq, dk, dv, dw, workspace): pass that tuple
+    back as `bufs` for the remaining stages.  A full call returns (dq, dk, dv, dw).
+    """
+    d = q.shape[-1]
+    q5, kc5, vc5 = _inner_contiguous(q), _as_cache5(k_cache, d), _as_cache5(v_cache, d)
+    _check_shapes(q5, kc5, vc5, indices, weights)
+    idx32 = indices.to(torch.int32).contiguous()
+    w32 = weights.to(torch.float32).contiguous()
+    return _backward_call(q5, kc5, vc5, idx32, w32, dout, lse, sm_scale, 1.0 if softmax_off_by_one else 0.0, algo,
+                          stages, bufs)
 
 
 def gca_indexed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, indices: torch.Tensor,

@@ -212,6 +212,45 @@ def test_determinism(lcm, algo):
         assert torch.equal(x, y)
 
 
+@pytest.mark.parametrize("algo", ALGOS)
+def test_backward_stage_by_stage_equals_one_call(lcm, algo):
+    """gca_bwd_stages: index, then the dQ/dw stage, then the dK/dV stage (in that unusual order)
+    give the bits of the single gca_bwd call."""
+    from long_context_modeling_b200 import gca as gmod
+    q, kc, vc, idx, w, dout = (t.cuda() for t in cases.gca_indexed_case(21, 2, 14, 4, 8, dtype=torch.bfloat16))
+    _, lse = gmod.gca_forward_with_lse(q, kc, vc, idx, w, 0.125, algo=algo)
+    full = gmod.gca_backward_stages(q, kc, vc, idx, w, dout, lse, 0.125, algo=algo)
+    bufs = gmod.gca_backward_stages(q, kc, vc, idx, w, dout, lse, 0.125, stages=gmod.BWD_STAGE_INDEX, algo=algo)
+    for t in bufs[:4]:
+        t.fill_(7)                                       # stale contents must be overwritten
+    gmod.gca_backward_stages(q, kc, vc, idx, w, dout, lse, 0.125, stages=gmod.BWD_STAGE_Q, bufs=bufs, algo=algo)
+    gmod.gca_backward_stages(q, kc, vc, idx, w, dout, lse, 0.125, stages=gmod.BWD_STAGE_KV, bufs=bufs, algo=algo)
+    torch.cuda.synchronize()
+    for x, y in zip(full, bufs[:4]):
+        assert torch.equal(x, y)
+    assert lcm.read_status() == 0
+
+
+def test_host_pipeline_matches_direct_calls(lcm):
+    """HostGcaPipeline (upload / kernels / download of consecutive steps overlapped on three
+    streams) returns, step by step and in order, the bits of the plain calls."""
+    steps = [cases.gca_indexed_case(30 + i, 2, 10, 4, 4, dtype=torch.bfloat16) for i in range(5)]
+    host = [tuple(t.pin_memory() for t in (q, kc, vc, idx.to(torch.int32), w, dout)) for q, kc, vc, idx, w, dout in steps]
+    want = [run_indexed(lcm, q, kc, vc, idx, w, 0.125, dout=dout) for q, kc, vc, idx, w, dout in steps]
+    pipe = lcm.HostGcaPipeline(torch.device("cuda", 0), 0.125, depth=2)
+    got = []
+    for hs in host:
+        done = pipe.submit(hs)
+        if done is not None:
+            got.append([t.clone() for t in done])
+    got += [[t.clone() for t in done] for done in pipe.drain()]
+    assert len(got) == len(want)
+    for g_, w_ in zip(got, want):
+        for x, y in zip(g_, w_):
+            assert torch.equal(x, y.cpu())
+    assert pipe.h2d_bytes > 0 and pipe.d2h_bytes > 0
+
+
 def test_strided_query_view_and_token_major_output(lcm):
     """q as a strided view of a (N, C, S, H*D) projection output, skipping chunk 0, and the
     output written token-major: no layout copies on either side."""
