@@ -257,7 +257,9 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
              STEP_K, STEP_MN, i > 0);
         umma_commit_elect(&bars[DS_EMPTY + sb]);
         umma_commit_elect(&bars[K_EMPTY + ring.st]);     // the K tiles of this slot are free once dQ is done
-        if (i == nv - 1) umma_commit_elect(&bars[DQ_FULL + ub]);
+        // dQ is written out by the worker group of the unit's last slot (it has just finished
+        // and its next slot is two slots away)
+        if (i == nv - 1) umma_commit_elect(&bars[DQ_FULL + sb]);
       }
       ring.next();
     }
@@ -276,6 +278,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
   c.init(p.HP);
   uint32_t ucnt = 0, g = 0;
   bool ok = true;
+  uint32_t epi = 0;                             // units this group has written out
   PhaseTimer pf;
   pf.init(p.prof != nullptr && blockIdx.x == 0 && wg == 0 && elected);
   int next_idx = q_load_row(p, c.u, c.outer, lane);
@@ -317,8 +320,10 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     const uint32_t ub = un & 1;
     const float* lse_base = p.lse + ((long long)c.outer * p.Hq + (live ? h : t.h0)) * p.K * 64 + row;
     pf.lap(10);
+    bool my_unit = false;                       // this group owns the unit's last slot: it writes dQ
     for (unsigned m = mask; m; m &= m - 1, ++g) {
-      if ((int)(g & 1) != wg) continue;
+      my_unit = (int)(g & 1) == wg;
+      if (!my_unit) continue;
       pf.lap(11);
       const int k = __ffs(m) - 1;
       const bool last = (m & (m - 1)) == 0;
@@ -358,9 +363,10 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       pf.lap(4);
     }
     if (!ok) break;
-    if ((int)ub == wg) {
+    if (my_unit) {
       pf.lap(7);
-      ok = mbar_wait_bounded(&bars[DQ_FULL + ub], (un >> 1) & 1, abort_flag);
+      ok = mbar_wait_bounded(&bars[DQ_FULL + wg], epi & 1, abort_flag);
+      ++epi;
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(5);
       tc_fence_after();
@@ -554,7 +560,7 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         mma4(tmem_base + COL_DK, pd + PAIR16, dQDOmn + stage, IDESC_MM, STEP_MN, STEP_MN, i > 0);
         umma_commit_elect(&bars[PDS_EMPTY + sb]);
         umma_commit_elect(&bars[QDO_EMPTY + ring.st]);   // Q / dO of this iteration are free once dV, dK are done
-        if (i == niter - 1) umma_commit_elect(&bars[ACC_FULL + (un & 1)]);
+        if (i == niter - 1) umma_commit_elect(&bars[ACC_FULL + sb]);   // written out by the last iteration's worker group
       }
       ring.next();
     }
@@ -573,6 +579,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
   c.init(p.HP);
   uint32_t ucnt = 0, g = 0;
   bool ok = true;
+  uint32_t epi = 0;                             // units this group has written out
   PhaseTimer pf;
   pf.init(p.prof != nullptr && blockIdx.x == 0 && wg == 0 && elected);
   int nbeg = c.u < p.units ? p.offsets[c.outer] : 0, nend = c.u < p.units ? p.offsets[c.outer + 1] : 0;
@@ -595,13 +602,15 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
     const uint32_t un = ucnt++;
     const uint32_t kb = un & 1;
     const int hk_safe = live ? hk : 2 * c.inner;
+    bool my_unit = false;                     // this group ran the unit's last iteration: it writes dK, dV
     for (int e = beg; e < end && ok; ++e) {
       float w = 0.f;
       long long zj = 0;
       int k = 0;
       bool fetched = false;            // (zj, k, w) of an entry are needed only for this group's iterations
       for (int gi = 0; gi < p.G; ++gi, ++g) {
-        if ((int)(g & 1) != wg) continue;
+        my_unit = (int)(g & 1) == wg;
+        if (!my_unit) continue;
         if (!fetched) {
           const int entry = (int)(p.sorted_keys[e] & 0xffffffffull);
           const int j = entry / p.K;
@@ -640,9 +649,10 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       }
     }
     if (!ok) break;
-    if ((int)(un & 1) == wg) {
+    if (my_unit) {
       pf.lap(7);
-      ok = mbar_wait_bounded(&bars[ACC_FULL + (un & 1)], (un >> 1) & 1, abort_flag);
+      ok = mbar_wait_bounded(&bars[ACC_FULL + wg], epi & 1, abort_flag);
+      ++epi;
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(5);
       tc_fence_after();

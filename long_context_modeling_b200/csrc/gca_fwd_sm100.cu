@@ -223,7 +223,6 @@ __device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars,
   c.init(p);
   uint32_t ucnt = 0, g = 0;                   // units with work; running slot number
   uint32_t sb = 0, sph = 0;                   // S/P buffer (= owning warpgroup) and its phase
-  uint32_t um = 0;                            // unit counter modulo NWG (who writes the output)
   bool ok = true;
   int next_idx = load_index_row(p, c.u, c.zj, lane);
   for (; c.u < p.units && ok; c.advance(p)) {
@@ -253,11 +252,12 @@ __device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars,
         umma_bf16_ss_elect(dt, a + kk * 2, b + kk * (MODE == 0 ? 2 : 128), idesc, MODE == 0 ? (uint32_t)(kk > 0) : (uint32_t)(i > 0 || kk > 0));
       umma_commit_elect(&bars[(MODE == 0 ? S_FULL : P_EMPTY) + sb]);
       umma_commit_elect(&bars[EMPTY + st]);
-      if (i == nv - 1) umma_commit_elect(&bars[MODE == 0 ? Q_EMPTY + ub : O_FULL + um]);
+      // the unit's output is written by the warpgroup of its last slot: it has just finished, and
+      // its next slot is NWG slots away
+      if (i == nv - 1) umma_commit_elect(&bars[MODE == 0 ? Q_EMPTY + ub : O_FULL + sb]);
       if (lane == 0) GCA_TRACE(4 + 3 * MODE, g);
       if (++sb == NWG) { sb = 0; sph ^= 1; }
     }
-    if (++um == NWG) um = 0;
   }
 }
 
@@ -279,7 +279,7 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
   UnitCursor c;
   c.init(p);
   uint32_t ucnt = 0, own = 0, epi = 0, g = 0;        // units with work; own slots / outputs done; running slot
-  int gm = 0, um = 0;                                // slot and unit counters modulo NWG
+  int gm = 0;                                        // slot counter modulo NWG
   bool ok = true;
   int next_idx = load_index_row(p, c.u, c.zj, lane);
   float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.zj * p.K + lane] : 0.f;
@@ -314,10 +314,10 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
     }
     if (mask == 0) continue;
     ++ucnt;
-    const bool my_unit = um == wg;                   // this group writes the unit's output
-    if (++um == NWG) um = 0;
+    bool my_unit = false;                            // this group owns the unit's last slot: it writes the output
     for (unsigned m = mask; m; m &= m - 1, ++g) {
       const bool mine = gm == wg;
+      my_unit = mine;
       if (++gm == NWG) gm = 0;
       if (!mine) continue;                           // another warpgroup's slot
       const int k = __ffs(m) - 1;
