@@ -104,6 +104,16 @@ def sharded_lmk_topk(lmk_q: torch.Tensor, lmk_k_local: torch.Tensor, topk: int, 
     rows = 1
     for s in rows_shape:
         rows *= s
+    if not validate and _tamper is None:
+        # lean path (no payload header, no host-side checks): one all-gather of the packed keys
+        # into a (world, rows, K) buffer; for a single row that buffer already is the merge input
+        gathered = torch.empty((world, rows, topk), dtype=torch.int64, device=local.keys.device)
+        try:
+            dist.all_gather_into_tensor(gathered, local.keys.reshape(rows, topk).contiguous(), group=group)
+        except RuntimeError as exc:
+            raise ShardExchangeError(f"candidate exchange failed: {exc}") from exc
+        keys = gathered.view(1, world * topk) if rows == 1 else gathered.permute(1, 0, 2).reshape(rows, world * topk)
+        return merge_fn(keys.reshape(rows_shape + (world * topk,)), topk)
     header = torch.tensor([rank, rows, topk, lo, hi, MAGIC], dtype=torch.int64, device=local.keys.device)
     payload = torch.cat([header, local.keys.reshape(-1)])
     if _tamper is not None:
