@@ -1,13 +1,17 @@
 // GCA forward for a handful of query rows (autoregressive decode: 1 or 2 rows per
 // sequence).  The work is a stream over K retrieved chunks x (K tile + V tile) per
-// (sequence, kv head): HBM-bound, no tensor cores.  One block per (n, j, kv head); each
-// warp owns whole slots.  At block start every warp puts its slot's two 8 KB tiles in flight
-// with two TMA copies (retrieved chunk index = tensor coordinate), so a block has its whole
-// 16*K KB working set outstanding at once and nothing is staged through registers.  The K
-// tile lands 128-byte-swizzled (conflict-free row reads), the V tile plain.  The warp then
-// scores the R = G*S query rows against the 64 keys (two keys per lane), normalises inside
-// the warp and accumulates its weighted P.V in registers.  The per-warp partial outputs are
-// summed in warp order at the end, so the result does not depend on scheduling.
+// (sequence, kv head): HBM-bound, no tensor cores.  Blocks are persistent (one per SM: each
+// warp keeps a K and a V tile, 128 KB per block) and walk the (n, j, kv head) items; each warp
+// owns whole slots and fetches its slot's two 8 KB tiles with two TMA copies (retrieved chunk
+// index = tensor coordinate) onto two mbarriers of its own, so nothing is staged through
+// registers.  As soon as a warp has scored its queries against the K tile it puts the K tile
+// of its NEXT slot in flight -- of the next item when this one has no more slots for it -- and
+// likewise the V tile after P.V: the loads of an item run under the arithmetic, the block-wide
+// merge and the output store of the one before.  The K tile lands 128-byte-swizzled
+// (conflict-free row reads), the V tile plain.  A warp scores the R = G*S query rows against
+// the 64 keys (two keys per lane), normalises inside the warp and accumulates its weighted
+// P.V in registers; the per-warp partial outputs are summed in warp order, so the result does
+// not depend on scheduling.
 #include "gca_common.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
@@ -40,146 +44,186 @@ __global__ void __launch_bounds__(NWARPS * 32)
 decode_kernel(const __grid_constant__ DecParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  // per warp: K tile (swizzled) then V tile (plain); after the slot loop the same memory holds
-  // the per-warp partial outputs.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  uint8_t* my_tiles = smem + warp * 2 * TILE_BYTES;
-  float* sQ = reinterpret_cast<float*>(smem + NWARPS * 2 * TILE_BYTES);                 // R x 64 floats
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NWARPS * 2 * TILE_BYTES + R * T * 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + NWARPS);
+  uint8_t* tile_k = smem + warp * 2 * TILE_BYTES;                                       // swizzled
+  uint8_t* tile_v = tile_k + TILE_BYTES;                                                // plain
+  float* sQ_all = reinterpret_cast<float*>(smem + NWARPS * 2 * TILE_BYTES);             // [2][R x 64] scaled queries
+  float* part_all = sQ_all + 2 * R * T;                                                 // [2][NWARPS][R x 64] partial outputs
+  uint64_t* bars = reinterpret_cast<uint64_t*>(part_all + 2 * NWARPS * R * T);          // [NWARPS][K, V]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * NWARPS);
   const Geom& g = p.g;
-  const int zj = blockIdx.x / g.Hkv, hk = blockIdx.x % g.Hkv;
-  const int n = zj / g.J, j = zj % g.J;
+  const int items = g.N * g.J * g.Hkv;
   const int rows = g.G * g.S;                                    // <= R
   const float c2 = g.sm_scale * GCA_LOG2E;
+  uint64_t* bar_k = &bars[2 * warp];
+  uint64_t* bar_v = &bars[2 * warp + 1];
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NWARPS; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 2 * NWARPS; ++i) mbar_init(&bars[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
   __syncthreads();
 
-  // first slot of every warp goes in flight before anything else happens
-  int k = warp;
-  int idx = k < g.K ? p.indices[(long long)zj * g.K + k] : -1;
-  auto issue = [&](int index) {
+  // This warp's slots, in order: (item, k) with k = warp, warp + 8, ... < K, then the next item.
+  // `cur` is the slot whose tiles are (or are about to be) in the buffers; idx < 0: no copy.
+  struct Slot { int item, k, idx; };
+  auto load_idx = [&](int item, int k) -> int {
+    const int zj = item / g.Hkv;
+    const int v = p.indices[(long long)zj * g.K + k];
+    if (v >= g.C) { if (p.status && lane == 0) atomicOr(p.status, GCA_STATUS_BAD_INDEX); return -1; }
+    return v;
+  };
+  auto next_slot = [&](const Slot& s) -> Slot {
+    Slot t;
+    t.item = s.item; t.k = s.k + NWARPS;
+    if (t.k >= g.K) { t.item = s.item + (int)gridDim.x; t.k = warp; }
+    t.idx = (t.item < items && t.k < g.K) ? load_idx(t.item, t.k) : -1;
+    return t;
+  };
+  auto issue = [&](const Slot& s, bool is_v) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(&bars[warp], 2 * TILE_BYTES);
-      tma_load_5d(my_tiles, &p.tm_k, &bars[warp], 0, 0, hk, index, n);
-      tma_load_5d(my_tiles + TILE_BYTES, &p.tm_v, &bars[warp], 0, 0, hk, index, n);
+      const int zj = s.item / g.Hkv, hk = s.item - zj * g.Hkv;
+      uint64_t* bar = is_v ? bar_v : bar_k;
+      mbar_arrive_expect_tx(bar, TILE_BYTES);
+      tma_load_5d(is_v ? tile_v : tile_k, is_v ? &p.tm_v : &p.tm_k, bar, 0, 0, hk, s.idx, zj / g.J);
     }
   };
-  if (idx >= 0 && idx < g.C) issue(idx);
 
-  for (int i = threadIdx.x; i < R * T; i += NWARPS * 32) {
-    const int r = i >> 6, d = i & 63;
-    float v = 0.f;
-    if (r < rows) {
-      const int gi = r / g.S, s = r % g.S;
-      v = __bfloat162float(p.q[n * g.qs[0] + j * g.qs[1] + (hk * g.G + gi) * g.qs[2] + s * g.qs[3] + d]);
-    }
-    sQ[i] = v * c2;
-  }
-  __syncthreads();
-
-  float o[R][2];
-#pragma unroll
-  for (int r = 0; r < R; ++r) { o[r][0] = 0.f; o[r][1] = 0.f; }
-
-  uint32_t phase = 0;
+  Slot cur;
+  cur.item = blockIdx.x; cur.k = warp;
+  cur.idx = (cur.item < items && cur.k < g.K) ? load_idx(cur.item, cur.k) : -1;
+  bool in_k = false, in_v = false;               // a copy is in flight (or landed, unread) in the K / V buffer
+  if (cur.idx >= 0) { issue(cur, false); issue(cur, true); in_k = in_v = true; }
+  uint32_t ph_k = 0, ph_v = 0;
   bool ok = true;
-  while (k < g.K) {
-    const int knext = k + NWARPS;
-    const int idx_next = knext < g.K ? p.indices[(long long)zj * g.K + knext] : -1;
-    if (idx < 0 || idx >= g.C) {
-      if (idx >= g.C && p.status && lane == 0) atomicOr(p.status, GCA_STATUS_BAD_INDEX);
-    } else if (ok) {
-      const float w = p.weights[(long long)zj * g.K + k];
-      ok = mbar_wait_bounded(&bars[warp], phase, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      phase ^= 1;
-      if (ok) {
+
+  int par = 0;
+  for (int item = blockIdx.x; item < items; item += gridDim.x, par ^= 1) {
+    const int zj = item / g.Hkv, hk = item - zj * g.Hkv;
+    const int n = zj / g.J, j = zj - n * g.J;
+    float* sQ = sQ_all + par * R * T;
+    float* part = part_all + par * NWARPS * R * T;
+    for (int i = threadIdx.x; i < R * T; i += NWARPS * 32) {
+      const int r = i >> 6, d = i & 63;
+      float v = 0.f;
+      if (r < rows) {
+        const int gi = r / g.S, s = r % g.S;
+        v = __bfloat162float(p.q[n * g.qs[0] + j * g.qs[1] + (hk * g.G + gi) * g.qs[2] + s * g.qs[3] + d]);
+      }
+      sQ[i] = v * c2;
+    }
+    __syncthreads();
+
+    float o[R][2];
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          if (r >= rows) break;
-          float s0 = 0.f, s1 = 0.f;
+    for (int r = 0; r < R; ++r) { o[r][0] = 0.f; o[r][1] = 0.f; }
+
+    while (cur.item == item && cur.k < g.K) {
+      const Slot nxt = next_slot(cur);           // its index load overlaps the waits below
+      float pr[R][2];
+      if (cur.idx >= 0 && ok) {
+        const float w = p.weights[(long long)zj * g.K + cur.k];
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_k, ph_k, abort_flag));
+        ph_k ^= 1;
+        in_k = false;
+        if (ok) {
 #pragma unroll
-          for (int pc = 0; pc < 8; ++pc) {
-            const uint4 a = *reinterpret_cast<const uint4*>(my_tiles + lane * 128 + ((pc ^ (lane & 7)) << 4));
-            const uint4 b = *reinterpret_cast<const uint4*>(my_tiles + (lane + 32) * 128 + ((pc ^ (lane & 7)) << 4));
-            const float* qr = sQ + r * T + pc * 8;
-            s0 = fmaf(qr[0], bf_lo(a.x), s0); s0 = fmaf(qr[1], bf_hi(a.x), s0);
-            s0 = fmaf(qr[2], bf_lo(a.y), s0); s0 = fmaf(qr[3], bf_hi(a.y), s0);
-            s0 = fmaf(qr[4], bf_lo(a.z), s0); s0 = fmaf(qr[5], bf_hi(a.z), s0);
-            s0 = fmaf(qr[6], bf_lo(a.w), s0); s0 = fmaf(qr[7], bf_hi(a.w), s0);
-            s1 = fmaf(qr[0], bf_lo(b.x), s1); s1 = fmaf(qr[1], bf_hi(b.x), s1);
-            s1 = fmaf(qr[2], bf_lo(b.y), s1); s1 = fmaf(qr[3], bf_hi(b.y), s1);
-            s1 = fmaf(qr[4], bf_lo(b.z), s1); s1 = fmaf(qr[5], bf_hi(b.z), s1);
-            s1 = fmaf(qr[6], bf_lo(b.w), s1); s1 = fmaf(qr[7], bf_hi(b.w), s1);
+          for (int r = 0; r < R; ++r) {
+            pr[r][0] = pr[r][1] = 0.f;
+            if (r >= rows) continue;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int pc = 0; pc < 8; ++pc) {
+              const uint4 a = *reinterpret_cast<const uint4*>(tile_k + lane * 128 + ((pc ^ (lane & 7)) << 4));
+              const uint4 b = *reinterpret_cast<const uint4*>(tile_k + (lane + 32) * 128 + ((pc ^ (lane & 7)) << 4));
+              const float* qr = sQ + r * T + pc * 8;
+              s0 = fmaf(qr[0], bf_lo(a.x), s0); s0 = fmaf(qr[1], bf_hi(a.x), s0);
+              s0 = fmaf(qr[2], bf_lo(a.y), s0); s0 = fmaf(qr[3], bf_hi(a.y), s0);
+              s0 = fmaf(qr[4], bf_lo(a.z), s0); s0 = fmaf(qr[5], bf_hi(a.z), s0);
+              s0 = fmaf(qr[6], bf_lo(a.w), s0); s0 = fmaf(qr[7], bf_hi(a.w), s0);
+              s1 = fmaf(qr[0], bf_lo(b.x), s1); s1 = fmaf(qr[1], bf_hi(b.x), s1);
+              s1 = fmaf(qr[2], bf_lo(b.y), s1); s1 = fmaf(qr[3], bf_hi(b.y), s1);
+              s1 = fmaf(qr[4], bf_lo(b.z), s1); s1 = fmaf(qr[5], bf_hi(b.z), s1);
+              s1 = fmaf(qr[6], bf_lo(b.w), s1); s1 = fmaf(qr[7], bf_hi(b.w), s1);
+            }
+            float m = fmaxf(s0, s1);
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, of));
+            if (g.off_by_one > 0.f) m = fmaxf(m, 0.f);
+            float p0 = exp2f(s0 - m), p1 = exp2f(s1 - m);
+            float l = p0 + p1;
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) l += __shfl_xor_sync(0xffffffffu, l, of);
+            if (g.off_by_one > 0.f) l += g.off_by_one * exp2f(-m);
+            const float f = w / l;
+            pr[r][0] = p0 * f; pr[r][1] = p1 * f;
           }
-          float m = fmaxf(s0, s1);
-#pragma unroll
-          for (int of = 16; of > 0; of >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, of));
-          if (g.off_by_one > 0.f) m = fmaxf(m, 0.f);
-          float p0 = exp2f(s0 - m), p1 = exp2f(s1 - m);
-          float l = p0 + p1;
-#pragma unroll
-          for (int of = 16; of > 0; of >>= 1) l += __shfl_xor_sync(0xffffffffu, l, of);
-          if (g.off_by_one > 0.f) l += g.off_by_one * exp2f(-m);
-          const float f = w / l;
-          p0 *= f; p1 *= f;
-          float a0 = 0.f, a1 = 0.f;
-#pragma unroll 8
-          for (int key = 0; key < 32; ++key) {
-            const float pa = __shfl_sync(0xffffffffu, p0, key);
-            const float pb = __shfl_sync(0xffffffffu, p1, key);
-            const unsigned va = *reinterpret_cast<const unsigned*>(my_tiles + TILE_BYTES + key * 128 + lane * 4);
-            const unsigned vb = *reinterpret_cast<const unsigned*>(my_tiles + TILE_BYTES + (key + 32) * 128 + lane * 4);
-            a0 = fmaf(pa, bf_lo(va), a0); a1 = fmaf(pa, bf_hi(va), a1);
-            a0 = fmaf(pb, bf_lo(vb), a0); a1 = fmaf(pb, bf_hi(vb), a1);
-          }
-          o[r][0] += a0; o[r][1] += a1;
         }
       }
-    }
-    k = knext;
-    idx = idx_next;
-    if (k < g.K && idx >= 0 && idx < g.C && ok) {
-      __syncwarp();                 // every lane is done reading the tiles of the previous slot
-      issue(idx);
-    }
-  }
-  // a warp that gave up may still have its last copy in flight: wait for it (bounded) so
-  // nothing lands in shared memory after the block has moved on
-  if (!ok && lane == 0)
-    for (int i = 0; i < (1 << 20); ++i)
-      if (mbar_try_wait(&bars[warp], phase ^ 1)) break;
-  // cross-warp sum in warp order
-  __syncthreads();
-  float* part = reinterpret_cast<float*>(smem);   // NWARPS x R x 64 floats (<= 32 KB)
+      // the K buffer has been read: the next slot's K tile goes in flight under the P.V below
+      __syncwarp();
+      if (nxt.idx >= 0 && ok) { issue(nxt, false); in_k = true; }
+      if (cur.idx >= 0 && ok) {
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_v, ph_v, abort_flag));
+        ph_v ^= 1;
+        in_v = false;
+        if (ok) {
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    part[(warp * R + r) * T + 2 * lane] = o[r][0];
-    part[(warp * R + r) * T + 2 * lane + 1] = o[r][1];
+          for (int r = 0; r < R; ++r) {
+            if (r >= rows) break;
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
+            for (int key = 0; key < 32; ++key) {
+              const float pa = __shfl_sync(0xffffffffu, pr[r][0], key);
+              const float pb = __shfl_sync(0xffffffffu, pr[r][1], key);
+              const unsigned va = *reinterpret_cast<const unsigned*>(tile_v + key * 128 + lane * 4);
+              const unsigned vb = *reinterpret_cast<const unsigned*>(tile_v + (key + 32) * 128 + lane * 4);
+              a0 = fmaf(pa, bf_lo(va), a0); a1 = fmaf(pa, bf_hi(va), a1);
+              a0 = fmaf(pb, bf_lo(vb), a0); a1 = fmaf(pb, bf_hi(vb), a1);
+            }
+            o[r][0] += a0; o[r][1] += a1;
+          }
+        }
+      }
+      __syncwarp();
+      if (nxt.idx >= 0 && ok) { issue(nxt, true); in_v = true; }
+      cur = nxt;
+    }
+    // cross-warp sum in warp order
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      part[(warp * R + r) * T + 2 * lane] = o[r][0];
+      part[(warp * R + r) * T + 2 * lane + 1] = o[r][1];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows * T; i += NWARPS * 32) {
+      const int r = i >> 6, d = i & 63;
+      float t = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < NWARPS; ++wv) t += part[(wv * R + r) * T + d];
+      const int gi = r / g.S, s = r % g.S;
+      p.out[n * g.os[0] + j * g.os[1] + (hk * g.G + gi) * g.os[2] + s * g.os[3] + d] = __float2bfloat16_rn(t);
+    }
+  }
+  // a warp that gave up may still have copies in flight: wait for them (bounded) so nothing
+  // lands in shared memory after the block has exited
+  if (lane == 0) {
+    if (in_k) for (int i = 0; i < (1 << 20); ++i) if (mbar_try_wait(bar_k, ph_k)) break;
+    if (in_v) for (int i = 0; i < (1 << 20); ++i) if (mbar_try_wait(bar_v, ph_v)) break;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < rows * T; i += NWARPS * 32) {
-    const int r = i >> 6, d = i & 63;
-    float t = 0.f;
-#pragma unroll
-    for (int wv = 0; wv < NWARPS; ++wv) t += part[(wv * R + r) * T + d];
-    const int gi = r / g.S, s = r % g.S;
-    p.out[n * g.os[0] + j * g.os[1] + (hk * g.G + gi) * g.os[2] + s * g.os[3] + d] = __float2bfloat16_rn(t);
-  }
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
 }
 
 template <int R>
 int launch_decode_r(const DecParams& p, int blocks, cudaStream_t stream) {
-  const size_t smem = NWARPS * 2 * TILE_BYTES + R * T * sizeof(float) + 256 + 1024;
+  const size_t smem = NWARPS * 2 * TILE_BYTES + 2 * (1 + NWARPS) * R * T * sizeof(float) + 256 + 1024;
   GCA_CUDA_CHECK(cudaFuncSetAttribute(decode_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  decode_kernel<R><<<(unsigned)blocks, NWARPS * 32, smem, stream>>>(p);
+  int dev = 0, sms = 0;
+  GCA_CUDA_CHECK(cudaGetDevice(&dev));
+  GCA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  decode_kernel<R><<<(unsigned)(blocks < sms ? blocks : sms), NWARPS * 32, smem, stream>>>(p);
   return (int)cudaGetLastError();
 }
 

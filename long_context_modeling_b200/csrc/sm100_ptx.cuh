@@ -34,6 +34,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       "{\n\t.reg .pred p;\n\t"
 #ifdef GCA_WAIT_HINT_NS
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+#elif defined(GCA_TEST_WAIT)
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
 #else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
 #endif
