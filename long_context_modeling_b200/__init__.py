@@ -8,4 +8,4 @@ from .retrieval import (lmk_score_topk, merge_topk, retrieve, perform_batch_retr
                         decode_retrieval, differentiable_weights, Retrieval)
 from .chunk_cache import ChunkKVManager  # noqa: F401
 from .host_pipeline import HostGcaPipeline  # noqa: F401
-from .modules import TritonGroupCrossAttention, preprocess_chunk_kv_cache  # noqa: F401
+from .modules import TritonGroupCrossAttention, GroupCrossAttention, preprocess_chunk_kv_cache  # noqa: F401

@@ -1,6 +1,8 @@
 """The GCA sub-layer as an ``nn.Module``: mirror of ``TritonGroupCrossAttention``
 (``model/DRT.py:304-398``) with the same parameter names (``pre_norm``, ``q_proj``,
-``o_proj``) so reference checkpoints load.
+``o_proj``) so reference checkpoints load; and of ``GroupCrossAttention``
+(``model/DRT.py:235-302``), the variant the reference runs through flash-attn when
+``_triton_gca`` is off, on the same kernels.
 
 ``forward`` keeps the reference's argument meaning (pre-gathered chunks).  ``forward_indexed``
 is the fast path: the query is handed to the kernel as a strided view of the projection
@@ -123,3 +125,39 @@ class TritonGroupCrossAttention(nn.Module):
         vals = vals.permute(0, 1, 3, 2, 4).reshape(n, -1, self.hidden_size)
         o = self.o_proj(vals)
         return self._pad_first_chunk(hidden_states, o) if chunk_size > 1 else o
+
+
+class GroupCrossAttention(TritonGroupCrossAttention):
+    """Mirror of the reference's non-Triton ``GroupCrossAttention`` (``model/DRT.py:235-302``):
+    same parameters, but the retrieved chunks arrive as (N*D'*K, S, h, d) -- the layout
+    ``flash_attn_func`` wants -- and ``sm_n`` does not exist.  The reference expands the query
+    K-fold, runs K independent attentions and merges them with an einsum; here the same tensors
+    are handed to the GCA kernels as strided views (no expansion, no copy)."""
+
+    def __init__(self, hidden_size: int, num_heads: int, enc_chunk_size: int = 63, chunk_topk: int = 8,
+                 rms_norm_eps: float = 1e-5, attention_bias: bool = False):
+        super().__init__(hidden_size, num_heads, enc_chunk_size, chunk_topk, rms_norm_eps, attention_bias, False)
+
+    @classmethod
+    def from_config(cls, config):
+        return cls(config.hidden_size, config.num_attention_heads, config.enc_chunk_size,
+                   getattr(config, "chunk_topk", 8), getattr(config, "rms_norm_eps", 1e-5),
+                   getattr(config, "attention_bias", False))
+
+    @staticmethod
+    def preprocess_chunk_kv_cache(chunk_k: torch.Tensor, chunk_v: torch.Tensor, weights: torch.Tensor, num_heads: int):
+        """``model/DRT.py:247-256``: chunk_k/v (N, D*K, S, h*d) -> (N*D*K, S, h, d) views; weights unchanged."""
+        n, dk, s, hd = chunk_k.shape
+        return (chunk_k.reshape(n * dk, s, num_heads, hd // num_heads),
+                chunk_v.reshape(n * dk, s, num_heads, hd // num_heads), weights)
+
+    def forward(self, hidden_states: torch.Tensor, chunk_k: torch.Tensor, chunk_v: torch.Tensor,
+                weights: torch.Tensor) -> torch.Tensor:
+        """hidden_states (N, D, S, dim); chunk_k/v (N*D'*K, S, h, d); weights (N, D', K)."""
+        if weights.shape[1] * weights.shape[2] == 0:
+            return self._zeros(hidden_states)
+        n, dprime, kk = weights.shape
+        s, h, d = chunk_k.shape[1:]
+        k5 = chunk_k.view(n * dprime, kk, s, h, d).permute(0, 3, 1, 2, 4)      # (Z, h, K, S, d) view
+        v5 = chunk_v.view(n * dprime, kk, s, h, d).permute(0, 3, 1, 2, 4)
+        return super().forward(hidden_states, k5, v5, weights.reshape(n * dprime, kk))

@@ -301,6 +301,39 @@ def test_module_drop_in_matches_indexed_path(lcm):
         assert rel(a, b) <= 2e-2
 
 
+def test_flash_layout_module_matches_triton_layout_module(lcm):
+    """GroupCrossAttention (the reference's flash-attn variant: chunks as (N*D*K, S, h, d), weights
+    (N, D, K), model/DRT.py:235-302) gives the bits of TritonGroupCrossAttention on the same
+    parameters and data, forward and backward."""
+    torch.manual_seed(1)
+    n, c, h, k, dim = 2, 5, 2, 4, 128
+    a_mod = lcm.TritonGroupCrossAttention(dim, h, 63, k).cuda().bfloat16()
+    b_mod = lcm.GroupCrossAttention(dim, h, 63, k).cuda().bfloat16()
+    b_mod.load_state_dict(a_mod.state_dict())
+    g = torch.Generator().manual_seed(17)
+    hidden = torch.randn(n, c, 64, dim, generator=g).bfloat16().cuda()
+    kc = torch.randn(n, c, 64, dim, generator=g).bfloat16().cuda()
+    vc = torch.randn(n, c, 64, dim, generator=g).bfloat16().cuda()
+    idx, scores = cases.causal_indices(g, n, c, k)
+    w = torch.nan_to_num(torch.softmax(scores, -1), nan=0.0).cuda()
+    safe = idx.clamp(min=0).cuda()                                    # padding slots carry weight 0
+    gathered_k = torch.stack([kc[b][safe[b].reshape(-1)] for b in range(n)])      # (N, D'*K, S, dim)
+    gathered_v = torch.stack([vc[b][safe[b].reshape(-1)] for b in range(n)])
+    tk, tv, tw = a_mod.preprocess_chunk_kv_cache(gathered_k, gathered_v, w, h)
+    fk, fv, fw = b_mod.preprocess_chunk_kv_cache(gathered_k, gathered_v, w, h)
+    assert fk.shape == (n * (c - 1) * k, 64, h, dim // h) and fw.shape == w.shape
+    outs = []
+    for mod, args in ((a_mod, (tk, tv, tw)), (b_mod, (fk, fv, fw))):
+        mod.zero_grad()
+        hs = hidden.clone().requires_grad_()
+        o = mod(hs, *args)
+        o.float().square().sum().backward()
+        outs.append((o, hs.grad, mod.q_proj.weight.grad.clone()))
+    for x, y in zip(*outs):
+        assert torch.equal(x, y)
+    assert outs[0][0].shape == (n, c * 64, dim)
+
+
 def test_full_size_config_properties(lcm):
     """BASELINE sweep point 16K tokens, B*H = 96, K = 8 (too large for the CPU oracle as a
     whole): size-independent properties + a sample of units against the oracle."""
