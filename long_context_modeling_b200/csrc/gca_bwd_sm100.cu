@@ -133,6 +133,7 @@ struct BwdQParams {
   long long dqs[4];
   int units;
   int N, J, Hq, Hkv, G, K, C, HP;
+  int wide_store;           // dq rows are 32-byte aligned: 256-bit stores
   float c2, sm_scale;
 };
 
@@ -280,7 +281,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
   bool ok = true;
   uint32_t epi = 0;                             // units this group has written out
   PhaseTimer pf;
-  pf.init(p.prof != nullptr && blockIdx.x == 0 && wg == 0 && elected);
+  pf.init(false);
   int next_idx = q_load_row(p, c.u, c.outer, lane);
   float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.outer * p.K + lane] : 0.f;
   for (; c.u < p.units && ok; c.advance()) {
@@ -376,7 +377,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&bars[DQ_EMPTY + ub]);
-      if (live) store_row_bf16(dq_row, acc, p.sm_scale);
+      if (live) store_row_bf16(dq_row, acc, p.sm_scale, p.wide_store);
       pf.lap(6);
     }
   }
@@ -454,6 +455,7 @@ struct BwdKvParams {
   long long dks[4], dvs[4];
   int units;
   int N, J, Hq, Hkv, G, K, C, HP;
+  int wide_store;           // dk / dv rows are 32-byte aligned: 256-bit stores
   float c2, sm_scale;
 };
 
@@ -490,6 +492,7 @@ __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars,
         ok = mbar_wait_bounded(&bars[QDO_EMPTY + ring.st], ring.ph ^ 1, abort_flag);
         if (!ok) break;
         uint8_t* dst = smem + OFF_QDO + ring.st * 2 * PAIR_BYTES;
+        GCA_TRACE_BUF(p.prof, 0, issued);
         mbar_arrive_expect_tx(&bars[QDO_FULL + ring.st], 2 * PAIR_BYTES);
         if (p.G == 1) {
           tma_load_5d(dst, &p.tm_q2, &bars[QDO_FULL + ring.st], 0, 0, hk0, j, n);
@@ -541,17 +544,21 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       const uint64_t stage = ring.st * 2 * PAIR16;
       if (ROLE != 2) {
         ok = mbar_wait_warp(&bars[QDO_FULL + ring.st], ring.ph, abort_flag, lane);
+        if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 1, g);
         if (ok) ok = mbar_wait_warp(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag, lane);
         if (!ok) break;
+        if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 2, g);
         tc_fence_after();
         const uint64_t kd = dKV + kb * 2 * PAIR16;
         if (ROLE == 0) mma4(tmem_base + COL_S, dQDO + stage, kd, IDESC_KK, STEP_K, STEP_K, false);
         else mma4(tmem_base + COL_DP, dQDO + stage + PAIR16, kd + PAIR16, IDESC_KK, STEP_K, STEP_K, false);
         umma_commit_elect(&bars[SP_FULL + (g & 1)]);
+        if (lane == 0) GCA_TRACE_BUF(p.prof, 3 + ROLE, g);
       } else {
         const uint32_t sb = g & 1;
         ok = mbar_wait_warp(&bars[PDS_FULL + sb], (g >> 1) & 1, abort_flag, lane);
         if (!ok) break;
+        if (lane == 0) GCA_TRACE_BUF(p.prof, 5, g);
         tc_fence_after();
         const uint64_t pd = dPDSmn + sb * 2 * PAIR16;
         // dV += (w P)^T dO : A = Pw read transposed (MN-major), B = dO (MN-major)
@@ -561,6 +568,7 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         umma_commit_elect(&bars[PDS_EMPTY + sb]);
         umma_commit_elect(&bars[QDO_EMPTY + ring.st]);   // Q / dO of this iteration are free once dV, dK are done
         if (i == niter - 1) umma_commit_elect(&bars[ACC_FULL + sb]);   // written out by the last iteration's worker group
+        if (lane == 0) GCA_TRACE_BUF(p.prof, 6, g);
       }
       ring.next();
     }
@@ -581,7 +589,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
   bool ok = true;
   uint32_t epi = 0;                             // units this group has written out
   PhaseTimer pf;
-  pf.init(p.prof != nullptr && blockIdx.x == 0 && wg == 0 && elected);
+  pf.init(false);
   int nbeg = c.u < p.units ? p.offsets[c.outer] : 0, nend = c.u < p.units ? p.offsets[c.outer + 1] : 0;
   for (; c.u < p.units && ok; c.advance()) {
     const int beg = nbeg, end = nend;
@@ -627,6 +635,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         ok = mbar_wait_bounded(&bars[SP_FULL + sb], (g >> 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
         pf.lap(0);
+        if (elected) GCA_TRACE_BUF(p.prof, 7, g);
         if (elected && last) mbar_arrive(&bars[KV_EMPTY + kb]);     // the unit's K/V tiles are no longer needed
         tc_fence_after();
         uint32_t s[64], dp[64];
@@ -638,6 +647,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         tc_fence_before();
         mbar_arrive(&bars[SP_EMPTY]);
         pf.lap(1);
+        if (elected) GCA_TRACE_BUF(p.prof, 8, g);
         ok = mbar_wait_bounded(&bars[PDS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
         pf.lap(2);
@@ -646,6 +656,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         fence_proxy_async_smem();
         mbar_arrive(&bars[PDS_FULL + sb]);
         pf.lap(3);
+        if (elected) GCA_TRACE_BUF(p.prof, 9, g);
       }
     }
     if (!ok) break;
@@ -656,17 +667,20 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(5);
       tc_fence_after();
-      uint32_t acc[64];
+      // both accumulators into registers first, so that the next unit's gradient MMAs (which wait
+      // for ACC_EMPTY) are not held up by this unit's global stores
+      uint32_t acc[64], acc2[64];
       tmem_ld_32x32b_x32(tlane + COL_DK + coff, acc);
       tmem_ld_32x32b_x32(tlane + COL_DK + coff + 32, acc + 32);
-      tmem_ld_wait();
-      if (live) store_row_bf16(dk_row, acc, p.sm_scale);
-      tmem_ld_32x32b_x32(tlane + COL_DV + coff, acc);
-      tmem_ld_32x32b_x32(tlane + COL_DV + coff + 32, acc + 32);
+      tmem_ld_32x32b_x32(tlane + COL_DV + coff, acc2);
+      tmem_ld_32x32b_x32(tlane + COL_DV + coff + 32, acc2 + 32);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&bars[ACC_EMPTY]);
-      if (live) store_row_bf16(dv_row, acc, 1.0f);
+      if (live) {
+        store_row_bf16(dk_row, acc, p.sm_scale, p.wide_store);
+        store_row_bf16(dv_row, acc2, 1.0f, p.wide_store);
+      }
       pf.lap(6);
     }
   }
@@ -719,6 +733,14 @@ bwd_kv_tc_kernel(const __grid_constant__ BwdKvParams p) {
 
 bool bwd_tc_available() { return true; }
 
+// every 64-element bf16 row of the tensor starts on a 32-byte boundary
+static bool rows_32b_aligned(const void* base, const int64_t* stride) {
+  if (reinterpret_cast<uintptr_t>(base) & 31u) return false;
+  for (int i = 0; i < 4; ++i)
+    if (stride[i] % 16 != 0) return false;
+  return true;
+}
+
 int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream, unsigned stages) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;
   int dev = 0, sms = 0;
@@ -748,6 +770,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
     if (units >= (1ll << 31) - 65536) return GCA_ERR_TOO_LARGE;
     p.units = (int)units;
     p.c2 = c2; p.sm_scale = a.sm_scale;
+    p.wide_store = rows_32b_aligned(a.dk_cache, a.dk_stride) && rows_32b_aligned(a.dv_cache, a.dv_stride);
     if (p.units > 0) {
       GCA_CUDA_CHECK(cudaFuncSetAttribute(bwd_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kv::SMEM_BYTES));
       const unsigned grid = (unsigned)(p.units < sms ? p.units : sms);
@@ -771,6 +794,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
     if (units >= (1ll << 31) - 65536) return GCA_ERR_TOO_LARGE;
     p.units = (int)units;
     p.c2 = c2; p.sm_scale = a.sm_scale;
+    p.wide_store = rows_32b_aligned(a.dq, a.dq_stride);
     if (p.units > 0) {
       GCA_CUDA_CHECK(cudaFuncSetAttribute(bwd_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, qk::SMEM_BYTES));
       const unsigned grid = (unsigned)(p.units < sms ? p.units : sms);

@@ -86,6 +86,7 @@ struct FwdTcParams {
   int N, J, Hq, Hkv, G, K, C, HP;
   int pair;                 // 1: a unit is a pair of q heads; 0: a single head (debug knob)
   int dbg;                  // profile builds only: bit mask of work to skip (timing experiments)
+  int wide_store;           // every output row is 32-byte aligned: 256-bit stores
   float c2;
   float off_by_one;
 };
@@ -412,14 +413,18 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
       tc_fence_before();
       mbar_arrive_warp(&bars[O_EMPTY], lane);
       if (live) {
+        uint32_t wv[32];
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-          uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(o[8 * cc + 0]), __uint_as_float(o[8 * cc + 1]));
-          v.y = pack_bf16x2(__uint_as_float(o[8 * cc + 2]), __uint_as_float(o[8 * cc + 3]));
-          v.z = pack_bf16x2(__uint_as_float(o[8 * cc + 4]), __uint_as_float(o[8 * cc + 5]));
-          v.w = pack_bf16x2(__uint_as_float(o[8 * cc + 6]), __uint_as_float(o[8 * cc + 7]));
-          reinterpret_cast<uint4*>(orow)[cc] = v;
+        for (int cc = 0; cc < 32; ++cc) wv[cc] = pack_bf16x2(__uint_as_float(o[2 * cc]), __uint_as_float(o[2 * cc + 1]));
+        if (p.wide_store) {                 // full 32-byte sectors instead of eight 16-byte halves
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc)
+            st_global_256(reinterpret_cast<uint8_t*>(orow) + 32 * cc, wv[8 * cc], wv[8 * cc + 1], wv[8 * cc + 2],
+                          wv[8 * cc + 3], wv[8 * cc + 4], wv[8 * cc + 5], wv[8 * cc + 6], wv[8 * cc + 7]);
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc)
+            reinterpret_cast<uint4*>(orow)[cc] = make_uint4(wv[4 * cc], wv[4 * cc + 1], wv[4 * cc + 2], wv[4 * cc + 3]);
         }
       }
     }
@@ -500,6 +505,8 @@ int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream) {
   p.c2 = a.sm_scale * GCA_LOG2E;
   p.off_by_one = a.off_by_one;
   p.prof = g_profile_buffer;
+  p.wide_store = (reinterpret_cast<uintptr_t>(a.out) & 31u) == 0;
+  for (int i = 0; i < 4; ++i) p.wide_store = p.wide_store && (a.o_stride[i] % 16 == 0);
   if (p.units == 0) return 0;
   int dev = 0, sms = 0;
   GCA_CUDA_CHECK(cudaGetDevice(&dev));

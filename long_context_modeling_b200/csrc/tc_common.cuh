@@ -34,6 +34,12 @@ struct Ring {
 
 // Debug profiling (compiled in only with -DGCA_PROFILE): cycles per phase of one lane.
 #ifdef GCA_PROFILE
+// Event trace of block 0 (debug builds only): buf[64 + event * 256 + slot] = clock at the event.
+#define GCA_TRACE_BUF(buf, ev, slot) do { if ((buf) != nullptr && blockIdx.x == 0 && (uint32_t)(slot) < 256u) (buf)[64 + (ev) * 256 + (slot)] = clock64(); } while (0)
+#else
+#define GCA_TRACE_BUF(buf, ev, slot) do { } while (0)
+#endif
+#ifdef GCA_PROFILE
 struct PhaseTimer {
   long long acc[12];
   long long t;
@@ -59,14 +65,24 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 __device__ __forceinline__ float2 f2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
 
 // 64 float32 accumulator values of one row -> bf16 (scaled) -> 128 contiguous bytes in global
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_t* acc, float scale) {
+// One accumulator row (64 float32 in `acc`) -> scaled bf16 -> 128 contiguous bytes at dst.
+// `wide`: dst is 32-byte aligned (checked on the host for the whole tensor).
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_t* acc, float scale, bool wide) {
   const float2 sv = make_float2(scale, scale);
+  uint32_t w[32];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const float2 a = __fmul2_rn(f2(acc[8 * c + 0], acc[8 * c + 1]), sv), b = __fmul2_rn(f2(acc[8 * c + 2], acc[8 * c + 3]), sv);
-    const float2 cc = __fmul2_rn(f2(acc[8 * c + 4], acc[8 * c + 5]), sv), d = __fmul2_rn(f2(acc[8 * c + 6], acc[8 * c + 7]), sv);
-    reinterpret_cast<uint4*>(dst)[c] = make_uint4(sm100::pack_bf16x2(a.x, a.y), sm100::pack_bf16x2(b.x, b.y),
-                                                  sm100::pack_bf16x2(cc.x, cc.y), sm100::pack_bf16x2(d.x, d.y));
+  for (int c = 0; c < 32; ++c) {
+    const float2 a = __fmul2_rn(f2(acc[2 * c], acc[2 * c + 1]), sv);
+    w[c] = sm100::pack_bf16x2(a.x, a.y);
+  }
+  if (wide) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      sm100::st_global_256(reinterpret_cast<uint8_t*>(dst) + 32 * c, w[8 * c], w[8 * c + 1], w[8 * c + 2], w[8 * c + 3],
+                    w[8 * c + 4], w[8 * c + 5], w[8 * c + 6], w[8 * c + 7]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(dst)[c] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
   }
 }
 
