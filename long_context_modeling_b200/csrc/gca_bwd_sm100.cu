@@ -45,7 +45,19 @@ constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
 constexpr int NTHREADS = 384;
 constexpr int PROD_WARP = 8, ISSUE_S = 9, ISSUE_DP = 10;   // warp 11: gradient-product issuer
 constexpr int TMEM_COLS = 512;
-constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC = 256;
+// TMEM columns.  S and dP are computed per head with 64-row MMAs: a 64-row accumulator uses lanes
+// 0-15 of every 32-lane quarter, so head A's tile and head B's tile (written at lane offset 16)
+// share the same 64 columns.  One S/dP buffer = 128 columns (S at +0, dP at +64) and there are two
+// of them: iteration g+1's S and dP are computed while the workers still read iteration g's.
+// The gradient accumulators keep the stacked 128-row form (one instruction for both heads).
+constexpr uint32_t COL_SP = 0, SP_COLS = 128, COL_DPOFF = 64, COL_ACC = 256;
+// The q-major kernel keeps S and dP as single stacked 128-row tiles (measured faster there: its
+// iterations are bound by the K ring, not by the S/dP turnaround, and the 64-row form doubles
+// the S/dP instruction count).
+constexpr uint32_t QCOL_S = 0, QCOL_DP = 128;
+constexpr uint32_t TILE16 = TILE_BYTES >> 4;
+constexpr uint32_t LANE16 = 16u << 16;            // TMEM lane offset of head B's 64-row tile
+constexpr uint32_t IDESC_64 = umma_idesc_bf16(64, 64, 0, 0);
 
 // Four K steps of one stacked product.  a_step / b_step: descriptor advance per K step of 16.
 // Called by ALL lanes of the issuing warp (converged, warp-uniform operands); elect.sync picks
@@ -56,6 +68,17 @@ __device__ __forceinline__ void mma4(uint32_t d, uint64_t a, uint64_t b, uint32_
                                      bool accumulate_first) {
 #pragma unroll
   for (int kk = 0; kk < 4; ++kk) umma_bf16_ss_elect(d, a + kk * a_step, b + kk * b_step, idesc, (uint32_t)(accumulate_first || kk > 0));
+}
+
+// S or dP of both heads of a pair as two 64-row products (tile tl: A rows a + tl tile, B rows
+// b + tl * b_tile_step tile), each four K steps, into the same 64 columns.
+__device__ __forceinline__ void mma_pair64(uint32_t d, uint64_t a, uint64_t b, uint32_t b_tile_step) {
+#pragma unroll
+  for (int tl = 0; tl < 2; ++tl)
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+      umma_bf16_ss_elect(d + (tl ? LANE16 : 0u), a + tl * TILE16 + kk * STEP_K, b + tl * b_tile_step + kk * STEP_K, IDESC_64,
+                         (uint32_t)(kk > 0));
 }
 
 // One thread, one query row.  s: raw scores (overwritten by P), dp: raw dP.  Writes dS
@@ -245,8 +268,8 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
         tc_fence_after();
         const uint32_t idesc = umma_idesc_bf16(128, ncol, 0, 0);
         const uint64_t q = dQDO + ub * 2 * PAIR16;
-        if (ROLE == 0) mma4(tmem_base + COL_S, q, dK + ring.st * PAIR16, idesc, STEP_K, STEP_K, false);
-        else mma4(tmem_base + COL_DP, q + PAIR16, dV + ring.st * PAIR16, idesc, STEP_K, STEP_K, false);
+        if (ROLE == 0) mma4(tmem_base + QCOL_S, q, dK + ring.st * PAIR16, idesc, STEP_K, STEP_K, false);
+        else mma4(tmem_base + QCOL_DP, q + PAIR16, dV + ring.st * PAIR16, idesc, STEP_K, STEP_K, false);
         umma_commit_elect(&bars[SP_FULL + (g & 1)]);    // the barrier expects both the S and the dP commit
       } else {
         const uint32_t sb = g & 1;
@@ -341,10 +364,10 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       }
       tc_fence_after();
       uint32_t s[64], dp[64];
-      tmem_ld_32x32b_x32(tlane + COL_S + coff, s);
-      tmem_ld_32x32b_x32(tlane + COL_S + coff + 32, s + 32);
-      tmem_ld_32x32b_x32(tlane + COL_DP + coff, dp);
-      tmem_ld_32x32b_x32(tlane + COL_DP + coff + 32, dp + 32);
+      tmem_ld_32x32b_x32(tlane + QCOL_S + coff, s);
+      tmem_ld_32x32b_x32(tlane + QCOL_S + coff + 32, s + 32);
+      tmem_ld_32x32b_x32(tlane + QCOL_DP + coff, dp);
+      tmem_ld_32x32b_x32(tlane + QCOL_DP + coff + 32, dp + 32);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&bars[SP_EMPTY]);
@@ -437,7 +460,7 @@ constexpr int OFF_PDS = OFF_QDO + NQ * 2 * PAIR_BYTES;       // [2 bufs][Pw pair
 constexpr int OFF_BAR = OFF_PDS + 2 * 2 * PAIR_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
 enum Bar { KV_FULL = 0, KV_EMPTY = 2, QDO_FULL = 4, QDO_EMPTY = QDO_FULL + NQ, SP_FULL = QDO_EMPTY + NQ,
-           SP_EMPTY = SP_FULL + 2, PDS_FULL = SP_EMPTY + 1, PDS_EMPTY = PDS_FULL + 2, ACC_FULL = PDS_EMPTY + 2,
+           SP_EMPTY = SP_FULL + 2, PDS_FULL = SP_EMPTY + 2, PDS_EMPTY = PDS_FULL + 2, ACC_FULL = PDS_EMPTY + 2,
            ACC_EMPTY = ACC_FULL + 2, NUM_BARS = ACC_EMPTY + 1 };
 constexpr uint32_t COL_DK = 256, COL_DV = 384;
 }  // namespace kv
@@ -524,7 +547,7 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
   const uint64_t dQDO = umma_desc_sw128(smem_u32(smem + OFF_QDO));
   const uint64_t dQDOmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_QDO), TILE_BYTES);
   const uint64_t dPDSmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_PDS), TILE_BYTES);
-  constexpr uint32_t IDESC_KK = umma_idesc_bf16(128, 128, 0, 0), IDESC_MM = umma_idesc_bf16(128, 128, 1, 1);
+  constexpr uint32_t IDESC_MM = umma_idesc_bf16(128, 128, 1, 1);
   PairCursor c;
   c.init(p.HP);
   Ring ring; ring.init(NQ);
@@ -545,14 +568,15 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       if (ROLE != 2) {
         ok = mbar_wait_warp(&bars[QDO_FULL + ring.st], ring.ph, abort_flag, lane);
         if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 1, g);
-        if (ok) ok = mbar_wait_warp(&bars[SP_EMPTY], (g & 1) ^ 1, abort_flag, lane);
+        const uint32_t spb = g & 1;                       // S/dP buffer = worker group of this iteration
+        if (ok) ok = mbar_wait_warp(&bars[SP_EMPTY + spb], ((g >> 1) & 1) ^ 1, abort_flag, lane);
         if (!ok) break;
         if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 2, g);
         tc_fence_after();
         const uint64_t kd = dKV + kb * 2 * PAIR16;
-        if (ROLE == 0) mma4(tmem_base + COL_S, dQDO + stage, kd, IDESC_KK, STEP_K, STEP_K, false);
-        else mma4(tmem_base + COL_DP, dQDO + stage + PAIR16, kd + PAIR16, IDESC_KK, STEP_K, STEP_K, false);
-        umma_commit_elect(&bars[SP_FULL + (g & 1)]);
+        if (ROLE == 0) mma_pair64(tmem_base + COL_SP + spb * SP_COLS, dQDO + stage, kd, TILE16);
+        else mma_pair64(tmem_base + COL_SP + spb * SP_COLS + COL_DPOFF, dQDO + stage + PAIR16, kd + PAIR16, TILE16);
+        umma_commit_elect(&bars[SP_FULL + spb]);
         if (lane == 0) GCA_TRACE_BUF(p.prof, 3 + ROLE, g);
       } else {
         const uint32_t sb = g & 1;
@@ -578,8 +602,12 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
 __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
                           int quad, int lane, uint32_t tmem_base) {
   using namespace kv;
+  // two thread -> (head tile, row) maps: the stacked 128-row accumulators (dK, dV) put head A in
+  // TMEM lanes 0-63; the 64-row S / dP tiles interleave the heads in 16-lane runs
   const int tile = quad >> 1;
   const int row = (quad & 1) * 32 + lane;
+  const int tile_s = lane >> 4;
+  const int row_s = quad * 16 + (lane & 15);
   const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
   const uint32_t coff = (uint32_t)tile * 64u;
   const bool elected = quad == 0 && lane == 0;
@@ -609,7 +637,8 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
     }
     const uint32_t un = ucnt++;
     const uint32_t kb = un & 1;
-    const int hk_safe = live ? hk : 2 * c.inner;
+    if (elected && p.prof != nullptr && blockIdx.x == 0 && un < 256u) p.prof[64 + 14 * 256 + un] = g;
+    const int hk_safe = (2 * c.inner + tile_s < p.Hkv) ? 2 * c.inner + tile_s : 2 * c.inner;   // head of the S / dP row
     bool my_unit = false;                     // this group ran the unit's last iteration: it writes dK, dV
     for (int e = beg; e < end && ok; ++e) {
       float w = 0.f;
@@ -629,7 +658,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         }
         const bool last = (e == end - 1) && (gi == p.G - 1);
         const int h = hk_safe * p.G + gi;
-        const float lse = p.lse[((zj * p.Hq + h) * p.K + k) * 64 + row];
+        const float lse = p.lse[((zj * p.Hq + h) * p.K + k) * 64 + row_s];
         const uint32_t sb = g & 1;
         pf.lap(7);
         ok = mbar_wait_bounded(&bars[SP_FULL + sb], (g >> 1) & 1, abort_flag);
@@ -639,20 +668,21 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         if (elected && last) mbar_arrive(&bars[KV_EMPTY + kb]);     // the unit's K/V tiles are no longer needed
         tc_fence_after();
         uint32_t s[64], dp[64];
-        tmem_ld_32x32b_x32(tlane + COL_S + coff, s);
-        tmem_ld_32x32b_x32(tlane + COL_S + coff + 32, s + 32);
-        tmem_ld_32x32b_x32(tlane + COL_DP + coff, dp);
-        tmem_ld_32x32b_x32(tlane + COL_DP + coff + 32, dp + 32);
+        const uint32_t tsp = tlane + COL_SP + sb * SP_COLS;      // this group's S/dP buffer
+        tmem_ld_32x32b_x32(tsp, s);
+        tmem_ld_32x32b_x32(tsp + 32, s + 32);
+        tmem_ld_32x32b_x32(tsp + COL_DPOFF, dp);
+        tmem_ld_32x32b_x32(tsp + COL_DPOFF + 32, dp + 32);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(&bars[SP_EMPTY]);
+        mbar_arrive(&bars[SP_EMPTY + sb]);
         pf.lap(1);
         if (elected) GCA_TRACE_BUF(p.prof, 8, g);
         ok = mbar_wait_bounded(&bars[PDS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
         pf.lap(2);
-        uint8_t* base = smem + OFF_PDS + sb * 2 * PAIR_BYTES + tile * TILE_BYTES + row * 128;
-        row_backward(s, dp, lse, p.c2, w, base, base + PAIR_BYTES, row);
+        uint8_t* base = smem + OFF_PDS + sb * 2 * PAIR_BYTES + tile_s * TILE_BYTES + row_s * 128;
+        row_backward(s, dp, lse, p.c2, w, base, base + PAIR_BYTES, row_s);
         fence_proxy_async_smem();
         mbar_arrive(&bars[PDS_FULL + sb]);
         pf.lap(3);
@@ -662,6 +692,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
     if (!ok) break;
     if (my_unit) {
       pf.lap(7);
+      if (elected) GCA_TRACE_BUF(p.prof, 10, un);
       ok = mbar_wait_bounded(&bars[ACC_FULL + wg], epi & 1, abort_flag);
       ++epi;
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
@@ -669,6 +700,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       tc_fence_after();
       // both accumulators into registers first, so that the next unit's gradient MMAs (which wait
       // for ACC_EMPTY) are not held up by this unit's global stores
+      if (elected) GCA_TRACE_BUF(p.prof, 11, un);
       uint32_t acc[64], acc2[64];
       tmem_ld_32x32b_x32(tlane + COL_DK + coff, acc);
       tmem_ld_32x32b_x32(tlane + COL_DK + coff + 32, acc + 32);
@@ -677,10 +709,12 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&bars[ACC_EMPTY]);
+      if (elected) GCA_TRACE_BUF(p.prof, 12, un);
       if (live) {
         store_row_bf16(dk_row, acc, p.sm_scale, p.wide_store);
         store_row_bf16(dv_row, acc2, 1.0f, p.wide_store);
       }
+      if (elected) GCA_TRACE_BUF(p.prof, 13, un);
       pf.lap(6);
     }
   }
@@ -701,10 +735,10 @@ bwd_kv_tc_kernel(const __grid_constant__ BwdKvParams p) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[KV_FULL + i], 1); mbar_init(&bars[KV_EMPTY + i], 1);
       mbar_init(&bars[SP_FULL + i], 2);                              // S commit + dP commit
+      mbar_init(&bars[SP_EMPTY + i], 128);
       mbar_init(&bars[PDS_FULL + i], 128); mbar_init(&bars[PDS_EMPTY + i], 1);
       mbar_init(&bars[ACC_FULL + i], 1);
     }
-    mbar_init(&bars[SP_EMPTY], 128);
     mbar_init(&bars[ACC_EMPTY], 128);
     for (int i = 0; i < NQ; ++i) { mbar_init(&bars[QDO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1); }
     *abort_flag = 0;
