@@ -453,9 +453,14 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
 // kv-major kernel: dK, dV
 // =============================================================================================
 namespace kv {
-constexpr int NQ = 3;
-constexpr int OFF_KV = 0;                                    // [2 bufs][K pair | V pair]
-constexpr int OFF_QDO = OFF_KV + 2 * 2 * PAIR_BYTES;         // [NQ][Q pair | dO pair]
+// Shared memory: a Q/dO stage is held from its TMA copy until the iteration's dK/dV products
+// are done (copy latency + S/dP + worker math + gradient MMAs, ~6,000 cycles), so the ring depth
+// (3) sets the iteration rate.  A fourth stage at the price of a single K/V buffer (NQ = 4,
+// NKV = 1) was measured slower (0.96 ms against 0.90 ms): every unit then starts with an exposed
+// K/V copy.
+constexpr int NQ = 3, NKV = 2;
+constexpr int OFF_KV = 0;                                    // [NKV][K pair | V pair]
+constexpr int OFF_QDO = OFF_KV + NKV * 2 * PAIR_BYTES;       // [NQ][Q pair | dO pair]
 constexpr int OFF_PDS = OFF_QDO + NQ * 2 * PAIR_BYTES;       // [2 bufs][Pw pair | dS pair]
 constexpr int OFF_BAR = OFF_PDS + 2 * 2 * PAIR_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
@@ -500,8 +505,8 @@ __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars,
     const bool two = hk0 + 1 < p.Hkv;
     const int n = c.outer / p.C, ch = c.outer - n * p.C;
     {
-      const uint32_t kb = un & 1;
-      ok = mbar_wait_bounded(&bars[KV_EMPTY + kb], ((un >> 1) & 1) ^ 1, abort_flag);
+      const uint32_t kb = un % NKV;
+      ok = mbar_wait_bounded(&bars[KV_EMPTY + kb], ((un / NKV) & 1) ^ 1, abort_flag);
       if (!ok) break;
       uint8_t* base = smem + OFF_KV + kb * 2 * PAIR_BYTES;
       mbar_arrive_expect_tx(&bars[KV_FULL + kb], 2 * PAIR_BYTES);
@@ -534,7 +539,7 @@ __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars,
   }
   if (*abort_flag) {
     drain(bars, QDO_FULL, issued, NQ);
-    drain(bars, KV_FULL, ucnt, 2);
+    drain(bars, KV_FULL, ucnt, NKV);
   }
 }
 
@@ -560,8 +565,8 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
     const int niter = (end - beg) * p.G;
     if (niter == 0) continue;
     const uint32_t un = ucnt++;
-    const uint32_t kb = un & 1;
-    if (ROLE != 2) ok = mbar_wait_warp(&bars[KV_FULL + kb], (un >> 1) & 1, abort_flag, lane);
+    const uint32_t kb = un % NKV;
+    if (ROLE != 2) ok = mbar_wait_warp(&bars[KV_FULL + kb], (un / NKV) & 1, abort_flag, lane);
     else ok = mbar_wait_warp(&bars[ACC_EMPTY], (un & 1) ^ 1, abort_flag, lane);
     for (int i = 0; i < niter && ok; ++i, ++g) {
       const uint64_t stage = ring.st * 2 * PAIR16;
@@ -636,7 +641,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       continue;
     }
     const uint32_t un = ucnt++;
-    const uint32_t kb = un & 1;
+    const uint32_t kb = un % NKV;
     if (elected && p.prof != nullptr && blockIdx.x == 0 && un < 256u) p.prof[64 + 14 * 256 + un] = g;
     const int hk_safe = (2 * c.inner + tile_s < p.Hkv) ? 2 * c.inner + tile_s : 2 * c.inner;   // head of the S / dP row
     bool my_unit = false;                     // this group ran the unit's last iteration: it writes dK, dV
