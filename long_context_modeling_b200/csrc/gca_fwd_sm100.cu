@@ -49,7 +49,7 @@ using namespace sm100;
 
 constexpr int TILE_BYTES = 64 * 64 * 2;
 constexpr int PAIR_BYTES = 2 * TILE_BYTES;
-constexpr int NK = 4, NV = 4;               // ring depths (16 KB per stage each)
+constexpr int NK = 3, NV = 3;               // ring depths (16 KB per stage each) == NWG, see K_EMPTY / V_EMPTY below
 constexpr int NWG = 3;                      // softmax warpgroups
 constexpr int NTHREADS = (4 * NWG + 4) * 32;
 constexpr int KPROD_WARP = 4 * NWG, VPROD_WARP = KPROD_WARP + 1, SMMA_WARP = KPROD_WARP + 2;   // last warp: PV issuer
@@ -64,8 +64,16 @@ constexpr int OFF_BAR = OFF_P + NWG * PAIR_BYTES;
 constexpr int OFF_IDX = OFF_BAR + 512;                // 2 producers x 32 retrieved indices
 constexpr int SMEM_BYTES = OFF_IDX + 256 + 1024;      // + alignment slack
 
-enum Bar { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + NK, V_FULL = K_EMPTY + NK, V_EMPTY = V_FULL + NV,
-           S_FULL = V_EMPTY + NV, S_EMPTY = S_FULL + NWG, P_FULL = S_EMPTY + NWG, P_EMPTY = P_FULL + NWG,
+// With as many ring stages as warpgroups, slot g uses K/V stage g % 3 and S/P buffer g % 3: "S of
+// slot g is done" (S_FULL) is also "K stage g % 3 is free", and "PV of slot g is done" (P_EMPTY)
+// is also "V stage g % 3 is free".  The producers wait on those barriers (second waiter, every
+// phase), which saves the issuing warps one tcgen05.commit per slot each: their instruction
+// stream (2 waits, 4 MMAs, commits: ~1,200 cycles) is what bounds a slot once the softmax
+// warpgroups overlap.
+static_assert(NK == NWG && NV == NWG, "ring stage == S/P buffer index");
+enum Bar { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, V_FULL = K_FULL + NK,
+           S_FULL = V_FULL + NV, S_EMPTY = S_FULL + NWG, P_FULL = S_EMPTY + NWG, P_EMPTY = P_FULL + NWG,
+           K_EMPTY = S_FULL, V_EMPTY = P_EMPTY,
            O_FULL = P_EMPTY + NWG, O_EMPTY = O_FULL + NWG, NUM_BARS = O_EMPTY + 1 };
 // Every barrier has ONE waiting party that waits for each of its phases in turn (a waiter that
 // skipped a phase would mistake an older completion for the one it wants): hence one O_FULL
@@ -215,7 +223,7 @@ template <int MODE>
 __device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
                             uint32_t tmem_base) {
   constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
-  constexpr uint32_t FULL = MODE == 0 ? K_FULL : V_FULL, EMPTY = MODE == 0 ? K_EMPTY : V_EMPTY;
+  constexpr uint32_t FULL = MODE == 0 ? K_FULL : V_FULL;
   constexpr uint32_t DEPTH = MODE == 0 ? NK : NV;
   const uint64_t dA = MODE == 0 ? umma_desc_sw128(smem_u32(smem + OFF_Q)) : umma_desc_sw128(smem_u32(smem + OFF_P));
   const uint64_t dB = MODE == 0 ? umma_desc_sw128(smem_u32(smem + OFF_K))
@@ -252,7 +260,6 @@ __device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars,
       for (int kk = 0; kk < 4; ++kk)
         umma_bf16_ss_elect(dt, a + kk * 2, b + kk * (MODE == 0 ? 2 : 128), idesc, MODE == 0 ? (uint32_t)(kk > 0) : (uint32_t)(i > 0 || kk > 0));
       umma_commit_elect(&bars[(MODE == 0 ? S_FULL : P_EMPTY) + sb]);
-      umma_commit_elect(&bars[EMPTY + st]);
       // the unit's output is written by the warpgroup of its last slot: it has just finished, and
       // its next slot is NWG slots away
       if (i == nv - 1) umma_commit_elect(&bars[MODE == 0 ? Q_EMPTY + ub : O_FULL + sb]);
@@ -448,8 +455,8 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams p) {
     }
     for (int i = 0; i < NWG; ++i) mbar_init(&bars[O_FULL + i], 1);
     mbar_init(&bars[O_EMPTY], 4);
-    for (int i = 0; i < NK; ++i) { mbar_init(&bars[K_FULL + i], 1); mbar_init(&bars[K_EMPTY + i], 1); }
-    for (int i = 0; i < NV; ++i) { mbar_init(&bars[V_FULL + i], 1); mbar_init(&bars[V_EMPTY + i], 1); }
+    for (int i = 0; i < NK; ++i) mbar_init(&bars[K_FULL + i], 1);
+    for (int i = 0; i < NV; ++i) mbar_init(&bars[V_FULL + i], 1);
     *abort_flag = 0;
     fence_barrier_init();
   }

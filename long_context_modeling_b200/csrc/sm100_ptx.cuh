@@ -48,10 +48,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: gives up after `limit` polls or as soon as *abort_flag is set (by another
 // role that already gave up).  Returns false on give-up; the caller must then unwind.
+// The first probe is the non-blocking test_wait: most waits of the MMA-issuing warps find their
+// barrier already complete, and the potentially-suspending try_wait costs a few hundred cycles
+// even then (measured).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   uint32_t limit = (1u << 22)) {
+#ifndef GCA_NO_FAST_PROBE
+  if (mbar_test_wait(bar, parity)) return true;
+#endif
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
 #ifdef GCA_WAIT_SLEEP_NS
