@@ -71,9 +71,14 @@ constexpr int SMEM_BYTES = OFF_IDX + 256 + 1024;      // + alignment slack
 // stream (2 waits, 4 MMAs, commits: ~1,200 cycles) is what bounds a slot once the softmax
 // warpgroups overlap.
 static_assert(NK == NWG && NV == NWG, "ring stage == S/P buffer index");
+// In the other direction the issuing warps wait on ONE barrier per slot: K_FULL[i] completes when
+// the K tile has landed (producer's expect_tx arrival + bytes) AND the four warps of group i have
+// read the previous S out of buffer i (S_EMPTY is the same barrier; the groups arrive once at
+// start for "the S before the first"); V_FULL[i] likewise when the V tile has landed AND the group
+// has stored P (P_FULL is the same barrier).
 enum Bar { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, V_FULL = K_FULL + NK,
-           S_FULL = V_FULL + NV, S_EMPTY = S_FULL + NWG, P_FULL = S_EMPTY + NWG, P_EMPTY = P_FULL + NWG,
-           K_EMPTY = S_FULL, V_EMPTY = P_EMPTY,
+           S_FULL = V_FULL + NV, P_EMPTY = S_FULL + NWG,
+           K_EMPTY = S_FULL, V_EMPTY = P_EMPTY, S_EMPTY = K_FULL, P_FULL = V_FULL,
            O_FULL = P_EMPTY + NWG, O_EMPTY = O_FULL + NWG, NUM_BARS = O_EMPTY + 1 };
 // Every barrier has ONE waiting party that waits for each of its phases in turn (a waiter that
 // skipped a phase would mistake an older completion for the one it wants): hence one O_FULL
@@ -248,9 +253,8 @@ __device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars,
     else ok = mbar_wait_warp(&bars[O_EMPTY], (un & 1) ^ 1, abort_flag, lane);
     for (int i = 0; i < nv && ok; ++i, ++g) {
       const uint32_t st = g % DEPTH, ph = (g / DEPTH) & 1u;
-      ok = mbar_wait_warp(&bars[FULL + st], ph, abort_flag, lane);
+      ok = mbar_wait_warp(&bars[FULL + st], ph, abort_flag, lane);     // tile landed and S buffer free / P stored
       if (lane == 0) GCA_TRACE(2 + 3 * MODE, g);
-      if (ok) ok = mbar_wait_warp(&bars[(MODE == 0 ? S_EMPTY : P_FULL) + sb], MODE == 0 ? (sph ^ 1u) : sph, abort_flag, lane);
       if (lane == 0) GCA_TRACE(3 + 3 * MODE, g);
       if (!ok) break;
       tc_fence_after();
@@ -291,6 +295,7 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
   bool ok = true;
   int next_idx = load_index_row(p, c.u, c.zj, lane);
   float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.zj * p.K + lane] : 0.f;
+  mbar_arrive_warp(&bars[S_EMPTY + wg], lane);         // "the S before the first has been read"
 
   for (; c.u < p.units && ok; c.advance(p)) {
     const int my_idx = next_idx;
@@ -450,13 +455,12 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams p) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) { mbar_init(&bars[Q_FULL + i], 1); mbar_init(&bars[Q_EMPTY + i], 1); }
     for (int i = 0; i < NWG; ++i) {
-      mbar_init(&bars[S_FULL + i], 1); mbar_init(&bars[S_EMPTY + i], 4);     // counts in warps
-      mbar_init(&bars[P_FULL + i], 4); mbar_init(&bars[P_EMPTY + i], 1);
+      mbar_init(&bars[S_FULL + i], 1); mbar_init(&bars[P_EMPTY + i], 1);
     }
     for (int i = 0; i < NWG; ++i) mbar_init(&bars[O_FULL + i], 1);
     mbar_init(&bars[O_EMPTY], 4);
-    for (int i = 0; i < NK; ++i) mbar_init(&bars[K_FULL + i], 1);
-    for (int i = 0; i < NV; ++i) mbar_init(&bars[V_FULL + i], 1);
+    for (int i = 0; i < NK; ++i) mbar_init(&bars[K_FULL + i], 5);     // producer + the 4 warps of group i
+    for (int i = 0; i < NV; ++i) mbar_init(&bars[V_FULL + i], 5);
     *abort_flag = 0;
     fence_barrier_init();
   }
