@@ -49,40 +49,43 @@ using namespace sm100;
 
 constexpr int TILE_BYTES = 64 * 64 * 2;
 constexpr int PAIR_BYTES = 2 * TILE_BYTES;
-constexpr int NK = 3, NV = 3;               // ring depths (16 KB per stage each) == NWG, see K_EMPTY / V_EMPTY below
-constexpr int NWG = 3;                      // softmax warpgroups
+constexpr int NWG = 3;                      // softmax warpgroups: slot g belongs to group g % 3
+constexpr int NSB = 2;                      // S accumulators in tensor memory: slot g uses g % 2
+constexpr int NRING = 6;                    // K / V ring stages AND barrier sets: slot g uses g % 6 (fixes g % 2 and g % 3)
+constexpr int NK = NRING, NV = NRING;
 constexpr int NTHREADS = (4 * NWG + 4) * 32;
 constexpr int KPROD_WARP = 4 * NWG, VPROD_WARP = KPROD_WARP + 1, SMMA_WARP = KPROD_WARP + 2;   // last warp: PV issuer
-constexpr int TMEM_COLS = 512;              // S0 | S1 | S2 | O, 128 columns each
-constexpr int TMEM_O = NWG * 128;
+// Tensor memory: S0 | S1 | O (128 columns each) | P0 P1 P2 (32 columns each).  P -- the bf16
+// probabilities, one row per lane, two values per column -- is the A operand of the PV product
+// straight from tensor memory: it never goes through shared memory, whose 128 bytes per clock
+// (operand reads of the MMAs + TMA writes) are the kernel's tightest resource.
+constexpr int TMEM_COLS = 512;
+constexpr int TMEM_O = NSB * 128, TMEM_P = TMEM_O + 128;
 
 constexpr int OFF_Q = 0;                              // [2 bufs][A B]
 constexpr int OFF_K = OFF_Q + 2 * PAIR_BYTES;         // [NK][A B]
 constexpr int OFF_V = OFF_K + NK * PAIR_BYTES;        // [NV][A B]
-constexpr int OFF_P = OFF_V + NV * PAIR_BYTES;        // [NWG bufs][A B]
-constexpr int OFF_BAR = OFF_P + NWG * PAIR_BYTES;
+constexpr int OFF_BAR = OFF_V + NV * PAIR_BYTES;
 constexpr int OFF_IDX = OFF_BAR + 512;                // 2 producers x 32 retrieved indices
 constexpr int SMEM_BYTES = OFF_IDX + 256 + 1024;      // + alignment slack
 
-// With as many ring stages as warpgroups, slot g uses K/V stage g % 3 and S/P buffer g % 3: "S of
-// slot g is done" (S_FULL) is also "K stage g % 3 is free", and "PV of slot g is done" (P_EMPTY)
-// is also "V stage g % 3 is free".  The producers wait on those barriers (second waiter, every
-// phase), which saves the issuing warps one tcgen05.commit per slot each: their instruction
-// stream (2 waits, 4 MMAs, commits: ~1,200 cycles) is what bounds a slot once the softmax
-// warpgroups overlap.
-static_assert(NK == NWG && NV == NWG, "ring stage == S/P buffer index");
-// In the other direction the issuing warps wait on ONE barrier per slot: K_FULL[i] completes when
-// the K tile has landed (producer's expect_tx arrival + bytes) AND the four warps of group i have
-// read the previous S out of buffer i (S_EMPTY is the same barrier; the groups arrive once at
-// start for "the S before the first"); V_FULL[i] likewise when the V tile has landed AND the group
-// has stored P (P_FULL is the same barrier).
-enum Bar { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, V_FULL = K_FULL + NK,
-           S_FULL = V_FULL + NV, P_EMPTY = S_FULL + NWG,
-           K_EMPTY = S_FULL, V_EMPTY = P_EMPTY, S_EMPTY = K_FULL, P_FULL = V_FULL,
-           O_FULL = P_EMPTY + NWG, O_EMPTY = O_FULL + NWG, NUM_BARS = O_EMPTY + 1 };
-// Every barrier has ONE waiting party that waits for each of its phases in turn (a waiter that
-// skipped a phase would mistake an older completion for the one it wants): hence one O_FULL
-// barrier per warpgroup although there is a single O accumulator.
+// Barriers, one set per slot number modulo 6:
+//   K_FULL[i]  the K tile of the slot has landed (producer's expect_tx arrival + bytes) AND the S
+//              accumulator the slot will use has been read by the group that used it two slots
+//              earlier (its 4 warps arrive here: "S_EMPTY"); the S issuer's only wait
+//   S_FULL[i]  S of the slot is complete (commit): waited on by the slot's group, and by the K
+//              producer as "stage i is free"
+//   V_FULL[i]  the V tile has landed AND the slot's group has written P ("P_FULL"); the PV
+//              issuer's only wait
+//   P_EMPTY[i] PV of the slot is complete (commit): waited on by the group (before it overwrites
+//              its P region, three slots later) and by the V producer as "stage i is free"
+// Every waiter of a barrier waits for each of its phases in turn (a waiter that skipped a phase
+// would mistake an older completion for the one it wants); hence also one O_FULL barrier per
+// group although there is a single O accumulator.
+enum Bar { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, V_FULL = K_FULL + NRING,
+           S_FULL = V_FULL + NRING, P_EMPTY = S_FULL + NRING,
+           K_EMPTY = S_FULL, V_EMPTY = P_EMPTY,
+           O_FULL = P_EMPTY + NRING, O_EMPTY = O_FULL + NWG, NUM_BARS = O_EMPTY + 1 };
 static_assert(NUM_BARS * 8 + 16 <= 512, "barrier block");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 
@@ -222,21 +225,21 @@ __device__ void producer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bar
 }
 
 // ----------------------------------------------------------------------------- MMA issuers
-// mode 0: S_b = Q K^T;  mode 1: O += P_b V  (b = slot number mod NWG).  All 32 lanes run this
-// code; elect.sync inside the MMA / commit wrappers picks the issuing lane.
+// mode 0: S = Q K^T into accumulator g % 2;  mode 1: O += P V with P (group g % 3's region of
+// tensor memory) as the A operand.  All 32 lanes run this code; elect.sync inside the MMA /
+// commit wrappers picks the issuing lane.
 template <int MODE>
 __device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
                             uint32_t tmem_base) {
   constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
   constexpr uint32_t FULL = MODE == 0 ? K_FULL : V_FULL;
-  constexpr uint32_t DEPTH = MODE == 0 ? NK : NV;
-  const uint64_t dA = MODE == 0 ? umma_desc_sw128(smem_u32(smem + OFF_Q)) : umma_desc_sw128(smem_u32(smem + OFF_P));
+  const uint64_t dQ = umma_desc_sw128(smem_u32(smem + OFF_Q));
   const uint64_t dB = MODE == 0 ? umma_desc_sw128(smem_u32(smem + OFF_K))
                                 : umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_V), TILE_BYTES);
   UnitCursor c;
   c.init(p);
   uint32_t ucnt = 0, g = 0;                   // units with work; running slot number
-  uint32_t sb = 0, sph = 0;                   // S/P buffer (= owning warpgroup) and its phase
+  uint32_t s6 = 0, ph6 = 0;                   // g % 6 and (g / 6) & 1
   bool ok = true;
   int next_idx = load_index_row(p, c.u, c.zj, lane);
   for (; c.u < p.units && ok; c.advance(p)) {
@@ -252,23 +255,31 @@ __device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars,
     if (MODE == 0) ok = mbar_wait_warp(&bars[Q_FULL + ub], (un >> 1) & 1, abort_flag, lane);
     else ok = mbar_wait_warp(&bars[O_EMPTY], (un & 1) ^ 1, abort_flag, lane);
     for (int i = 0; i < nv && ok; ++i, ++g) {
-      const uint32_t st = g % DEPTH, ph = (g / DEPTH) & 1u;
-      ok = mbar_wait_warp(&bars[FULL + st], ph, abort_flag, lane);     // tile landed and S buffer free / P stored
+      ok = mbar_wait_warp(&bars[FULL + s6], ph6, abort_flag, lane);    // tile landed and S accumulator free / P written
       if (lane == 0) GCA_TRACE(2 + 3 * MODE, g);
-      if (lane == 0) GCA_TRACE(3 + 3 * MODE, g);
       if (!ok) break;
       tc_fence_after();
-      const uint64_t a = MODE == 0 ? dA + ub * PAIR16 : dA + sb * PAIR16, b = dB + st * PAIR16;
-      const uint32_t dt = tmem_base + (MODE == 0 ? sb * 128 : TMEM_O);
+      const uint32_t w3 = s6 >= 3 ? s6 - 3 : s6;                       // g % 3: the slot's warpgroup
+      const uint64_t b = dB + s6 * PAIR16;
+      if (MODE == 0) {
+        const uint64_t a = dQ + ub * PAIR16;
+        const uint32_t dt = tmem_base + (s6 & 1u) * 128;
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_bf16_ss_elect(dt, a + kk * 2, b + kk * (MODE == 0 ? 2 : 128), idesc, MODE == 0 ? (uint32_t)(kk > 0) : (uint32_t)(i > 0 || kk > 0));
-      umma_commit_elect(&bars[(MODE == 0 ? S_FULL : P_EMPTY) + sb]);
-      // the unit's output is written by the warpgroup of its last slot: it has just finished, and
-      // its next slot is NWG slots away
-      if (i == nv - 1) umma_commit_elect(&bars[MODE == 0 ? Q_EMPTY + ub : O_FULL + sb]);
+        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss_elect(dt, a + kk * 2, b + kk * 2, idesc, (uint32_t)(kk > 0));
+        umma_commit_elect(&bars[S_FULL + s6]);
+        if (i == nv - 1) umma_commit_elect(&bars[Q_EMPTY + ub]);
+      } else {
+        const uint32_t at = tmem_base + TMEM_P + w3 * 32;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ts_elect(tmem_base + TMEM_O, at + kk * 8, b + kk * 128, idesc, (uint32_t)(i > 0 || kk > 0));
+        umma_commit_elect(&bars[P_EMPTY + s6]);
+        // the unit's output is written by the warpgroup of its last slot: it has just finished, and
+        // its next slot is NWG slots away
+        if (i == nv - 1) umma_commit_elect(&bars[O_FULL + w3]);
+      }
       if (lane == 0) GCA_TRACE(4 + 3 * MODE, g);
-      if (++sb == NWG) { sb = 0; sph ^= 1; }
+      if (++s6 == NRING) { s6 = 0; ph6 ^= 1; }
     }
   }
 }
@@ -286,8 +297,7 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
   const int row = (quad & 1) * 32 + lane;           // query row inside the head
   const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
   const bool elected = quad == 0 && lane == 0;
-  uint8_t* sP = smem + OFF_P + wg * PAIR_BYTES;      // this warpgroup's P buffer
-  const uint32_t tS = tlane + (uint32_t)wg * 128;    // and its S accumulator
+  const uint32_t tP = tlane + TMEM_P + (uint32_t)wg * 32;   // this warpgroup's P region of tensor memory
   UnitCursor c;
   c.init(p);
   uint32_t ucnt = 0, own = 0, epi = 0, g = 0;        // units with work; own slots / outputs done; running slot
@@ -295,7 +305,9 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
   bool ok = true;
   int next_idx = load_index_row(p, c.u, c.zj, lane);
   float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.zj * p.K + lane] : 0.f;
-  mbar_arrive_warp(&bars[S_EMPTY + wg], lane);         // "the S before the first has been read"
+  // slots 0 and 1 find their S accumulators untouched: groups 1 and 2 stand in for the readers of
+  // "slots -2 and -1" (a slot's reader arrives on the barrier set of the slot two later)
+  if (wg >= 1) mbar_arrive_warp(&bars[K_FULL + (wg - 1)], lane);
 
   for (; c.u < p.units && ok; c.advance(p)) {
     const int my_idx = next_idx;
@@ -335,20 +347,24 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
       if (!mine) continue;                           // another warpgroup's slot
       const int k = __ffs(m) - 1;
       const float wk = __shfl_sync(0xffffffffu, my_w, k);
-      const uint32_t oph = own & 1;
+      // this group's slots are g = wg, wg + 3, wg + 6, ...: g % 6 alternates between wg and wg + 3
+      const uint32_t s6 = (uint32_t)wg + 3u * (own & 1u), ph6 = (own >> 1) & 1u;
       const uint32_t gt = g;                         // (trace builds only)
       (void)gt;
-      ++own;
-      ok = mbar_wait_warp(&bars[S_FULL + wg], oph, abort_flag, lane);
+      ok = mbar_wait_warp(&bars[S_FULL + s6], ph6, abort_flag, lane);
       if (!ok) break;
       if (elected) GCA_TRACE(8, gt);
       tc_fence_after();
       uint32_t x[64];
-      tmem_ld_32x32b_x32(tS + coff, x);
-      tmem_ld_32x32b_x32(tS + coff + 32, x + 32);
+      const uint32_t tS = tlane + (s6 & 1u) * 128 + coff;       // accumulator g % 2
+      tmem_ld_32x32b_x32(tS, x);
+      tmem_ld_32x32b_x32(tS + 32, x + 32);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive_warp(&bars[S_EMPTY + wg], lane);
+      {                                              // the accumulator is free for slot g + 2: barrier set (g + 2) % 6
+        const uint32_t n6 = s6 + 2 >= NRING ? s6 + 2 - NRING : s6 + 2;
+        mbar_arrive_warp(&bars[K_FULL + n6], lane);
+      }
       if (elected) GCA_TRACE(9, gt);
 
       // row max: four independent chains of 3-input max
@@ -393,22 +409,31 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
       const float2 fv = make_float2(f, f);
 
       if (elected) GCA_TRACE(10, gt);
-      ok = mbar_wait_warp(&bars[P_EMPTY + wg], oph ^ 1, abort_flag, lane);   // PV of this group's previous slot
-      if (!ok) break;
-      if (elected) GCA_TRACE(11, gt);
-      uint8_t* prow = sP + tile * TILE_BYTES + row * 128;
-      if (!GCA_DBG(2))
-#pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        const float2 q0 = __fmul2_rn(make_float2(__uint_as_float(x[8 * cc + 0]), __uint_as_float(x[8 * cc + 1])), fv);
-        const float2 q1 = __fmul2_rn(make_float2(__uint_as_float(x[8 * cc + 2]), __uint_as_float(x[8 * cc + 3])), fv);
-        const float2 q2 = __fmul2_rn(make_float2(__uint_as_float(x[8 * cc + 4]), __uint_as_float(x[8 * cc + 5])), fv);
-        const float2 q3 = __fmul2_rn(make_float2(__uint_as_float(x[8 * cc + 6]), __uint_as_float(x[8 * cc + 7])), fv);
-        *reinterpret_cast<uint4*>(prow + ((cc ^ (row & 7)) << 4)) =
-            make_uint4(pack_bf16x2(q0.x, q0.y), pack_bf16x2(q1.x, q1.y), pack_bf16x2(q2.x, q2.y), pack_bf16x2(q3.x, q3.y));
+      if (own > 0) {                                 // PV of this group's previous slot (g - 3) has consumed its P
+        const uint32_t p6 = (uint32_t)wg + 3u * ((own - 1) & 1u), pph = ((own - 1) >> 1) & 1u;
+        ok = mbar_wait_warp(&bars[P_EMPTY + p6], pph, abort_flag, lane);
+        if (!ok) break;
       }
-      fence_proxy_async_smem();
-      mbar_arrive_warp(&bars[P_FULL + wg], lane);
+      if (elected) GCA_TRACE(11, gt);
+      // P = (w / l) * exp2(...) in bf16, two per 32-bit column, straight into tensor memory: the
+      // A operand of the PV product
+      uint32_t pk[32];
+#pragma unroll
+      for (int cc = 0; cc < 32; cc += 4) {
+        const float2 q0 = __fmul2_rn(make_float2(__uint_as_float(x[2 * cc + 0]), __uint_as_float(x[2 * cc + 1])), fv);
+        const float2 q1 = __fmul2_rn(make_float2(__uint_as_float(x[2 * cc + 2]), __uint_as_float(x[2 * cc + 3])), fv);
+        const float2 q2 = __fmul2_rn(make_float2(__uint_as_float(x[2 * cc + 4]), __uint_as_float(x[2 * cc + 5])), fv);
+        const float2 q3 = __fmul2_rn(make_float2(__uint_as_float(x[2 * cc + 6]), __uint_as_float(x[2 * cc + 7])), fv);
+        pk[cc + 0] = pack_bf16x2(q0.x, q0.y); pk[cc + 1] = pack_bf16x2(q1.x, q1.y);
+        pk[cc + 2] = pack_bf16x2(q2.x, q2.y); pk[cc + 3] = pack_bf16x2(q3.x, q3.y);
+      }
+      if (!GCA_DBG(2)) {
+        tmem_st_32x32b_x32(tP, pk);
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      mbar_arrive_warp(&bars[V_FULL + s6], lane);    // "P of this slot is written"
+      ++own;
       if (elected) GCA_TRACE(12, gt);
     }
     if (!ok) break;
@@ -454,9 +479,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams p) {
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) { mbar_init(&bars[Q_FULL + i], 1); mbar_init(&bars[Q_EMPTY + i], 1); }
-    for (int i = 0; i < NWG; ++i) {
-      mbar_init(&bars[S_FULL + i], 1); mbar_init(&bars[P_EMPTY + i], 1);
-    }
+    for (int i = 0; i < NRING; ++i) { mbar_init(&bars[S_FULL + i], 1); mbar_init(&bars[P_EMPTY + i], 1); }
     for (int i = 0; i < NWG; ++i) mbar_init(&bars[O_FULL + i], 1);
     mbar_init(&bars[O_EMPTY], 4);
     for (int i = 0; i < NK; ++i) mbar_init(&bars[K_FULL + i], 5);     // producer + the 4 warps of group i
