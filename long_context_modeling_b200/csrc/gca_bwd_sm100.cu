@@ -119,6 +119,40 @@ __device__ __forceinline__ float row_backward(uint32_t* s, const uint32_t* dp, f
   return di;
 }
 
+// Same row, for the q-major kernel: dS stays in registers, packed two keys per word in key order
+// (the layout of an A operand in tensor memory); w*P is not needed there.  ds may alias s.
+__device__ __forceinline__ float row_backward_packed(uint32_t* s, const uint32_t* dp, float lse, float c2, float w,
+                                                     uint32_t* ds) {
+  const float2 c2v = make_float2(c2, c2), nl = make_float2(-lse, -lse);
+  float2 d0 = make_float2(0.f, 0.f), d1 = d0, d2 = d0, d3 = d0;
+#pragma unroll
+  for (int c = 0; c < 64; c += 8) {
+    float2 a0 = __ffma2_rn(f2(s[c + 0], s[c + 1]), c2v, nl), a1 = __ffma2_rn(f2(s[c + 2], s[c + 3]), c2v, nl);
+    float2 a2 = __ffma2_rn(f2(s[c + 4], s[c + 5]), c2v, nl), a3 = __ffma2_rn(f2(s[c + 6], s[c + 7]), c2v, nl);
+    a0.x = ex2_approx(a0.x); a0.y = ex2_approx(a0.y); a1.x = ex2_approx(a1.x); a1.y = ex2_approx(a1.y);
+    a2.x = ex2_approx(a2.x); a2.y = ex2_approx(a2.y); a3.x = ex2_approx(a3.x); a3.y = ex2_approx(a3.y);
+    d0 = __ffma2_rn(a0, f2(dp[c + 0], dp[c + 1]), d0); d1 = __ffma2_rn(a1, f2(dp[c + 2], dp[c + 3]), d1);
+    d2 = __ffma2_rn(a2, f2(dp[c + 4], dp[c + 5]), d2); d3 = __ffma2_rn(a3, f2(dp[c + 6], dp[c + 7]), d3);
+    s[c + 0] = __float_as_uint(a0.x); s[c + 1] = __float_as_uint(a0.y); s[c + 2] = __float_as_uint(a1.x); s[c + 3] = __float_as_uint(a1.y);
+    s[c + 4] = __float_as_uint(a2.x); s[c + 5] = __float_as_uint(a2.y); s[c + 6] = __float_as_uint(a3.x); s[c + 7] = __float_as_uint(a3.y);
+  }
+  const float2 dsum = __fadd2_rn(__fadd2_rn(d0, d1), __fadd2_rn(d2, d3));
+  const float di = dsum.x + dsum.y;
+  const float2 wv = make_float2(w, w), ndi = make_float2(-di, -di);
+#pragma unroll
+  for (int c8 = 0; c8 < 8; ++c8) {
+    const float2 p0 = __fmul2_rn(f2(s[8 * c8 + 0], s[8 * c8 + 1]), wv), p1 = __fmul2_rn(f2(s[8 * c8 + 2], s[8 * c8 + 3]), wv);
+    const float2 p2 = __fmul2_rn(f2(s[8 * c8 + 4], s[8 * c8 + 5]), wv), p3 = __fmul2_rn(f2(s[8 * c8 + 6], s[8 * c8 + 7]), wv);
+    const float2 e0 = __fmul2_rn(p0, __fadd2_rn(f2(dp[8 * c8 + 0], dp[8 * c8 + 1]), ndi));
+    const float2 e1 = __fmul2_rn(p1, __fadd2_rn(f2(dp[8 * c8 + 2], dp[8 * c8 + 3]), ndi));
+    const float2 e2 = __fmul2_rn(p2, __fadd2_rn(f2(dp[8 * c8 + 4], dp[8 * c8 + 5]), ndi));
+    const float2 e3 = __fmul2_rn(p3, __fadd2_rn(f2(dp[8 * c8 + 6], dp[8 * c8 + 7]), ndi));
+    ds[4 * c8 + 0] = pack_bf16x2(e0.x, e0.y); ds[4 * c8 + 1] = pack_bf16x2(e1.x, e1.y);
+    ds[4 * c8 + 2] = pack_bf16x2(e2.x, e2.y); ds[4 * c8 + 3] = pack_bf16x2(e3.x, e3.y);
+  }
+  return di;
+}
+
 __device__ __forceinline__ void drain(uint64_t* bars, int full0, uint32_t issued, int depth) {
   for (uint32_t back = 0; back < (uint32_t)depth && back < issued; ++back) {
     const uint32_t g = issued - 1 - back;
@@ -131,17 +165,22 @@ __device__ __forceinline__ void drain(uint64_t* bars, int full0, uint32_t issued
 // q-major kernel: dQ, dw
 // =============================================================================================
 namespace qk {
-constexpr int NKS = 4, NVS = 3;
+// dS never touches shared memory: the worker that computed a row writes it (bf16, two keys per
+// 32-bit column) into tensor memory, where the dQ product reads it as its A operand.  The 32 KB
+// this frees hold one more K and one more V stage.
+constexpr int NKS = 5, NVS = 4;
 constexpr int OFF_QDO = 0;                                   // [2 bufs][Q pair | dO pair]
 constexpr int OFF_K = OFF_QDO + 2 * 2 * PAIR_BYTES;          // [NKS][K pair]
 constexpr int OFF_V = OFF_K + NKS * PAIR_BYTES;              // [NVS][V pair]
-constexpr int OFF_DS = OFF_V + NVS * PAIR_BYTES;             // [2 bufs][dS pair]
-constexpr int OFF_BAR = OFF_DS + 2 * PAIR_BYTES;
+constexpr int OFF_BAR = OFF_V + NVS * PAIR_BYTES;
 constexpr int OFF_IDX = OFF_BAR + 512;
 constexpr int SMEM_BYTES = OFF_IDX + 256 + 1024;
 enum Bar { QDO_FULL = 0, QDO_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + NKS, V_FULL = K_EMPTY + NKS,
            V_EMPTY = V_FULL + NVS, SP_FULL = V_EMPTY + NVS, SP_EMPTY = SP_FULL + 2, DS_FULL = SP_EMPTY + 1,
-           DS_EMPTY = DS_FULL + 2, DQ_FULL = DS_EMPTY + 2, DQ_EMPTY = DQ_FULL + 2, NUM_BARS = DQ_EMPTY + 2 };
+           DS_EMPTY = DS_FULL + 2, DQ_FULL = DS_EMPTY + 2, DQ_EMPTY = DQ_FULL + 2, NUM_BARS = DQ_EMPTY + 1 };
+// TMEM columns: S | dP | dQ (one accumulator: the group that wrote the unit's last dS copies it
+// to registers and releases it before it stores) | dS of even slots | dS of odd slots
+constexpr uint32_t QCOL_DQ = 256, QCOL_DS = 384, DS_COLS = 32;
 }  // namespace qk
 
 struct BwdQParams {
@@ -241,7 +280,6 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
   const uint64_t dQDO = umma_desc_sw128(smem_u32(smem + OFF_QDO));
   const uint64_t dK = umma_desc_sw128(smem_u32(smem + OFF_K)), dV = umma_desc_sw128(smem_u32(smem + OFF_V));
   const uint64_t dKmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_K), TILE_BYTES);
-  const uint64_t dDS = umma_desc_sw128(smem_u32(smem + OFF_DS));
   PairCursor c;
   c.init(p.HP);
   Ring ring; ring.init(ROLE == 1 ? NVS : NKS);
@@ -259,7 +297,7 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     const uint32_t ub = un & 1, uph = (un >> 1) & 1;
     const int ncol = t.share ? 64 : 128;
     if (ROLE != 2) ok = mbar_wait_warp(&bars[QDO_FULL + ub], uph, abort_flag, lane);
-    else ok = mbar_wait_warp(&bars[DQ_EMPTY + ub], uph ^ 1, abort_flag, lane);
+    else ok = mbar_wait_warp(&bars[DQ_EMPTY], (un & 1) ^ 1, abort_flag, lane);
     for (int i = 0; i < nv && ok; ++i, ++g) {
       if (ROLE != 2) {
         ok = mbar_wait_warp(&bars[(ROLE == 0 ? K_FULL : V_FULL) + ring.st], ring.ph, abort_flag, lane);
@@ -276,9 +314,13 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
         ok = mbar_wait_warp(&bars[DS_FULL + sb], (g >> 1) & 1, abort_flag, lane);
         if (!ok) break;
         tc_fence_after();
-        // dQ += dS K_k : A = dS (K-major), B = K_k (MN-major, both heads' tiles)
-        mma4(tmem_base + COL_ACC + ub * 128, dDS + sb * PAIR16, dKmn + ring.st * PAIR16, umma_idesc_bf16(128, ncol, 0, 1),
-             STEP_K, STEP_MN, i > 0);
+        // dQ += dS K_k : A = dS (tensor memory), B = K_k (MN-major, both heads' tiles)
+        const uint32_t idesc = umma_idesc_bf16(128, ncol, 0, 1);
+        const uint64_t b = dKmn + ring.st * PAIR16;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ts_elect(tmem_base + QCOL_DQ, tmem_base + QCOL_DS + sb * DS_COLS + kk * 8, b + kk * STEP_MN, idesc,
+                             (uint32_t)(i > 0 || kk > 0));
         umma_commit_elect(&bars[DS_EMPTY + sb]);
         umma_commit_elect(&bars[K_EMPTY + ring.st]);     // the K tiles of this slot are free once dQ is done
         // dQ is written out by the worker group of the unit's last slot (it has just finished
@@ -375,9 +417,10 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       ok = mbar_wait_bounded(&bars[DS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(2);
-      uint8_t* ds_row = smem + OFF_DS + sb * PAIR_BYTES + tile * TILE_BYTES + row * 128;
-      float di = row_backward(s, dp, lse, p.c2, w, nullptr, ds_row, row);
-      fence_proxy_async_smem();
+      float di = row_backward_packed(s, dp, lse, p.c2, w, s);
+      tmem_st_32x32b_x32(tlane + QCOL_DS + sb * DS_COLS, s);
+      tmem_st_wait();
+      tc_fence_before();
       mbar_arrive(&bars[DS_FULL + sb]);
       pf.lap(3);
       // dw: sum of Di over the 32 rows this warp holds of its tile -> one partial per warp
@@ -395,11 +438,11 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       pf.lap(5);
       tc_fence_after();
       uint32_t acc[64];
-      tmem_ld_32x32b_x32(tlane + COL_ACC + ub * 128 + coff, acc);
-      tmem_ld_32x32b_x32(tlane + COL_ACC + ub * 128 + coff + 32, acc + 32);
+      tmem_ld_32x32b_x32(tlane + QCOL_DQ + coff, acc);
+      tmem_ld_32x32b_x32(tlane + QCOL_DQ + coff + 32, acc + 32);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&bars[DQ_EMPTY + ub]);
+      mbar_arrive(&bars[DQ_EMPTY]);
       if (live) store_row_bf16(dq_row, acc, p.sm_scale, p.wide_store);
       pf.lap(6);
     }
@@ -422,8 +465,9 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
       mbar_init(&bars[QDO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1);
       mbar_init(&bars[SP_FULL + i], 2);                              // S commit + dP commit
       mbar_init(&bars[DS_FULL + i], 128); mbar_init(&bars[DS_EMPTY + i], 1);
-      mbar_init(&bars[DQ_FULL + i], 1); mbar_init(&bars[DQ_EMPTY + i], 128);
+      mbar_init(&bars[DQ_FULL + i], 1);
     }
+    mbar_init(&bars[DQ_EMPTY], 128);
     mbar_init(&bars[SP_EMPTY], 128);
     for (int i = 0; i < NKS; ++i) { mbar_init(&bars[K_FULL + i], 1); mbar_init(&bars[K_EMPTY + i], 1); }
     for (int i = 0; i < NVS; ++i) { mbar_init(&bars[V_FULL + i], 1); mbar_init(&bars[V_EMPTY + i], 1); }
