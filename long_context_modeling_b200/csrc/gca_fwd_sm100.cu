@@ -49,10 +49,10 @@ using namespace sm100;
 
 constexpr int TILE_BYTES = 64 * 64 * 2;
 constexpr int PAIR_BYTES = 2 * TILE_BYTES;
-constexpr int NWG = 3;                      // softmax warpgroups: slot g belongs to group g % 3
+constexpr int NWG = 3;                      // softmax warpgroups
 constexpr int NSB = 2;                      // S accumulators in tensor memory: slot g uses g % 2
-constexpr int NRING = 6;                    // K / V ring stages AND barrier sets: slot g uses g % 6 (fixes g % 2 and g % 3)
-constexpr int NK = NRING, NV = NRING;
+constexpr int NK = 6, NV = 6;               // K / V ring stages
+constexpr int ND = 4;                       // unit descriptors in flight
 constexpr int NTHREADS = (4 * NWG + 4) * 32;
 constexpr int KPROD_WARP = 4 * NWG, VPROD_WARP = KPROD_WARP + 1, SMMA_WARP = KPROD_WARP + 2;   // last warp: PV issuer
 // Tensor memory: S0 | S1 | O (128 columns each) | P0 P1 P2 (32 columns each).  P -- the bf16
@@ -62,30 +62,53 @@ constexpr int KPROD_WARP = 4 * NWG, VPROD_WARP = KPROD_WARP + 1, SMMA_WARP = KPR
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_O = NSB * 128, TMEM_P = TMEM_O + 128;
 
+// What the other roles need to know about a unit.  The warp that issues the Q / K copies walks
+// the unit list, reads the retrieved indices and weights, does all the index and address
+// arithmetic ONCE and publishes the result here; the other 15 warps only follow descriptors.
+// (Each role used to walk the list itself: ~100 rarely executed, branchy instructions per unit
+// that are never in the instruction cache, ~2,000 cycles per unit on every warpgroup's critical path.)
+struct UnitDesc {
+  uint32_t mask;            // valid slots of the unit
+  uint32_t flags;           // DESC_*; bits 4-5: the warpgroup that writes the unit's output
+  int32_t n, hk0;           // sequence and first kv head: tensor coordinates of the V copies
+  long long lse_off;        // element offset of (unit, head A, slot 0, row 0) in lse
+  long long out_off;        // element offset of (unit, head A, row 0) in out
+  uint32_t own[3];          // the slots of each warpgroup
+  uint32_t g0;              // running number of the unit's first slot (traces)
+};
+constexpr uint32_t DESC_END = 1, DESC_TWO = 2, DESC_SHARE = 4, DESC_EPI_SHIFT = 4;
+static_assert(sizeof(UnitDesc) == 48, "descriptor header");
+// Per slot one byte: bits 0-2 = slot number modulo 6 (ring stage / barrier of the slot; bit 0 is
+// also the S accumulator), bits 3-4 = the slot's warpgroup.
+constexpr int DESC_HDR = 48, DESC_ONE = DESC_HDR + 128 + 128 + 32;
+
 constexpr int OFF_Q = 0;                              // [2 bufs][A B]
 constexpr int OFF_K = OFF_Q + 2 * PAIR_BYTES;         // [NK][A B]
 constexpr int OFF_V = OFF_K + NK * PAIR_BYTES;        // [NV][A B]
 constexpr int OFF_BAR = OFF_V + NV * PAIR_BYTES;
-constexpr int OFF_IDX = OFF_BAR + 512;                // 2 producers x 32 retrieved indices
-constexpr int SMEM_BYTES = OFF_IDX + 256 + 1024;      // + alignment slack
+constexpr int OFF_DESC = OFF_BAR + 512;               // [ND] headers | [ND][32] indices | [ND][32] weights | [ND][32] slot bytes
+constexpr int DESC_BYTES = ND * DESC_ONE;
+static_assert(NK == 6 && NV == 6, "slot bytes carry the slot number modulo 6");
+constexpr int SMEM_BYTES = OFF_DESC + DESC_BYTES + 1024;   // + alignment slack
 
-// Barriers, one set per slot number modulo 6:
-//   K_FULL[i]  the K tile of the slot has landed (producer's expect_tx arrival + bytes) AND the S
-//              accumulator the slot will use has been read by the group that used it two slots
-//              earlier (its 4 warps arrive here: "S_EMPTY"); the S issuer's only wait
-//   S_FULL[i]  S of the slot is complete (commit): waited on by the slot's group, and by the K
-//              producer as "stage i is free"
-//   V_FULL[i]  the V tile has landed AND the slot's group has written P ("P_FULL"); the PV
-//              issuer's only wait
-//   P_EMPTY[i] PV of the slot is complete (commit): waited on by the group (before it overwrites
-//              its P region, three slots later) and by the V producer as "stage i is free"
-// Every waiter of a barrier waits for each of its phases in turn (a waiter that skipped a phase
-// would mistake an older completion for the one it wants); hence also one O_FULL barrier per
-// group although there is a single O accumulator.
-enum Bar { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, V_FULL = K_FULL + NRING,
-           S_FULL = V_FULL + NRING, P_EMPTY = S_FULL + NRING,
-           K_EMPTY = S_FULL, V_EMPTY = P_EMPTY,
-           O_FULL = P_EMPTY + NRING, O_EMPTY = O_FULL + NWG, NUM_BARS = O_EMPTY + 1 };
+// Barriers.
+//   DESC_FULL[d]   descriptor d is written (1 arrival);  DESC_EMPTY[d]: its 15 readers are done
+//   K_FULL[stage]  the slot's K tile has landed (producer's expect_tx arrival + bytes) AND the S
+//                  accumulator the slot will use has been read by the group that had it two slots
+//                  earlier (its 4 warps arrive here); the S issuer's only wait
+//   S_FULL[group]  S of the group's next slot is complete (commit)
+//   K_EMPTY[stage] same commit, for the K producer
+//   V_FULL[stage]  the V tile has landed AND the slot's group has written P; the PV issuer's only wait
+//   P_EMPTY[group] PV of the group's latest slot is complete (commit): its P region may be rewritten
+//   V_EMPTY[stage] same commit, for the V producer
+//   O_FULL[group]  the unit whose last slot the group had is accumulated; O_EMPTY: O has been read
+// A barrier that belongs to a group completes one phase per slot of that group, and the next
+// phase cannot complete before the group has acted on this one, so parity is never ambiguous
+// whatever the assignment of slots to groups is.
+enum Bar { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, K_EMPTY = K_FULL + NK, V_FULL = K_EMPTY + NK, V_EMPTY = V_FULL + NV,
+           S_FULL = V_EMPTY + NV, P_EMPTY = S_FULL + NWG, O_FULL = P_EMPTY + NWG, O_EMPTY = O_FULL + NWG,
+           DESC_FULL = O_EMPTY + 1, DESC_EMPTY = DESC_FULL + ND, NUM_BARS = DESC_EMPTY + ND };
+constexpr int DESC_READERS = 4 * NWG + 3;   // softmax warps, the two MMA issuers, the V producer
 static_assert(NUM_BARS * 8 + 16 <= 512, "barrier block");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 
@@ -162,125 +185,239 @@ struct Ring {
   __device__ __forceinline__ void next() { if (++st == (uint32_t)depth) { st = 0; ph ^= 1; } }
 };
 
-// ----------------------------------------------------------------------------- producers
-// mode 0: Q (per unit) + K (per slot);  mode 1: V (per slot)
-template <int MODE>
-__device__ void producer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane) {
-  int* sidx = reinterpret_cast<int*>(smem + OFF_IDX) + MODE * 32;
-  constexpr int FULL = MODE == 0 ? K_FULL : V_FULL, EMPTY = MODE == 0 ? K_EMPTY : V_EMPTY;
-  constexpr int DEPTH = MODE == 0 ? NK : NV, OFF = MODE == 0 ? OFF_K : OFF_V;
-  UnitCursor c;
-  c.init(p);
-  Ring ring; ring.init(DEPTH);
-  uint32_t ucnt = 0, issued = 0;
-  bool ok = true;
-  int next_idx = load_index_row(p, c.u, c.zj, lane);
-  for (; c.u < p.units; c.advance(p)) {
-    const int my_idx = next_idx;
-    next_idx = load_index_row(p, c.u + gridDim.x, c.next_zj(p), lane);
-    const unsigned mask = valid_mask(p, my_idx);
-    if (mask == 0) continue;
-    __syncwarp();
-    sidx[lane] = my_idx;
-    __syncwarp();
-    const uint32_t un = ucnt++;
-    if (lane != 0 || !ok) continue;
-    const UnitInfo t = unit_info(p, c.hp);
-    const int n = c.zj / p.J, j = c.zj - n * p.J;
-    if (MODE == 0) {
-      const uint32_t qb = un & 1;
-      ok = mbar_wait_bounded(&bars[Q_EMPTY + qb], ((un >> 1) & 1) ^ 1, abort_flag);
-      if (!ok) continue;
-      mbar_arrive_expect_tx(&bars[Q_FULL + qb], PAIR_BYTES);
-      tma_load_5d(smem + OFF_Q + qb * PAIR_BYTES, &p.tm_q, &bars[Q_FULL + qb], 0, 0, t.h0, j, n);
-    }
-    const CUtensorMap* tm = MODE == 0 ? (t.share ? &p.tm_k1 : &p.tm_k2) : (t.share ? &p.tm_v1 : &p.tm_v2);
-    const uint32_t bytes = t.share ? TILE_BYTES : PAIR_BYTES;
-    for (unsigned m = mask; m; m &= m - 1) {
-      const int k = __ffs(m) - 1;
-      ok = mbar_wait_bounded(&bars[EMPTY + ring.st], ring.ph ^ 1, abort_flag);
-      if (!ok) break;
-      mbar_arrive_expect_tx(&bars[FULL + ring.st], bytes);
-      GCA_TRACE(MODE, issued);
-      tma_load_5d(smem + OFF + ring.st * PAIR_BYTES, tm, &bars[FULL + ring.st], 0, 0, t.hk0, sidx[k], n);
-      ring.next();
-      ++issued;
-    }
-  }
-  // If anybody gave up, wait (bounded) for the copies this lane still has in flight so no
-  // bulk copy can land in shared memory after the CTA has exited.
-  if (lane == 0 && *abort_flag) {
-    for (uint32_t back = 0; back < (uint32_t)DEPTH && back < issued; ++back) {
-      const uint32_t g = issued - 1 - back;
-      for (int i = 0; i < (1 << 20); ++i)
-        if (mbar_try_wait(&bars[FULL + g % DEPTH], (g / DEPTH) & 1)) break;
-    }
-    if (MODE == 0)
-      for (uint32_t back = 0; back < 2 && back < ucnt; ++back) {
-        const uint32_t g = ucnt - 1 - back;
-        for (int i = 0; i < (1 << 20); ++i)
-          if (mbar_try_wait(&bars[Q_FULL + (g & 1)], (g >> 1) & 1)) break;
-      }
+__device__ __forceinline__ UnitDesc* desc_hdr(uint8_t* smem) { return reinterpret_cast<UnitDesc*>(smem + OFF_DESC); }
+__device__ __forceinline__ int* desc_idx(uint8_t* smem) { return reinterpret_cast<int*>(smem + OFF_DESC + ND * DESC_HDR); }
+__device__ __forceinline__ float* desc_w(uint8_t* smem) { return reinterpret_cast<float*>(smem + OFF_DESC + ND * (DESC_HDR + 128)); }
+__device__ __forceinline__ uint8_t* desc_slot(uint8_t* smem) { return smem + OFF_DESC + ND * (DESC_HDR + 256); }
+
+// Bounded wait (one lane) for the copies of a ring that may still be in flight: no bulk copy
+// may land in shared memory after the CTA has exited.
+__device__ __forceinline__ void drain_ring(uint64_t* bars, int full0, uint32_t issued, int depth) {
+  for (uint32_t back = 0; back < (uint32_t)depth && back < issued; ++back) {
+    const uint32_t g = issued - 1 - back;
+    for (int i = 0; i < (1 << 20); ++i)
+      if (mbar_try_wait(&bars[full0 + g % depth], (g / depth) & 1)) break;
   }
 }
 
+// ----------------------------------------------------------------------------- Q / K producer
+// Walks this CTA's units, publishes one descriptor per unit that has valid slots, issues the
+// unit's Q copy and one K copy per slot.  Everything a unit needs that no slot will write is
+// also done here (rare: the first K chunks of a sequence): zero output rows of a unit without
+// valid slots, zero lse of padding slots, the bad-index status bit.
+__device__ void kproducer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane) {
+  UnitDesc* hdr = desc_hdr(smem);
+  int* didx = desc_idx(smem);
+  float* dw = desc_w(smem);
+  uint8_t* dslot = desc_slot(smem);
+  UnitCursor c;
+  c.init(p);
+  Ring ring; ring.init(NK);
+  Ring dr; dr.init(ND);
+  uint32_t un = 0, issued = 0;
+  uint32_t g0 = 0, g0m6 = 0;             // running number of the unit's first slot, and modulo 6
+  int L = NWG - 1;                       // the group that wrote the previous unit's output
+  bool ok = true;
+  const unsigned full = (p.K >= 32) ? 0xffffffffu : ((1u << p.K) - 1u);
+  int next_idx = load_index_row(p, c.u, c.zj, lane);
+  float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.zj * p.K + lane] : 0.f;
+  for (; c.u < p.units && ok; c.advance(p)) {
+    const int my_idx = next_idx;
+    const float my_w = next_w;
+    {
+      const int nzj = c.next_zj(p);
+      next_idx = load_index_row(p, c.u + gridDim.x, nzj, lane);
+      next_w = (c.u + gridDim.x < p.units && lane < p.K) ? p.weights[(long long)nzj * p.K + lane] : 0.f;
+    }
+    const unsigned mask = valid_mask(p, my_idx);
+    const UnitInfo t = unit_info(p, c.hp);
+    const int n = c.zj / p.J, j = c.zj - n * p.J;
+    const long long lse_off = ((long long)c.zj * p.Hq + t.h0) * p.K * 64;
+    const long long out_off = n * p.os[0] + j * p.os[1] + t.h0 * p.os[2];
+    if (__any_sync(0xffffffffu, my_idx >= p.C) && p.status && lane == 0) atomicOr(p.status, GCA_STATUS_BAD_INDEX);
+    if (mask != full) {
+      const int rows = t.two ? 128 : 64;                       // rows of the unit: head A, then head B
+      if (p.lse)
+        for (int k = 0; k < p.K; ++k)
+          if (!((mask >> k) & 1))
+            for (int i = lane; i < rows; i += 32) p.lse[lse_off + ((long long)(i >> 6) * p.K + k) * 64 + (i & 63)] = 0.f;
+      if (mask == 0) {
+        for (int i = lane; i < rows * 8; i += 32) {
+          const int r = i >> 3;
+          reinterpret_cast<uint4*>(p.out + out_off + (r >> 6) * p.os[2] + (r & 63) * p.os[3])[i & 7] = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+    }
+    // publish the descriptor
+    ok = mbar_wait_warp(&bars[DESC_EMPTY + dr.st], dr.ph ^ 1, abort_flag, lane);
+    if (!ok) break;
+    didx[dr.st * 32 + lane] = my_idx;
+    dw[dr.st * 32 + lane] = my_w;
+    // Which warpgroup takes which slot (lane k works out slot k).  The group that has a unit's
+    // last slot also writes the unit's output (wait for the last PV, read O, store: ~3,000
+    // cycles); with plain rotation its next slot -- and, O being accumulated in slot order, every
+    // slot behind it -- would wait for that.  So the first four slots of the next unit alternate
+    // between the other two groups and the writer rejoins at the fifth: L = writer of the
+    // previous unit, A, B the other two:  slot 0 1 2 3 4 5 6 7 8 ...  ->  A B A B L A B L A ...
+    // No group ever has two consecutive slots.
+    const bool valid = (mask >> lane) & 1u;
+    const int r = __popc(mask & ((1u << lane) - 1u));          // the slot's number inside the unit
+    int wgk;
+    {
+#ifdef GCA_FWD_ROUND_ROBIN
+      const int x = (int)(g0 % 3u) + r;
+      wgk = x - 3 * ((x * 86) >> 8);
+#else
+      const int A = L + 1 == NWG ? 0 : L + 1, B = A + 1 == NWG ? 0 : A + 1;
+      const int y = r - 4, y3 = y - 3 * ((y * 86) >> 8);       // (r - 4) % 3 for 4 <= r < 32
+      wgk = r < 4 ? ((r & 1) ? B : A) : (y3 == 0 ? L : (y3 == 1 ? A : B));
+#endif
+    }
+    const int xs = (int)g0m6 + r, s6 = xs - 6 * ((xs * 43) >> 8);   // (g0 + r) % 6
+    if (valid) dslot[dr.st * 32 + lane] = (uint8_t)(s6 | (wgk << 3));
+    const uint32_t own0 = __ballot_sync(0xffffffffu, valid && wgk == 0);
+    const uint32_t own1 = __ballot_sync(0xffffffffu, valid && wgk == 1);
+    const uint32_t own2 = __ballot_sync(0xffffffffu, valid && wgk == 2);
+    const int nv = __popc(mask);
+    L = __shfl_sync(0xffffffffu, wgk, 31 - __clz(mask));       // the group of the unit's last slot
+    if (lane == 0) {
+      UnitDesc h;
+      h.mask = mask;
+      h.flags = (t.two ? DESC_TWO : 0u) | (t.share ? DESC_SHARE : 0u) | ((uint32_t)L << DESC_EPI_SHIFT);
+      h.n = n; h.hk0 = t.hk0; h.lse_off = lse_off; h.out_off = out_off;
+      h.own[0] = own0; h.own[1] = own1; h.own[2] = own2; h.g0 = g0;
+      hdr[dr.st] = h;
+    }
+    g0 += nv;
+    g0m6 += nv; g0m6 -= 6 * ((g0m6 * 43) >> 8);
+    mbar_arrive_warp(&bars[DESC_FULL + dr.st], lane);
+    const uint32_t ds = dr.st;
+    dr.next();
+    if (lane == 0) {
+      const uint32_t qb = un & 1;
+      ok = mbar_wait_bounded(&bars[Q_EMPTY + qb], ((un >> 1) & 1) ^ 1, abort_flag);
+      if (ok) {
+        mbar_arrive_expect_tx(&bars[Q_FULL + qb], PAIR_BYTES);
+        tma_load_5d(smem + OFF_Q + qb * PAIR_BYTES, &p.tm_q, &bars[Q_FULL + qb], 0, 0, t.h0, j, n);
+        const CUtensorMap* tm = t.share ? &p.tm_k1 : &p.tm_k2;
+        const uint32_t bytes = t.share ? TILE_BYTES : PAIR_BYTES;
+        for (unsigned m = mask; m; m &= m - 1) {
+          ok = mbar_wait_bounded(&bars[K_EMPTY + ring.st], ring.ph ^ 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars[K_FULL + ring.st], bytes);
+          tma_load_5d(smem + OFF_K + ring.st * PAIR_BYTES, tm, &bars[K_FULL + ring.st], 0, 0, t.hk0,
+                      didx[ds * 32 + __ffs(m) - 1], n);
+          ring.next();
+          ++issued;
+        }
+      }
+    }
+    ++un;
+    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+  }
+  // end of work
+  if (ok && mbar_wait_warp(&bars[DESC_EMPTY + dr.st], dr.ph ^ 1, abort_flag, lane)) {
+    if (lane == 0) { hdr[dr.st].mask = 0; hdr[dr.st].flags = DESC_END; }
+    mbar_arrive_warp(&bars[DESC_FULL + dr.st], lane);
+  }
+  if (lane == 0 && *abort_flag) {
+    drain_ring(bars, K_FULL, issued, NK);
+    drain_ring(bars, Q_FULL, un, 2);
+  }
+}
+
+// ----------------------------------------------------------------------------- V producer
+__device__ void vproducer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane) {
+  const UnitDesc* hdr = desc_hdr(smem);
+  const int* didx = desc_idx(smem);
+  Ring ring; ring.init(NV);
+  Ring dr; dr.init(ND);
+  uint32_t issued = 0;
+  bool ok = true;
+  while (ok) {
+    ok = mbar_wait_warp(&bars[DESC_FULL + dr.st], dr.ph, abort_flag, lane);
+    if (!ok) break;
+    const UnitDesc h = hdr[dr.st];
+    if (h.flags & DESC_END) break;
+    if (lane == 0) {
+      const bool share = (h.flags & DESC_SHARE) != 0;
+      const CUtensorMap* tm = share ? &p.tm_v1 : &p.tm_v2;
+      const uint32_t bytes = share ? TILE_BYTES : PAIR_BYTES;
+      for (unsigned m = h.mask; m; m &= m - 1) {
+        ok = mbar_wait_bounded(&bars[V_EMPTY + ring.st], ring.ph ^ 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars[V_FULL + ring.st], bytes);
+        tma_load_5d(smem + OFF_V + ring.st * PAIR_BYTES, tm, &bars[V_FULL + ring.st], 0, 0, h.hk0,
+                    didx[dr.st * 32 + __ffs(m) - 1], h.n);
+        ring.next();
+        ++issued;
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+    mbar_arrive_warp(&bars[DESC_EMPTY + dr.st], lane);
+    dr.next();
+  }
+  if (lane == 0 && *abort_flag) drain_ring(bars, V_FULL, issued, NV);
+}
+
 // ----------------------------------------------------------------------------- MMA issuers
-// mode 0: S = Q K^T into accumulator g % 2;  mode 1: O += P V with P (group g % 3's region of
-// tensor memory) as the A operand.  All 32 lanes run this code; elect.sync inside the MMA /
+// mode 0: S = Q K^T into accumulator g % 2;  mode 1: O += P V with P (the slot's group's region
+// of tensor memory) as the A operand.  All 32 lanes run this code; elect.sync inside the MMA /
 // commit wrappers picks the issuing lane.
 template <int MODE>
 __device__ void issuer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
                             uint32_t tmem_base) {
   constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
-  constexpr uint32_t FULL = MODE == 0 ? K_FULL : V_FULL;
+  constexpr uint32_t FULL = MODE == 0 ? K_FULL : V_FULL, EMPTY = MODE == 0 ? K_EMPTY : V_EMPTY;
+  const UnitDesc* hdr = desc_hdr(smem);
   const uint64_t dQ = umma_desc_sw128(smem_u32(smem + OFF_Q));
   const uint64_t dB = MODE == 0 ? umma_desc_sw128(smem_u32(smem + OFF_K))
                                 : umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_V), TILE_BYTES);
-  UnitCursor c;
-  c.init(p);
-  uint32_t ucnt = 0, g = 0;                   // units with work; running slot number
-  uint32_t s6 = 0, ph6 = 0;                   // g % 6 and (g / 6) & 1
+  const uint8_t* dslot = desc_slot(smem);
+  Ring dr; dr.init(ND);
+  uint32_t un = 0, g = 0;                     // units; running slot number
+  uint32_t ph6 = 0;                           // (g / 6) & 1
   bool ok = true;
-  int next_idx = load_index_row(p, c.u, c.zj, lane);
-  for (; c.u < p.units && ok; c.advance(p)) {
-    const int my_idx = next_idx;
-    next_idx = load_index_row(p, c.u + gridDim.x, c.next_zj(p), lane);
-    const unsigned mask = valid_mask(p, my_idx);
-    if (mask == 0) continue;
-    const uint32_t un = ucnt++;
-    const int nv = __popc(mask);
-    const UnitInfo t = unit_info(p, c.hp);
+  while (ok) {
+    ok = mbar_wait_warp(&bars[DESC_FULL + dr.st], dr.ph, abort_flag, lane);
+    if (!ok) break;
+    const uint32_t mask = hdr[dr.st].mask, flags = hdr[dr.st].flags;
+    if (flags & DESC_END) break;
     const uint32_t ub = un & 1;
-    const uint32_t idesc = umma_idesc_bf16(128, t.share ? 64 : 128, 0, MODE);
+    const uint32_t idesc = umma_idesc_bf16(128, (flags & DESC_SHARE) ? 64 : 128, 0, MODE);
     if (MODE == 0) ok = mbar_wait_warp(&bars[Q_FULL + ub], (un >> 1) & 1, abort_flag, lane);
     else ok = mbar_wait_warp(&bars[O_EMPTY], (un & 1) ^ 1, abort_flag, lane);
-    for (int i = 0; i < nv && ok; ++i, ++g) {
+    ++un;
+    for (uint32_t m = mask; m && ok; m &= m - 1, ++g) {
+      const uint32_t info = dslot[dr.st * 32 + __ffs(m) - 1];
+      const uint32_t s6 = info & 7u, w = info >> 3;                    // slot number mod 6; the slot's warpgroup
       ok = mbar_wait_warp(&bars[FULL + s6], ph6, abort_flag, lane);    // tile landed and S accumulator free / P written
       if (lane == 0) GCA_TRACE(2 + 3 * MODE, g);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t w3 = s6 >= 3 ? s6 - 3 : s6;                       // g % 3: the slot's warpgroup
       const uint64_t b = dB + s6 * PAIR16;
+      const bool last = (m & (m - 1)) == 0;
       if (MODE == 0) {
         const uint64_t a = dQ + ub * PAIR16;
         const uint32_t dt = tmem_base + (s6 & 1u) * 128;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) umma_bf16_ss_elect(dt, a + kk * 2, b + kk * 2, idesc, (uint32_t)(kk > 0));
-        umma_commit_elect(&bars[S_FULL + s6]);
-        if (i == nv - 1) umma_commit_elect(&bars[Q_EMPTY + ub]);
+        umma_commit_elect(&bars[S_FULL + w]);
       } else {
-        const uint32_t at = tmem_base + TMEM_P + w3 * 32;
+        const uint32_t at = tmem_base + TMEM_P + w * 32;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_bf16_ts_elect(tmem_base + TMEM_O, at + kk * 8, b + kk * 128, idesc, (uint32_t)(i > 0 || kk > 0));
-        umma_commit_elect(&bars[P_EMPTY + s6]);
-        // the unit's output is written by the warpgroup of its last slot: it has just finished, and
-        // its next slot is NWG slots away
-        if (i == nv - 1) umma_commit_elect(&bars[O_FULL + w3]);
+          umma_bf16_ts_elect(tmem_base + TMEM_O, at + kk * 8, b + kk * 128, idesc, (uint32_t)(m != mask || kk > 0));
+        umma_commit_elect(&bars[P_EMPTY + w]);
       }
+      umma_commit_elect(&bars[EMPTY + s6]);                            // the ring stage is free
+      if (last) umma_commit_elect(&bars[MODE == 0 ? Q_EMPTY + ub : O_FULL + w]);
       if (lane == 0) GCA_TRACE(4 + 3 * MODE, g);
-      if (++s6 == NRING) { s6 = 0; ph6 ^= 1; }
+      if (s6 == 5) ph6 ^= 1;
     }
+    mbar_arrive_warp(&bars[DESC_EMPTY + dr.st], lane);
+    dr.next();
   }
 }
 
@@ -298,73 +435,58 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
   const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
   const bool elected = quad == 0 && lane == 0;
   const uint32_t tP = tlane + TMEM_P + (uint32_t)wg * 32;   // this warpgroup's P region of tensor memory
-  UnitCursor c;
-  c.init(p);
-  uint32_t ucnt = 0, own = 0, epi = 0, g = 0;        // units with work; own slots / outputs done; running slot
-  int gm = 0;                                        // slot counter modulo NWG
+  const UnitDesc* hdr = desc_hdr(smem);
+  const float* dw = desc_w(smem);
+  // this thread's row inside a unit's output / lse block
+  __nv_bfloat16* const out_t = p.out + tile * p.os[2] + row * p.os[3];
+  const long long lse_t = (long long)tile * p.K * 64 + row;
+  const bool wide_store = p.wide_store != 0;
+  const uint8_t* dslot = desc_slot(smem);
+  Ring dr; dr.init(ND);
+  uint32_t own = 0, epi = 0;                        // own slots / outputs done
   bool ok = true;
-  int next_idx = load_index_row(p, c.u, c.zj, lane);
-  float next_w = (c.u < p.units && lane < p.K) ? p.weights[(long long)c.zj * p.K + lane] : 0.f;
   // slots 0 and 1 find their S accumulators untouched: groups 1 and 2 stand in for the readers of
-  // "slots -2 and -1" (a slot's reader arrives on the barrier set of the slot two later)
+  // "slots -2 and -1" (a slot's reader arrives on the K barrier of the slot two later)
   if (wg >= 1) mbar_arrive_warp(&bars[K_FULL + (wg - 1)], lane);
 
-  for (; c.u < p.units && ok; c.advance(p)) {
-    const int my_idx = next_idx;
-    const float my_w = next_w;
-    {
-      const int nzj = c.next_zj(p);
-      next_idx = load_index_row(p, c.u + gridDim.x, nzj, lane);
-      next_w = (c.u + gridDim.x < p.units && lane < p.K) ? p.weights[(long long)nzj * p.K + lane] : 0.f;
-    }
-    const unsigned mask = valid_mask(p, my_idx);
-    const UnitInfo t = unit_info(p, c.hp);
-    const int h = t.h0 + tile;
-    const bool live = (tile == 0 || t.two) && h < p.Hq;
-    const uint32_t coff = t.share ? 0u : (uint32_t)tile * 64u;
-    const int n = c.zj / p.J, j = c.zj - n * p.J;
-    float* lse_base = p.lse ? p.lse + ((long long)c.zj * p.Hq + h) * p.K * 64 + row : nullptr;
-    __nv_bfloat16* orow = p.out + n * p.os[0] + j * p.os[1] + h * p.os[2] + row * p.os[3];
-    if (wg == 0) {
-      const bool bad = __any_sync(0xffffffffu, my_idx >= p.C);
-      if (bad && p.status && elected) atomicOr(p.status, GCA_STATUS_BAD_INDEX);
-      if (lse_base && live && mask != ((p.K >= 32) ? 0xffffffffu : ((1u << p.K) - 1u)))
-        for (int k = 0; k < p.K; ++k)
-          if (!((mask >> k) & 1)) lse_base[k * 64] = 0.f;
-      if (mask == 0 && live) {
-        const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc) reinterpret_cast<uint4*>(orow)[cc] = z;
-      }
-    }
-    if (mask == 0) continue;
-    ++ucnt;
-    bool my_unit = false;                            // this group owns the unit's last slot: it writes the output
-    for (unsigned m = mask; m; m &= m - 1, ++g) {
-      const bool mine = gm == wg;
-      my_unit = mine;
-      if (++gm == NWG) gm = 0;
-      if (!mine) continue;                           // another warpgroup's slot
+  while (ok) {
+    ok = mbar_wait_warp(&bars[DESC_FULL + dr.st], dr.ph, abort_flag, lane);
+    if (!ok) break;
+    const uint32_t flags = hdr[dr.st].flags;
+    if (flags & DESC_END) break;
+    const uint32_t mine = hdr[dr.st].own[wg];        // this group's slots
+    const long long lse_off = hdr[dr.st].lse_off, out_off = hdr[dr.st].out_off;
+    const float my_w = dw[dr.st * 32 + lane];        // lane k: weight and slot byte of slot k
+    const uint32_t my_info = dslot[dr.st * 32 + lane];
+#ifdef GCA_PROFILE
+    const uint32_t umask = hdr[dr.st].mask, g0 = hdr[dr.st].g0;
+#endif
+    mbar_arrive_warp(&bars[DESC_EMPTY + dr.st], lane);
+    dr.next();
+    const bool live = tile == 0 || (flags & DESC_TWO);
+    const uint32_t coff = (flags & DESC_SHARE) ? 0u : (uint32_t)tile * 64u;
+    float* lse_base = p.lse ? p.lse + lse_off + lse_t : nullptr;
+    __nv_bfloat16* orow = out_t + out_off;
+    for (unsigned m = mine; m; m &= m - 1) {
       const int k = __ffs(m) - 1;
       const float wk = __shfl_sync(0xffffffffu, my_w, k);
-      // this group's slots are g = wg, wg + 3, wg + 6, ...: g % 6 alternates between wg and wg + 3
-      const uint32_t s6 = (uint32_t)wg + 3u * (own & 1u), ph6 = (own >> 1) & 1u;
-      const uint32_t gt = g;                         // (trace builds only)
-      (void)gt;
-      ok = mbar_wait_warp(&bars[S_FULL + s6], ph6, abort_flag, lane);
+      const uint32_t vs = __shfl_sync(0xffffffffu, my_info, k) & 7u;   // slot number mod 6: V barrier, S accumulator
+      const uint32_t kn = vs + 2 >= 6 ? vs - 4 : vs + 2;               // K barrier of the slot two later
+#ifdef GCA_PROFILE
+      const uint32_t gt = g0 + __popc(umask & ((1u << k) - 1u));
+#endif
+      if (elected) GCA_TRACE(13, gt);
+      ok = mbar_wait_warp(&bars[S_FULL + wg], own & 1u, abort_flag, lane);
       if (!ok) break;
       if (elected) GCA_TRACE(8, gt);
       tc_fence_after();
       uint32_t x[64];
-      const uint32_t tS = tlane + (s6 & 1u) * 128 + coff;       // accumulator g % 2
+      const uint32_t tS = tlane + (vs & 1u) * 128 + coff;       // accumulator g % 2
       tmem_ld_32x32b_x32(tS, x);
       tmem_ld_32x32b_x32(tS + 32, x + 32);
       tmem_ld_wait();
       tc_fence_before();
-      {                                              // the accumulator is free for slot g + 2: barrier set (g + 2) % 6
-        const uint32_t n6 = s6 + 2 >= NRING ? s6 + 2 - NRING : s6 + 2;
-        mbar_arrive_warp(&bars[K_FULL + n6], lane);
-      }
+      mbar_arrive_warp(&bars[K_FULL + kn], lane);    // the accumulator is free for slot g + 2
       if (elected) GCA_TRACE(9, gt);
 
       // row max: four independent chains of 3-input max
@@ -409,9 +531,8 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
       const float2 fv = make_float2(f, f);
 
       if (elected) GCA_TRACE(10, gt);
-      if (own > 0) {                                 // PV of this group's previous slot (g - 3) has consumed its P
-        const uint32_t p6 = (uint32_t)wg + 3u * ((own - 1) & 1u), pph = ((own - 1) >> 1) & 1u;
-        ok = mbar_wait_warp(&bars[P_EMPTY + p6], pph, abort_flag, lane);
+      if (own > 0) {                                 // PV of this group's previous slot has consumed its P
+        ok = mbar_wait_warp(&bars[P_EMPTY + wg], (own - 1) & 1u, abort_flag, lane);
         if (!ok) break;
       }
       if (elected) GCA_TRACE(11, gt);
@@ -432,28 +553,33 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
         tmem_st_wait();
       }
       tc_fence_before();
-      mbar_arrive_warp(&bars[V_FULL + s6], lane);    // "P of this slot is written"
+      mbar_arrive_warp(&bars[V_FULL + vs], lane);    // "P of this slot is written"
       ++own;
       if (elected) GCA_TRACE(12, gt);
     }
     if (!ok) break;
-    // epilogue, the warpgroups taking turns: O tile -> bf16 -> global
-    if (my_unit) {
+    // epilogue by the group that had the unit's last slot: O tile -> bf16 -> global
+    if (((flags >> DESC_EPI_SHIFT) & 3u) == (uint32_t)wg) {
+#ifdef GCA_PROFILE
+      const uint32_t g = g0 + __popc(umask);
+#endif
       ok = mbar_wait_warp(&bars[O_FULL + wg], epi & 1, abort_flag, lane);
       ++epi;
       if (!ok) break;
+      if (elected) GCA_TRACE(3, g - 1);
       tc_fence_after();
       uint32_t o[64];
       tmem_ld_32x32b_x32(tlane + TMEM_O + coff, o);
       tmem_ld_32x32b_x32(tlane + TMEM_O + coff + 32, o + 32);
       tmem_ld_wait();
       tc_fence_before();
+      if (elected) GCA_TRACE(0, g - 1);
       mbar_arrive_warp(&bars[O_EMPTY], lane);
-      if (live) {
+      if (live && !GCA_DBG(4)) {
         uint32_t wv[32];
 #pragma unroll
         for (int cc = 0; cc < 32; ++cc) wv[cc] = pack_bf16x2(__uint_as_float(o[2 * cc]), __uint_as_float(o[2 * cc + 1]));
-        if (p.wide_store) {                 // full 32-byte sectors instead of eight 16-byte halves
+        if (wide_store) {                   // full 32-byte sectors instead of eight 16-byte halves
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc)
             st_global_256(reinterpret_cast<uint8_t*>(orow) + 32 * cc, wv[8 * cc], wv[8 * cc + 1], wv[8 * cc + 2],
@@ -464,6 +590,7 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
             reinterpret_cast<uint4*>(orow)[cc] = make_uint4(wv[4 * cc], wv[4 * cc + 1], wv[4 * cc + 2], wv[4 * cc + 3]);
         }
       }
+      if (elected) GCA_TRACE(6, g - 1);
     }
   }
 }
@@ -479,11 +606,11 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams p) {
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) { mbar_init(&bars[Q_FULL + i], 1); mbar_init(&bars[Q_EMPTY + i], 1); }
-    for (int i = 0; i < NRING; ++i) { mbar_init(&bars[S_FULL + i], 1); mbar_init(&bars[P_EMPTY + i], 1); }
-    for (int i = 0; i < NWG; ++i) mbar_init(&bars[O_FULL + i], 1);
+    for (int i = 0; i < NWG; ++i) { mbar_init(&bars[S_FULL + i], 1); mbar_init(&bars[P_EMPTY + i], 1); mbar_init(&bars[O_FULL + i], 1); }
     mbar_init(&bars[O_EMPTY], 4);
-    for (int i = 0; i < NK; ++i) mbar_init(&bars[K_FULL + i], 5);     // producer + the 4 warps of group i
-    for (int i = 0; i < NV; ++i) mbar_init(&bars[V_FULL + i], 5);
+    for (int i = 0; i < ND; ++i) { mbar_init(&bars[DESC_FULL + i], 1); mbar_init(&bars[DESC_EMPTY + i], DESC_READERS); }
+    for (int i = 0; i < NK; ++i) { mbar_init(&bars[K_FULL + i], 5); mbar_init(&bars[K_EMPTY + i], 1); }   // FULL: producer + 4 warps
+    for (int i = 0; i < NV; ++i) { mbar_init(&bars[V_FULL + i], 5); mbar_init(&bars[V_EMPTY + i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -496,8 +623,8 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams p) {
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4 * NWG) softmax_role(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
-  else if (warp == KPROD_WARP) producer_role<0>(p, smem, bars, abort_flag, lane);
-  else if (warp == VPROD_WARP) producer_role<1>(p, smem, bars, abort_flag, lane);
+  else if (warp == KPROD_WARP) kproducer_role(p, smem, bars, abort_flag, lane);
+  else if (warp == VPROD_WARP) vproducer_role(p, smem, bars, abort_flag, lane);
   else if (warp == SMMA_WARP) issuer_role<0>(p, smem, bars, abort_flag, lane, tmem_base);
   else issuer_role<1>(p, smem, bars, abort_flag, lane, tmem_base);
 
