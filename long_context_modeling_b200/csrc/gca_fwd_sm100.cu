@@ -21,13 +21,18 @@
 // cache with the retrieved chunk index as a tensor coordinate (no gathered copy exists).
 //
 // CTA = 16 warps.
-//   warps 0-11  three softmax warpgroups taking the slots round-robin (thread = TMEM lane =
-//               row); each owns one S accumulator and one P buffer, so one group's chain
-//               S -> TMEM read -> exp2 -> P -> PV overlaps the other two groups' chains
-//   warp  12    TMA producer for Q and K;  warp 13: TMA producer for V (separate rings; K is
-//               released as soon as S is done)
+//   warps 0-11  three softmax warpgroups (thread = TMEM lane = row); a group reads S from one of
+//               two accumulators and writes P into its own 32 columns of tensor memory, so one
+//               group's chain S -> TMEM read -> exp2 -> P -> PV overlaps the other two groups'
+//   warp  12    walks the unit list, publishes one DESCRIPTOR per unit in shared memory (valid
+//               slots, retrieved indices, weights, output / lse offsets, and which group takes
+//               which slot), issues the TMA copies of Q and K
+//   warp  13    TMA producer for V (separate ring; K is released as soon as S is done)
 //   warp  14    issues the S MMAs;  warp 15 the PV MMAs (one O accumulator, slots in order, so
 //               the result does not depend on timing)
+// Warps 0-11 and 13-15 only follow descriptors: the unit bookkeeping (index rows, divisions,
+// 64-bit offsets, padding slots) is ~100 rarely executed, branchy instructions that cost a
+// warp ~10 cycles each, and it used to sit on every warpgroup's critical path once per unit.
 // A warp can issue one tcgen05.mma per ~100 cycles when it runs converged with warp-uniform
 // operands and only the instruction itself is predicated on elect.sync (~150 inside a
 // divergent `if (lane == 0)` region), so the issuing warps run all lanes.  Ring stages are
