@@ -50,7 +50,7 @@ constexpr int TMEM_COLS = 512;
 // share the same 64 columns.  One S/dP buffer = 128 columns (S at +0, dP at +64) and there are two
 // of them: iteration g+1's S and dP are computed while the workers still read iteration g's.
 // The gradient accumulators keep the stacked 128-row form (one instruction for both heads).
-constexpr uint32_t COL_SP = 0, SP_COLS = 128, COL_DPOFF = 64, COL_ACC = 256;
+constexpr uint32_t COL_SP = 0, SP_COLS = 128, COL_DPOFF = 64;
 // The q-major kernel keeps S and dP as single stacked 128-row tiles (measured faster there: its
 // iterations are bound by the K ring, not by the S/dP turnaround, and the 64-row form doubles
 // the S/dP instruction count).
@@ -437,13 +437,17 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(5);
       tc_fence_after();
-      uint32_t acc[64];
-      tmem_ld_32x32b_x32(tlane + QCOL_DQ + coff, acc);
-      tmem_ld_32x32b_x32(tlane + QCOL_DQ + coff + 32, acc + 32);
-      tmem_ld_wait();
+      // dQ leaves in four passes of one small loop body (16 columns: TMEM -> bf16 -> one 32-byte
+      // store per row): after the first pass the body is in the instruction cache
+#pragma unroll 1
+      for (int part = 0; part < 4; ++part) {
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(tlane + QCOL_DQ + coff + part * 16, v);
+        tmem_ld_wait();
+        if (live) store16_bf16(reinterpret_cast<uint8_t*>(dq_row) + part * 32, v, p.sm_scale, p.wide_store);
+      }
       tc_fence_before();
       mbar_arrive(&bars[DQ_EMPTY]);
-      if (live) store_row_bf16(dq_row, acc, p.sm_scale, p.wide_store);
       pf.lap(6);
     }
   }
@@ -518,7 +522,9 @@ struct BwdKvParams {
   CUtensorMap tm_q2, tm_do2, tm_q1, tm_do1, tm_k2, tm_v2;
   const float* weights;
   const float* lse;
-  const int* offsets;
+  const unsigned* unit_keys;            // units in walking order (see Csr): count = cmax - (key & cmask),
+  const unsigned long long* unit_vals;  // value = chunk id << 32 | first entry
+  unsigned unit_cmax, unit_cmask;
   const unsigned long long* sorted_keys;
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
@@ -539,15 +545,16 @@ __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars,
   Ring ring; ring.init(NQ);
   uint32_t ucnt = 0, issued = 0;
   bool ok = true;
-  int nbeg = c.u < p.units ? p.offsets[c.outer] : 0, nend = c.u < p.units ? p.offsets[c.outer + 1] : 0;
+  unsigned nkey = c.u < p.units ? p.unit_keys[c.outer] : p.unit_cmax;
+  unsigned long long nval = c.u < p.units ? p.unit_vals[c.outer] : 0ull;
   for (; c.u < p.units && ok; c.advance()) {
-    const int beg = nbeg, end = nend;
-    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nbeg = p.offsets[no]; nend = p.offsets[no + 1]; }
+    const int beg = (int)(unsigned)nval, end = beg + (int)(p.unit_cmax - (nkey & p.unit_cmask)), chunk = (int)(nval >> 32);
+    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nkey = p.unit_keys[no]; nval = p.unit_vals[no]; }
     if (end == beg) continue;
     const uint32_t un = ucnt++;
     const int hk0 = 2 * c.inner;
     const bool two = hk0 + 1 < p.Hkv;
-    const int n = c.outer / p.C, ch = c.outer - n * p.C;
+    const int n = chunk / p.C, ch = chunk - n * p.C;
     {
       const uint32_t kb = un % NKV;
       ok = mbar_wait_bounded(&bars[KV_EMPTY + kb], ((un / NKV) & 1) ^ 1, abort_flag);
@@ -602,10 +609,11 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
   Ring ring; ring.init(NQ);
   uint32_t ucnt = 0, g = 0;
   bool ok = true;
-  int nbeg = c.u < p.units ? p.offsets[c.outer] : 0, nend = c.u < p.units ? p.offsets[c.outer + 1] : 0;
+  unsigned nkey = c.u < p.units ? p.unit_keys[c.outer] : p.unit_cmax;
+  unsigned long long nval = c.u < p.units ? p.unit_vals[c.outer] : 0ull;
   for (; c.u < p.units && ok; c.advance()) {
-    const int beg = nbeg, end = nend;
-    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nbeg = p.offsets[no]; nend = p.offsets[no + 1]; }
+    const int beg = (int)(unsigned)nval, end = beg + (int)(p.unit_cmax - (nkey & p.unit_cmask));
+    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nkey = p.unit_keys[no]; nval = p.unit_vals[no]; }
     const int niter = (end - beg) * p.G;
     if (niter == 0) continue;
     const uint32_t un = ucnt++;
@@ -667,13 +675,14 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
   uint32_t epi = 0;                             // units this group has written out
   PhaseTimer pf;
   pf.init(false);
-  int nbeg = c.u < p.units ? p.offsets[c.outer] : 0, nend = c.u < p.units ? p.offsets[c.outer + 1] : 0;
+  unsigned nkey = c.u < p.units ? p.unit_keys[c.outer] : p.unit_cmax;
+  unsigned long long nval = c.u < p.units ? p.unit_vals[c.outer] : 0ull;
   for (; c.u < p.units && ok; c.advance()) {
-    const int beg = nbeg, end = nend;
-    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nbeg = p.offsets[no]; nend = p.offsets[no + 1]; }
+    const int beg = (int)(unsigned)nval, end = beg + (int)(p.unit_cmax - (nkey & p.unit_cmask)), chunk = (int)(nval >> 32);
+    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nkey = p.unit_keys[no]; nval = p.unit_vals[no]; }
     const int hk = 2 * c.inner + tile;
     const bool live = hk < p.Hkv;
-    const int n = c.outer / p.C, ch = c.outer - n * p.C;
+    const int n = chunk / p.C, ch = chunk - n * p.C;
     __nv_bfloat16* dk_row = p.dk + n * p.dks[0] + ch * p.dks[1] + row * p.dks[2] + hk * p.dks[3];
     __nv_bfloat16* dv_row = p.dv + n * p.dvs[0] + ch * p.dvs[1] + row * p.dvs[2] + hk * p.dvs[3];
     if (end == beg) {
@@ -747,22 +756,24 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(5);
       tc_fence_after();
-      // both accumulators into registers first, so that the next unit's gradient MMAs (which wait
-      // for ACC_EMPTY) are not held up by this unit's global stores
+      // The two tiles leave in eight passes of ONE small loop body (16 columns: TMEM -> bf16 ->
+      // one 32-byte store per row): after the first pass the body is in the instruction cache,
+      // where a straight-line conversion of all 128 columns (~250 instructions, executed once per
+      // unit) runs at instruction-fetch speed.
       if (elected) GCA_TRACE_BUF(p.prof, 11, un);
-      uint32_t acc[64], acc2[64];
-      tmem_ld_32x32b_x32(tlane + COL_DK + coff, acc);
-      tmem_ld_32x32b_x32(tlane + COL_DK + coff + 32, acc + 32);
-      tmem_ld_32x32b_x32(tlane + COL_DV + coff, acc2);
-      tmem_ld_32x32b_x32(tlane + COL_DV + coff + 32, acc2 + 32);
-      tmem_ld_wait();
+#pragma unroll 1
+      for (int part = 0; part < 8; ++part) {
+        const bool is_dv = part >= 4;
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(tlane + (is_dv ? COL_DV : COL_DK) + coff + (part & 3) * 16, v);
+        tmem_ld_wait();
+        if (live)
+          store16_bf16(reinterpret_cast<uint8_t*>(is_dv ? dv_row : dk_row) + (part & 3) * 32, v, is_dv ? 1.0f : p.sm_scale,
+                       p.wide_store);
+      }
       tc_fence_before();
       mbar_arrive(&bars[ACC_EMPTY]);
       if (elected) GCA_TRACE_BUF(p.prof, 12, un);
-      if (live) {
-        store_row_bf16(dk_row, acc, p.sm_scale, p.wide_store);
-        store_row_bf16(dv_row, acc2, 1.0f, p.wide_store);
-      }
       if (elected) GCA_TRACE_BUF(p.prof, 13, un);
       pf.lap(6);
     }
@@ -843,7 +854,8 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
         (rc = qmap(&p.tm_q1, a.q, a.q_stride, 1)) || (rc = qmap(&p.tm_do1, a.dout, a.do_stride, 1)) ||
         (rc = kmap(&p.tm_k2, a.k_cache, a.k_stride, 2)) || (rc = kmap(&p.tm_v2, a.v_cache, a.v_stride, 2)))
       return rc;
-    p.weights = a.weights; p.lse = a.lse; p.offsets = csr.offsets; p.sorted_keys = csr.sorted_keys;
+    p.weights = a.weights; p.lse = a.lse; p.unit_keys = csr.unit_keys; p.unit_vals = csr.unit_vals; p.unit_cmax = csr.unit_cmax; p.unit_cmask = csr.unit_cmask;
+    p.sorted_keys = csr.sorted_keys;
     p.dk = (__nv_bfloat16*)a.dk_cache; p.dv = (__nv_bfloat16*)a.dv_cache; p.status = a.status;
     p.prof = profile_buffer();
     for (int i = 0; i < 4; ++i) { p.dks[i] = a.dk_stride[i]; p.dvs[i] = a.dv_stride[i]; }

@@ -573,28 +573,30 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
       if (!ok) break;
       if (elected) GCA_TRACE(3, g - 1);
       tc_fence_after();
-      uint32_t o[64];
-      tmem_ld_32x32b_x32(tlane + TMEM_O + coff, o);
-      tmem_ld_32x32b_x32(tlane + TMEM_O + coff + 32, o + 32);
-      tmem_ld_wait();
+      // O leaves in four passes of ONE small loop body (16 columns: TMEM -> bf16 -> one 32-byte
+      // store per row): after the first pass the body is in the instruction cache, where a
+      // straight-line conversion of all 64 columns, executed once per unit, runs at
+      // instruction-fetch speed (~10 cycles per instruction measured)
+#pragma unroll 1
+      for (int part = 0; part < 4; ++part) {
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(tlane + TMEM_O + coff + part * 16, v);
+        tmem_ld_wait();
+        uint32_t wv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wv[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+        uint8_t* dst = reinterpret_cast<uint8_t*>(orow) + part * 32;
+        if (live && !GCA_DBG(4)) {
+          if (wide_store) st_global_256(dst, wv[0], wv[1], wv[2], wv[3], wv[4], wv[5], wv[6], wv[7]);
+          else {
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(wv[4], wv[5], wv[6], wv[7]);
+          }
+        }
+      }
       tc_fence_before();
       if (elected) GCA_TRACE(0, g - 1);
       mbar_arrive_warp(&bars[O_EMPTY], lane);
-      if (live && !GCA_DBG(4)) {
-        uint32_t wv[32];
-#pragma unroll
-        for (int cc = 0; cc < 32; ++cc) wv[cc] = pack_bf16x2(__uint_as_float(o[2 * cc]), __uint_as_float(o[2 * cc + 1]));
-        if (wide_store) {                   // full 32-byte sectors instead of eight 16-byte halves
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc)
-            st_global_256(reinterpret_cast<uint8_t*>(orow) + 32 * cc, wv[8 * cc], wv[8 * cc + 1], wv[8 * cc + 2],
-                          wv[8 * cc + 3], wv[8 * cc + 4], wv[8 * cc + 5], wv[8 * cc + 6], wv[8 * cc + 7]);
-        } else {
-#pragma unroll
-          for (int cc = 0; cc < 8; ++cc)
-            reinterpret_cast<uint4*>(orow)[cc] = make_uint4(wv[4 * cc], wv[4 * cc + 1], wv[4 * cc + 2], wv[4 * cc + 3]);
-        }
-      }
       if (elected) GCA_TRACE(6, g - 1);
     }
   }

@@ -64,55 +64,22 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 
 __device__ __forceinline__ float2 f2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
 
-// 64 float32 accumulator values of one row -> bf16 (scaled) -> 128 contiguous bytes in global
-// One accumulator row (64 float32 in `acc`) -> scaled bf16 -> 128 contiguous bytes at dst.
-// `wide`: dst is 32-byte aligned (checked on the host for the whole tensor).
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_t* acc, float scale, bool wide) {
+// 16 float32 accumulator values of one row -> scaled bf16 -> 32 contiguous bytes at dst.
+// `wide`: dst is 32-byte aligned (checked on the host for the whole tensor): one 256-bit store,
+// a full sector, instead of two 16-byte halves.
+__device__ __forceinline__ void store16_bf16(uint8_t* dst, const uint32_t* v, float scale, bool wide) {
   const float2 sv = make_float2(scale, scale);
-  uint32_t w[32];
+  uint32_t w[8];
 #pragma unroll
-  for (int c = 0; c < 32; ++c) {
-    const float2 a = __fmul2_rn(f2(acc[2 * c], acc[2 * c + 1]), sv);
-    w[c] = sm100::pack_bf16x2(a.x, a.y);
+  for (int i = 0; i < 8; ++i) {
+    const float2 a = __fmul2_rn(f2(v[2 * i], v[2 * i + 1]), sv);
+    w[i] = sm100::pack_bf16x2(a.x, a.y);
   }
-  if (wide) {
-#pragma unroll
-    for (int c = 0; c < 4; ++c)
-      sm100::st_global_256(reinterpret_cast<uint8_t*>(dst) + 32 * c, w[8 * c], w[8 * c + 1], w[8 * c + 2], w[8 * c + 3],
-                    w[8 * c + 4], w[8 * c + 5], w[8 * c + 6], w[8 * c + 7]);
-  } else {
-#pragma unroll
-    for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(dst)[c] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+  if (wide) sm100::st_global_256(dst, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+  else {
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
   }
-}
-
-// One warp, 32 accumulator rows (lane = row, 64 float32 each in `acc`) -> scaled bf16 -> global
-// rows dst_row0 + r * row_stride (elements), 128 contiguous bytes each.  Stored straight from
-// the registers every lane of a store instruction would touch a different line; through 4 KB of
-// this warp's shared memory (16-byte pieces, XOR-swizzled so that neither the writes nor the
-// reads have bank conflicts) every store instruction covers four whole rows instead.
-// The staging rows 0-15 start at `stage`, rows 16-31 at `stage + half` (half = 2048: contiguous).
-// Rows must be 16-byte aligned.  Ends with all lanes past their reads of the staging memory.
-__device__ __forceinline__ void store_rows_staged(uint8_t* stage, int half, __nv_bfloat16* dst_row0, long long row_stride,
-                                                  const uint32_t* acc, float scale, int lane) {
-  const float2 sv = make_float2(scale, scale);
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const float2 a0 = __fmul2_rn(f2(acc[8 * c + 0], acc[8 * c + 1]), sv), a1 = __fmul2_rn(f2(acc[8 * c + 2], acc[8 * c + 3]), sv);
-    const float2 a2 = __fmul2_rn(f2(acc[8 * c + 4], acc[8 * c + 5]), sv), a3 = __fmul2_rn(f2(acc[8 * c + 6], acc[8 * c + 7]), sv);
-    *reinterpret_cast<uint4*>(stage + (lane >> 4) * half + (lane & 15) * 128 + ((c ^ (lane & 7)) << 4)) =
-        make_uint4(sm100::pack_bf16x2(a0.x, a0.y), sm100::pack_bf16x2(a1.x, a1.y), sm100::pack_bf16x2(a2.x, a2.y),
-                   sm100::pack_bf16x2(a3.x, a3.y));
-  }
-  __syncwarp();
-  const int pc = lane & 7, r0 = lane >> 3;
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const int r = it * 4 + r0;
-    const uint4 v = *reinterpret_cast<const uint4*>(stage + (r >> 4) * half + (r & 15) * 128 + ((pc ^ (r & 7)) << 4));
-    reinterpret_cast<uint4*>(dst_row0 + r * row_stride)[pc] = v;
-  }
-  __syncwarp();
 }
 
 }  // namespace gca
