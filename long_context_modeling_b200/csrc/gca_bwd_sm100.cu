@@ -522,9 +522,7 @@ struct BwdKvParams {
   CUtensorMap tm_q2, tm_do2, tm_q1, tm_do1, tm_k2, tm_v2;
   const float* weights;
   const float* lse;
-  const unsigned* unit_keys;            // units in walking order (see Csr): count = cmax - (key & cmask),
-  const unsigned long long* unit_vals;  // value = chunk id << 32 | first entry
-  unsigned unit_cmax, unit_cmask;
+  const int4* unit_tab;     // units in walking order: (first entry, one past the last, chunk id n*C + c)
   const unsigned long long* sorted_keys;
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
@@ -545,11 +543,10 @@ __device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars,
   Ring ring; ring.init(NQ);
   uint32_t ucnt = 0, issued = 0;
   bool ok = true;
-  unsigned nkey = c.u < p.units ? p.unit_keys[c.outer] : p.unit_cmax;
-  unsigned long long nval = c.u < p.units ? p.unit_vals[c.outer] : 0ull;
+  int4 nxt = c.u < p.units ? p.unit_tab[c.outer] : make_int4(0, 0, 0, 0);
   for (; c.u < p.units && ok; c.advance()) {
-    const int beg = (int)(unsigned)nval, end = beg + (int)(p.unit_cmax - (nkey & p.unit_cmask)), chunk = (int)(nval >> 32);
-    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nkey = p.unit_keys[no]; nval = p.unit_vals[no]; }
+    const int beg = nxt.x, end = nxt.y, chunk = nxt.z;
+    if (c.u + (int)gridDim.x < p.units) nxt = p.unit_tab[c.next_outer()];
     if (end == beg) continue;
     const uint32_t un = ucnt++;
     const int hk0 = 2 * c.inner;
@@ -609,11 +606,10 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
   Ring ring; ring.init(NQ);
   uint32_t ucnt = 0, g = 0;
   bool ok = true;
-  unsigned nkey = c.u < p.units ? p.unit_keys[c.outer] : p.unit_cmax;
-  unsigned long long nval = c.u < p.units ? p.unit_vals[c.outer] : 0ull;
+  int4 nxt = c.u < p.units ? p.unit_tab[c.outer] : make_int4(0, 0, 0, 0);
   for (; c.u < p.units && ok; c.advance()) {
-    const int beg = (int)(unsigned)nval, end = beg + (int)(p.unit_cmax - (nkey & p.unit_cmask));
-    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nkey = p.unit_keys[no]; nval = p.unit_vals[no]; }
+    const int beg = nxt.x, end = nxt.y;
+    if (c.u + (int)gridDim.x < p.units) nxt = p.unit_tab[c.next_outer()];
     const int niter = (end - beg) * p.G;
     if (niter == 0) continue;
     const uint32_t un = ucnt++;
@@ -675,11 +671,10 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
   uint32_t epi = 0;                             // units this group has written out
   PhaseTimer pf;
   pf.init(false);
-  unsigned nkey = c.u < p.units ? p.unit_keys[c.outer] : p.unit_cmax;
-  unsigned long long nval = c.u < p.units ? p.unit_vals[c.outer] : 0ull;
+  int4 nxt = c.u < p.units ? p.unit_tab[c.outer] : make_int4(0, 0, 0, 0);
   for (; c.u < p.units && ok; c.advance()) {
-    const int beg = (int)(unsigned)nval, end = beg + (int)(p.unit_cmax - (nkey & p.unit_cmask)), chunk = (int)(nval >> 32);
-    if (c.u + (int)gridDim.x < p.units) { const int no = c.next_outer(); nkey = p.unit_keys[no]; nval = p.unit_vals[no]; }
+    const int beg = nxt.x, end = nxt.y, chunk = nxt.z;
+    if (c.u + (int)gridDim.x < p.units) nxt = p.unit_tab[c.next_outer()];
     const int hk = 2 * c.inner + tile;
     const bool live = hk < p.Hkv;
     const int n = chunk / p.C, ch = chunk - n * p.C;
@@ -854,8 +849,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
         (rc = qmap(&p.tm_q1, a.q, a.q_stride, 1)) || (rc = qmap(&p.tm_do1, a.dout, a.do_stride, 1)) ||
         (rc = kmap(&p.tm_k2, a.k_cache, a.k_stride, 2)) || (rc = kmap(&p.tm_v2, a.v_cache, a.v_stride, 2)))
       return rc;
-    p.weights = a.weights; p.lse = a.lse; p.unit_keys = csr.unit_keys; p.unit_vals = csr.unit_vals; p.unit_cmax = csr.unit_cmax; p.unit_cmask = csr.unit_cmask;
-    p.sorted_keys = csr.sorted_keys;
+    p.weights = a.weights; p.lse = a.lse; p.unit_tab = csr.unit_tab; p.sorted_keys = csr.sorted_keys;
     p.dk = (__nv_bfloat16*)a.dk_cache; p.dv = (__nv_bfloat16*)a.dv_cache; p.status = a.status;
     p.prof = profile_buffer();
     for (int i = 0; i < 4; ++i) { p.dks[i] = a.dk_stride[i]; p.dvs[i] = a.dv_stride[i]; }

@@ -43,18 +43,15 @@ struct Geom {
 // Inverse retrieval index: for every cache chunk (n, c) the sorted list of (j*K + k)
 // entries that retrieved it.  `offsets` has N*C + 1 entries into `sorted_keys`, whose low
 // 32 bits hold the entry.
-// `unit_keys` / `unit_vals` list the chunks in the order the kv-major tensor-core kernel walks
-// them: sequence by sequence, and inside a sequence by DECREASING number of retrievers.  Entry r:
-// number of retrievers = unit_cmax - (unit_keys[r] & unit_cmask); unit_vals[r] = chunk id
-// (n*C + c) << 32 | first entry.  CTAs take units round-robin, so every CTA gets chunks of every
-// size class; in chunk order the busiest CTA had 8 % more work than the average (chunks near the
-// start of a sequence are retrieved by many more queries than late ones).
+// `unit_tab` lists the chunks in the order the kv-major tensor-core kernel walks them: sequence
+// by sequence, and inside a sequence by DECREASING number of retrievers (x = first entry,
+// y = one past the last, z = chunk id n*C + c).  CTAs take units round-robin, so every CTA gets
+// chunks of every size class; in chunk order the busiest CTA had 8 % more work than the average
+// (chunks near the start of a sequence are retrieved by many more queries than late ones).
 struct Csr {
   const int* offsets;
   const unsigned long long* sorted_keys;
-  const unsigned* unit_keys;
-  const unsigned long long* unit_vals;
-  unsigned unit_cmax, unit_cmask;
+  const int4* unit_tab;
 };
 
 // launch == false: only lay the index out in `workspace` (it was built by an earlier call)

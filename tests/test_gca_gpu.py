@@ -231,6 +231,29 @@ def test_backward_stage_by_stage_equals_one_call(lcm, algo):
     assert lcm.read_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(2, 14, 4, 8), (3, 40, 2, 4), (1, 70, 4, 16)])
+def test_inverse_index_single_launch_equals_radix_sort(lcm, shape, monkeypatch):
+    """The single-launch counting sort that builds the inverse retrieval index for small problems
+    (stable by (query chunk, slot) inside a chunk; units walked by decreasing number of
+    retrievers) gives the bits of the radix-sort path: same entry order means the same float32
+    accumulation order in dK / dV."""
+    from long_context_modeling_b200 import gca as gmod
+    n, c, h, k = shape
+    q, kc, vc, idx, w, dout = (t.cuda() for t in cases.gca_indexed_case(41, n, c, h, k, dtype=torch.bfloat16))
+    idx = idx.clone()
+    idx[:, c // 2:, 0] = 0                               # many retrievers of one chunk
+    idx[:, -1, 1:] = -1                                  # padding slots
+    _, lse = gmod.gca_forward_with_lse(q, kc, vc, idx, w, 0.125)
+    monkeypatch.delenv("GCA_CSR_PATH", raising=False)
+    fast = gmod.gca_backward_stages(q, kc, vc, idx, w, dout, lse, 0.125)
+    monkeypatch.setenv("GCA_CSR_PATH", "sort")
+    slow = gmod.gca_backward_stages(q, kc, vc, idx, w, dout, lse, 0.125)
+    torch.cuda.synchronize()
+    for x, y in zip(fast, slow):
+        assert torch.equal(x, y)
+    assert lcm.read_status() == 0
+
+
 def test_host_pipeline_matches_direct_calls(lcm):
     """HostGcaPipeline (upload / kernels / download of consecutive steps overlapped on three
     streams) returns, step by step and in order, the bits of the plain calls."""
