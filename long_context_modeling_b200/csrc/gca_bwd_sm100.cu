@@ -19,6 +19,16 @@
 // N-contiguous B operand) are read through MN-major shared-memory descriptors spanning both
 // heads' tiles, so nothing is transposed in software.
 //
+// In the q-major kernel dS stays in TENSOR memory (bf16, two keys per 32-bit column, written by
+// the thread that computed the row) and is the A operand of the dQ product from there: shared
+// memory, whose 128 bytes per clock bound these 64-wide tiles, sees neither its store nor its
+// operand reads.  The kv-major kernel cannot do that for P^T / dS^T: a tensor-memory A operand
+// has lane = row of A, and there A's rows are keys while a worker thread holds a query row.
+// The kv-major kernel walks its units in the order the index build emits: per sequence by
+// decreasing number of retrievers, so that the round-robin share of every CTA is balanced.
+// Output tiles leave in rolled passes of 16 columns (one small loop body that stays in the
+// instruction cache) rather than as ~250 straight-line instructions executed once per unit.
+//
 // CTA = 12 warps: two worker warpgroups (thread = TMEM lane = row) taking alternate
 // iterations, one TMA producer, and THREE MMA issuers: S, dP and the gradient products each
 // have their own warp, because S and dP share one TMEM buffer each (the accumulators take
