@@ -171,17 +171,6 @@ __device__ __forceinline__ void drain(uint64_t* bars, int full0, uint32_t issued
   }
 }
 
-// Worker-group arrivals.  GCA_BWD_THREAD_ARRIVE: every thread arrives (barrier counts 128);
-// default: one arrival per warp after __syncwarp() (counts 4): 32 times fewer operations on the
-// barrier's shared-memory word, which sits on the path to the waiting MMA issuer.
-#ifdef GCA_BWD_THREAD_ARRIVE
-#define WG_ARRIVE(bar) mbar_arrive(bar)
-constexpr uint32_t WG_COUNT = 128;
-#else
-#define WG_ARRIVE(bar) mbar_arrive_warp(bar, lane)
-constexpr uint32_t WG_COUNT = 4;
-#endif
-
 // =============================================================================================
 // q-major kernel: dQ, dw
 // =============================================================================================
@@ -433,7 +422,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       tmem_ld_32x32b_x32(tlane + QCOL_DP + coff + 32, dp + 32);
       tmem_ld_wait();
       tc_fence_before();
-      WG_ARRIVE(&bars[SP_EMPTY]);
+      mbar_arrive(&bars[SP_EMPTY]);
       pf.lap(1);
       ok = mbar_wait_bounded(&bars[DS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
@@ -442,7 +431,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       tmem_st_32x32b_x32(tlane + QCOL_DS + sb * DS_COLS, s);
       tmem_st_wait();
       tc_fence_before();
-      WG_ARRIVE(&bars[DS_FULL + sb]);
+      mbar_arrive(&bars[DS_FULL + sb]);
       pf.lap(3);
       // dw: sum of Di over the 32 rows this warp holds of its tile -> one partial per warp
 #pragma unroll
@@ -468,7 +457,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
         if (live) store16_bf16(reinterpret_cast<uint8_t*>(dq_row) + part * 32, v, p.sm_scale, p.wide_store);
       }
       tc_fence_before();
-      WG_ARRIVE(&bars[DQ_EMPTY]);
+      mbar_arrive(&bars[DQ_EMPTY]);
       pf.lap(6);
     }
   }
@@ -489,11 +478,11 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[QDO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1);
       mbar_init(&bars[SP_FULL + i], 2);                              // S commit + dP commit
-      mbar_init(&bars[DS_FULL + i], WG_COUNT); mbar_init(&bars[DS_EMPTY + i], 1);
+      mbar_init(&bars[DS_FULL + i], 128); mbar_init(&bars[DS_EMPTY + i], 1);
       mbar_init(&bars[DQ_FULL + i], 1);
     }
-    mbar_init(&bars[DQ_EMPTY], WG_COUNT);
-    mbar_init(&bars[SP_EMPTY], WG_COUNT);
+    mbar_init(&bars[DQ_EMPTY], 128);
+    mbar_init(&bars[SP_EMPTY], 128);
     for (int i = 0; i < NKS; ++i) { mbar_init(&bars[K_FULL + i], 1); mbar_init(&bars[K_EMPTY + i], 1); }
     for (int i = 0; i < NVS; ++i) { mbar_init(&bars[V_FULL + i], 1); mbar_init(&bars[V_EMPTY + i], 1); }
     *abort_flag = 0;
@@ -749,7 +738,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         tmem_ld_32x32b_x32(tsp + COL_DPOFF + 32, dp + 32);
         tmem_ld_wait();
         tc_fence_before();
-        WG_ARRIVE(&bars[SP_EMPTY + sb]);
+        mbar_arrive(&bars[SP_EMPTY + sb]);
         pf.lap(1);
         if (elected) GCA_TRACE_BUF(p.prof, 8, g);
         ok = mbar_wait_bounded(&bars[PDS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
@@ -758,7 +747,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         uint8_t* base = smem + OFF_PDS + sb * 2 * PAIR_BYTES + tile_s * TILE_BYTES + row_s * 128;
         row_backward(s, dp, lse, p.c2, w, base, base + PAIR_BYTES, row_s);
         fence_proxy_async_smem();
-        WG_ARRIVE(&bars[PDS_FULL + sb]);
+        mbar_arrive(&bars[PDS_FULL + sb]);
         pf.lap(3);
         if (elected) GCA_TRACE_BUF(p.prof, 9, g);
       }
@@ -788,7 +777,7 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
                        p.wide_store);
       }
       tc_fence_before();
-      WG_ARRIVE(&bars[ACC_EMPTY]);
+      mbar_arrive(&bars[ACC_EMPTY]);
       if (elected) GCA_TRACE_BUF(p.prof, 12, un);
       if (elected) GCA_TRACE_BUF(p.prof, 13, un);
       pf.lap(6);
@@ -811,11 +800,11 @@ bwd_kv_tc_kernel(const __grid_constant__ BwdKvParams p) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[KV_FULL + i], 1); mbar_init(&bars[KV_EMPTY + i], 1);
       mbar_init(&bars[SP_FULL + i], 2);                              // S commit + dP commit
-      mbar_init(&bars[SP_EMPTY + i], WG_COUNT);
-      mbar_init(&bars[PDS_FULL + i], WG_COUNT); mbar_init(&bars[PDS_EMPTY + i], 1);
+      mbar_init(&bars[SP_EMPTY + i], 128);
+      mbar_init(&bars[PDS_FULL + i], 128); mbar_init(&bars[PDS_EMPTY + i], 1);
       mbar_init(&bars[ACC_FULL + i], 1);
     }
-    mbar_init(&bars[ACC_EMPTY], WG_COUNT);
+    mbar_init(&bars[ACC_EMPTY], 128);
     for (int i = 0; i < NQ; ++i) { mbar_init(&bars[QDO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
