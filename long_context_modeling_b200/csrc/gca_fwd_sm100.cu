@@ -58,6 +58,10 @@ constexpr int NWG = 3;                      // softmax warpgroups
 constexpr int NSB = 2;                      // S accumulators in tensor memory: slot g uses g % 2
 constexpr int NK = 6, NV = 6;               // K / V ring stages
 constexpr int ND = 4;                       // unit descriptors in flight
+#ifndef GCA_FWD_SKIP
+#define GCA_FWD_SKIP 4
+#endif
+constexpr int FWD_SKIP = GCA_FWD_SKIP;      // slots at the start of a unit that the previous unit's output writer sits out (even)
 constexpr int NTHREADS = (4 * NWG + 4) * 32;
 constexpr int KPROD_WARP = 4 * NWG, VPROD_WARP = KPROD_WARP + 1, SMMA_WARP = KPROD_WARP + 2;   // last warp: PV issuer
 // Tensor memory: S0 | S1 | O (128 columns each) | P0 P1 P2 (32 columns each).  P -- the bf16
@@ -275,8 +279,8 @@ __device__ void kproducer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* ba
       wgk = x - 3 * ((x * 86) >> 8);
 #else
       const int A = L + 1 == NWG ? 0 : L + 1, B = A + 1 == NWG ? 0 : A + 1;
-      const int y = r - 4, y3 = y - 3 * ((y * 86) >> 8);       // (r - 4) % 3 for 4 <= r < 32
-      wgk = r < 4 ? ((r & 1) ? B : A) : (y3 == 0 ? L : (y3 == 1 ? A : B));
+      const int y = r - FWD_SKIP, y3 = y - 3 * ((y * 86) >> 8);   // (r - FWD_SKIP) % 3 for FWD_SKIP <= r < 32
+      wgk = r < FWD_SKIP ? ((r & 1) ? B : A) : (y3 == 0 ? L : (y3 == 1 ? A : B));
 #endif
     }
     const int xs = (int)g0m6 + r, s6 = xs - 6 * ((xs * 43) >> 8);   // (g0 + r) % 6
