@@ -171,6 +171,20 @@ __device__ __forceinline__ void drain(uint64_t* bars, int full0, uint32_t issued
   }
 }
 
+// Output tiles leave in OUT_PASSES passes of OUT_COLS columns per row (see the epilogues).
+#ifndef GCA_OUT_COLS
+#define GCA_OUT_COLS 16
+#endif
+constexpr int OUT_COLS = GCA_OUT_COLS, OUT_PASSES = 64 / OUT_COLS;
+__device__ __forceinline__ void out_pass_load(uint32_t taddr, uint32_t* v) {
+  if (OUT_COLS == 32) tmem_ld_32x32b_x32(taddr, v); else tmem_ld_32x32b_x16(taddr, v);
+  tmem_ld_wait();
+}
+__device__ __forceinline__ void out_pass_store(uint8_t* dst, const uint32_t* v, float scale, bool wide) {
+  store16_bf16(dst, v, scale, wide);
+  if (OUT_COLS == 32) store16_bf16(dst + 32, v + 16, scale, wide);
+}
+
 // =============================================================================================
 // q-major kernel: dQ, dw
 // =============================================================================================
@@ -450,11 +464,10 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       // dQ leaves in four passes of one small loop body (16 columns: TMEM -> bf16 -> one 32-byte
       // store per row): after the first pass the body is in the instruction cache
 #pragma unroll 1
-      for (int part = 0; part < 4; ++part) {
-        uint32_t v[16];
-        tmem_ld_32x32b_x16(tlane + QCOL_DQ + coff + part * 16, v);
-        tmem_ld_wait();
-        if (live) store16_bf16(reinterpret_cast<uint8_t*>(dq_row) + part * 32, v, p.sm_scale, p.wide_store);
+      for (int part = 0; part < OUT_PASSES; ++part) {
+        uint32_t v[OUT_COLS];
+        out_pass_load(tlane + QCOL_DQ + coff + part * OUT_COLS, v);
+        if (live) out_pass_store(reinterpret_cast<uint8_t*>(dq_row) + part * OUT_COLS * 2, v, p.sm_scale, p.wide_store);
       }
       tc_fence_before();
       mbar_arrive(&bars[DQ_EMPTY]);
@@ -767,14 +780,14 @@ __device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       // unit) runs at instruction-fetch speed.
       if (elected) GCA_TRACE_BUF(p.prof, 11, un);
 #pragma unroll 1
-      for (int part = 0; part < 8; ++part) {
-        const bool is_dv = part >= 4;
-        uint32_t v[16];
-        tmem_ld_32x32b_x16(tlane + (is_dv ? COL_DV : COL_DK) + coff + (part & 3) * 16, v);
-        tmem_ld_wait();
+      for (int part = 0; part < 2 * OUT_PASSES; ++part) {
+        const bool is_dv = part >= OUT_PASSES;
+        const int pp = is_dv ? part - OUT_PASSES : part;
+        uint32_t v[OUT_COLS];
+        out_pass_load(tlane + (is_dv ? COL_DV : COL_DK) + coff + pp * OUT_COLS, v);
         if (live)
-          store16_bf16(reinterpret_cast<uint8_t*>(is_dv ? dv_row : dk_row) + (part & 3) * 32, v, is_dv ? 1.0f : p.sm_scale,
-                       p.wide_store);
+          out_pass_store(reinterpret_cast<uint8_t*>(is_dv ? dv_row : dk_row) + pp * OUT_COLS * 2, v, is_dv ? 1.0f : p.sm_scale,
+                         p.wide_store);
       }
       tc_fence_before();
       mbar_arrive(&bars[ACC_EMPTY]);

@@ -61,6 +61,10 @@ constexpr int ND = 4;                       // unit descriptors in flight
 #ifndef GCA_FWD_SKIP
 #define GCA_FWD_SKIP 4
 #endif
+#ifndef GCA_OUT_COLS
+#define GCA_OUT_COLS 16
+#endif
+constexpr int OUT_COLS = GCA_OUT_COLS;      // columns per pass of the output loop (16 or 32)
 constexpr int FWD_SKIP = GCA_FWD_SKIP;      // slots at the start of a unit that the previous unit's output writer sits out (even)
 constexpr int NTHREADS = (4 * NWG + 4) * 32;
 constexpr int KPROD_WARP = 4 * NWG, VPROD_WARP = KPROD_WARP + 1, SMMA_WARP = KPROD_WARP + 2;   // last warp: PV issuer
@@ -582,19 +586,24 @@ __device__ void softmax_role(const FwdTcParams& p, uint8_t* smem, uint64_t* bars
       // straight-line conversion of all 64 columns, executed once per unit, runs at
       // instruction-fetch speed (~10 cycles per instruction measured)
 #pragma unroll 1
-      for (int part = 0; part < 4; ++part) {
-        uint32_t v[16];
-        tmem_ld_32x32b_x16(tlane + TMEM_O + coff + part * 16, v);
+      for (int part = 0; part < 64 / OUT_COLS; ++part) {
+        uint32_t v[OUT_COLS];
+        if (OUT_COLS == 32) tmem_ld_32x32b_x32(tlane + TMEM_O + coff + part * OUT_COLS, v);
+        else tmem_ld_32x32b_x16(tlane + TMEM_O + coff + part * OUT_COLS, v);
         tmem_ld_wait();
-        uint32_t wv[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) wv[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-        uint8_t* dst = reinterpret_cast<uint8_t*>(orow) + part * 32;
         if (live && !GCA_DBG(4)) {
-          if (wide_store) st_global_256(dst, wv[0], wv[1], wv[2], wv[3], wv[4], wv[5], wv[6], wv[7]);
-          else {
-            reinterpret_cast<uint4*>(dst)[0] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-            reinterpret_cast<uint4*>(dst)[1] = make_uint4(wv[4], wv[5], wv[6], wv[7]);
+#pragma unroll
+          for (int h16 = 0; h16 < OUT_COLS / 16; ++h16) {
+            uint32_t wv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              wv[i] = pack_bf16x2(__uint_as_float(v[16 * h16 + 2 * i]), __uint_as_float(v[16 * h16 + 2 * i + 1]));
+            uint8_t* dst = reinterpret_cast<uint8_t*>(orow) + part * OUT_COLS * 2 + h16 * 32;
+            if (wide_store) st_global_256(dst, wv[0], wv[1], wv[2], wv[3], wv[4], wv[5], wv[6], wv[7]);
+            else {
+              reinterpret_cast<uint4*>(dst)[0] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+              reinterpret_cast<uint4*>(dst)[1] = make_uint4(wv[4], wv[5], wv[6], wv[7]);
+            }
           }
         }
       }
