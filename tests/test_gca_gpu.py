@@ -231,7 +231,7 @@ def test_backward_stage_by_stage_equals_one_call(lcm, algo):
     assert lcm.read_status() == 0
 
 
-@pytest.mark.parametrize("shape", [(2, 14, 4, 8), (3, 40, 2, 4), (1, 70, 4, 16)])
+@pytest.mark.parametrize("shape", [(2, 14, 4, 8), (3, 40, 2, 4), (1, 70, 4, 16), (8, 256, 2, 8), (1, 1024, 2, 4)])
 def test_inverse_index_single_launch_equals_radix_sort(lcm, shape, monkeypatch):
     """The single-launch counting sort that builds the inverse retrieval index for small problems
     (stable by (query chunk, slot) inside a chunk; units walked by decreasing number of
