@@ -311,10 +311,95 @@ def gpu_arm(args):
         line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
                                 "sample": "1 of the 8 sequences (256 chunks x 12 heads x top-8), fp32 einsum + "
                                           "gather + autograd, 2 timed steps"}
+    if rank == 0 and world == 1 and args.triton_ref:
+        del dev_sets, fwd_out, bufs
+        torch.cuda.empty_cache()
+        line["reference_triton_gpu"] = run_triton_ref_subprocess(N_SEQ)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------------
+# The reference's own Triton kernels on this GPU (a GPU-vs-GPU anchor beside the CPU baseline)
+# --------------------------------------------------------------------------------------------
+def triton_ref_arm(args):
+    """Times the reference's unmodified Triton GCA (`ltriton/gca.py`: `attention` = `_attention.apply`,
+    line 844), staged under oracle/_ref by oracle/make_ref.py, at the same workload: the K/V chunks
+    are first gathered and laid out as the reference model does (`model/DRT.py:193-199,321-332`),
+    then `attention` forward and forward + backward are timed with CUDA events.  Prints one JSON
+    object; on any failure the object carries `unavailable` with the reason."""
+    out = {"impl": "reference_triton", "what": "ltriton/gca.py attention fwd / fwd+bwd on pre-gathered chunks, same inputs"}
+    try:
+        import triton
+        out["triton"] = triton.__version__
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import make_ref
+        from oracle import gca_oracle as G
+        mod = make_ref.load()
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(0)
+        n_seq = args.n_seq
+        q, kc, vc, idx, w, dout = (t.to(dev) for t in make_inputs(0, n_seq))
+        z = n_seq * (CHUNKS - 1)
+
+        def ev_time(fn, reps):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps
+
+        gather = lambda: G.gather_chunks(kc, vc, idx, HEADS)     # noqa: E731  (advanced-index gather + head split + contiguous)
+        ms_gather = ev_time(gather, 5)
+        gk, gv = gather()
+        gk, gv = gk.contiguous().requires_grad_(), gv.contiguous().requires_grad_()
+        qz = q.reshape(z, HEADS, CHUNK, HEAD_DIM).contiguous().requires_grad_()
+        wz = torch.where(idx < 0, torch.zeros_like(w), w).reshape(z, TOPK).contiguous().requires_grad_()
+        dz = dout.reshape(z, HEADS, CHUNK, HEAD_DIM).contiguous()
+        scale = 1.0 / 8.0
+        ms_fwd = ev_time(lambda: mod.attention(qz, gk, gv, wz, scale, 0.0), 10)
+
+        def fwd_bwd():
+            o = mod.attention(qz, gk, gv, wz, scale, 0.0)
+            o.backward(dz)
+            qz.grad = gk.grad = gv.grad = wz.grad = None
+        ms_step = ev_time(fwd_bwd, 10)
+        flops = workload_flops(n_seq)
+        out.update({"n_seq": n_seq, "gather_ms": ms_gather, "fwd_ms": ms_fwd, "fwd_bwd_ms": ms_step,
+                    "fwd_tflops": flops / (ms_fwd * 1e-3) / 1e12,
+                    "fwd_bwd_tflops": flops * FWD_BWD_FACTOR / (ms_step * 1e-3) / 1e12,
+                    "fwd_bwd_with_gather_tflops": flops * FWD_BWD_FACTOR / ((ms_step + ms_gather) * 1e-3) / 1e12,
+                    "note": "backward excludes the scatter-add of the gathered dK/dV into the cache that the model's autograd adds"})
+    except BaseException as e:      # noqa: BLE001
+        out["unavailable"] = f"{type(e).__name__}: {str(e)[:400]}"
+    print(json.dumps(out), flush=True)
+
+
+def run_triton_ref_subprocess(n_seq: int, timeout_s: int = 420):
+    """The Triton leg in a process of its own (its JIT, autotuner and 8 GB of gathered tensors stay
+    out of this process), bounded in time."""
+    import subprocess
+    if not os.path.isfile(os.path.join(ROOT, "oracle", "_ref", "ltriton_gca.py")):
+        return {"unavailable": "oracle/_ref/ltriton_gca.py not staged"}
+    env = dict(os.environ)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        env.pop(k, None)
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--workload", "triton-ref", "--n-seq", str(n_seq)],
+                           capture_output=True, text=True, timeout=timeout_s, env=env)
+        for ln in reversed(r.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                return json.loads(ln)
+        return {"unavailable": f"no output (exit {r.returncode}): {r.stderr[-300:]}"}
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"did not finish within {timeout_s} s"}
 
 
 # --------------------------------------------------------------------------------------------
@@ -549,9 +634,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="gca", choices=["gca", "retrieval", "decode"],
+    ap.add_argument("--workload", default="gca", choices=["gca", "retrieval", "decode", "triton-ref"],
                     help="gca (default, the headline): GCA fwd+bwd at the DRT-16K shape; retrieval: landmark top-k over "
                          "a 16M-token cache; decode: one-row GCA for 32 sequences")
+    ap.add_argument("--triton-ref", action="store_true",
+                    help="gca workload, 1 GPU: also time the reference's own Triton kernels (staged under oracle/_ref) "
+                         "in a subprocess and add the result as `reference_triton_gpu`")
     ap.add_argument("--per-head", action="store_true", help="retrieval workload: one 64-d score and top-k per head")
     ap.add_argument("--n-seq", type=int, default=N_SEQ,
                     help="sequences per GPU (default: the DRT-16K batch of 8; smaller values are for profiling captures)")
@@ -563,6 +651,8 @@ def main():
         retrieval_arm(args)
     elif args.workload == "decode":
         decode_arm(args)
+    elif args.workload == "triton-ref":
+        triton_ref_arm(args)
     else:
         gpu_arm(args)
 

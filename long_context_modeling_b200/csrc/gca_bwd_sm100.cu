@@ -1,39 +1,31 @@
-// GCA backward on tcgen05 / TMEM / TMA, bf16, S = L = D = 64.  Two persistent kernels,
-// neither uses atomics, so gradients are bit-reproducible:
+// GCA backward, q-major pass (dQ, dw and the per-row terms the kv-major pass needs) on tcgen05 /
+// TMEM / TMA, bf16, S = L = D = 64, plus the launch sequence of the whole tensor-core backward.
 //
-//  * bwd_kv_tc_kernel  (kv-major)  unit = (sequence n, cache chunk c, PAIR of kv heads).
-//    K_c and V_c stay in shared memory; the kernel walks the inverse retrieval index (every
-//    (query chunk j, slot k) that retrieved chunk c, times the q heads of the group) and
-//    accumulates   dV_c += (w P)^T dO   and   dK_c += dS^T Q   in TMEM across all of them;
-//    the scatter-add of the reference's gather backward becomes one tile store per chunk.
-//  * bwd_q_tc_kernel   (q-major)   unit = (n, query chunk j, PAIR of q heads) as in the
-//    forward: dQ += dS K_k accumulated over the K slots in TMEM, and the per-head part of
-//    dw_k = sum_rows <dO, O_k> = sum_rows rowsum(P * dP).
+// Unit = (sequence n, query chunk j, PAIR of q heads) as in the forward.  Per retrieved slot the
+// kernel recomputes  S = Q K^T  and  dP = dO V^T;  one thread per query row forms
+// P = exp2(S c - LSE),  Di = rowsum(P * dP)  (which replaces the reference's extra o = v^T p^T
+// product, ltriton/gca.py:382),  dS = w P (dP - Di);  dQ += dS K_k accumulates over the K slots in
+// tensor memory, and the per-head parts of  dw_k = sum_rows Di  go to a partials buffer that a tiny
+// fixed-order kernel reduces.  The pair (-LSE, -Di) of every (row, slot) is also written to the
+// workspace: the kv-major pass (gca_bwd_kv_sm100.cu), which runs AFTER this one, needs both per
+// query row and then needs no row reduction of its own (the reference hands Di from one of its
+// two kernels to the other in the same way, ltriton/gca.py:385,459).
 //
-// Per (query tile, key tile) both kernels recompute  S = Q K^T  and  dP = dO V^T, then one
-// thread per query row forms  P = exp2(S c - LSE),  Di = rowsum(P*dP),  dS = w P (dP - Di)
-// and stages bf16 tiles for the follow-up MMAs.  As in the forward, the two heads of a pair
-// are stacked so that every tcgen05.mma is a 128-row instruction whose diagonal 64x64
-// blocks are the two heads' results (the issue cost of an MMA does not depend on its shape,
-// so fewer, larger instructions win).  Transposed operands (P^T, dS^T, and dO / Q / K as the
-// N-contiguous B operand) are read through MN-major shared-memory descriptors spanning both
-// heads' tiles, so nothing is transposed in software.
-//
-// In the q-major kernel dS stays in TENSOR memory (bf16, two keys per 32-bit column, written by
-// the thread that computed the row) and is the A operand of the dQ product from there: shared
-// memory, whose 128 bytes per clock bound these 64-wide tiles, sees neither its store nor its
-// operand reads.  The kv-major kernel cannot do that for P^T / dS^T: a tensor-memory A operand
-// has lane = row of A, and there A's rows are keys while a worker thread holds a query row.
-// The kv-major kernel walks its units in the order the index build emits: per sequence by
-// decreasing number of retrievers, so that the round-robin share of every CTA is balanced.
+// The two heads of a pair are stacked so that every tcgen05.mma is a 128-row instruction whose
+// diagonal 64x64 blocks are the two heads' results (the issue cost of an MMA does not depend on
+// its shape, so fewer, larger instructions win).  dS stays in TENSOR memory (bf16, two keys per
+// 32-bit column, written by the thread that computed the row) and is the A operand of the dQ
+// product from there: shared memory, whose 128 bytes per clock bound these 64-wide tiles, sees
+// neither its store nor its operand reads.  K as the N-contiguous B operand of that product is
+// read through an MN-major descriptor spanning both heads' tiles: nothing is transposed in software.
 // Output tiles leave in rolled passes of 16 columns (one small loop body that stays in the
-// instruction cache) rather than as ~250 straight-line instructions executed once per unit.
+// instruction cache) rather than as ~150 straight-line instructions executed once per unit.
 //
-// CTA = 12 warps: two worker warpgroups (thread = TMEM lane = row) taking alternate
-// iterations, one TMA producer, and THREE MMA issuers: S, dP and the gradient products each
-// have their own warp, because S and dP share one TMEM buffer each (the accumulators take
-// the rest of TMEM) and their issue latency therefore sits on the critical path of every
-// iteration.  Every wait is bounded (GCA_STATUS_TIMEOUT on expiry).
+// CTA = 12 warps: two worker warpgroups (thread = TMEM lane = row) taking alternate slots, one
+// TMA producer, and THREE MMA issuers: S, dP and dQ each have their own warp, because S and dP
+// share one TMEM buffer each and their issue latency sits on the critical path of every slot.
+// Neither pass uses atomics, so gradients are bit-reproducible.  Every wait is bounded
+// (GCA_STATUS_TIMEOUT on expiry).
 #include <cstdlib>
 
 #include "gca_common.cuh"
@@ -53,21 +45,12 @@ constexpr int TILE_BYTES = 64 * 64 * 2;
 constexpr int PAIR_BYTES = 2 * TILE_BYTES;
 constexpr uint32_t PAIR16 = PAIR_BYTES >> 4;
 constexpr int NTHREADS = 384;
-constexpr int PROD_WARP = 8, ISSUE_S = 9, ISSUE_DP = 10;   // warp 11: gradient-product issuer
+constexpr int PROD_WARP = 8, ISSUE_S = 9, ISSUE_DP = 10;   // warp 11: dQ issuer
 constexpr int TMEM_COLS = 512;
-// TMEM columns.  S and dP are computed per head with 64-row MMAs: a 64-row accumulator uses lanes
-// 0-15 of every 32-lane quarter, so head A's tile and head B's tile (written at lane offset 16)
-// share the same 64 columns.  One S/dP buffer = 128 columns (S at +0, dP at +64) and there are two
-// of them: iteration g+1's S and dP are computed while the workers still read iteration g's.
-// The gradient accumulators keep the stacked 128-row form (one instruction for both heads).
-constexpr uint32_t COL_SP = 0, SP_COLS = 128, COL_DPOFF = 64;
-// The q-major kernel keeps S and dP as single stacked 128-row tiles (measured faster there: its
-// iterations are bound by the K ring, not by the S/dP turnaround, and the 64-row form doubles
-// the S/dP instruction count).
+// S and dP are single stacked 128-row tiles (per-head 64-row products were measured 5 % slower
+// here: twice the S / dP instructions, and the slots are bound by the K ring, not by the S / dP
+// turnaround).
 constexpr uint32_t QCOL_S = 0, QCOL_DP = 128;
-constexpr uint32_t TILE16 = TILE_BYTES >> 4;
-constexpr uint32_t LANE16 = 16u << 16;            // TMEM lane offset of head B's 64-row tile
-constexpr uint32_t IDESC_64 = umma_idesc_bf16(64, 64, 0, 0);
 
 // Four K steps of one stacked product.  a_step / b_step: descriptor advance per K step of 16.
 // Called by ALL lanes of the issuing warp (converged, warp-uniform operands); elect.sync picks
@@ -80,57 +63,9 @@ __device__ __forceinline__ void mma4(uint32_t d, uint64_t a, uint64_t b, uint32_
   for (int kk = 0; kk < 4; ++kk) umma_bf16_ss_elect(d, a + kk * a_step, b + kk * b_step, idesc, (uint32_t)(accumulate_first || kk > 0));
 }
 
-// S or dP of both heads of a pair as two 64-row products (tile tl: A rows a + tl tile, B rows
-// b + tl * b_tile_step tile), each four K steps, into the same 64 columns.
-__device__ __forceinline__ void mma_pair64(uint32_t d, uint64_t a, uint64_t b, uint32_t b_tile_step) {
-#pragma unroll
-  for (int tl = 0; tl < 2; ++tl)
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk)
-      umma_bf16_ss_elect(d + (tl ? LANE16 : 0u), a + tl * TILE16 + kk * STEP_K, b + tl * b_tile_step + kk * STEP_K, IDESC_64,
-                         (uint32_t)(kk > 0));
-}
-
-// One thread, one query row.  s: raw scores (overwritten by P), dp: raw dP.  Writes dS
-// (and w*P when pw_row != nullptr) as bf16 into swizzled [row][key] tiles; returns Di.
-__device__ __forceinline__ float row_backward(uint32_t* s, const uint32_t* dp, float lse, float c2, float w,
-                                              uint8_t* pw_row, uint8_t* ds_row, int row) {
-  const float2 c2v = make_float2(c2, c2), nl = make_float2(-lse, -lse);
-  float2 d0 = make_float2(0.f, 0.f), d1 = d0, d2 = d0, d3 = d0;
-#pragma unroll
-  for (int c = 0; c < 64; c += 8) {
-    float2 a0 = __ffma2_rn(f2(s[c + 0], s[c + 1]), c2v, nl), a1 = __ffma2_rn(f2(s[c + 2], s[c + 3]), c2v, nl);
-    float2 a2 = __ffma2_rn(f2(s[c + 4], s[c + 5]), c2v, nl), a3 = __ffma2_rn(f2(s[c + 6], s[c + 7]), c2v, nl);
-    a0.x = ex2_approx(a0.x); a0.y = ex2_approx(a0.y); a1.x = ex2_approx(a1.x); a1.y = ex2_approx(a1.y);
-    a2.x = ex2_approx(a2.x); a2.y = ex2_approx(a2.y); a3.x = ex2_approx(a3.x); a3.y = ex2_approx(a3.y);
-    d0 = __ffma2_rn(a0, f2(dp[c + 0], dp[c + 1]), d0); d1 = __ffma2_rn(a1, f2(dp[c + 2], dp[c + 3]), d1);
-    d2 = __ffma2_rn(a2, f2(dp[c + 4], dp[c + 5]), d2); d3 = __ffma2_rn(a3, f2(dp[c + 6], dp[c + 7]), d3);
-    s[c + 0] = __float_as_uint(a0.x); s[c + 1] = __float_as_uint(a0.y); s[c + 2] = __float_as_uint(a1.x); s[c + 3] = __float_as_uint(a1.y);
-    s[c + 4] = __float_as_uint(a2.x); s[c + 5] = __float_as_uint(a2.y); s[c + 6] = __float_as_uint(a3.x); s[c + 7] = __float_as_uint(a3.y);
-  }
-  const float2 dsum = __fadd2_rn(__fadd2_rn(d0, d1), __fadd2_rn(d2, d3));
-  const float di = dsum.x + dsum.y;
-  const float2 wv = make_float2(w, w), ndi = make_float2(-di, -di);
-  const int sw = row & 7;
-#pragma unroll
-  for (int c8 = 0; c8 < 8; ++c8) {
-    const float2 p0 = __fmul2_rn(f2(s[8 * c8 + 0], s[8 * c8 + 1]), wv), p1 = __fmul2_rn(f2(s[8 * c8 + 2], s[8 * c8 + 3]), wv);
-    const float2 p2 = __fmul2_rn(f2(s[8 * c8 + 4], s[8 * c8 + 5]), wv), p3 = __fmul2_rn(f2(s[8 * c8 + 6], s[8 * c8 + 7]), wv);
-    if (pw_row)
-      *reinterpret_cast<uint4*>(pw_row + ((c8 ^ sw) << 4)) =
-          make_uint4(pack_bf16x2(p0.x, p0.y), pack_bf16x2(p1.x, p1.y), pack_bf16x2(p2.x, p2.y), pack_bf16x2(p3.x, p3.y));
-    const float2 e0 = __fmul2_rn(p0, __fadd2_rn(f2(dp[8 * c8 + 0], dp[8 * c8 + 1]), ndi));
-    const float2 e1 = __fmul2_rn(p1, __fadd2_rn(f2(dp[8 * c8 + 2], dp[8 * c8 + 3]), ndi));
-    const float2 e2 = __fmul2_rn(p2, __fadd2_rn(f2(dp[8 * c8 + 4], dp[8 * c8 + 5]), ndi));
-    const float2 e3 = __fmul2_rn(p3, __fadd2_rn(f2(dp[8 * c8 + 6], dp[8 * c8 + 7]), ndi));
-    *reinterpret_cast<uint4*>(ds_row + ((c8 ^ sw) << 4)) =
-        make_uint4(pack_bf16x2(e0.x, e0.y), pack_bf16x2(e1.x, e1.y), pack_bf16x2(e2.x, e2.y), pack_bf16x2(e3.x, e3.y));
-  }
-  return di;
-}
-
-// Same row, for the q-major kernel: dS stays in registers, packed two keys per word in key order
-// (the layout of an A operand in tensor memory); w*P is not needed there.  ds may alias s.
+// One thread, one query row.  s: raw scores (overwritten by P), dp: raw dP.  dS stays in registers,
+// packed two keys per word in key order (the layout of an A operand in tensor memory).  ds may
+// alias s.  Returns Di = rowsum(P * dP).
 __device__ __forceinline__ float row_backward_packed(uint32_t* s, const uint32_t* dp, float lse, float c2, float w,
                                                      uint32_t* ds) {
   const float2 c2v = make_float2(c2, c2), nl = make_float2(-lse, -lse);
@@ -214,6 +149,7 @@ struct BwdQParams {
   const float* lse;
   __nv_bfloat16* dq;
   float* dw_part;           // (N*J, Hq, K, 2): two half-tile partials per (row block, head, slot)
+  float2* nld;              // (N*J, Hq, K, 64): (-lse, -Di) per (row block, head, slot, row), for the kv-major pass
   int32_t* status;
   long long* prof;
   long long dqs[4];
@@ -408,7 +344,9 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     if (mask == 0) continue;
     const uint32_t un = ucnt++;
     const uint32_t ub = un & 1;
-    const float* lse_base = p.lse + ((long long)c.outer * p.Hq + (live ? h : t.h0)) * p.K * 64 + row;
+    const long long row_off = ((long long)c.outer * p.Hq + (live ? h : t.h0)) * p.K * 64 + row;
+    const float* lse_base = p.lse + row_off;
+    float2* nld_base = p.nld + row_off;
     pf.lap(10);
     bool my_unit = false;                       // this group owns the unit's last slot: it writes dQ
     for (unsigned m = mask; m; m &= m - 1, ++g) {
@@ -442,6 +380,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(2);
       float di = row_backward_packed(s, dp, lse, p.c2, w, s);
+      if (live) nld_base[k * 64] = make_float2(-lse, -di);
       tmem_st_32x32b_x32(tlane + QCOL_DS + sb * DS_COLS, s);
       tmem_st_wait();
       tc_fence_before();
@@ -520,327 +459,6 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
 }
 
-// =============================================================================================
-// kv-major kernel: dK, dV
-// =============================================================================================
-namespace kv {
-// Shared memory: a Q/dO stage is held from its TMA copy until the iteration's dK/dV products
-// are done (copy latency + S/dP + worker math + gradient MMAs, ~6,000 cycles), so the ring depth
-// (3) sets the iteration rate.  A fourth stage at the price of a single K/V buffer (NQ = 4,
-// NKV = 1) was measured slower (0.96 ms against 0.90 ms): every unit then starts with an exposed
-// K/V copy.
-constexpr int NQ = 3, NKV = 2;
-constexpr int OFF_KV = 0;                                    // [NKV][K pair | V pair]
-constexpr int OFF_QDO = OFF_KV + NKV * 2 * PAIR_BYTES;       // [NQ][Q pair | dO pair]
-constexpr int OFF_PDS = OFF_QDO + NQ * 2 * PAIR_BYTES;       // [2 bufs][Pw pair | dS pair]
-constexpr int OFF_BAR = OFF_PDS + 2 * 2 * PAIR_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
-enum Bar { KV_FULL = 0, KV_EMPTY = 2, QDO_FULL = 4, QDO_EMPTY = QDO_FULL + NQ, SP_FULL = QDO_EMPTY + NQ,
-           SP_EMPTY = SP_FULL + 2, PDS_FULL = SP_EMPTY + 2, PDS_EMPTY = PDS_FULL + 2, ACC_FULL = PDS_EMPTY + 2,
-           ACC_EMPTY = ACC_FULL + 2, NUM_BARS = ACC_EMPTY + 1 };
-constexpr uint32_t COL_DK = 256, COL_DV = 384;
-}  // namespace kv
-
-struct BwdKvParams {
-  CUtensorMap tm_q2, tm_do2, tm_q1, tm_do1, tm_k2, tm_v2;
-  const float* weights;
-  const float* lse;
-  const int4* unit_tab;     // units in walking order: (first entry, one past the last, chunk id n*C + c)
-  const unsigned long long* sorted_keys;
-  __nv_bfloat16* dk;
-  __nv_bfloat16* dv;
-  int32_t* status;
-  long long* prof;
-  long long dks[4], dvs[4];
-  int units;
-  int N, J, Hq, Hkv, G, K, C, HP;
-  int wide_store;           // dk / dv rows are 32-byte aligned: 256-bit stores
-  float c2, sm_scale;
-};
-
-// One lane: K + V per unit, Q + dO per iteration.
-__device__ void kv_producer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
-  using namespace kv;
-  PairCursor c;
-  c.init(p.HP);
-  Ring ring; ring.init(NQ);
-  uint32_t ucnt = 0, issued = 0;
-  bool ok = true;
-  int4 nxt = c.u < p.units ? p.unit_tab[c.outer] : make_int4(0, 0, 0, 0);
-  for (; c.u < p.units && ok; c.advance()) {
-    const int beg = nxt.x, end = nxt.y, chunk = nxt.z;
-    if (c.u + (int)gridDim.x < p.units) nxt = p.unit_tab[c.next_outer()];
-    if (end == beg) continue;
-    const uint32_t un = ucnt++;
-    const int hk0 = 2 * c.inner;
-    const bool two = hk0 + 1 < p.Hkv;
-    const int n = chunk / p.C, ch = chunk - n * p.C;
-    {
-      const uint32_t kb = un % NKV;
-      ok = mbar_wait_bounded(&bars[KV_EMPTY + kb], ((un / NKV) & 1) ^ 1, abort_flag);
-      if (!ok) break;
-      uint8_t* base = smem + OFF_KV + kb * 2 * PAIR_BYTES;
-      mbar_arrive_expect_tx(&bars[KV_FULL + kb], 2 * PAIR_BYTES);
-      tma_load_5d(base, &p.tm_k2, &bars[KV_FULL + kb], 0, 0, hk0, ch, n);
-      tma_load_5d(base + PAIR_BYTES, &p.tm_v2, &bars[KV_FULL + kb], 0, 0, hk0, ch, n);
-    }
-    for (int e = beg; e < end && ok; ++e) {
-      const int entry = (int)(p.sorted_keys[e] & 0xffffffffull);
-      const int j = entry / p.K;
-      for (int gi = 0; gi < p.G; ++gi) {
-        ok = mbar_wait_bounded(&bars[QDO_EMPTY + ring.st], ring.ph ^ 1, abort_flag);
-        if (!ok) break;
-        uint8_t* dst = smem + OFF_QDO + ring.st * 2 * PAIR_BYTES;
-        GCA_TRACE_BUF(p.prof, 0, issued);
-        mbar_arrive_expect_tx(&bars[QDO_FULL + ring.st], 2 * PAIR_BYTES);
-        if (p.G == 1) {
-          tma_load_5d(dst, &p.tm_q2, &bars[QDO_FULL + ring.st], 0, 0, hk0, j, n);
-          tma_load_5d(dst + PAIR_BYTES, &p.tm_do2, &bars[QDO_FULL + ring.st], 0, 0, hk0, j, n);
-        } else {      // the two q heads of the pair are G apart: one copy per head
-          const int ha = hk0 * p.G + gi, hb = two ? (hk0 + 1) * p.G + gi : ha;
-          tma_load_5d(dst, &p.tm_q1, &bars[QDO_FULL + ring.st], 0, 0, ha, j, n);
-          tma_load_5d(dst + TILE_BYTES, &p.tm_q1, &bars[QDO_FULL + ring.st], 0, 0, hb, j, n);
-          tma_load_5d(dst + PAIR_BYTES, &p.tm_do1, &bars[QDO_FULL + ring.st], 0, 0, ha, j, n);
-          tma_load_5d(dst + PAIR_BYTES + TILE_BYTES, &p.tm_do1, &bars[QDO_FULL + ring.st], 0, 0, hb, j, n);
-        }
-        ring.next();
-        ++issued;
-      }
-    }
-  }
-  if (*abort_flag) {
-    drain(bars, QDO_FULL, issued, NQ);
-    drain(bars, KV_FULL, ucnt, NKV);
-  }
-}
-
-// role 0: S per iteration;  role 1: dP per iteration;  role 2: dV and dK per iteration
-template <int ROLE>
-__device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int lane,
-                          uint32_t tmem_base) {
-  using namespace kv;
-  const uint64_t dKV = umma_desc_sw128(smem_u32(smem + OFF_KV));
-  const uint64_t dQDO = umma_desc_sw128(smem_u32(smem + OFF_QDO));
-  const uint64_t dQDOmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_QDO), TILE_BYTES);
-  const uint64_t dPDSmn = umma_desc_sw128_mn_blocks(smem_u32(smem + OFF_PDS), TILE_BYTES);
-  constexpr uint32_t IDESC_MM = umma_idesc_bf16(128, 128, 1, 1);
-  PairCursor c;
-  c.init(p.HP);
-  Ring ring; ring.init(NQ);
-  uint32_t ucnt = 0, g = 0;
-  bool ok = true;
-  int4 nxt = c.u < p.units ? p.unit_tab[c.outer] : make_int4(0, 0, 0, 0);
-  for (; c.u < p.units && ok; c.advance()) {
-    const int beg = nxt.x, end = nxt.y;
-    if (c.u + (int)gridDim.x < p.units) nxt = p.unit_tab[c.next_outer()];
-    const int niter = (end - beg) * p.G;
-    if (niter == 0) continue;
-    const uint32_t un = ucnt++;
-    const uint32_t kb = un % NKV;
-    if (ROLE != 2) ok = mbar_wait_warp(&bars[KV_FULL + kb], (un / NKV) & 1, abort_flag, lane);
-    else ok = mbar_wait_warp(&bars[ACC_EMPTY], (un & 1) ^ 1, abort_flag, lane);
-    for (int i = 0; i < niter && ok; ++i, ++g) {
-      const uint64_t stage = ring.st * 2 * PAIR16;
-      if (ROLE != 2) {
-        ok = mbar_wait_warp(&bars[QDO_FULL + ring.st], ring.ph, abort_flag, lane);
-        if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 1, g);
-        const uint32_t spb = g & 1;                       // S/dP buffer = worker group of this iteration
-        if (ok) ok = mbar_wait_warp(&bars[SP_EMPTY + spb], ((g >> 1) & 1) ^ 1, abort_flag, lane);
-        if (!ok) break;
-        if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 2, g);
-        tc_fence_after();
-        const uint64_t kd = dKV + kb * 2 * PAIR16;
-        if (ROLE == 0) mma_pair64(tmem_base + COL_SP + spb * SP_COLS, dQDO + stage, kd, TILE16);
-        else mma_pair64(tmem_base + COL_SP + spb * SP_COLS + COL_DPOFF, dQDO + stage + PAIR16, kd + PAIR16, TILE16);
-        umma_commit_elect(&bars[SP_FULL + spb]);
-        if (lane == 0) GCA_TRACE_BUF(p.prof, 3 + ROLE, g);
-      } else {
-        const uint32_t sb = g & 1;
-        ok = mbar_wait_warp(&bars[PDS_FULL + sb], (g >> 1) & 1, abort_flag, lane);
-        if (!ok) break;
-        if (lane == 0) GCA_TRACE_BUF(p.prof, 5, g);
-        tc_fence_after();
-        const uint64_t pd = dPDSmn + sb * 2 * PAIR16;
-        // dV += (w P)^T dO : A = Pw read transposed (MN-major), B = dO (MN-major)
-        mma4(tmem_base + COL_DV, pd, dQDOmn + stage + PAIR16, IDESC_MM, STEP_MN, STEP_MN, i > 0);
-        // dK += dS^T Q
-        mma4(tmem_base + COL_DK, pd + PAIR16, dQDOmn + stage, IDESC_MM, STEP_MN, STEP_MN, i > 0);
-        umma_commit_elect(&bars[PDS_EMPTY + sb]);
-        umma_commit_elect(&bars[QDO_EMPTY + ring.st]);   // Q / dO of this iteration are free once dV, dK are done
-        if (i == niter - 1) umma_commit_elect(&bars[ACC_FULL + sb]);   // written out by the last iteration's worker group
-        if (lane == 0) GCA_TRACE_BUF(p.prof, 6, g);
-      }
-      ring.next();
-    }
-  }
-}
-
-__device__ void kv_worker(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
-                          int quad, int lane, uint32_t tmem_base) {
-  using namespace kv;
-  // two thread -> (head tile, row) maps: the stacked 128-row accumulators (dK, dV) put head A in
-  // TMEM lanes 0-63; the 64-row S / dP tiles interleave the heads in 16-lane runs
-  const int tile = quad >> 1;
-  const int row = (quad & 1) * 32 + lane;
-  const int tile_s = lane >> 4;
-  const int row_s = quad * 16 + (lane & 15);
-  const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
-  const uint32_t coff = (uint32_t)tile * 64u;
-  const bool elected = quad == 0 && lane == 0;
-  PairCursor c;
-  c.init(p.HP);
-  uint32_t ucnt = 0, g = 0;
-  bool ok = true;
-  uint32_t epi = 0;                             // units this group has written out
-  PhaseTimer pf;
-  pf.init(false);
-  int4 nxt = c.u < p.units ? p.unit_tab[c.outer] : make_int4(0, 0, 0, 0);
-  for (; c.u < p.units && ok; c.advance()) {
-    const int beg = nxt.x, end = nxt.y, chunk = nxt.z;
-    if (c.u + (int)gridDim.x < p.units) nxt = p.unit_tab[c.next_outer()];
-    const int hk = 2 * c.inner + tile;
-    const bool live = hk < p.Hkv;
-    const int n = chunk / p.C, ch = chunk - n * p.C;
-    __nv_bfloat16* dk_row = p.dk + n * p.dks[0] + ch * p.dks[1] + row * p.dks[2] + hk * p.dks[3];
-    __nv_bfloat16* dv_row = p.dv + n * p.dvs[0] + ch * p.dvs[1] + row * p.dvs[2] + hk * p.dvs[3];
-    if (end == beg) {
-      if (wg == 0 && live) {
-        const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc) { reinterpret_cast<uint4*>(dk_row)[cc] = z; reinterpret_cast<uint4*>(dv_row)[cc] = z; }
-      }
-      continue;
-    }
-    const uint32_t un = ucnt++;
-    const uint32_t kb = un % NKV;
-    if (elected && p.prof != nullptr && blockIdx.x == 0 && un < 256u) p.prof[64 + 14 * 256 + un] = g;
-    const int hk_safe = (2 * c.inner + tile_s < p.Hkv) ? 2 * c.inner + tile_s : 2 * c.inner;   // head of the S / dP row
-    bool my_unit = false;                     // this group ran the unit's last iteration: it writes dK, dV
-    for (int e = beg; e < end && ok; ++e) {
-      float w = 0.f;
-      long long zj = 0;
-      int k = 0;
-      bool fetched = false;            // (zj, k, w) of an entry are needed only for this group's iterations
-      for (int gi = 0; gi < p.G; ++gi, ++g) {
-        my_unit = (int)(g & 1) == wg;
-        if (!my_unit) continue;
-        if (!fetched) {
-          const int entry = (int)(p.sorted_keys[e] & 0xffffffffull);
-          const int j = entry / p.K;
-          k = entry - j * p.K;
-          zj = (long long)n * p.J + j;
-          w = p.weights[zj * p.K + k];
-          fetched = true;
-        }
-        const bool last = (e == end - 1) && (gi == p.G - 1);
-        const int h = hk_safe * p.G + gi;
-        const float lse = p.lse[((zj * p.Hq + h) * p.K + k) * 64 + row_s];
-        const uint32_t sb = g & 1;
-        pf.lap(7);
-        ok = mbar_wait_bounded(&bars[SP_FULL + sb], (g >> 1) & 1, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-        pf.lap(0);
-        if (elected) GCA_TRACE_BUF(p.prof, 7, g);
-        if (elected && last) mbar_arrive(&bars[KV_EMPTY + kb]);     // the unit's K/V tiles are no longer needed
-        tc_fence_after();
-        uint32_t s[64], dp[64];
-        const uint32_t tsp = tlane + COL_SP + sb * SP_COLS;      // this group's S/dP buffer
-        tmem_ld_32x32b_x32(tsp, s);
-        tmem_ld_32x32b_x32(tsp + 32, s + 32);
-        tmem_ld_32x32b_x32(tsp + COL_DPOFF, dp);
-        tmem_ld_32x32b_x32(tsp + COL_DPOFF + 32, dp + 32);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(&bars[SP_EMPTY + sb]);
-        pf.lap(1);
-        if (elected) GCA_TRACE_BUF(p.prof, 8, g);
-        ok = mbar_wait_bounded(&bars[PDS_EMPTY + sb], ((g >> 1) & 1) ^ 1, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-        pf.lap(2);
-        uint8_t* base = smem + OFF_PDS + sb * 2 * PAIR_BYTES + tile_s * TILE_BYTES + row_s * 128;
-        row_backward(s, dp, lse, p.c2, w, base, base + PAIR_BYTES, row_s);
-        fence_proxy_async_smem();
-        mbar_arrive(&bars[PDS_FULL + sb]);
-        pf.lap(3);
-        if (elected) GCA_TRACE_BUF(p.prof, 9, g);
-      }
-    }
-    if (!ok) break;
-    if (my_unit) {
-      pf.lap(7);
-      if (elected) GCA_TRACE_BUF(p.prof, 10, un);
-      ok = mbar_wait_bounded(&bars[ACC_FULL + wg], epi & 1, abort_flag);
-      ++epi;
-      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-      pf.lap(5);
-      tc_fence_after();
-      // The two tiles leave in eight passes of ONE small loop body (16 columns: TMEM -> bf16 ->
-      // one 32-byte store per row): after the first pass the body is in the instruction cache,
-      // where a straight-line conversion of all 128 columns (~250 instructions, executed once per
-      // unit) runs at instruction-fetch speed.
-      if (elected) GCA_TRACE_BUF(p.prof, 11, un);
-#pragma unroll 1
-      for (int part = 0; part < 2 * OUT_PASSES; ++part) {
-        const bool is_dv = part >= OUT_PASSES;
-        const int pp = is_dv ? part - OUT_PASSES : part;
-        uint32_t v[OUT_COLS];
-        out_pass_load(tlane + (is_dv ? COL_DV : COL_DK) + coff + pp * OUT_COLS, v);
-        if (live)
-          out_pass_store(reinterpret_cast<uint8_t*>(is_dv ? dv_row : dk_row) + pp * OUT_COLS * 2, v, is_dv ? 1.0f : p.sm_scale,
-                         p.wide_store);
-      }
-      tc_fence_before();
-      mbar_arrive(&bars[ACC_EMPTY]);
-      if (elected) GCA_TRACE_BUF(p.prof, 12, un);
-      if (elected) GCA_TRACE_BUF(p.prof, 13, un);
-      pf.lap(6);
-    }
-  }
-  pf.lap(7);
-  pf.dump(p.prof + 72);
-}
-
-__global__ void __launch_bounds__(NTHREADS, 1)
-bwd_kv_tc_kernel(const __grid_constant__ BwdKvParams p) {
-  using namespace kv;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + NUM_BARS + 1);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars[KV_FULL + i], 1); mbar_init(&bars[KV_EMPTY + i], 1);
-      mbar_init(&bars[SP_FULL + i], 2);                              // S commit + dP commit
-      mbar_init(&bars[SP_EMPTY + i], 128);
-      mbar_init(&bars[PDS_FULL + i], 128); mbar_init(&bars[PDS_EMPTY + i], 1);
-      mbar_init(&bars[ACC_FULL + i], 1);
-    }
-    mbar_init(&bars[ACC_EMPTY], 128);
-    for (int i = 0; i < NQ; ++i) { mbar_init(&bars[QDO_FULL + i], 1); mbar_init(&bars[QDO_EMPTY + i], 1); }
-    *abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == ISSUE_S) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-  if (warp == PROD_WARP && lane == 0) {
-    tma_prefetch_desc(&p.tm_q2); tma_prefetch_desc(&p.tm_do2); tma_prefetch_desc(&p.tm_k2); tma_prefetch_desc(&p.tm_v2);
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  if (warp < 8) kv_worker(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
-  else if (warp == PROD_WARP) { if (lane == 0) kv_producer(p, smem, bars, abort_flag); }
-  else if (warp == ISSUE_S) kv_issuer<0>(p, smem, bars, abort_flag, lane, tmem_base);
-  else if (warp == ISSUE_DP) kv_issuer<1>(p, smem, bars, abort_flag, lane, tmem_base);
-  else kv_issuer<2>(p, smem, bars, abort_flag, lane, tmem_base);
-  tc_fence_before();
-  __syncthreads();
-  if (warp == ISSUE_S) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
-}
-
 }  // namespace
 
 bool bwd_tc_available() { return true; }
@@ -853,7 +471,12 @@ static bool rows_32b_aligned(const void* base, const int64_t* stride) {
   return true;
 }
 
-int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream, unsigned stages) {
+int launch_bwd_kv_tc(const GcaBwdArgs& a, const Csr& csr, const float2* nld, int sms, cudaStream_t stream);
+
+// Stage order inside one call: the q-major pass first (it writes the (-lse, -Di) rows), then the
+// kv-major pass, which reads them.  A caller that runs the stages in separate calls must keep
+// that order on the stream (or synchronise between them).
+int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, float2* nld, cudaStream_t stream, unsigned stages) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;
   int dev = 0, sms = 0;
   GCA_CUDA_CHECK(cudaGetDevice(&dev));
@@ -866,30 +489,6 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
   auto kmap = [&](CUtensorMap* m, const void* base, const int64_t* st, int box) {
     return make_tile_map_5d(m, base, 64, 64, a.Hkv, a.C, a.N, st[2], st[3], st[1], st[0], box);
   };
-  if (stages & GCA_BWD_STAGE_KV) {
-    BwdKvParams p;
-    if ((rc = qmap(&p.tm_q2, a.q, a.q_stride, 2)) || (rc = qmap(&p.tm_do2, a.dout, a.do_stride, 2)) ||
-        (rc = qmap(&p.tm_q1, a.q, a.q_stride, 1)) || (rc = qmap(&p.tm_do1, a.dout, a.do_stride, 1)) ||
-        (rc = kmap(&p.tm_k2, a.k_cache, a.k_stride, 2)) || (rc = kmap(&p.tm_v2, a.v_cache, a.v_stride, 2)))
-      return rc;
-    p.weights = a.weights; p.lse = a.lse; p.unit_tab = csr.unit_tab; p.sorted_keys = csr.sorted_keys;
-    p.dk = (__nv_bfloat16*)a.dk_cache; p.dv = (__nv_bfloat16*)a.dv_cache; p.status = a.status;
-    p.prof = profile_buffer();
-    for (int i = 0; i < 4; ++i) { p.dks[i] = a.dk_stride[i]; p.dvs[i] = a.dv_stride[i]; }
-    p.N = a.N; p.J = a.J; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = a.Hq / a.Hkv; p.K = a.K; p.C = a.C;
-    p.HP = (a.Hkv + 1) / 2;
-    const long long units = (long long)a.N * a.C * p.HP;
-    if (units >= (1ll << 31) - 65536) return GCA_ERR_TOO_LARGE;
-    p.units = (int)units;
-    p.c2 = c2; p.sm_scale = a.sm_scale;
-    p.wide_store = rows_32b_aligned(a.dk_cache, a.dk_stride) && rows_32b_aligned(a.dv_cache, a.dv_stride);
-    if (p.units > 0) {
-      GCA_CUDA_CHECK(cudaFuncSetAttribute(bwd_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kv::SMEM_BYTES));
-      const unsigned grid = (unsigned)(p.units < sms ? p.units : sms);
-      bwd_kv_tc_kernel<<<grid, NTHREADS, kv::SMEM_BYTES, stream>>>(p);
-      GCA_CUDA_CHECK(cudaGetLastError());
-    }
-  }
   if (stages & GCA_BWD_STAGE_Q) {
     BwdQParams p;
     if ((rc = qmap(&p.tm_q, a.q, a.q_stride, 2)) || (rc = qmap(&p.tm_do, a.dout, a.do_stride, 2)) ||
@@ -897,7 +496,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
         (rc = kmap(&p.tm_k1, a.k_cache, a.k_stride, 1)) || (rc = kmap(&p.tm_v1, a.v_cache, a.v_stride, 1)))
       return rc;
     p.indices = a.indices; p.weights = a.weights; p.lse = a.lse;
-    p.dq = (__nv_bfloat16*)a.dq; p.dw_part = dw_part; p.status = a.status;
+    p.dq = (__nv_bfloat16*)a.dq; p.dw_part = dw_part; p.nld = nld; p.status = a.status;
     p.prof = profile_buffer();
     for (int i = 0; i < 4; ++i) p.dqs[i] = a.dq_stride[i];
     p.N = a.N; p.J = a.J; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = a.Hq / a.Hkv; p.K = a.K; p.C = a.C;
@@ -913,6 +512,9 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStrea
       bwd_q_tc_kernel<<<grid, NTHREADS, qk::SMEM_BYTES, stream>>>(p);
       GCA_CUDA_CHECK(cudaGetLastError());
     }
+  }
+  if (stages & GCA_BWD_STAGE_KV) {
+    if ((rc = launch_bwd_kv_tc(a, csr, nld, sms, stream))) return rc;
   }
   return 0;
 }
