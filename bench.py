@@ -266,8 +266,8 @@ def gpu_arm(args):
         gmod.gca_backward_stages(*ds[:5], ds[5], fwd_out[i % 2][1], scale, stages=which, bufs=bufs[i % 2])
 
     ms_idx = time_calls(lambda i: stage(i, gmod.BWD_STAGE_INDEX), reps)
+    ms_q = time_calls(lambda i: stage(i, gmod.BWD_STAGE_Q), reps)      # first: it writes the per-row terms the kv-major pass reads
     ms_kv = time_calls(lambda i: stage(i, gmod.BWD_STAGE_KV), reps)
-    ms_q = time_calls(lambda i: stage(i, gmod.BWD_STAGE_Q), reps)
     status = lcm.read_status()
 
     flops_fwd = workload_flops(N_SEQ)

@@ -139,14 +139,14 @@ static size_t dw_part_bytes(const GcaBwdArgs* a) {
   return gca::align_up((size_t)2 * a->N * a->J * a->Hq * a->K * sizeof(float), 256);   // two partials per (row block, head, slot)
 }
 
-// (-lse, -Di) per (row block, head, slot, row): written by the q-major pass, read by the kv-major pass
-static size_t nld_bytes(const GcaBwdArgs* a) {
-  return gca::align_up((size_t)a->N * a->J * a->Hq * a->K * 64 * sizeof(float2), 256);
+// 16 bytes per (row block, head, slot, row): written by the q-major pass, read by the kv-major pass
+static size_t rowterm_bytes(const GcaBwdArgs* a) {
+  return gca::align_up((size_t)a->N * a->J * a->Hq * a->K * 64 * sizeof(uint4), 256);
 }
 
 size_t gca_bwd_workspace_bytes(const GcaBwdArgs* a) {
   if (!a) return 0;
-  return gca::csr_workspace_bytes(a->N, a->J, a->K, a->C) + dw_part_bytes(a) + nld_bytes(a);
+  return gca::csr_workspace_bytes(a->N, a->J, a->K, a->C) + dw_part_bytes(a) + rowterm_bytes(a);
 }
 
 int gca_bwd(const GcaBwdArgs* a, void* stream) { return gca_bwd_stages(a, GCA_BWD_STAGE_ALL, stream); }
@@ -181,12 +181,12 @@ int gca_bwd_stages(const GcaBwdArgs* a, unsigned stages, void* stream) {
   if (rc) return rc;
   if (!(stages & (GCA_BWD_STAGE_KV | GCA_BWD_STAGE_Q))) return 0;
   float* dw_part = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + used);
-  float2* nld = reinterpret_cast<float2*>(static_cast<char*>(a->workspace) + used + dw_part_bytes(a));
+  uint4* rowterm = reinterpret_cast<uint4*>(static_cast<char*>(a->workspace) + used + dw_part_bytes(a));
   int algo = a->algo;
   const bool tc_ok = a->dtype == GCA_BF16 && a->S == 64;
   if (algo == GCA_ALGO_AUTO) algo = (tc_ok && gca::bwd_tc_available()) ? GCA_ALGO_TC : GCA_ALGO_SIMT;
   if (algo == GCA_ALGO_TC && !gca::bwd_tc_available()) algo = GCA_ALGO_SIMT;   // until the tensor-core backward lands
-  if (algo == GCA_ALGO_TC) rc = tc_ok ? gca::launch_bwd_tc(*a, csr, dw_part, nld, s, stages) : GCA_ERR_ALGO;
+  if (algo == GCA_ALGO_TC) rc = tc_ok ? gca::launch_bwd_tc(*a, csr, dw_part, rowterm, s, stages) : GCA_ERR_ALGO;
   else if (algo == GCA_ALGO_SIMT) rc = gca::launch_bwd_simt(*a, csr, dw_part, s, stages);
   else rc = GCA_ERR_ALGO;
   if (rc) return rc;

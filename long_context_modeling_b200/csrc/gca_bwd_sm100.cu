@@ -6,10 +6,12 @@
 // P = exp2(S c - LSE),  Di = rowsum(P * dP)  (which replaces the reference's extra o = v^T p^T
 // product, ltriton/gca.py:382),  dS = w P (dP - Di);  dQ += dS K_k accumulates over the K slots in
 // tensor memory, and the per-head parts of  dw_k = sum_rows Di  go to a partials buffer that a tiny
-// fixed-order kernel reduces.  The pair (-LSE, -Di) of every (row, slot) is also written to the
-// workspace: the kv-major pass (gca_bwd_kv_sm100.cu), which runs AFTER this one, needs both per
-// query row and then needs no row reduction of its own (the reference hands Di from one of its
-// two kernels to the other in the same way, ltriton/gca.py:385,459).
+// fixed-order kernel reduces.  For every (row, slot) the two per-row terms of the kv-major pass,
+// (log2|w| - LSE) / c and -Di, are also written to the workspace, each split into three bf16
+// values: the kv-major pass (gca_bwd_kv_sm100.cu), which runs AFTER this one, adds them to its
+// recomputed scores with one extra MMA K step and then needs neither a row reduction nor any
+// per-row operand of its own (the reference hands Di from one of its two kernels to the other in
+// the same way, ltriton/gca.py:385,459).
 //
 // The two heads of a pair are stacked so that every tcgen05.mma is a 128-row instruction whose
 // diagonal 64x64 blocks are the two heads' results (the issue cost of an MMA does not depend on
@@ -61,6 +63,29 @@ __device__ __forceinline__ void mma4(uint32_t d, uint64_t a, uint64_t b, uint32_
                                      bool accumulate_first) {
 #pragma unroll
   for (int kk = 0; kk < 4; ++kk) umma_bf16_ss_elect(d, a + kk * a_step, b + kk * b_step, idesc, (uint32_t)(accumulate_first || kk > 0));
+}
+
+// x as the sum of three bf16 values (24 mantissa bits: float32 precision).
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& h, __nv_bfloat16& m, __nv_bfloat16& l) {
+  h = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(h);
+  m = __float2bfloat16_rn(r1);
+  l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+}
+// The 16-byte record of one (query row, slot) for the kv-major pass: see BwdQParams::rowterm.
+__device__ __forceinline__ uint4 row_terms(float a, float b) {
+  __nv_bfloat16 a0, a1, a2, b0, b1, b2;
+  split3(a, a0, a1, a2);
+  split3(b, b0, b1, b2);
+  auto pk = [](__nv_bfloat16 lo, __nv_bfloat16 hi) {
+    return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+  };
+  return make_uint4(pk(a0, a1), pk(a2, b0), pk(b1, b2), 0u);
+}
+// log2|w|, kept finite: a weight of zero becomes 2^-200, which the exponential flushes to zero.
+__device__ __forceinline__ float log2_abs_clamped(float w) {
+  const float a = fabsf(w);
+  return a > 0.f ? fmaxf(__log2f(a), -200.f) : -200.f;
 }
 
 // One thread, one query row.  s: raw scores (overwritten by P), dp: raw dP.  dS stays in registers,
@@ -149,7 +174,10 @@ struct BwdQParams {
   const float* lse;
   __nv_bfloat16* dq;
   float* dw_part;           // (N*J, Hq, K, 2): two half-tile partials per (row block, head, slot)
-  float2* nld;              // (N*J, Hq, K, 64): (-lse, -Di) per (row block, head, slot, row), for the kv-major pass
+  uint4* rowterm;           // (N*J, Hq, K, 64) x 16 bytes: per (row block, head, slot, query row) eight bf16 values
+                            // (a0, a1, a2, b0, b1, b2, 0, 0) with a0 + a1 + a2 = (log2|w| - lse) / c2 and
+                            // b0 + b1 + b2 = -Di: the kv-major pass adds them to its scores with one MMA K step
+  float inv_c2;
   int32_t* status;
   long long* prof;
   long long dqs[4];
@@ -346,7 +374,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     const uint32_t ub = un & 1;
     const long long row_off = ((long long)c.outer * p.Hq + (live ? h : t.h0)) * p.K * 64 + row;
     const float* lse_base = p.lse + row_off;
-    float2* nld_base = p.nld + row_off;
+    uint4* rt_base = p.rowterm + row_off;
     pf.lap(10);
     bool my_unit = false;                       // this group owns the unit's last slot: it writes dQ
     for (unsigned m = mask; m; m &= m - 1, ++g) {
@@ -380,7 +408,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       pf.lap(2);
       float di = row_backward_packed(s, dp, lse, p.c2, w, s);
-      if (live) nld_base[k * 64] = make_float2(-lse, -di);
+      if (live) rt_base[k * 64] = row_terms((log2_abs_clamped(w) - lse) * p.inv_c2, -di);
       tmem_st_32x32b_x32(tlane + QCOL_DS + sb * DS_COLS, s);
       tmem_st_wait();
       tc_fence_before();
@@ -471,12 +499,12 @@ static bool rows_32b_aligned(const void* base, const int64_t* stride) {
   return true;
 }
 
-int launch_bwd_kv_tc(const GcaBwdArgs& a, const Csr& csr, const float2* nld, int sms, cudaStream_t stream);
+int launch_bwd_kv_tc(const GcaBwdArgs& a, const Csr& csr, const uint4* rowterm, int sms, cudaStream_t stream);
 
-// Stage order inside one call: the q-major pass first (it writes the (-lse, -Di) rows), then the
+// Stage order inside one call: the q-major pass first (it writes the per-row terms), then the
 // kv-major pass, which reads them.  A caller that runs the stages in separate calls must keep
 // that order on the stream (or synchronise between them).
-int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, float2* nld, cudaStream_t stream, unsigned stages) {
+int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, uint4* rowterm, cudaStream_t stream, unsigned stages) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;
   int dev = 0, sms = 0;
   GCA_CUDA_CHECK(cudaGetDevice(&dev));
@@ -496,7 +524,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, float2* n
         (rc = kmap(&p.tm_k1, a.k_cache, a.k_stride, 1)) || (rc = kmap(&p.tm_v1, a.v_cache, a.v_stride, 1)))
       return rc;
     p.indices = a.indices; p.weights = a.weights; p.lse = a.lse;
-    p.dq = (__nv_bfloat16*)a.dq; p.dw_part = dw_part; p.nld = nld; p.status = a.status;
+    p.dq = (__nv_bfloat16*)a.dq; p.dw_part = dw_part; p.rowterm = rowterm; p.inv_c2 = 1.0f / c2; p.status = a.status;
     p.prof = profile_buffer();
     for (int i = 0; i < 4; ++i) p.dqs[i] = a.dq_stride[i];
     p.N = a.N; p.J = a.J; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = a.Hq / a.Hkv; p.K = a.K; p.C = a.C;
@@ -514,7 +542,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, float2* n
     }
   }
   if (stages & GCA_BWD_STAGE_KV) {
-    if ((rc = launch_bwd_kv_tc(a, csr, nld, sms, stream))) return rc;
+    if ((rc = launch_bwd_kv_tc(a, csr, rowterm, sms, stream))) return rc;
   }
   return 0;
 }

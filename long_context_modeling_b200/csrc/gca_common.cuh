@@ -66,8 +66,8 @@ int launch_bwd_simt(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStr
 
 // tcgen05 / TMEM / TMA kernels: bf16, S = L = D = 64.
 int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream);
-// nld: (N*J, Hq, K, 64) float2 scratch the q-major pass fills with (-lse, -Di) for the kv-major pass
-int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, float2* nld, cudaStream_t stream, unsigned stages);
+// rowterm: (N*J, Hq, K, 64) x 16 bytes of scratch the q-major pass fills with the per-row terms of the kv-major pass
+int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, uint4* rowterm, cudaStream_t stream, unsigned stages);
 
 // dw[zj, k] = sum over heads and `parts` partials of dw_part[zj, h, k, part], in a fixed order
 int launch_dw_reduce(const float* dw_part, float* dw, int ZJ, int Hq, int K, int parts, cudaStream_t stream);
