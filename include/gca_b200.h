@@ -11,7 +11,10 @@
  *   - every pointer is a DEVICE pointer owned by the caller (also workspaces and the
  *     optional status word); the library keeps nothing after the call returns except work
  *     already enqueued on `stream`;
- *   - all launches are asynchronous on `stream` (a cudaStream_t passed as void*);
+ *   - all launches are asynchronous on `stream` (a cudaStream_t passed as void*), which must
+ *     belong to the device that holds the buffers; the entry points take the device from the
+ *     pointers (not from the calling thread's current device) and restore the caller's
+ *     current device before they return;
  *   - strides are in ELEMENTS; the innermost (head_dim) axis must be contiguous;
  *   - return value: 0 = ok, negative = argument rejected on the host before any launch
  *     (GCA_ERR_*), positive = CUDA runtime error code;
@@ -27,7 +30,7 @@
 extern "C" {
 #endif
 
-#define GCA_ABI_VERSION 1
+#define GCA_ABI_VERSION 2
 
 enum GcaDtype { GCA_BF16 = 0, GCA_F32 = 1 };
 
@@ -49,7 +52,10 @@ enum GcaError {
 enum GcaAlgo {
   GCA_ALGO_AUTO = 0,        /* bf16 + S=L=D=64 -> tensor-core kernel, everything else -> SIMT */
   GCA_ALGO_SIMT = 1,        /* fp32-accumulating CUDA-core kernel (bf16 or fp32 data) */
-  GCA_ALGO_TC = 2           /* tcgen05/TMEM/TMA kernel (bf16 only) */
+  GCA_ALGO_TC = 2,          /* tcgen05/TMEM/TMA kernel (bf16 only) */
+  GCA_ALGO_TC_UNPAIRED = 3  /* forward only: the tensor-core kernel with ONE q head per work unit instead of a
+                               pair (same per-row arithmetic, same bits; a cross-check of the pairing logic);
+                               the backward treats it as GCA_ALGO_TC */
 };
 
 /* device-side soft status bits written (OR-ed) into *status when it is given */
@@ -156,17 +162,23 @@ int gca_bwd(const GcaBwdArgs* args, void* stream);
 size_t gca_bwd_workspace_bytes(const GcaBwdArgs* args);
 
 /*
- * The same backward, one stage at a time (gca_bwd == all three, in this order, on one stream).
- * The reference runs its two backward kernels back to back inside `_attention.backward`
- * (ltriton/gca.py:786-838); the stages exist here so that a caller can put the dK/dV and the
- * dQ/dw kernels on two streams (both only read the inverse index) and time them separately.
+ * The same backward, one stage at a time (gca_bwd == all three on one stream).  The reference
+ * runs its two backward kernels back to back inside `_attention.backward`
+ * (ltriton/gca.py:786-838); the stages exist here so that a caller can build the index early
+ * (it depends on the indices only) and time the kernels separately.
  *   GCA_BWD_STAGE_INDEX  build the inverse retrieval index (chunk -> retrieving slots) in
  *                        `workspace`; must have completed before the other two stages run
+ *   GCA_BWD_STAGE_Q      dq, dw, and the per-row terms (kept in `workspace`) that
+ *                        GCA_BWD_STAGE_KV reads: it must run before GCA_BWD_STAGE_KV (same
+ *                        stream, or ordered by the caller), as the reference's kernels hand
+ *                        `delta` from one to the other (ltriton/gca.py:385,459)
  *   GCA_BWD_STAGE_KV     dk_cache, dv_cache
- *   GCA_BWD_STAGE_Q      dq, dw
  * All calls of one backward pass the same argument block (same workspace).
+ * GCA_BWD_INDEX_BY_SORT, a flag beside GCA_BWD_STAGE_INDEX, builds the index with the radix-sort
+ * path that large problems take anyway; it has the same bits as the single-launch path.
  */
-enum { GCA_BWD_STAGE_INDEX = 1, GCA_BWD_STAGE_KV = 2, GCA_BWD_STAGE_Q = 4, GCA_BWD_STAGE_ALL = 7 };
+enum { GCA_BWD_STAGE_INDEX = 1, GCA_BWD_STAGE_KV = 2, GCA_BWD_STAGE_Q = 4, GCA_BWD_STAGE_ALL = 7,
+       GCA_BWD_INDEX_BY_SORT = 8 };
 int gca_bwd_stages(const GcaBwdArgs* args, unsigned stages, void* stream);
 
 /*
@@ -265,6 +277,8 @@ int lmk_topk_merge(const LmkMergeArgs* args, void* stream);
  * and V (N, count, L, Hkv*D) into a preallocated cache (N, capacity, L, Hkv*D) at chunk
  * position `pos`, writing zeros into the last row of every chunk when zero_landmark != 0,
  * and copies the landmark embeddings (N, count, Dm) into the landmark cache.
+ * `capacity` / `lmk_capacity` are the chunk capacities of the destination buffers: a call with
+ * pos + count beyond either is rejected with GCA_ERR_SHAPE before anything is launched.
  */
 typedef struct CacheAppendArgs {
   const void* new_k;
@@ -279,16 +293,11 @@ typedef struct CacheAppendArgs {
   int32_t N, count, pos, L, HD, Dm;
   int32_t dtype;
   int32_t zero_landmark;
+  int32_t capacity;          /* chunks the k / v cache buffers hold per sequence */
+  int32_t lmk_capacity;      /* rows the landmark cache holds per sequence (ignored when lmk_cache is NULL) */
 } CacheAppendArgs;
 
 int gca_cache_append(const CacheAppendArgs* args, void* stream);
-
-/*
- * Development aid: when given a device buffer of 36 int64 words, block 0 of the tensor-core
- * forward kernel records the cycles its three roles (softmax warp, MMA issuer, TMA producer;
- * 12 words each) spend in each phase of the pipeline.  NULL switches it off (default).
- */
-int gca_debug_profile_buffer(void* device_ptr);
 
 const char* gca_strerror(int code);
 int gca_abi_version(void);

@@ -11,10 +11,13 @@ import os
 from typing import Optional
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
+# GCA_B200_LIB names another build of the same library (a profiling build, or the test build
+# whose forward withholds a copy so that a bounded wait expires); default: the in-tree build.
 LIB_PATH = os.environ.get("GCA_B200_LIB") or os.path.join(_HERE, "libgca_b200.so")
 
 BF16, F32 = 0, 1
-ALGO_AUTO, ALGO_SIMT, ALGO_TC = 0, 1, 2
+ALGO_AUTO, ALGO_SIMT, ALGO_TC, ALGO_TC_UNPAIRED = 0, 1, 2, 3
+ABI_VERSION = 2
 STATUS_BAD_INDEX, STATUS_TIMEOUT = 1, 2
 
 _i64x4 = C.c_int64 * 4
@@ -76,6 +79,7 @@ class CacheAppendArgs(C.Structure):
         ("new_lmk_batch_stride", C.c_int64), ("lmk_cache_batch_stride", C.c_int64),
         ("N", C.c_int32), ("count", C.c_int32), ("pos", C.c_int32), ("L", C.c_int32),
         ("HD", C.c_int32), ("Dm", C.c_int32), ("dtype", C.c_int32), ("zero_landmark", C.c_int32),
+        ("capacity", C.c_int32), ("lmk_capacity", C.c_int32),
     ]
 
 
@@ -90,7 +94,6 @@ EXPORTS = {
     "lmk_score_topk_static": (C.c_int, [C.POINTER(LmkTopkArgs), C.c_void_p]),
     "lmk_topk_merge": (C.c_int, [C.POINTER(LmkMergeArgs), C.c_void_p]),
     "gca_cache_append": (C.c_int, [C.POINTER(CacheAppendArgs), C.c_void_p]),
-    "gca_debug_profile_buffer": (C.c_int, [C.c_void_p]),
     "gca_strerror": (C.c_char_p, [C.c_int]),
     "gca_abi_version": (C.c_int, []),
     "gca_sizeof": (C.c_size_t, [C.c_int]),
@@ -112,7 +115,7 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)          # AttributeError if a symbol is missing
             fn.restype = res
             fn.argtypes = argtypes
-        if handle.gca_abi_version() != 1:
+        if handle.gca_abi_version() != ABI_VERSION:
             raise RuntimeError("libgca_b200.so has an unexpected ABI version")
         for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs)):
             if handle.gca_sizeof(which) != C.sizeof(struct):

@@ -55,5 +55,28 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_variant(out_dir: str, defines, verbose: bool = False) -> str:
+    """Compile the whole library with extra `-D...` flags into `out_dir` (used by the test that
+    needs a build whose forward withholds a copy; the in-tree library is not touched)."""
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    os.makedirs(out_dir, exist_ok=True)
+    procs, objs = [], []
+    for src in SOURCES:
+        obj = os.path.join(out_dir, src.replace(".cu", ".o"))
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
+               "-I", INCLUDE, "-I", CSRC] + list(defines) + ["-c", os.path.join(CSRC, src), "-o", obj]
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        objs.append(obj)
+    for src, p in procs:
+        out, _ = p.communicate()
+        if p.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n{out}")
+        if verbose:
+            sys.stderr.write(out)
+    lib = os.path.join(out_dir, "libgca_b200_variant.so")
+    subprocess.check_call([nvcc, "-shared", "-o", lib] + objs + ["-lcudart"])
+    return lib
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

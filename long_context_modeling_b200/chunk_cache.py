@@ -7,6 +7,16 @@ buffer that is filled in place by one CUDA kernel per append and doubled when fu
 kernels read it by chunk index, so ``retrieve_chunks`` (the materialised gather) is needed
 only by callers that want the reference's gathered tensors.  The public methods keep the
 reference's names and argument meaning.
+
+Training.  The reference's manager keeps the autograd tensors it is given
+(``model/DRT.py:87-133,784``), so gradients flow from GCA and from the retrieval weights back
+into ``chunk_k_proj`` / ``chunk_v_proj``, the chunk encoder and the cached landmarks.  The
+in-place buffer would cut that graph, so an ``append`` whose inputs require grad (with grad
+mode on) switches the manager to a FUNCTIONAL mode: the appended tensors themselves are kept
+(one append per forward pass, as in the reference's training step, is stored without any copy;
+further appends are concatenated with ``torch.cat`` like the reference's), ``chunk_k``,
+``chunk_v`` and ``past_lmk_embeds`` return them, and ``gca_indexed`` / ``retrieve`` on those
+tensors back-propagate into the caller's graph.
 """
 from __future__ import annotations
 
@@ -31,6 +41,10 @@ class ChunkKVManager:
         self._v: Optional[torch.Tensor] = None
         self._lmk: Optional[torch.Tensor] = None     # (N, capacity, Dm)
         self._len = 0
+        self._grad_mode = False                      # functional storage: the tensors below carry autograd history
+        self._gk: Optional[torch.Tensor] = None
+        self._gv: Optional[torch.Tensor] = None
+        self._glmk: Optional[torch.Tensor] = None
         self._cur_idx: List[Optional[torch.Tensor]] = [None] * group_size
         self._cur_w: List[Optional[torch.Tensor]] = [None] * group_size
         self._current_hidden_states = None
@@ -41,15 +55,45 @@ class ChunkKVManager:
 
     @property
     def chunk_k(self) -> Optional[torch.Tensor]:
+        if self._grad_mode:
+            return self._gk
         return None if self._k is None else self._k[:, :self._len]
 
     @property
     def chunk_v(self) -> Optional[torch.Tensor]:
+        if self._grad_mode:
+            return self._gv
         return None if self._v is None else self._v[:, :self._len]
 
     @property
     def lmk_embs(self) -> Optional[torch.Tensor]:
+        if self._grad_mode:
+            return self._glmk
         return None if self._lmk is None else self._lmk[:, :self._len]
+
+    @property
+    def tracks_gradients(self) -> bool:
+        """True once an append with grad-requiring inputs switched the manager to functional storage."""
+        return self._grad_mode
+
+    def _append_functional(self, chunk_k: torch.Tensor, chunk_v: torch.Tensor, lmk_embs: torch.Tensor) -> None:
+        if self._zero_landmark:                   # the landmark row of every chunk is cleared (model/DRT.py:771-781)
+            keep = torch.ones(chunk_k.shape[-2], 1, dtype=chunk_k.dtype, device=chunk_k.device)
+            keep[-1] = 0
+            chunk_k, chunk_v = chunk_k * keep, chunk_v * keep
+        if not self._grad_mode:
+            self._grad_mode = True
+            if self._len:                         # what the buffer holds so far joins as constants
+                self._gk, self._gv = self._k[:, :self._len].clone(), self._v[:, :self._len].clone()
+                self._glmk = self._lmk[:, :self._len].clone()
+            self._k = self._v = self._lmk = None
+        if self._gk is None:
+            self._gk, self._gv, self._glmk = chunk_k, chunk_v, lmk_embs
+        else:
+            self._gk = torch.cat([self._gk, chunk_k.to(self._gk.dtype)], dim=1)
+            self._gv = torch.cat([self._gv, chunk_v.to(self._gv.dtype)], dim=1)
+            self._glmk = torch.cat([self._glmk, lmk_embs.to(self._glmk.dtype)], dim=1)
+        self._len += chunk_k.shape[1]
 
     @property
     def past_lmk_embeds(self) -> Optional[torch.Tensor]:
@@ -78,6 +122,10 @@ class ChunkKVManager:
             raise ValueError("expected chunk_k/chunk_v (N, D, S, dim) and lmk_embs (N, D, dim)")
         if self._k is not None and (chunk_k.shape[-2] != self._k.shape[-2] or chunk_k.shape[0] != self._k.shape[0]):
             raise ValueError("chunk shape does not match the cache")
+        if self._grad_mode or (torch.is_grad_enabled() and
+                               (chunk_k.requires_grad or chunk_v.requires_grad or lmk_embs.requires_grad)):
+            self._append_functional(chunk_k, chunk_v, lmk_embs)
+            return
         if self._k is not None:
             chunk_k, chunk_v = chunk_k.to(self._k.dtype), chunk_v.to(self._k.dtype)
             lmk_embs = lmk_embs.to(self._lmk.dtype)
@@ -102,6 +150,7 @@ class ChunkKVManager:
         if chunk_k.dtype not in (torch.bfloat16, torch.float32):
             raise ValueError(f"unsupported cache dtype {chunk_k.dtype}")
         a.zero_landmark = 1 if self._zero_landmark else 0
+        a.capacity, a.lmk_capacity = self._k.shape[1], self._lmk.shape[1]
         with torch.cuda.device(chunk_k.device):
             _lib.check(_lib.lib().gca_cache_append(C.byref(a), torch.cuda.current_stream().cuda_stream),
                        "gca_cache_append")

@@ -1,18 +1,44 @@
 // extern "C" entry points of libgca_b200.so: argument validation on the host, kernel
 // selection, launches on the caller's stream.  Nothing here allocates device memory.
-#include <cstdlib>
-#include <cstring>
+#include <mutex>
 
 #include "gca_common.cuh"
 
 namespace gca {
-int launch_decode(const GcaFwdArgs& a, cudaStream_t stream);
-int launch_lmk_score_topk(const LmkTopkArgs& a, void* scratch, cudaStream_t stream);
+int launch_decode(const GcaFwdArgs& a, int sms, cudaStream_t stream);
+int launch_lmk_score_topk(const LmkTopkArgs& a, void* scratch, int sms, cudaStream_t stream);
 int launch_lmk_merge(const LmkMergeArgs& a, cudaStream_t stream);
-size_t lmk_topk_workspace_bytes_impl(const LmkTopkArgs& a);
+size_t lmk_topk_workspace_bytes_impl(const LmkTopkArgs& a, int sms);
 bool bwd_tc_available();
 void set_fwd_profile_buffer(void* device_ptr);
 int launch_cache_append(const CacheAppendArgs& a, cudaStream_t stream);
+
+DeviceScope::DeviceScope(const void* device_ptr) {
+  cudaPointerAttributes at;
+  cudaError_t e = cudaPointerGetAttributes(&at, device_ptr);
+  if (e != cudaSuccess) { rc = (int)e; (void)cudaGetLastError(); return; }
+  if (at.type != cudaMemoryTypeDevice && at.type != cudaMemoryTypeManaged) { rc = GCA_ERR_NULL; return; }   // not device memory
+  dev = at.device;
+  if ((e = cudaGetDevice(&prev)) != cudaSuccess) { rc = (int)e; prev = -1; return; }
+  if (prev != dev && (e = cudaSetDevice(dev)) != cudaSuccess) { rc = (int)e; prev = -1; }
+}
+DeviceScope::~DeviceScope() {
+  if (prev >= 0 && prev != dev) (void)cudaSetDevice(prev);
+}
+
+int sm_count(int dev) {
+  constexpr int MAXD = 64;
+  static std::mutex mu;
+  static int cached[MAXD] = {};
+  if (dev < 0 || dev >= MAXD) return 1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 }  // namespace gca
 
 namespace {
@@ -20,12 +46,6 @@ namespace {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int esize_of(int dtype) { return dtype == GCA_BF16 ? 2 : dtype == GCA_F32 ? 4 : 0; }
-
-// Debug knob: GCA_DEFAULT_ALGO=simt makes GCA_ALGO_AUTO pick the CUDA-core kernels.
-bool prefer_simt() {
-  const char* e = getenv("GCA_DEFAULT_ALGO");
-  return e && strcmp(e, "simt") == 0;
-}
 
 // Strides of the four outer axes must keep every row 16-byte aligned.
 int check_strides(const int64_t s[4], int esize, const int32_t dims[4]) {
@@ -72,10 +92,14 @@ extern "C" {
 
 int gca_abi_version(void) { return GCA_ABI_VERSION; }
 
+#ifdef GCA_PROFILE
+// Profile builds only (never declared in the public header): a device buffer of 64 + 16 * 256
+// int64 words into which block 0 of the tensor-core kernels records event clocks; NULL = off.
 int gca_debug_profile_buffer(void* device_ptr) {
   gca::set_fwd_profile_buffer(device_ptr);
   return 0;
 }
+#endif
 
 size_t gca_sizeof(int which) {
   switch (which) {
@@ -114,10 +138,17 @@ int gca_fwd(const GcaFwdArgs* a, void* stream) {
   if (rc) return rc;
   if (a->N == 0 || a->J == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  gca::DeviceScope scope(a->q);
+  if (scope.rc) return scope.rc;
   int algo = a->algo;
   const bool tc_ok = a->dtype == GCA_BF16 && a->S == 64;
-  if (algo == GCA_ALGO_AUTO) algo = (tc_ok && !prefer_simt()) ? GCA_ALGO_TC : GCA_ALGO_SIMT;
-  if (algo == GCA_ALGO_TC) return tc_ok ? gca::launch_fwd_tc(*a, s) : GCA_ERR_ALGO;
+  if (algo == GCA_ALGO_AUTO) algo = tc_ok ? GCA_ALGO_TC : GCA_ALGO_SIMT;
+  if (algo == GCA_ALGO_TC || algo == GCA_ALGO_TC_UNPAIRED) {
+    if (!tc_ok) return GCA_ERR_ALGO;
+    GcaFwdArgs b = *a;
+    b.algo = algo;
+    return gca::launch_fwd_tc(b, gca::sm_count(scope.dev), s);
+  }
   if (algo == GCA_ALGO_SIMT) return gca::launch_fwd_simt(*a, s);
   return GCA_ERR_ALGO;
 }
@@ -128,8 +159,11 @@ int gca_decode(const GcaFwdArgs* a, void* stream) {
   if (a->S > 16) return GCA_ERR_SHAPE;
   if (a->N == 0 || a->J == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  if (a->algo != GCA_ALGO_SIMT && a->dtype == GCA_BF16 && (a->Hq / a->Hkv) * a->S <= 16) return gca::launch_decode(*a, s);
-  if (a->algo == GCA_ALGO_TC) return GCA_ERR_ALGO;
+  gca::DeviceScope scope(a->q);
+  if (scope.rc) return scope.rc;
+  if (a->algo != GCA_ALGO_SIMT && a->dtype == GCA_BF16 && (a->Hq / a->Hkv) * a->S <= 16)
+    return gca::launch_decode(*a, gca::sm_count(scope.dev), s);
+  if (a->algo == GCA_ALGO_TC || a->algo == GCA_ALGO_TC_UNPAIRED) return GCA_ERR_ALGO;
   GcaFwdArgs b = *a;
   b.lse = nullptr;
   return gca::launch_fwd_simt(b, s);
@@ -153,7 +187,8 @@ int gca_bwd(const GcaBwdArgs* a, void* stream) { return gca_bwd_stages(a, GCA_BW
 
 int gca_bwd_stages(const GcaBwdArgs* a, unsigned stages, void* stream) {
   if (!a) return GCA_ERR_NULL;
-  if (stages == 0 || (stages & ~(unsigned)GCA_BWD_STAGE_ALL)) return GCA_ERR_SHAPE;
+  if ((stages & (unsigned)GCA_BWD_STAGE_ALL) == 0 || (stages & ~(unsigned)(GCA_BWD_STAGE_ALL | GCA_BWD_INDEX_BY_SORT)))
+    return GCA_ERR_SHAPE;
   int rc = check_common(a->q, a->k_cache, a->v_cache, a->indices, a->weights, a->dtype, a->N, a->J, a->Hq, a->Hkv,
                         a->S, a->L, a->D, a->K, a->C);
   if (rc) return rc;
@@ -174,27 +209,32 @@ int gca_bwd_stages(const GcaBwdArgs* a, unsigned stages, void* stream) {
   if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255u)) return GCA_ERR_WORKSPACE;
   if (a->workspace_bytes < gca_bwd_workspace_bytes(a)) return GCA_ERR_WORKSPACE;
   cudaStream_t s = (cudaStream_t)stream;
+  gca::DeviceScope scope(a->q);
+  if (scope.rc) return scope.rc;
   gca::Csr csr;
   size_t used = 0;
   rc = gca::build_csr(a->indices, a->N, a->J, a->K, a->C, a->workspace, a->workspace_bytes, &csr, &used, s,
-                      (stages & GCA_BWD_STAGE_INDEX) != 0);
+                      (stages & GCA_BWD_STAGE_INDEX) != 0, (stages & GCA_BWD_INDEX_BY_SORT) != 0);
   if (rc) return rc;
   if (!(stages & (GCA_BWD_STAGE_KV | GCA_BWD_STAGE_Q))) return 0;
   float* dw_part = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + used);
   uint4* rowterm = reinterpret_cast<uint4*>(static_cast<char*>(a->workspace) + used + dw_part_bytes(a));
   int algo = a->algo;
   const bool tc_ok = a->dtype == GCA_BF16 && a->S == 64;
-  if (algo == GCA_ALGO_AUTO) algo = (tc_ok && gca::bwd_tc_available()) ? GCA_ALGO_TC : GCA_ALGO_SIMT;
-  if (algo == GCA_ALGO_TC && !gca::bwd_tc_available()) algo = GCA_ALGO_SIMT;   // until the tensor-core backward lands
-  if (algo == GCA_ALGO_TC) rc = tc_ok ? gca::launch_bwd_tc(*a, csr, dw_part, rowterm, s, stages) : GCA_ERR_ALGO;
-  else if (algo == GCA_ALGO_SIMT) rc = gca::launch_bwd_simt(*a, csr, dw_part, s, stages);
+  if (algo == GCA_ALGO_TC_UNPAIRED) algo = GCA_ALGO_TC;
+  if (algo == GCA_ALGO_AUTO) algo = tc_ok ? GCA_ALGO_TC : GCA_ALGO_SIMT;
+  if (algo == GCA_ALGO_TC)
+    rc = tc_ok ? gca::launch_bwd_tc(*a, csr, dw_part, rowterm, gca::sm_count(scope.dev), s, stages & GCA_BWD_STAGE_ALL) : GCA_ERR_ALGO;
+  else if (algo == GCA_ALGO_SIMT) rc = gca::launch_bwd_simt(*a, csr, dw_part, s, stages & GCA_BWD_STAGE_ALL);
   else rc = GCA_ERR_ALGO;
   if (rc) return rc;
   if (!(stages & GCA_BWD_STAGE_Q)) return 0;
   return gca::launch_dw_reduce(dw_part, a->dw, a->N * a->J, a->Hq, a->K, algo == GCA_ALGO_TC ? 2 : 1, s);
 }
 
-static int check_topk(const LmkTopkArgs* a) {
+}  // extern "C"
+
+int gca::check_topk(const LmkTopkArgs* a) {
   if (!a) return GCA_ERR_NULL;
   if (!a->lmk_q || !a->lmk_k || !a->out_keys) return GCA_ERR_NULL;
   if (a->N < 0 || a->Cq < 0 || a->E < 0) return GCA_ERR_SHAPE;
@@ -207,24 +247,36 @@ static int check_topk(const LmkTopkArgs* a) {
   return 0;
 }
 
+extern "C" {
+
 size_t lmk_topk_workspace_bytes(const LmkTopkArgs* a) {
-  if (check_topk(a)) return 0;
-  return gca::lmk_topk_workspace_bytes_impl(*a);
+  if (gca::check_topk(a)) return 0;
+  // A size query must not fail for lack of a device: when the landmark pointer cannot be
+  // attributed to one, 256 SMs are assumed, which can only over-estimate (more SMs = more splits).
+  gca::DeviceScope scope(a->lmk_k);
+  return gca::lmk_topk_workspace_bytes_impl(*a, scope.rc ? 256 : gca::sm_count(scope.dev));
 }
 
 int lmk_score_topk(const LmkTopkArgs* a, void* stream) {
-  int rc = check_topk(a);
+  int rc = gca::check_topk(a);
   if (rc) return rc;
   if (a->N == 0 || a->Cq == 0) return 0;
-  const size_t need = gca::lmk_topk_workspace_bytes_impl(*a);
-  if (!a->workspace || a->workspace_bytes < need) return GCA_ERR_WORKSPACE;
-  return gca::launch_lmk_score_topk(*a, a->workspace, (cudaStream_t)stream);
+  if (!a->workspace) return GCA_ERR_WORKSPACE;
+  gca::DeviceScope scope(a->lmk_k);
+  if (scope.rc) return scope.rc;
+  const int sms = gca::sm_count(scope.dev);
+  const size_t need = gca::lmk_topk_workspace_bytes_impl(*a, sms);
+  if (a->workspace_bytes < need) return GCA_ERR_WORKSPACE;
+  return gca::launch_lmk_score_topk(*a, a->workspace, sms, (cudaStream_t)stream);
 }
 
 int lmk_topk_merge(const LmkMergeArgs* a, void* stream) {
   if (!a) return GCA_ERR_NULL;
   if (!a->keys || !a->out_keys) return GCA_ERR_NULL;
   if (a->R < 0 || a->P < 1 || a->K < 1 || a->K > 32) return GCA_ERR_SHAPE;
+  if (a->R == 0) return 0;
+  gca::DeviceScope scope(a->keys);
+  if (scope.rc) return scope.rc;
   return gca::launch_lmk_merge(*a, (cudaStream_t)stream);
 }
 
@@ -239,6 +291,12 @@ int gca_cache_append(const CacheAppendArgs* a, void* stream) {
   if (a->new_lmk && ((a->new_lmk_batch_stride * es) % 16 || (a->lmk_cache_batch_stride * es) % 16)) return GCA_ERR_STRIDE;
   if (!aligned16(a->new_k) || !aligned16(a->new_v) || !aligned16(a->k_cache) || !aligned16(a->v_cache)) return GCA_ERR_ALIGN;
   if (a->new_lmk && (!aligned16(a->new_lmk) || !a->lmk_cache || !aligned16(a->lmk_cache))) return GCA_ERR_ALIGN;
+  // the destination must hold chunks pos .. pos + count - 1
+  if ((long long)a->pos + a->count > a->capacity) return GCA_ERR_SHAPE;
+  if (a->new_lmk && (long long)a->pos + a->count > a->lmk_capacity) return GCA_ERR_SHAPE;
+  if (a->N == 0 || a->count == 0) return 0;
+  gca::DeviceScope scope(a->k_cache);
+  if (scope.rc) return scope.rc;
   return gca::launch_cache_append(*a, (cudaStream_t)stream);
 }
 

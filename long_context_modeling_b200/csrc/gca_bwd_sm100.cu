@@ -504,11 +504,8 @@ int launch_bwd_kv_tc(const GcaBwdArgs& a, const Csr& csr, const uint4* rowterm, 
 // Stage order inside one call: the q-major pass first (it writes the per-row terms), then the
 // kv-major pass, which reads them.  A caller that runs the stages in separate calls must keep
 // that order on the stream (or synchronise between them).
-int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, uint4* rowterm, cudaStream_t stream, unsigned stages) {
+int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, uint4* rowterm, int sms, cudaStream_t stream, unsigned stages) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;
-  int dev = 0, sms = 0;
-  GCA_CUDA_CHECK(cudaGetDevice(&dev));
-  GCA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const float c2 = a.sm_scale * GCA_LOG2E;
   int rc;
   auto qmap = [&](CUtensorMap* m, const void* base, const int64_t* st, int box) {

@@ -55,8 +55,9 @@ struct Csr {
 };
 
 // launch == false: only lay the index out in `workspace` (it was built by an earlier call)
+// by_sort: take the radix-sort path even where the single-launch path would do (same bits)
 int build_csr(const int32_t* indices, int N, int J, int K, int C, void* workspace, size_t workspace_bytes,
-              Csr* out, size_t* used_bytes, cudaStream_t stream, bool launch = true);
+              Csr* out, size_t* used_bytes, cudaStream_t stream, bool launch = true, bool by_sort = false);
 size_t csr_workspace_bytes(int N, int J, int K, int C);
 
 // SIMT (CUDA-core, fp32 accumulate) kernels: every dtype, S <= 64, L = D = 64.
@@ -65,13 +66,30 @@ int launch_fwd_simt(const GcaFwdArgs& a, cudaStream_t stream);
 int launch_bwd_simt(const GcaBwdArgs& a, const Csr& csr, float* dw_part, cudaStream_t stream, unsigned stages);
 
 // tcgen05 / TMEM / TMA kernels: bf16, S = L = D = 64.
-int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream);
+int launch_fwd_tc(const GcaFwdArgs& a, int sms, cudaStream_t stream);
 // rowterm: (N*J, Hq, K, 64) x 16 bytes of scratch the q-major pass fills with the per-row terms of the kv-major pass
-int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, uint4* rowterm, cudaStream_t stream, unsigned stages);
+int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, uint4* rowterm, int sms, cudaStream_t stream, unsigned stages);
 
 // dw[zj, k] = sum over heads and `parts` partials of dw_part[zj, h, k, part], in a fixed order
 int launch_dw_reduce(const float* dw_part, float* dw, int ZJ, int Hq, int K, int parts, cudaStream_t stream);
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// The entry points run on the device that HOLDS THE BUFFERS, whatever the calling thread's
+// current device is (PyTorch calls the backward from an autograd worker thread; a plain C caller
+// may never have called cudaSetDevice).  DeviceScope finds the device of a device pointer,
+// makes it current for the duration of the call and restores the previous one.
+struct DeviceScope {
+  int prev = -1, dev = -1, rc = 0;
+  explicit DeviceScope(const void* device_ptr);
+  ~DeviceScope();
+  DeviceScope(const DeviceScope&) = delete;
+  DeviceScope& operator=(const DeviceScope&) = delete;
+};
+// Number of SMs of a device (asked once per device).
+int sm_count(int dev);
+
+// Argument rules shared by lmk_score_topk, lmk_topk_workspace_bytes and lmk_score_topk_static.
+int check_topk(const LmkTopkArgs* a);
 
 }  // namespace gca

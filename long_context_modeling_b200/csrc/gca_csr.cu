@@ -175,10 +175,7 @@ csr_small_kernel(const int32_t* __restrict__ indices, unsigned long long* __rest
 
 size_t small_smem_bytes(int C) { return (size_t)(32 * C + (C + 1) + C + SMALL_C + 33) * 4; }
 
-// GCA_CSR_PATH=sort forces the radix-sort path (tests compare the two).
 bool small_path(int N, int JK, int C) {
-  const char* e = getenv("GCA_CSR_PATH");
-  if (e && e[0] == 's') return false;
   return C <= SMALL_C && JK < (1 << 21) && (long long)N * JK <= (1ll << 18);
 }
 
@@ -212,7 +209,7 @@ size_t csr_workspace_bytes(int N, int J, int K, int C) {
 }
 
 int build_csr(const int32_t* indices, int N, int J, int K, int C, void* workspace, size_t workspace_bytes,
-              Csr* out, size_t* used_bytes, cudaStream_t stream, bool launch) {
+              Csr* out, size_t* used_bytes, cudaStream_t stream, bool launch, bool by_sort) {
   const long long total = (long long)N * J * K;
   const long long NC = (long long)N * C;
   if (total >= (1ll << 31) || NC >= (1ll << 31)) return GCA_ERR_TOO_LARGE;
@@ -234,7 +231,7 @@ int build_csr(const int32_t* indices, int N, int J, int K, int C, void* workspac
   const long long cmax = (long long)J * K;
   const int cbits = bits_for(cmax), nbits = bits_for(N);
   if (cbits + nbits > 32) return GCA_ERR_TOO_LARGE;
-  if (launch && NC > 0 && total > 0 && small_path(N, J * K, C)) {
+  if (launch && NC > 0 && total > 0 && !by_sort && small_path(N, J * K, C)) {
     const size_t smem = small_smem_bytes(C);
     GCA_CUDA_CHECK(cudaFuncSetAttribute(csr_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     csr_small_kernel<<<N, SMALL_THREADS, smem, stream>>>(indices, keys_out, offsets, uvals_out, N, J * K, C);

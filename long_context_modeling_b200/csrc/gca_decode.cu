@@ -217,12 +217,9 @@ decode_kernel(const __grid_constant__ DecParams p) {
 }
 
 template <int R>
-int launch_decode_r(const DecParams& p, int blocks, cudaStream_t stream) {
+int launch_decode_r(const DecParams& p, int blocks, int sms, cudaStream_t stream) {
   const size_t smem = NWARPS * 2 * TILE_BYTES + 2 * (1 + NWARPS) * R * T * sizeof(float) + 256 + 1024;
   GCA_CUDA_CHECK(cudaFuncSetAttribute(decode_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  int dev = 0, sms = 0;
-  GCA_CUDA_CHECK(cudaGetDevice(&dev));
-  GCA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   decode_kernel<R><<<(unsigned)(blocks < sms ? blocks : sms), NWARPS * 32, smem, stream>>>(p);
   return (int)cudaGetLastError();
 }
@@ -230,7 +227,7 @@ int launch_decode_r(const DecParams& p, int blocks, cudaStream_t stream) {
 }  // namespace
 
 // bf16, G*S <= 16 rows.  Returns GCA_ERR_ALGO when the problem is outside that envelope.
-int launch_decode(const GcaFwdArgs& a, cudaStream_t stream) {
+int launch_decode(const GcaFwdArgs& a, int sms, cudaStream_t stream) {
   if (a.dtype != GCA_BF16) return GCA_ERR_ALGO;
   DecParams p;
   int rc;
@@ -245,11 +242,11 @@ int launch_decode(const GcaFwdArgs& a, cudaStream_t stream) {
   g.sm_scale = a.sm_scale; g.off_by_one = a.off_by_one;
   const int rows = g.G * a.S;
   const int blocks = a.N * a.J * a.Hkv;
-  if (rows <= 1) return launch_decode_r<1>(p, blocks, stream);
-  if (rows <= 2) return launch_decode_r<2>(p, blocks, stream);
-  if (rows <= 4) return launch_decode_r<4>(p, blocks, stream);
-  if (rows <= 8) return launch_decode_r<8>(p, blocks, stream);
-  if (rows <= 16) return launch_decode_r<16>(p, blocks, stream);
+  if (rows <= 1) return launch_decode_r<1>(p, blocks, sms, stream);
+  if (rows <= 2) return launch_decode_r<2>(p, blocks, sms, stream);
+  if (rows <= 4) return launch_decode_r<4>(p, blocks, sms, stream);
+  if (rows <= 8) return launch_decode_r<8>(p, blocks, sms, stream);
+  if (rows <= 16) return launch_decode_r<16>(p, blocks, sms, stream);
   return GCA_ERR_ALGO;
 }
 

@@ -136,7 +136,7 @@ struct FwdTcParams {
   long long os[4];
   int units;
   int N, J, Hq, Hkv, G, K, C, HP;
-  int pair;                 // 1: a unit is a pair of q heads; 0: a single head (debug knob)
+  int pair;                 // 1: a unit is a pair of q heads; 0: a single head (GCA_ALGO_TC_UNPAIRED)
   int dbg;                  // profile builds only: bit mask of work to skip (timing experiments)
   int wide_store;           // every output row is 32-byte aligned: 256-bit stores
   float c2;
@@ -316,6 +316,17 @@ __device__ void kproducer_role(const FwdTcParams& p, uint8_t* smem, uint64_t* ba
         const CUtensorMap* tm = t.share ? &p.tm_k1 : &p.tm_k2;
         const uint32_t bytes = t.share ? TILE_BYTES : PAIR_BYTES;
         for (unsigned m = mask; m; m &= m - 1) {
+#ifdef GCA_TEST_WITHHOLD_K
+          // Test build only: the CTA's first K tile is never requested, so the S issuer's bounded
+          // wait for it must expire.  This lane idles (bounded) until some role has given up, then
+          // unwinds like after any expired wait: nothing was issued that could still be in flight
+          // except the Q copy, which the drain below waits for.
+          if (issued == 0) {
+            for (uint32_t spin = 0; spin < 64u * GCA_WAIT_LIMIT && !*abort_flag; ++spin) __nanosleep(32);
+            ok = false;
+            break;
+          }
+#endif
           ok = mbar_wait_bounded(&bars[K_EMPTY + ring.st], ring.ph ^ 1, abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(&bars[K_FULL + ring.st], bytes);
@@ -661,7 +672,7 @@ long long* g_profile_buffer = nullptr;
 void set_fwd_profile_buffer(void* device_ptr) { g_profile_buffer = static_cast<long long*>(device_ptr); }
 long long* profile_buffer() { return g_profile_buffer; }
 
-int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream) {
+int launch_fwd_tc(const GcaFwdArgs& a, int sms, cudaStream_t stream) {
   if (a.dtype != GCA_BF16 || a.S != 64 || a.L != 64 || a.D != 64 || a.K > 32) return GCA_ERR_ALGO;
   FwdTcParams p;
   // q viewed as (d, s, h, j, n); caches as (d, l, h, c, n).  One copy moves a 64 x 64 tile of
@@ -675,10 +686,11 @@ int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream) {
   p.indices = a.indices; p.weights = a.weights; p.out = (__nv_bfloat16*)a.out; p.lse = a.lse; p.status = a.status;
   for (int i = 0; i < 4; ++i) p.os[i] = a.o_stride[i];
   p.N = a.N; p.J = a.J; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = a.Hq / a.Hkv; p.K = a.K; p.C = a.C;
-  const char* pair_env = getenv("GCA_TC_PAIR");
-  p.pair = (pair_env && pair_env[0] == '0') ? 0 : 1;
-  const char* dbg_env = getenv("GCA_DBG");
-  p.dbg = dbg_env ? atoi(dbg_env) : 0;
+  p.pair = a.algo == GCA_ALGO_TC_UNPAIRED ? 0 : 1;
+  p.dbg = 0;
+#ifdef GCA_DBGKNOBS
+  if (const char* dbg_env = getenv("GCA_DBG")) p.dbg = atoi(dbg_env);      // timing experiments, never in the product build
+#endif
   p.HP = p.pair ? (a.Hq + 1) / 2 : a.Hq;
   const long long units = (long long)a.N * a.J * p.HP;
   if (units >= (1ll << 31) - 65536) return GCA_ERR_TOO_LARGE;
@@ -689,9 +701,6 @@ int launch_fwd_tc(const GcaFwdArgs& a, cudaStream_t stream) {
   p.wide_store = (reinterpret_cast<uintptr_t>(a.out) & 31u) == 0;
   for (int i = 0; i < 4; ++i) p.wide_store = p.wide_store && (a.o_stride[i] % 16 == 0);
   if (p.units == 0) return 0;
-  int dev = 0, sms = 0;
-  GCA_CUDA_CHECK(cudaGetDevice(&dev));
-  GCA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   GCA_CUDA_CHECK(cudaFuncSetAttribute(fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   const unsigned grid = (unsigned)(p.units < sms ? p.units : sms);
   fwd_tc_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(p);

@@ -299,10 +299,11 @@ lmk_finalize_kernel(FinalParams p) {
   if (lane == 0 && p.out_nvalid) p.out_nvalid[row] = (int)nv;
 }
 
-int choose_splits(const LmkTopkArgs& a, int tq) {
+// Two CTAs per SM when the query tile count alone does not fill the GPU.
+int choose_splits(const LmkTopkArgs& a, int tq, int sms) {
   if (a.splits > 0) return a.splits;
   const long long blocks = (long long)a.N * ((a.Cq + tq - 1) / tq);
-  long long s = (2 * 148 + blocks - 1) / blocks;
+  long long s = (2 * (long long)sms + blocks - 1) / blocks;
   const long long max_s = (a.E + 255) / 256;              // keep at least 256 rows per split
   if (s > max_s) s = max_s;
   if (s < 1) s = 1;
@@ -325,18 +326,18 @@ size_t lmk_topk_rows(const LmkTopkArgs& a) {
   return (size_t)a.N * a.Cq * H;
 }
 
-size_t lmk_topk_workspace_bytes_impl(const LmkTopkArgs& a) {
-  const int splits = choose_splits(a, pick_tq(a));
+size_t lmk_topk_workspace_bytes_impl(const LmkTopkArgs& a, int sms) {
+  const int splits = choose_splits(a, pick_tq(a), sms);
   return align_up(lmk_topk_rows(a) * (size_t)splits * a.K * sizeof(unsigned long long), 256);
 }
 
 // Scan + finalize on caller-provided scratch.  `scratch` must hold
-// lmk_topk_workspace_bytes_impl(a) bytes.
-int launch_lmk_score_topk(const LmkTopkArgs& a, void* scratch, cudaStream_t stream) {
+// lmk_topk_workspace_bytes_impl(a, sms) bytes.
+int launch_lmk_score_topk(const LmkTopkArgs& a, void* scratch, int sms, cudaStream_t stream) {
   const bool per_head = a.head_dim > 0;
   const int H = per_head ? a.D / a.head_dim : 1;
   const int tq = pick_tq(a);
-  const int splits = choose_splits(a, tq);
+  const int splits = choose_splits(a, tq, sms);
   ScanParams sp;
   sp.lq = (const __nv_bfloat16*)a.lmk_q; sp.lk = (const __nv_bfloat16*)a.lmk_k; sp.noise = a.noise;
   sp.part = (unsigned long long*)scratch;
@@ -397,8 +398,9 @@ int launch_lmk_merge(const LmkMergeArgs& a, cudaStream_t stream) {
 // The array is file-scope device memory: every GPU that loads this library carries it
 // (LMK_STATIC_SCRATCH_BYTES = 1 MiB) until the process exits.  In host code its name is only a
 // stand-in for the symbol, not a device address, so the address is looked up with
-// cudaGetSymbolAddress -- once per device, with that device current, on the first call made on
-// that device -- and only that looked-up pointer is handed to the kernels.  Because of that
+// cudaGetSymbolAddress -- once per device, with that device current (the device that holds the
+// landmark cache, made current for the call), on the first call made for that device -- and only
+// that looked-up pointer is handed to the kernels.  Because of that
 // look-up, make the first call on each device before starting any stream capture.
 //
 // All calls on one GPU share the array.  It keeps whatever the previous call left in it; that
@@ -417,10 +419,8 @@ constexpr int MAX_DEVICES = 64;
 std::mutex g_static_mu;
 void* g_static_ptr[MAX_DEVICES] = {};
 
-// Device address of the static scratch on the current device (resolved once per device).
-int static_scratch_ptr(void** out) {
-  int dev = 0;
-  GCA_CUDA_CHECK(cudaGetDevice(&dev));
+// Device address of the static scratch on device `dev`, which must be current (resolved once per device).
+int static_scratch_ptr(int dev, void** out) {
   if (dev < 0 || dev >= MAX_DEVICES) return GCA_ERR_TOO_LARGE;
   std::lock_guard<std::mutex> lock(g_static_mu);
   if (!g_static_ptr[dev]) {
@@ -437,20 +437,16 @@ int static_scratch_ptr(void** out) {
 
 extern "C" int lmk_score_topk_static(const LmkTopkArgs* a, void* stream) {
   // same argument rules as lmk_score_topk; `workspace` / `workspace_bytes` are ignored
-  if (!a) return GCA_ERR_NULL;
-  if (!a->lmk_q || !a->lmk_k || !a->out_keys) return GCA_ERR_NULL;
-  if (a->N < 0 || a->Cq < 0 || a->E < 0) return GCA_ERR_SHAPE;
-  if (a->D < 8 || a->D % 8 != 0 || a->D > 1024 || a->K < 1 || a->K > 32) return GCA_ERR_SHAPE;
-  if (a->head_dim != 0 && (a->head_dim != 64 || a->D % 64 != 0 || a->noise)) return GCA_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(a->lmk_q) & 15u) || (reinterpret_cast<uintptr_t>(a->lmk_k) & 15u)) return GCA_ERR_ALIGN;
-  if (a->q_row_stride % 8 || a->k_row_stride % 8 || a->q_batch_stride % 8 || a->k_batch_stride % 8) return GCA_ERR_STRIDE;
-  if (a->e_base < 0 || a->e_base + a->E >= 0xffffffffll) return GCA_ERR_TOO_LARGE;
-  if (a->splits < 0) return GCA_ERR_SHAPE;
-  if (a->N == 0 || a->Cq == 0) return 0;
-  // rows x splits x K candidate keys of 8 bytes must fit the built-in array
-  if (gca::lmk_topk_workspace_bytes_impl(*a) > (size_t)LMK_STATIC_SCRATCH_BYTES) return GCA_ERR_STATIC_SCRATCH;
-  void* scratch = nullptr;
-  int rc = gca::static_scratch_ptr(&scratch);
+  int rc = gca::check_topk(a);
   if (rc) return rc;
-  return gca::launch_lmk_score_topk(*a, scratch, (cudaStream_t)stream);
+  if (a->N == 0 || a->Cq == 0) return 0;
+  gca::DeviceScope scope(a->lmk_k);        // the array of the GPU that holds the landmarks
+  if (scope.rc) return scope.rc;
+  const int sms = gca::sm_count(scope.dev);
+  // rows x splits x K candidate keys of 8 bytes must fit the built-in array
+  if (gca::lmk_topk_workspace_bytes_impl(*a, sms) > (size_t)LMK_STATIC_SCRATCH_BYTES) return GCA_ERR_STATIC_SCRATCH;
+  void* scratch = nullptr;
+  rc = gca::static_scratch_ptr(scope.dev, &scratch);
+  if (rc) return rc;
+  return gca::launch_lmk_score_topk(*a, scratch, sms, (cudaStream_t)stream);
 }

@@ -64,8 +64,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // The first probe is the non-blocking test_wait: most waits of the MMA-issuing warps find their
 // barrier already complete, and the potentially-suspending try_wait costs a few hundred cycles
 // even then (measured).
+#ifndef GCA_WAIT_LIMIT
+#define GCA_WAIT_LIMIT (1u << 22)
+#endif
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  uint32_t limit = (1u << 22)) {
+                                                  uint32_t limit = GCA_WAIT_LIMIT) {
 #ifndef GCA_NO_FAST_PROBE
   if (mbar_test_wait(bar, parity)) return true;
 #endif

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "gca_b200.h"
 
 namespace gca {
@@ -26,6 +28,43 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Encoded tensor maps are kept in a small table keyed by everything that went into them
+// (base pointer, extents, strides, box, swizzle): a training loop calls with the same few tensors
+// over and over, and every launch used to re-encode 5 (forward) to 12 (backward) maps through the
+// driver.  The table is shared by all threads of the process (one mutex; an entry is a plain
+// 128-byte value that is copied out, so nothing is retained by pointer).
+struct TileMapKey {
+  const void* base;
+  long long dims[5];
+  long long strides[4];
+  int box_d2;
+  int swizzle;
+  bool operator==(const TileMapKey& o) const {
+    if (base != o.base || box_d2 != o.box_d2 || swizzle != o.swizzle) return false;
+    for (int i = 0; i < 5; ++i) if (dims[i] != o.dims[i]) return false;
+    for (int i = 0; i < 4; ++i) if (strides[i] != o.strides[i]) return false;
+    return true;
+  }
+};
+struct TileMapCache {
+  static constexpr int SLOTS = 256;
+  std::mutex mu;
+  TileMapKey keys[SLOTS];
+  CUtensorMap maps[SLOTS];
+  bool used[SLOTS] = {};
+  static unsigned slot_of(const TileMapKey& k) {
+    unsigned long long h = reinterpret_cast<unsigned long long>(k.base) * 0x9E3779B97F4A7C15ull;
+    for (int i = 0; i < 5; ++i) h = (h ^ (unsigned long long)k.dims[i]) * 0x100000001B3ull;
+    for (int i = 0; i < 4; ++i) h = (h ^ (unsigned long long)k.strides[i]) * 0x100000001B3ull;
+    h = (h ^ (unsigned long long)(k.box_d2 * 2 + k.swizzle)) * 0x100000001B3ull;
+    return (unsigned)(h >> 40) % SLOTS;
+  }
+};
+inline TileMapCache& tile_map_cache() {
+  static TileMapCache c;
+  return c;
+}
+
 // A bf16 tensor viewed as (d0 = 64 contiguous, d1, d2, d3, d4) with element strides s1..s4;
 // every copy moves one (64 x 64 x 1 x 1 x 1) box, i.e. 64 rows of 128 bytes, swizzled.
 // `box_d2` > 1 makes one copy fetch that many consecutive entries of axis d2 (e.g. the two
@@ -38,6 +77,16 @@ inline int make_tile_map_5d(CUtensorMap* map, const void* base, int d0, int d1, 
   if (!fn) return GCA_ERR_TMA;
   const long long dims_in[5] = {d0, d1, d2, d3, d4};
   long long str_in[4] = {s1, s2, s3, s4};
+  TileMapKey key;
+  key.base = base; key.box_d2 = box_d2; key.swizzle = swizzle128 ? 1 : 0;
+  for (int i = 0; i < 5; ++i) key.dims[i] = dims_in[i];
+  for (int i = 0; i < 4; ++i) key.strides[i] = str_in[i];
+  TileMapCache& cache = tile_map_cache();
+  const unsigned slot = TileMapCache::slot_of(key);
+  {
+    std::lock_guard<std::mutex> lock(cache.mu);
+    if (cache.used[slot] && cache.keys[slot] == key) { *map = cache.maps[slot]; return 0; }
+  }
   cuuint64_t dims[5];
   cuuint64_t strides[4];
   for (int i = 0; i < 5; ++i) dims[i] = (cuuint64_t)dims_in[i];
@@ -53,7 +102,12 @@ inline int make_tile_map_5d(CUtensorMap* map, const void* base, int d0, int d1, 
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : GCA_ERR_TMA;
+  if (r != CUDA_SUCCESS) return GCA_ERR_TMA;
+  {
+    std::lock_guard<std::mutex> lock(cache.mu);
+    cache.keys[slot] = key; cache.maps[slot] = *map; cache.used[slot] = true;
+  }
+  return 0;
 }
 
 }  // namespace gca

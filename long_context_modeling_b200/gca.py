@@ -18,7 +18,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import ALGO_AUTO, ALGO_SIMT, ALGO_TC  # noqa: F401  (re-exported)
+from ._lib import ALGO_AUTO, ALGO_SIMT, ALGO_TC, ALGO_TC_UNPAIRED  # noqa: F401  (re-exported)
 
 _status_words: Dict[int, torch.Tensor] = {}
 
@@ -46,6 +46,33 @@ def read_status(device=None, clear: bool = True) -> int:
     if clear:
         word.zero_()
     return val
+
+
+_check_after_launch = False
+
+
+def set_status_checks(enabled: bool) -> None:
+    """When enabled, every GCA call of this module reads the device status word after its launch
+    (one synchronisation per call) and raises ``GcaError`` if a kernel reported that a bounded
+    wait expired (outputs invalid).  Off by default; ``HostGcaPipeline`` always checks, at the
+    point where it synchronises anyway."""
+    global _check_after_launch
+    _check_after_launch = bool(enabled)
+
+
+def check_status(device=None, clear: bool = True) -> int:
+    """Reads the status word (synchronises).  ``STATUS_TIMEOUT`` -- a kernel gave up a bounded
+    on-chip wait, its outputs are not valid -- raises ``GcaError``; other bits (a retrieved index
+    outside the cache: that slot was skipped) are returned to the caller."""
+    bits = read_status(device, clear)
+    if bits & _lib.STATUS_TIMEOUT:
+        raise _lib.GcaError("a GCA kernel gave up a bounded wait (GCA_STATUS_TIMEOUT): its outputs are not valid")
+    return bits
+
+
+def _maybe_check(device) -> None:
+    if _check_after_launch:
+        check_status(device)
 
 
 def _require_cuda(*tensors):
@@ -123,6 +150,7 @@ class _GcaIndexed(torch.autograd.Function):
         with torch.cuda.device(q5.device):
             a = _fwd_args(q5, kc5, vc5, idx32, w32, out, lse, sm_scale, off_by_one, algo)
             _lib.check(_lib.lib().gca_fwd(C.byref(a), _stream()), "gca_fwd")
+        _maybe_check(q5.device)
         ctx.save_for_backward(q5, kc5, vc5, idx32, w32, lse)
         ctx.sm_scale, ctx.off_by_one, ctx.algo = sm_scale, off_by_one, algo
         return out
@@ -135,6 +163,7 @@ class _GcaIndexed(torch.autograd.Function):
 
 
 BWD_STAGE_INDEX, BWD_STAGE_KV, BWD_STAGE_Q, BWD_STAGE_ALL = 1, 2, 4, 7
+BWD_INDEX_BY_SORT = 8          # flag beside BWD_STAGE_INDEX: build the inverse index by radix sort (same bits)
 
 
 def _backward_call(q5, kc5, vc5, idx32, w32, dout, lse, sm_scale, off_by_one, algo, stages=BWD_STAGE_ALL, bufs=None):
@@ -178,15 +207,18 @@ def _backward_call(q5, kc5, vc5, idx32, w32, dout, lse, sm_scale, off_by_one, al
         a.workspace = (ws.data_ptr() + 255) // 256 * 256
         a.workspace_bytes = ws.numel() - 256
         _lib.check(_lib.lib().gca_bwd_stages(C.byref(a), stages, _stream()), "gca_bwd_stages")
-    if bufs is None and stages != BWD_STAGE_ALL:
+    _maybe_check(q5.device)
+    if bufs is None and (stages & BWD_STAGE_ALL) != BWD_STAGE_ALL:
         return dq, dk, dv, dw, ws
     return dq, dk, dv, dw
 
 
 def gca_backward_stages(q, k_cache, v_cache, indices, weights, dout, lse, sm_scale, *, stages=BWD_STAGE_ALL,
                         bufs=None, softmax_off_by_one=False, algo: int = ALGO_AUTO):
-    """The backward of `gca_indexed` without autograd, optionally one stage at a time
-    (BWD_STAGE_INDEX, then BWD_STAGE_KV and BWD_STAGE_Q in any order or on two streams).
+    """The backward of `gca_indexed` without autograd, optionally one stage at a time:
+    BWD_STAGE_INDEX, then BWD_STAGE_Q, then BWD_STAGE_KV (the dK/dV kernel reads per-row terms
+    that the dQ kernel leaves in the workspace).  `stages | BWD_INDEX_BY_SORT` builds the index
+    by radix sort.
 
     q (N, J, Hq, S, D); caches (N, C, L, Hkv*D); dout like q; lse as returned by
     `gca_forward_with_lse`.  A partial call returns (dq, dk, dv, dw, workspace): pass that tuple
@@ -271,6 +303,7 @@ def _forward_nograd(q5, kc5, vc5, idx32, w32, sm_scale, off_by_one, algo) -> tor
             if s != 64 and algo == ALGO_AUTO:
                 a.algo = ALGO_SIMT
             _lib.check(_lib.lib().gca_fwd(C.byref(a), _stream()), "gca_fwd")
+    _maybe_check(q5.device)
     return out
 
 

@@ -52,6 +52,9 @@ class HostGcaPipeline:
     def _pop(self) -> List[torch.Tensor]:
         ob = self._inflight.pop(0)
         self._ev_out[ob].synchronize()
+        # the step's kernels are complete: a bounded wait that expired in one of them means that
+        # these outputs are not valid (raises GcaError)
+        _gca.check_status(self.device)
         return self._host_out[ob]
 
     def submit(self, host: Sequence[torch.Tensor]) -> Optional[List[torch.Tensor]]:

@@ -47,9 +47,24 @@ def preprocess_chunk_kv_cache(chunk_k: torch.Tensor, chunk_v: torch.Tensor, weig
 
 
 class TritonGroupCrossAttention(nn.Module):
-    def __init__(self, hidden_size: int, num_heads: int, enc_chunk_size: int = 63, chunk_topk: int = 8,
+    """``TritonGroupCrossAttention(config)`` like the reference's constructor
+    (``model/DRT.py:305-318``: reads ``hidden_size``, ``num_attention_heads``, ``enc_chunk_size``,
+    ``chunk_topk``, ``rms_norm_eps``, ``attention_bias``, ``enable_softmax_one``), or the same
+    values spelled out: ``TritonGroupCrossAttention(hidden_size, num_heads, ...)``."""
+
+    def __init__(self, hidden_size, num_heads: int = None, enc_chunk_size: int = 63, chunk_topk: int = 8,
                  rms_norm_eps: float = 1e-5, attention_bias: bool = False, enable_softmax_one: bool = False):
         super().__init__()
+        if hasattr(hidden_size, "hidden_size"):              # a model config object
+            config = hidden_size
+            hidden_size, num_heads = config.hidden_size, config.num_attention_heads
+            enc_chunk_size = getattr(config, "enc_chunk_size", enc_chunk_size)
+            chunk_topk = getattr(config, "chunk_topk", chunk_topk)
+            rms_norm_eps = getattr(config, "rms_norm_eps", rms_norm_eps)
+            attention_bias = getattr(config, "attention_bias", attention_bias)
+            enable_softmax_one = getattr(config, "enable_softmax_one", enable_softmax_one)
+        if num_heads is None:
+            raise TypeError("TritonGroupCrossAttention needs a config object or (hidden_size, num_heads, ...)")
         self.hidden_size = hidden_size
         self.num_heads = num_heads
         self.head_dim = hidden_size // num_heads
@@ -63,9 +78,7 @@ class TritonGroupCrossAttention(nn.Module):
 
     @classmethod
     def from_config(cls, config):
-        return cls(config.hidden_size, config.num_attention_heads, config.enc_chunk_size, config.chunk_topk,
-                   getattr(config, "rms_norm_eps", 1e-5), getattr(config, "attention_bias", False),
-                   getattr(config, "enable_softmax_one", False))
+        return cls(config)
 
     preprocess_chunk_kv_cache = staticmethod(preprocess_chunk_kv_cache)
 
@@ -134,15 +147,10 @@ class GroupCrossAttention(TritonGroupCrossAttention):
     K-fold, runs K independent attentions and merges them with an einsum; here the same tensors
     are handed to the GCA kernels as strided views (no expansion, no copy)."""
 
-    def __init__(self, hidden_size: int, num_heads: int, enc_chunk_size: int = 63, chunk_topk: int = 8,
+    def __init__(self, hidden_size, num_heads: int = None, enc_chunk_size: int = 63, chunk_topk: int = 8,
                  rms_norm_eps: float = 1e-5, attention_bias: bool = False):
         super().__init__(hidden_size, num_heads, enc_chunk_size, chunk_topk, rms_norm_eps, attention_bias, False)
-
-    @classmethod
-    def from_config(cls, config):
-        return cls(config.hidden_size, config.num_attention_heads, config.enc_chunk_size,
-                   getattr(config, "chunk_topk", 8), getattr(config, "rms_norm_eps", 1e-5),
-                   getattr(config, "attention_bias", False))
+        self.enable_softmax_one, self.sm_n = False, 0.0        # this variant has no sm_n (model/DRT.py:235-302)
 
     @staticmethod
     def preprocess_chunk_kv_cache(chunk_k: torch.Tensor, chunk_v: torch.Tensor, weights: torch.Tensor, num_heads: int):

@@ -33,25 +33,36 @@ class Retrieval(NamedTuple):
     n_valid: torch.Tensor    # (R..)    int32
 
 
-def _bf16_rows(t: torch.Tensor) -> torch.Tensor:
-    t = t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
+def _bf16_rows(t: torch.Tensor, require_bf16: bool = False) -> torch.Tensor:
+    """The scan kernel reads bf16 landmarks.  Landmarks in another dtype are ROUNDED to bf16 first:
+    that is what the reference's scoring einsum sees under the trainer's bf16 autocast
+    (``trainer/slidewindow_trainer.py:198``, ``model/DRT.py:612``), but a float32 run of the
+    reference scores in float32 and may pick another chunk on a near tie.  ``require_bf16``
+    turns the rounding into an error."""
+    if t.dtype != torch.bfloat16:
+        if require_bf16:
+            raise ValueError(f"landmarks are {t.dtype}: the scan kernel scores bf16 landmarks and would round them "
+                             "(pass bf16 tensors, or drop require_bf16 to accept the rounding)")
+        t = t.to(torch.bfloat16)
     return t if t.stride(-1) == 1 else t.contiguous()
 
 
 def lmk_score_topk(lmk_q: torch.Tensor, lmk_k: torch.Tensor, topk: int, *, q_pos0: Optional[int] = None,
                    e_base: int = 0, noise: Optional[torch.Tensor] = None, head_dim: int = 0,
-                   score_round: str = "fp32", splits: int = 0) -> Retrieval:
+                   score_round: str = "fp32", splits: int = 0, require_bf16: bool = False) -> Retrieval:
     """lmk_q (N, Cq, D), lmk_k (N, E, D) -> top-``topk`` cached chunks per query row.
 
     Row ``i`` sees cached chunk ``e`` iff ``e_base + e < q_pos0 + i``; the default
     ``q_pos0 = E - Cq`` is the reference's causal chunk mask (``model/DRT.py:590-607``).
     ``head_dim`` = 64 switches to one score / one top-k per head (outputs (N, Cq, H, K)).
+    Landmarks that are not bf16 are rounded to bf16 before scoring (see ``_bf16_rows``);
+    ``require_bf16=True`` raises instead.
     """
     if not (lmk_q.is_cuda and lmk_k.is_cuda):
         raise RuntimeError("landmark retrieval runs on CUDA tensors only (there is no CPU path)")
     if lmk_q.dim() != 3 or lmk_k.dim() != 3 or lmk_q.shape[0] != lmk_k.shape[0] or lmk_q.shape[2] != lmk_k.shape[2]:
         raise ValueError("expected lmk_q (N, Cq, D) and lmk_k (N, E, D)")
-    lq, lk = _bf16_rows(lmk_q.detach()), _bf16_rows(lmk_k.detach())
+    lq, lk = _bf16_rows(lmk_q.detach(), require_bf16), _bf16_rows(lmk_k.detach(), require_bf16)
     n, cq, d = lq.shape
     e = lk.shape[1]
     heads = d // head_dim if head_dim else 1

@@ -10,6 +10,13 @@ and executes them on CPU tensors:
 * ``model/DRT.py``   -- class ``ChunkKVManager``, ``DRT._enc_dec_score_mask``,
   ``DRT._perform_batch_retrieval``, ``TritonGroupCrossAttention.preprocess_chunk_kv_cache``
   (lifted with ``ast``), and the decode-time retrieval statements inside ``DRT.forward``.
+* ``model/DRT.py``   -- the whole classes ``TritonGroupCrossAttention`` and
+  ``GroupCrossAttention`` (constructor, ``preprocess_chunk_kv_cache``, ``forward``), executed
+  with stand-ins for the three third-party callables they use: the fused ``RMSNorm`` (plain
+  formula), ``gca_attn`` / ``gca_kv_cache`` (the reference's einsum ground truth lifted above)
+  and ``flash_attn_func`` (plain softmax attention).  What the fixture pins is the glue: norm,
+  projection, head split, dropping the first chunk, the K-fold query expansion of the flash
+  variant, the weighted merge, the output projection and the zero rows of the first chunk.
 
 Usage (only where the reference checkout exists):
     python tests/golden/make_golden.py /path/to/reference
@@ -102,6 +109,61 @@ def lift_reference_retrieval(ref_root: str):
     return ns["ChunkKVManager"], DummyDRT, decode_block
 
 
+def module_case(seed: int, n: int, c: int, heads: int, k: int, dim: int):
+    """Seeded inputs of the module fixtures: hidden (N, C, 64, dim), gathered chunks
+    (N, (C-1)*K, 64, dim), weights (N, C-1, K), upstream gradient (N, C*64, dim), and the three
+    parameter tensors."""
+    g = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(n, c, 64, dim, generator=g)
+    gk = torch.randn(n, (c - 1) * k, 64, dim, generator=g)
+    gv = torch.randn(n, (c - 1) * k, 64, dim, generator=g)
+    w = torch.softmax(torch.randn(n, c - 1, k, generator=g), -1)
+    dout = torch.randn(n, c * 64, dim, generator=g)
+    params = {"pre_norm.weight": 1.0 + 0.1 * torch.randn(dim, generator=g),
+              "q_proj.weight": torch.randn(dim, dim, generator=g) / math.sqrt(dim),
+              "o_proj.weight": torch.randn(dim, dim, generator=g) / math.sqrt(dim)}
+    return hidden, gk, gv, w, dout, params
+
+
+def lift_reference_modules(ref_root: str, einsum_block: str):
+    """The reference's two GCA module classes, executable on CPU."""
+    import torch.nn as nn
+    src = open(os.path.join(ref_root, "model", "DRT.py")).read()
+    tree = ast.parse(src)
+    segs = {node.name: ast.get_source_segment(src, node) for node in tree.body
+            if isinstance(node, ast.ClassDef) and node.name in ("TritonGroupCrossAttention", "GroupCrossAttention")}
+
+    class RMSNorm(nn.Module):                     # stand-in for flash_attn.ops.rms_norm.RMSNorm: the plain formula
+        def __init__(self, hidden_size, eps=1e-5):
+            super().__init__()
+            self.weight = nn.Parameter(torch.ones(hidden_size))
+            self.eps = eps
+
+        def forward(self, x):
+            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight
+
+    def gca_einsum(q, k, v, weights, sm_scale, sm_n):     # the reference's einsum ground truth as the operator
+        group = q.shape[1] // k.shape[1]
+        ns_ = dict(torch=torch, q=q, k=k, v=v, weights=weights, sm_scale=sm_scale, dtype=q.dtype)
+        exec(einsum_block.replace("repeats=4", f"repeats={group}"), ns_)
+        return ns_["ref_out"]
+
+    def flash_attn_func(q, k, v, causal=False):           # (B, S, h, d) plain softmax attention
+        p = torch.softmax(torch.einsum('bqhd,bkhd->bhqk', q, k) / math.sqrt(q.shape[-1]), -1)
+        return torch.einsum('bhqk,bkhd->bqhd', p, v)
+
+    ns = dict(torch=torch, nn=nn, math=math, rearrange=rearrange, repeat=repeat, RMSNorm=RMSNorm, LlamaConfig=object,
+              gca_attn=gca_einsum, gca_kv_cache=gca_einsum, flash_attn_func=flash_attn_func)
+    exec(segs["GroupCrossAttention"], ns)
+    exec(segs["TritonGroupCrossAttention"], ns)
+    return ns["TritonGroupCrossAttention"], ns["GroupCrossAttention"]
+
+
+class ModuleConfig:
+    hidden_size, num_attention_heads, enc_chunk_size, chunk_topk = 128, 2, 63, 3
+    rms_norm_eps, attention_bias, enable_softmax_one = 1e-5, False, False
+
+
 def main(ref_root: str):
     torch.manual_seed(0)
     # ---- 1. GCA op: the reference's einsum ground truth, fp32 and its bf16 dtype path ----
@@ -168,6 +230,38 @@ def main(ref_root: str):
                         in_checksum=cases.checksum(hidden_states, lk),
                         indices=ns["indices"].numpy(), weights=ns["weights"].numpy())
     print("retrieval_ref_decode ok", tuple(ns["indices"].shape))
+
+    # ---- 5. the GCA sub-layer modules (DRT.py:235-398), forward + backward, train and eval mode ----
+    src_gca = open(os.path.join(ref_root, "ltriton", "gca.py")).read()
+    einsum_block = _slice_between(src_gca, "k_ = torch.repeat_interleave(k, dim=1, repeats=4)",
+                                  "ref_out = torch.einsum('Z H K M h, Z K->Z H M h', o_k, weights)")
+    TritonMod, FlashMod = lift_reference_modules(ref_root, einsum_block)
+    cfg = ModuleConfig()
+    n_, c_, k_ = 1, 3, cfg.chunk_topk
+    hidden, gk, gv, w, dout, params = module_case(51, n_, c_, cfg.num_attention_heads, k_, cfg.hidden_size)
+    out = {"in_checksum": cases.checksum(hidden, gk, gv, w, dout, *params.values())}
+    for tag, cls in (("triton", TritonMod), ("flash", FlashMod)):
+        mod = cls(cfg)
+        mod.load_state_dict(params)
+        ck, cv, cw = cls.preprocess_chunk_kv_cache(gk, gv, w, cfg.num_attention_heads)
+        for mode in ("train", "eval"):
+            mod.train(mode == "train")
+            mod.zero_grad()
+            hs = hidden.clone().requires_grad_()
+            o = mod(hs, ck, cv, cw)
+            o.backward(dout)
+            out[f"{tag}_{mode}_o"] = o.detach().numpy()
+            if mode == "train":
+                out[f"{tag}_dhidden"] = hs.grad.numpy()
+                out[f"{tag}_dq_proj"] = mod.q_proj.weight.grad.numpy().copy()
+                out[f"{tag}_do_proj"] = mod.o_proj.weight.grad.numpy().copy()
+        # decode step: one chunk, one row (D = 1, S = 1): no first-chunk padding
+        mod.eval()
+        with torch.no_grad():
+            o1 = mod(hidden[:, 1:2, :1], *cls.preprocess_chunk_kv_cache(gk[:, :k_], gv[:, :k_], w[:, :1], cfg.num_attention_heads))
+        out[f"{tag}_decode_o"] = o1.numpy()
+    np.savez_compressed(os.path.join(HERE, "module_ref.npz"), **out)
+    print("module_ref ok", {k2: v2.shape for k2, v2 in out.items() if hasattr(v2, "shape") and v2.ndim > 0 and "train_o" in k2})
 
     # ---- 4. mask (DRT.py:590-607) for a few shapes ----
     masks = {}

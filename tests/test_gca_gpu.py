@@ -214,8 +214,8 @@ def test_determinism(lcm, algo):
 
 @pytest.mark.parametrize("algo", ALGOS)
 def test_backward_stage_by_stage_equals_one_call(lcm, algo):
-    """gca_bwd_stages: index, then the dQ/dw stage, then the dK/dV stage (in that unusual order)
-    give the bits of the single gca_bwd call."""
+    """gca_bwd_stages: index, then the dQ/dw stage, then the dK/dV stage give the bits of the
+    single gca_bwd call."""
     from long_context_modeling_b200 import gca as gmod
     q, kc, vc, idx, w, dout = (t.cuda() for t in cases.gca_indexed_case(21, 2, 14, 4, 8, dtype=torch.bfloat16))
     _, lse = gmod.gca_forward_with_lse(q, kc, vc, idx, w, 0.125, algo=algo)
@@ -232,7 +232,7 @@ def test_backward_stage_by_stage_equals_one_call(lcm, algo):
 
 
 @pytest.mark.parametrize("shape", [(2, 14, 4, 8), (3, 40, 2, 4), (1, 70, 4, 16), (8, 256, 2, 8), (1, 1024, 2, 4)])
-def test_inverse_index_single_launch_equals_radix_sort(lcm, shape, monkeypatch):
+def test_inverse_index_single_launch_equals_radix_sort(lcm, shape):
     """The single-launch counting sort that builds the inverse retrieval index for small problems
     (stable by (query chunk, slot) inside a chunk; units walked by decreasing number of
     retrievers) gives the bits of the radix-sort path: same entry order means the same float32
@@ -244,10 +244,8 @@ def test_inverse_index_single_launch_equals_radix_sort(lcm, shape, monkeypatch):
     idx[:, c // 2:, 0] = 0                               # many retrievers of one chunk
     idx[:, -1, 1:] = -1                                  # padding slots
     _, lse = gmod.gca_forward_with_lse(q, kc, vc, idx, w, 0.125)
-    monkeypatch.delenv("GCA_CSR_PATH", raising=False)
     fast = gmod.gca_backward_stages(q, kc, vc, idx, w, dout, lse, 0.125)
-    monkeypatch.setenv("GCA_CSR_PATH", "sort")
-    slow = gmod.gca_backward_stages(q, kc, vc, idx, w, dout, lse, 0.125)
+    slow = gmod.gca_backward_stages(q, kc, vc, idx, w, dout, lse, 0.125, stages=gmod.BWD_STAGE_ALL | gmod.BWD_INDEX_BY_SORT)
     torch.cuda.synchronize()
     for x, y in zip(fast, slow):
         assert torch.equal(x, y)
@@ -289,15 +287,11 @@ def test_strided_query_view_and_token_major_output(lcm):
 
 
 def test_single_head_units_match_head_pairs(lcm):
-    """The tensor-core kernel's debug layout (one head per unit) gives the same bits as the
-    paired layout: both run the same per-row arithmetic."""
+    """The tensor-core forward with one head per work unit (GCA_ALGO_TC_UNPAIRED) gives the same
+    bits as the paired layout: both run the same per-row arithmetic."""
     q, kc, vc, idx, w, _ = cases.gca_indexed_case(9, 1, 8, 3, 4, dtype=torch.bfloat16)
     a = run_indexed(lcm, q, kc, vc, idx, w, 0.125, algo=2)
-    os.environ["GCA_TC_PAIR"] = "0"
-    try:
-        b = run_indexed(lcm, q, kc, vc, idx, w, 0.125, algo=2)
-    finally:
-        del os.environ["GCA_TC_PAIR"]
+    b = run_indexed(lcm, q, kc, vc, idx, w, 0.125, algo=3)          # GCA_ALGO_TC_UNPAIRED
     assert torch.equal(a, b)
 
 

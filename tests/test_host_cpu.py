@@ -34,7 +34,7 @@ def test_library_exports_every_declared_symbol(lib):
     for name in declared:
         assert hasattr(handle, name), f"{name} declared in the header but not exported"
     assert set(lib.EXPORTS) == declared
-    assert handle.gca_abi_version() == 1
+    assert handle.gca_abi_version() == lib.ABI_VERSION == 2
 
 
 def test_struct_layouts_match(lib):
@@ -106,6 +106,13 @@ def test_decode_and_topk_validation(lib):
     assert lib.lib().lmk_topk_merge(C.byref(m), None) == -1
     c = lib.CacheAppendArgs()
     assert lib.lib().gca_cache_append(C.byref(c), None) == -1
+    # a position beyond the destination's capacity is refused on the host (nothing is written)
+    for f in ("new_k", "new_v", "k_cache", "v_cache"):
+        setattr(c, f, 0x10000)
+    c.N, c.count, c.pos, c.L, c.HD, c.Dm, c.dtype = 1, 3, 14, 64, 128, 0, lib.BF16
+    c.new_batch_stride, c.cache_batch_stride = 3 * 64 * 128, 16 * 64 * 128
+    c.capacity = 16
+    assert lib.lib().gca_cache_append(C.byref(c), None) == -3          # chunks 14..16 of a 16-chunk buffer
     b = lib.GcaBwdArgs()
     assert lib.lib().gca_bwd(C.byref(b), None) == -1
 

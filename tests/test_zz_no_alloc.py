@@ -21,7 +21,7 @@ import cases
 pytestmark = pytest.mark.gpu
 
 
-def _args(lib, lq, lk, k, outs, head_dim=0, splits=0):
+def _args(lib, lq, lk, k, outs, head_dim=0, splits=0, noise=None):
     keys, idx, sc, w, nv = outs
     a = lib.LmkTopkArgs()
     a.lmk_q, a.lmk_k = lq.data_ptr(), lk.data_ptr()
@@ -34,6 +34,7 @@ def _args(lib, lq, lk, k, outs, head_dim=0, splits=0):
     a.q_pos0, a.e_base = e - cq, 0
     a.N, a.Cq, a.E, a.D, a.K = n, cq, e, d, k
     a.head_dim, a.score_round, a.splits = head_dim, 0, splits
+    a.noise = noise.data_ptr() if noise is not None else None
     return a
 
 
@@ -56,19 +57,25 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
     # batch-shaped one with per-head lists (the second reuses the array the first one filled)
     problems = [dict(seed=41, n=1, cq=1, e=40000, d=768, k=8, head_dim=0),
                 dict(seed=42, n=2, cq=9, e=300, d=768, k=4, head_dim=0),
-                dict(seed=43, n=1, cq=1, e=5000, d=768, k=8, head_dim=64)]
+                dict(seed=43, n=1, cq=1, e=5000, d=768, k=8, head_dim=64),
+                dict(seed=45, n=2, cq=5, e=400, d=768, k=8, head_dim=0, noise=True)]   # selection on noisy scores,
+                                                                                    # noise-free scores recomputed
     for pb in problems:
         lq, lk = cases.landmark_case(pb["seed"], pb["n"], pb["cq"], pb["e"], d=pb["d"])
         lq, lk = lq.to(dev), lk.to(dev)
         rows_shape = (pb["n"], pb["cq"]) + ((pb["d"] // 64,) if pb["head_dim"] else ())
+        noise = None
+        if pb.get("noise"):
+            g = torch.Generator().manual_seed(pb["seed"])
+            noise = (-torch.empty(pb["n"], pb["cq"], pb["e"]).exponential_(generator=g).log()).to(dev)
         ref_out = _outputs(rows_shape, pb["k"], dev)
-        a = _args(lib, lq, lk, pb["k"], ref_out, head_dim=pb["head_dim"])
+        a = _args(lib, lq, lk, pb["k"], ref_out, head_dim=pb["head_dim"], noise=noise)
         nbytes = handle.lmk_topk_workspace_bytes(C.byref(a))
         ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
         a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
         assert handle.lmk_score_topk(C.byref(a), stream) == 0
         got_out = _outputs(rows_shape, pb["k"], dev)
-        b = _args(lib, lq, lk, pb["k"], got_out, head_dim=pb["head_dim"])      # no workspace at all
+        b = _args(lib, lq, lk, pb["k"], got_out, head_dim=pb["head_dim"], noise=noise)      # no workspace at all
         assert handle.lmk_score_topk_static(C.byref(b), stream) == 0
         torch.cuda.synchronize()
         for name, r, g in zip(("keys", "indices", "scores", "weights", "n_valid"), ref_out, got_out):
