@@ -311,6 +311,21 @@ def gpu_arm(args):
         line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
                                 "sample": "1 of the 8 sequences (256 chunks x 12 heads x top-8), fp32 einsum + "
                                           "gather + autograd, 2 timed steps"}
+    if world > 1:
+        # the path that DOES exchange data between GPUs: 16M-token landmark retrieval over a cache
+        # sharded by chunk range (both scoring modes), so that multi-GPU runs of the default line
+        # carry it
+        del dev_sets, fwd_out, bufs
+        torch.cuda.empty_cache()
+        sub = {}
+        for mode, per_head in (("per_sequence", False), ("per_head", True)):
+            r = measure_retrieval(dev, world, rank, local, per_head, 100, 10, peaks)
+            sub[mode] = {"n_gpu_us": r["ms_per_step"] * 1e3, "n_gpu_eager_us": (r["eager_ms_per_step"] or 0) * 1e3,
+                         "local_scan_us": r["roofline"]["us_per_launch"], "local_scan_gbs_per_gpu": r["roofline"]["achieved"],
+                         "local_scan_frac_of_hbm_peak": r["roofline"]["frac"], "whole_cache_gbs": r["value"]}
+        line["retrieval"] = {"what": "landmark top-8 over 262,144 cached chunks (16M tokens), batch 1, cache sharded by chunk "
+                                     "range over the ranks; CUDA-graph replay of scan + all-gather + merge, max over ranks",
+                             **sub}
     if rank == 0 and world == 1 and args.triton_ref:
         del dev_sets, fwd_out, bufs
         torch.cuda.empty_cache()
@@ -432,23 +447,16 @@ def _graph_time(fn, flush, inner=10, reps=15):
     return statistics.median(ts)
 
 
-def retrieval_arm(args):
-    """Landmark scoring + top-k over 262,144 cached chunks (a 16M-token context), batch 1:
-    the decode-time retrieval block (model/DRT.py:825-849).  With N GPUs the cache is sharded by
-    chunk range (strong scaling): local scan, one all-gather of the packed candidates, merge."""
+def measure_retrieval(dev, world, rank, local, per_head, steps, warmup, peaks, with_cpu=False):
+    """Landmark scoring + top-k over 262,144 cached chunks (a 16M-token context), batch 1: the
+    decode-time retrieval block (model/DRT.py:825-849).  With N GPUs the cache is sharded by chunk
+    range (strong scaling): local scan, one all-gather of the packed candidates, merge -- replayed
+    from a CUDA graph (`ShardedRetriever`), and eager for comparison.  Returns the JSON line."""
     import torch.distributed as dist
     import long_context_modeling_b200 as lcm
     from long_context_modeling_b200 import sharded
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    peaks = load_peaks()
     e_total, d, topk = 262144, 768, 8
-    head_dim = 64 if args.per_head else 0
+    head_dim = 64 if per_head else 0
     lo, hi = sharded.shard_range(e_total, world, rank)
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     lk = (torch.randn(1, hi - lo, d, generator=g, device=dev) * 0.125).bfloat16()
@@ -456,18 +464,20 @@ def retrieval_arm(args):
     lq_host = (torch.randn(1, 1, d, generator=gq) * 0.125).bfloat16().pin_memory()
     lq = lq_host.to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    retriever = None
 
     def step():
         if world == 1:
             return lcm.lmk_score_topk(lq, lk, topk, head_dim=head_dim)
+        return eager_step()
+
+    def eager_step():
         return sharded.sharded_lmk_topk(lq, lk, topk, e_total=e_total, head_dim=head_dim, validate=False)
 
     def e2e_step():
         q = lq_host.to(dev, non_blocking=True)
-        if world == 1:
-            r = lcm.lmk_score_topk(q, lk, topk, head_dim=head_dim)
-        else:
-            r = sharded.sharded_lmk_topk(q, lk, topk, e_total=e_total, head_dim=head_dim, validate=False)
+        r = (lcm.lmk_score_topk(q, lk, topk, head_dim=head_dim) if world == 1 else
+             sharded.sharded_lmk_topk(q, lk, topk, e_total=e_total, head_dim=head_dim, validate=False))
         return r.indices.cpu(), r.weights.cpu()
 
     def barrier():
@@ -495,9 +505,9 @@ def retrieval_arm(args):
             ms = float(t.item())
         return ms, clocks
 
-    steps, warmup = max(args.steps, 50), max(5, args.warmup)
     ms, clocks = timed(step, steps, warmup)
     ms_e2e, _ = timed(e2e_step, steps, warmup)
+    ms_eager = timed(eager_step, steps, warmup)[0] if world > 1 else None
     # the scan + finalize kernels of this rank alone, launch overhead removed
     ms_scan = _graph_time(lambda: lcm.lmk_score_topk(lq, lk, topk, head_dim=head_dim), flush)
     bytes_total = e_total * d * 2
@@ -512,17 +522,19 @@ def retrieval_arm(args):
                        "landmarks": e_total, "hidden": d, "topk": topk, "per_head": bool(head_dim),
                        "cache_policy": "the landmark cache (403 MB / n_gpus per GPU) exceeds the 126 MB L2 at N <= 2; "
                                        "the graph-timed kernel figure flushes L2 between replays",
-                       "parallelism": "cache sharded by chunk range; one all-gather of 64 B per row per rank; same merge on every rank"},
+                       "parallelism": "cache sharded by chunk range; one all-gather of 64 B per row per rank; same merge on "
+                                      "every rank; the step is replayed from a CUDA graph (eager time reported beside it)"},
             "clocks": clocks,
             "e2e": {"value": bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": lq_host.numel() * 2,
                     "d2h_bytes_per_step": topk * 8 * (d // 64 if head_dim else 1), "ms_per_step": ms_e2e},
+            "eager_ms_per_step": ms_eager,
             "gpu_launches": (2 if world == 1 else 3) * steps,
             "roofline": {"kernel": "lmk_scan_kernel + lmk_finalize_kernel", "bound": "hbm", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "peak_source": peaks["source"] + " copy bandwidth", "traffic": None,
                          "algorithmic_bytes_per_launch": bytes_local, "us_per_launch": ms_scan * 1e3},
             "device_status": lcm.read_status()}
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if with_cpu:
         torch.set_num_threads(os.cpu_count() or 1)
         lkc, lqc = lk.float().cpu(), lq.float().cpu()
         t0 = time.perf_counter()
@@ -533,6 +545,22 @@ def retrieval_arm(args):
         dt = (time.perf_counter() - t0) / reps
         line["cpu_baseline"] = {"value": bytes_total / dt / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
                                 "sample": f"the full 262,144 x 768 scan in fp32 (einsum + topk + softmax), {reps} queries"}
+    del retriever, lk, flush
+    torch.cuda.empty_cache()
+    return line
+
+
+def retrieval_arm(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    line = measure_retrieval(dev, world, rank, local, args.per_head, max(args.steps, 50), max(5, args.warmup), load_peaks(),
+                             with_cpu=(rank == 0 and world == 1 and not args.no_cpu))
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
