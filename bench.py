@@ -464,20 +464,21 @@ def measure_retrieval(dev, world, rank, local, per_head, steps, warmup, peaks, w
     lq_host = (torch.randn(1, 1, d, generator=gq) * 0.125).bfloat16().pin_memory()
     lq = lq_host.to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    retriever = None
+    exchange = sharded.PeerExchange(dev, max_rows=16) if world > 1 else None
+    retriever = (sharded.ShardedRetriever(lq, lk, topk, e_total=e_total, exchange=exchange, head_dim=head_dim)
+                 if world > 1 else None)
 
     def step():
         if world == 1:
             return lcm.lmk_score_topk(lq, lk, topk, head_dim=head_dim)
-        return eager_step()
+        return retriever(lq)
 
     def eager_step():
         return sharded.sharded_lmk_topk(lq, lk, topk, e_total=e_total, head_dim=head_dim, validate=False)
 
     def e2e_step():
         q = lq_host.to(dev, non_blocking=True)
-        r = (lcm.lmk_score_topk(q, lk, topk, head_dim=head_dim) if world == 1 else
-             sharded.sharded_lmk_topk(q, lk, topk, e_total=e_total, head_dim=head_dim, validate=False))
+        r = lcm.lmk_score_topk(q, lk, topk, head_dim=head_dim) if world == 1 else retriever(q)
         return r.indices.cpu(), r.weights.cpu()
 
     def barrier():
@@ -507,7 +508,9 @@ def measure_retrieval(dev, world, rank, local, per_head, steps, warmup, peaks, w
 
     ms, clocks = timed(step, steps, warmup)
     ms_e2e, _ = timed(e2e_step, steps, warmup)
-    ms_eager = timed(eager_step, steps, warmup)[0] if world > 1 else None
+    ms_eager = timed(eager_step, steps, warmup)[0] if world > 1 else None            # NCCL all-gather + merge, issued from Python
+    ms_p2p_eager = (timed(lambda: sharded.sharded_lmk_topk(lq, lk, topk, e_total=e_total, head_dim=head_dim, exchange=exchange),
+                          steps, warmup)[0] if world > 1 else None)
     # the scan + finalize kernels of this rank alone, launch overhead removed
     ms_scan = _graph_time(lambda: lcm.lmk_score_topk(lq, lk, topk, head_dim=head_dim), flush)
     bytes_total = e_total * d * 2
@@ -522,13 +525,14 @@ def measure_retrieval(dev, world, rank, local, per_head, steps, warmup, peaks, w
                        "landmarks": e_total, "hidden": d, "topk": topk, "per_head": bool(head_dim),
                        "cache_policy": "the landmark cache (403 MB / n_gpus per GPU) exceeds the 126 MB L2 at N <= 2; "
                                        "the graph-timed kernel figure flushes L2 between replays",
-                       "parallelism": "cache sharded by chunk range; one all-gather of 64 B per row per rank; same merge on "
-                                      "every rank; the step is replayed from a CUDA graph (eager time reported beside it)"},
+                       "parallelism": "cache sharded by chunk range; candidates exchanged by peer stores into every rank's mailbox "
+                                      "and merged in the same kernel (one launch per rank); scan + exchange replayed from a CUDA "
+                                      "graph; eager times (NCCL all-gather path, peer-exchange path) reported beside it"},
             "clocks": clocks,
             "e2e": {"value": bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": lq_host.numel() * 2,
                     "d2h_bytes_per_step": topk * 8 * (d // 64 if head_dim else 1), "ms_per_step": ms_e2e},
-            "eager_ms_per_step": ms_eager,
-            "gpu_launches": (2 if world == 1 else 3) * steps,
+            "eager_ms_per_step": ms_eager, "eager_peer_exchange_ms_per_step": ms_p2p_eager,
+            "gpu_launches": (2 if world == 1 else 3) * steps,      # scan, finalize (+ exchange-and-merge)
             "roofline": {"kernel": "lmk_scan_kernel + lmk_finalize_kernel", "bound": "hbm", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "peak_source": peaks["source"] + " copy bandwidth", "traffic": None,
@@ -545,7 +549,11 @@ def measure_retrieval(dev, world, rank, local, per_head, steps, warmup, peaks, w
         dt = (time.perf_counter() - t0) / reps
         line["cpu_baseline"] = {"value": bytes_total / dt / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
                                 "sample": f"the full 262,144 x 768 scan in fp32 (einsum + topk + softmax), {reps} queries"}
-    del retriever, lk, flush
+    torch.cuda.synchronize()
+    del retriever
+    if exchange is not None:
+        exchange.close()
+    del lk, flush
     torch.cuda.empty_cache()
     return line
 

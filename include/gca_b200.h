@@ -272,6 +272,45 @@ typedef struct LmkMergeArgs {
 int lmk_topk_merge(const LmkMergeArgs* args, void* stream);
 
 /*
+ * Candidate exchange between the GPUs of ONE node for the chunk-range-sharded cache, fused with
+ * the merge (no counterpart in the reference, which parks the cache on the host instead,
+ * model/DRT.py:87-128): one launch per rank and step.  Each rank stores its K packed candidates
+ * per row into its slot of every rank's mailbox through peer mappings (stores only; nothing
+ * reads remote memory), raises a flag, waits -- bounded by `wait_ms` -- for all ranks' flags in
+ * its own mailbox, and merges the world x K candidates exactly like lmk_topk_merge, so every
+ * rank ends with the identical global top-k.  If the wait expires, GCA_STATUS_TIMEOUT is OR-ed
+ * into *status, the outputs of that row are not written, and the kernel returns; the host then
+ * brings the ranks back in step (a barrier of its own, then lmk_exchange_mailbox_reset on every
+ * rank).  The step counter lives in the mailbox, so the launch can be part of a CUDA graph.
+ *
+ * Set-up, once per rank: lmk_exchange_mailbox_create (allocates and clears the mailbox with
+ * cudaMalloc on the current device and fills a 64-byte IPC handle), exchange the handles among the
+ * ranks by any host means, lmk_exchange_mailbox_open for every other rank's handle, and put the
+ * `world` pointers (own mailbox at index `rank`) into a device array: that array is `mailboxes`.
+ */
+typedef struct LmkExchangeArgs {
+  const uint64_t* local_keys;   /* (R, K) this rank's candidates: out_keys of lmk_score_topk */
+  void* const* mailboxes;       /* DEVICE array of `world` mailbox pointers as mapped in this process */
+  uint64_t* out_keys;           /* (R, K) outputs as in lmk_topk_merge */
+  int32_t* out_indices;
+  float* out_scores;
+  float* out_weights;
+  int32_t* out_nvalid;
+  int32_t* status;              /* device status word, or NULL */
+  int32_t R, K, world, rank;
+  int32_t R_max;                /* rows the mailboxes were created for (the same on every rank) */
+  int32_t wait_ms;              /* bound of the wait for the other ranks' flags; 0 = 1000 */
+} LmkExchangeArgs;
+
+size_t lmk_exchange_mailbox_bytes(int r_max, int world);
+int lmk_exchange_mailbox_create(int r_max, int world, void** mailbox, void* ipc_handle64);
+int lmk_exchange_mailbox_open(const void* ipc_handle64, void** peer_ptr);
+int lmk_exchange_mailbox_close(void* peer_ptr);
+int lmk_exchange_mailbox_destroy(void* mailbox);
+int lmk_exchange_mailbox_reset(void* mailbox, int r_max, int world, void* stream);
+int lmk_topk_exchange(const LmkExchangeArgs* args, void* stream);
+
+/*
  * Chunk cache append with the landmark row cleared.  Stands in for the tensor work of
  * model/DRT.py:770-784 + ChunkKVManager.append (:87-133): copies `count` new chunks of K
  * and V (N, count, L, Hkv*D) into a preallocated cache (N, capacity, L, Hkv*D) at chunk
@@ -302,7 +341,7 @@ int gca_cache_append(const CacheAppendArgs* args, void* stream);
 const char* gca_strerror(int code);
 int gca_abi_version(void);
 /* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,
- * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs): lets a foreign-language binding verify
+ * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs): lets a foreign-language binding verify
  * its struct layout before the first call. */
 size_t gca_sizeof(int which);
 

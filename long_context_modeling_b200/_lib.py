@@ -83,6 +83,16 @@ class CacheAppendArgs(C.Structure):
     ]
 
 
+class LmkExchangeArgs(C.Structure):
+    _fields_ = [
+        ("local_keys", C.c_void_p), ("mailboxes", C.c_void_p),
+        ("out_keys", C.c_void_p), ("out_indices", C.c_void_p), ("out_scores", C.c_void_p),
+        ("out_weights", C.c_void_p), ("out_nvalid", C.c_void_p), ("status", C.c_void_p),
+        ("R", C.c_int32), ("K", C.c_int32), ("world", C.c_int32), ("rank", C.c_int32),
+        ("R_max", C.c_int32), ("wait_ms", C.c_int32),
+    ]
+
+
 EXPORTS = {
     "gca_fwd": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
     "gca_decode": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
@@ -94,6 +104,13 @@ EXPORTS = {
     "lmk_score_topk_static": (C.c_int, [C.POINTER(LmkTopkArgs), C.c_void_p]),
     "lmk_topk_merge": (C.c_int, [C.POINTER(LmkMergeArgs), C.c_void_p]),
     "gca_cache_append": (C.c_int, [C.POINTER(CacheAppendArgs), C.c_void_p]),
+    "lmk_exchange_mailbox_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "lmk_exchange_mailbox_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p]),
+    "lmk_exchange_mailbox_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "lmk_exchange_mailbox_close": (C.c_int, [C.c_void_p]),
+    "lmk_exchange_mailbox_destroy": (C.c_int, [C.c_void_p]),
+    "lmk_exchange_mailbox_reset": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "lmk_topk_exchange": (C.c_int, [C.POINTER(LmkExchangeArgs), C.c_void_p]),
     "gca_strerror": (C.c_char_p, [C.c_int]),
     "gca_abi_version": (C.c_int, []),
     "gca_sizeof": (C.c_size_t, [C.c_int]),
@@ -117,7 +134,7 @@ def lib() -> C.CDLL:
             fn.argtypes = argtypes
         if handle.gca_abi_version() != ABI_VERSION:
             raise RuntimeError("libgca_b200.so has an unexpected ABI version")
-        for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs)):
+        for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs, LmkExchangeArgs)):
             if handle.gca_sizeof(which) != C.sizeof(struct):
                 raise RuntimeError(f"struct layout mismatch for {struct.__name__}: "
                                    f"library {handle.gca_sizeof(which)} vs binding {C.sizeof(struct)}")

@@ -108,6 +108,7 @@ size_t gca_sizeof(int which) {
     case 2: return sizeof(LmkTopkArgs);
     case 3: return sizeof(LmkMergeArgs);
     case 4: return sizeof(CacheAppendArgs);
+    case 5: return sizeof(LmkExchangeArgs);
     default: return 0;
   }
 }

@@ -219,18 +219,17 @@ struct FinalParams {
 
 constexpr int FIN_WARPS = 8;
 
-__global__ void __launch_bounds__(FIN_WARPS * 32)
-lmk_finalize_kernel(FinalParams p) {
-  __shared__ unsigned long long sL[FIN_WARPS][MAXK];
+// The merge of one row's P candidates (src) by one block of FIN_WARPS warps (sL: FIN_WARPS x MAXK
+// keys of shared memory), and the decoded outputs of the row.
+__device__ void finalize_row(const FinalParams& p, long long row, const unsigned long long* src,
+                             unsigned long long (*sL)[MAXK]) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long row = blockIdx.x;
-  const unsigned long long* src = p.keys + row * p.P;
   // each warp merges a contiguous share of the candidates
   const int per = (p.P + FIN_WARPS - 1) / FIN_WARPS;
   const int lo = warp * per, hi = min(p.P, lo + per);
   unsigned long long m = 0ull, th = 0ull;
   for (int i0 = lo; i0 < hi; i0 += 32) {
-    const unsigned long long mykey = (i0 + lane < hi) ? src[i0 + lane] : 0ull;
+    const unsigned long long mykey = (i0 + lane < hi) ? __ldcg(src + i0 + lane) : 0ull;   // may have been written by another GPU
     unsigned pending = __ballot_sync(0xffffffffu, mykey > th);
     while (pending) {
       const int srcl = __ffs(pending) - 1;
@@ -297,6 +296,106 @@ lmk_finalize_kernel(FinalParams p) {
     if (p.out_weights) p.out_weights[o] = wgt;
   }
   if (lane == 0 && p.out_nvalid) p.out_nvalid[row] = (int)nv;
+}
+
+__global__ void __launch_bounds__(FIN_WARPS * 32)
+lmk_finalize_kernel(FinalParams p) {
+  __shared__ unsigned long long sL[FIN_WARPS][MAXK];
+  finalize_row(p, blockIdx.x, p.keys + (long long)blockIdx.x * p.P, sL);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Candidate exchange between the GPUs of a chunk-range-sharded cache, fused with the merge.
+//
+// Every rank owns a MAILBOX in its own memory that the other ranks of the node have mapped
+// (CUDA IPC).  One launch per rank and retrieval step: a block per query row
+//   1. STORES this rank's K packed candidates of the row into its slot of every rank's mailbox
+//      (plain stores through the peer mapping; over NVLink for the other GPUs),
+//   2. raises its flag there (system-scope release after a system-scope fence),
+//   3. waits -- for at most `wait_ns` -- until every rank's flag of this step stands in its OWN
+//      mailbox (system-scope acquire loads of local memory),
+//   4. merges the world x K candidates (same merge, same canonical order as on one GPU, so every
+//      rank gets the identical result) and writes indices / scores / weights.
+// No rank reads another GPU's memory and nothing is multicast: remote traffic is stores only.
+// Steps are numbered by an epoch the kernel keeps in the mailbox header (one per row, advanced
+// when the row's merge is done), so the launch can sit in a CUDA graph; two mailbox buffers
+// alternate by epoch parity: a rank can be at most one step ahead of another (to finish step e
+// it needs everybody's flag of step e), so a buffer is never overwritten while it is being read.
+// When the wait expires the block raises GCA_STATUS_TIMEOUT, leaves the epoch where it was and
+// returns: the context stays usable, and the host decides (PeerExchange.reset()).
+//
+// Mailbox layout (bytes): epoch[R_max] u32 | pad to 256 | 2 x { keys[R_max][world][MAXK] u64 |
+// flags[R_max][world] u32 | pad to 256 }.
+struct ExchangeParams {
+  const unsigned long long* local_keys;     // (R, K)
+  void* const* mailboxes;                   // device array of `world` pointers (this process's mappings)
+  FinalParams fin;
+  int32_t* status;
+  int R, K, world, rank, r_max;
+  unsigned long long wait_ns;
+};
+
+__host__ __device__ inline size_t exch_buf_bytes(int r_max, int world) {
+  const size_t keys = (size_t)r_max * world * MAXK * 8, flags = (size_t)r_max * world * 4;
+  return (keys + flags + 255) / 256 * 256;
+}
+__host__ __device__ inline size_t exch_hdr_bytes(int r_max) { return ((size_t)r_max * 4 + 255) / 256 * 256; }
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void __launch_bounds__(FIN_WARPS * 32)
+lmk_exchange_kernel(ExchangeParams p) {
+  __shared__ unsigned long long sL[FIN_WARPS][MAXK];
+  __shared__ int s_ok;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  char* mine = static_cast<char*>(p.mailboxes[p.rank]);
+  unsigned* epochs = reinterpret_cast<unsigned*>(mine);
+  const unsigned e = *reinterpret_cast<volatile unsigned*>(epochs + row) + 1u;
+  const size_t buf_off = exch_hdr_bytes(p.r_max) + (size_t)(e & 1u) * exch_buf_bytes(p.r_max, p.world);
+  const size_t flags_off = buf_off + (size_t)p.r_max * p.world * MAXK * 8;
+  // 1. my candidates into my slot of every rank's mailbox (thread = (destination rank, key); a
+  //    slot is MAXK keys wide, the keys past K are written as "empty")
+  if (tid < p.world * MAXK) {
+    const int dst = tid / MAXK, i = tid - dst * MAXK;
+    unsigned long long* slot = reinterpret_cast<unsigned long long*>(static_cast<char*>(p.mailboxes[dst]) + buf_off) +
+                               ((size_t)row * p.world + p.rank) * MAXK;
+    slot[i] = i < p.K ? p.local_keys[(size_t)row * p.K + i] : 0ull;
+  }
+  __threadfence_system();
+  __syncthreads();
+  // 2. my flag of this step in every rank's mailbox
+  if (tid < p.world) {
+    unsigned* flag = reinterpret_cast<unsigned*>(static_cast<char*>(p.mailboxes[tid]) + flags_off) + (size_t)row * p.world + p.rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(e) : "memory");
+  }
+  // 3. bounded wait for every rank's flag in MY mailbox
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+  if (tid < p.world) {
+    const unsigned* flag = reinterpret_cast<const unsigned*>(mine + flags_off) + (size_t)row * p.world + tid;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v == e) break;
+      if (global_ns() - t0 > p.wait_ns) { s_ok = 0; break; }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  if (!s_ok) {
+    if (tid == 0 && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
+    return;
+  }
+  // 4. the row's candidates sit contiguously in my mailbox, MAXK per rank with empty keys (0) as
+  //    filler: the merge takes them in place as P = world x MAXK candidates
+  const unsigned long long* src = reinterpret_cast<const unsigned long long*>(mine + buf_off) + (size_t)row * p.world * MAXK;
+  finalize_row(p.fin, row, src, sL);
+  if (tid == 0) epochs[row] = e;
 }
 
 // Two CTAs per SM when the query tile count alone does not fill the GPU.
@@ -408,6 +507,7 @@ int launch_lmk_merge(const LmkMergeArgs& a, cudaStream_t stream) {
 // needs to start at zero.  Two calls that overlap on the same GPU (different streams, or
 // different host threads) would overwrite each other's lists: serialise them.
 // ---------------------------------------------------------------------------------------------
+#include <cstring>
 #include <mutex>
 
 namespace gca {
@@ -449,4 +549,76 @@ extern "C" int lmk_score_topk_static(const LmkTopkArgs* a, void* stream) {
   rc = gca::static_scratch_ptr(scope.dev, &scratch);
   if (rc) return rc;
   return gca::launch_lmk_score_topk(*a, scratch, sms, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side of the candidate exchange: mailbox set-up (CUDA IPC) and the launch.
+// ---------------------------------------------------------------------------------------------
+extern "C" size_t lmk_exchange_mailbox_bytes(int r_max, int world) {
+  if (r_max < 1 || world < 1) return 0;
+  return gca::exch_hdr_bytes(r_max) + 2 * gca::exch_buf_bytes(r_max, world);
+}
+
+extern "C" int lmk_exchange_mailbox_create(int r_max, int world, void** mailbox, void* ipc_handle64) {
+  if (!mailbox || !ipc_handle64) return GCA_ERR_NULL;
+  if (r_max < 1 || world < 1 || world > 8) return GCA_ERR_SHAPE;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is exchanged as 64 bytes");
+  const size_t bytes = lmk_exchange_mailbox_bytes(r_max, world);
+  void* p = nullptr;
+  GCA_CUDA_CHECK(cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(ipc_handle64), p);
+  if (e != cudaSuccess) { cudaFree(p); return (int)e; }
+  *mailbox = p;
+  return 0;
+}
+
+extern "C" int lmk_exchange_mailbox_open(const void* ipc_handle64, void** peer_ptr) {
+  if (!ipc_handle64 || !peer_ptr) return GCA_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, ipc_handle64, sizeof(h));
+  GCA_CUDA_CHECK(cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+
+extern "C" int lmk_exchange_mailbox_close(void* peer_ptr) {
+  if (!peer_ptr) return GCA_ERR_NULL;
+  GCA_CUDA_CHECK(cudaIpcCloseMemHandle(peer_ptr));
+  return 0;
+}
+
+extern "C" int lmk_exchange_mailbox_destroy(void* mailbox) {
+  if (!mailbox) return GCA_ERR_NULL;
+  GCA_CUDA_CHECK(cudaFree(mailbox));
+  return 0;
+}
+
+extern "C" int lmk_exchange_mailbox_reset(void* mailbox, int r_max, int world, void* stream) {
+  if (!mailbox) return GCA_ERR_NULL;
+  GCA_CUDA_CHECK(cudaMemsetAsync(mailbox, 0, lmk_exchange_mailbox_bytes(r_max, world), (cudaStream_t)stream));
+  return 0;
+}
+
+extern "C" int lmk_topk_exchange(const LmkExchangeArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->local_keys || !a->mailboxes || !a->out_keys) return GCA_ERR_NULL;
+  if (a->world < 1 || a->world > 8 || a->rank < 0 || a->rank >= a->world) return GCA_ERR_SHAPE;
+  if (a->R < 0 || a->R > a->R_max || a->K < 1 || a->K > gca::MAXK) return GCA_ERR_SHAPE;
+  if (a->R == 0) return 0;
+  gca::DeviceScope scope(a->local_keys);
+  if (scope.rc) return scope.rc;
+  gca::ExchangeParams p;
+  p.local_keys = reinterpret_cast<const unsigned long long*>(a->local_keys);
+  p.mailboxes = a->mailboxes;
+  p.status = a->status;
+  p.R = a->R; p.K = a->K; p.world = a->world; p.rank = a->rank; p.r_max = a->R_max;
+  p.wait_ns = (unsigned long long)(a->wait_ms > 0 ? a->wait_ms : 1000) * 1000000ull;
+  gca::FinalParams& fp = p.fin;
+  fp.keys = nullptr; fp.out_keys = reinterpret_cast<unsigned long long*>(a->out_keys); fp.out_indices = a->out_indices;
+  fp.out_scores = a->out_scores; fp.out_weights = a->out_weights; fp.out_nvalid = a->out_nvalid;
+  fp.lq = nullptr; fp.lk = nullptr; fp.qbs = fp.qrs = fp.kbs = fp.krs = fp.e_base = 0;
+  fp.Cq = 1; fp.D = 0; fp.score_round = 0; fp.scale = 1.f;
+  fp.R = a->R; fp.P = a->world * gca::MAXK; fp.K = a->K;
+  gca::lmk_exchange_kernel<<<(unsigned)a->R, gca::FIN_WARPS * 32, 0, (cudaStream_t)stream>>>(p);
+  return (int)cudaGetLastError();
 }

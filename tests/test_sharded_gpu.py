@@ -1,10 +1,14 @@
-"""Chunk-range-sharded retrieval and GCA decode over NCCL on 2+ GPUs (skipped on a 1-GPU box).
+"""Chunk-range-sharded retrieval and GCA decode on 2+ GPUs (skipped on a 1-GPU box).
 
 Each rank is a child process with its own GPU.  Every rank also runs the single-GPU kernels
 over the whole cache on its own device and compares: the sharded selection must be
-bit-identical (same packed keys, same indices), the weights equal, and the owner-computes
-decode within bf16 tolerance of the one-GPU result (the partial outputs are summed in a
-different order).
+bit-identical (same packed keys, same indices), the weights equal -- through the NCCL
+all-gather, through the fused peer-store exchange kernel, and through the CUDA-graph replay of
+scan + exchange -- and the owner-computes decode within bf16 tolerance of the one-GPU result
+(the partial outputs are summed in a different order).  A step in which one rank withholds its
+publish ON THE HOST must end on the other ranks with GCA_STATUS_TIMEOUT within the exchange's
+time bound (no device fault, no endless wait), after which a reset brings the ranks back in step.
+NVLS is off and the exchange uses plain peer stores.
 """
 import datetime
 import os
@@ -28,11 +32,13 @@ def _rank_main(rank, world, port, out):
         from long_context_modeling_b200 import sharded
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
                                 timeout=datetime.timedelta(seconds=60))
         report = {}
+        ex = sharded.PeerExchange(dev, max_rows=64, wait_ms=2000)
         for mode, head_dim in (("per_sequence", 0), ("per_head", 64)):
             e_total, topk, n = 4099, 8, 2
             lq, lk = cases.landmark_case(77, n, 1, e_total, d=768, std=0.125)
@@ -42,9 +48,49 @@ def _rank_main(rank, world, port, out):
             want = lcm.lmk_score_topk(lq.to(dev), lk.to(dev), topk, q_pos0=e_total - 1, head_dim=head_dim)
             lean = sharded.sharded_lmk_topk(lq.to(dev), lk[:, lo:hi].contiguous().to(dev), topk, e_total=e_total,
                                             head_dim=head_dim, validate=False)     # no header, no host checks
+            # the fused peer-store exchange + merge kernel instead of the all-gather
+            p2p = sharded.sharded_lmk_topk(lq.to(dev), lk[:, lo:hi].contiguous().to(dev), topk, e_total=e_total,
+                                           head_dim=head_dim, exchange=ex)
+            p2p_ok = (bool(torch.equal(p2p.keys, want.keys)) and bool(torch.equal(p2p.indices, want.indices)) and
+                      float((p2p.weights - want.weights).abs().max()) <= 1e-6 and bool(torch.equal(p2p.n_valid, want.n_valid)))
+            # scan + exchange replayed from a CUDA graph, with two different queries
+            retr = sharded.ShardedRetriever(lq.to(dev), lk[:, lo:hi].contiguous().to(dev), topk, e_total=e_total,
+                                            exchange=ex, head_dim=head_dim)
+            lq2, _ = cases.landmark_case(78, n, 1, 8, d=768, std=0.125)
+            g2 = retr(lq2.to(dev))
+            want2 = lcm.lmk_score_topk(lq2.to(dev), lk.to(dev), topk, q_pos0=e_total - 1, head_dim=head_dim)
+            graph_ok = bool(torch.equal(g2.keys, want2.keys))
+            g1 = retr(lq.to(dev))
+            graph_ok = graph_ok and bool(torch.equal(g1.keys, want.keys)) and bool(torch.equal(g1.indices, want.indices))
+            torch.cuda.synchronize()
+            del retr
+            report[mode + "_p2p"] = p2p_ok
+            report[mode + "_graph"] = graph_ok
             report[mode] = (bool(torch.equal(got.keys, want.keys)) and bool(torch.equal(lean.keys, want.keys)),
                             bool(torch.equal(got.indices, want.indices)) and bool(torch.equal(lean.indices, want.indices)),
                             float((got.weights - want.weights).abs().max()))
+        report["status_before_fault"] = int(lcm.read_status())
+        # a rank that never publishes (decided on the HOST): the others' bounded wait expires
+        import time
+        exf = sharded.PeerExchange(dev, max_rows=8, wait_ms=300)
+        keys_local = torch.arange(1, 9, dtype=torch.int64, device=dev).view(1, 8) + (rank << 40)
+        if rank != world - 1:
+            exf.exchange(keys_local, 8)
+            try:
+                lcm.check_status()
+                report["timeout_raised"] = False
+            except lcm.GcaError:
+                report["timeout_raised"] = True
+        else:
+            time.sleep(1.0)                                # the withholding rank launches nothing
+            report["timeout_raised"] = True
+        exf.reset()                                        # host barrier, cleared mailboxes, host barrier
+        back = exf.exchange(keys_local, 8)                 # everybody publishes again: the step completes
+        torch.cuda.synchronize()
+        expect = torch.cat([torch.arange(1, 9, dtype=torch.int64) + (r << 40) for r in range(world)]).sort(descending=True).values[:8]
+        report["after_reset_ok"] = bool(torch.equal(back.keys.cpu().view(-1), expect)) and int(lcm.read_status()) == 0
+        exf.close()
+        ex.close()
         # owner-computes decode over a sharded K/V cache
         n, c, h, k = 2, 37, 4, 8
         g = torch.Generator().manual_seed(5)
@@ -76,15 +122,20 @@ def test_sharded_retrieval_and_decode_over_nccl():
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = 29700 + os.getpid() % 200
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, out)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, out), daemon=True) for r in range(world)]
     for p in procs:
         p.start()
     results = {}
-    for _ in range(world):
-        item = out.get(timeout=300)
-        results[item[0]] = item[1:]
-    for p in procs:
-        p.join(timeout=120)
+    try:
+        for _ in range(world):
+            item = out.get(timeout=240)
+            results[item[0]] = item[1:]
+        for p in procs:
+            p.join(timeout=60)
+    finally:
+        for p in procs:                       # a rank that is still alive here is stuck: end exactly that process
+            if p.is_alive():
+                p.terminate()
     for r in range(world):
         assert results[r][0] == "ok", results
         rep = results[r][1]
@@ -92,5 +143,12 @@ def test_sharded_retrieval_and_decode_over_nccl():
             keys_eq, idx_eq, werr = rep[mode]
             assert keys_eq and idx_eq, (r, mode)
             assert werr <= 1e-6
+            assert rep[mode + "_p2p"], (r, mode, "fused peer-store exchange")
+            assert rep[mode + "_graph"], (r, mode, "CUDA-graph replay of scan + exchange")
+        assert rep["status_before_fault"] == 0
+        assert rep["timeout_raised"], (r, "a withheld publish must end as GCA_STATUS_TIMEOUT")
+        assert rep["after_reset_ok"], (r, "exchange after reset")
+        for mode in ():
+            pass
         assert rep["decode_rel_err"] <= 2e-2
         assert rep["status"] == 0
