@@ -663,6 +663,166 @@ def decode_arm(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------
+# Whole-model legs of the metric: the minimal DRT body with the kernels plugged in
+# --------------------------------------------------------------------------------------------
+def _init_dist():
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    return dist, world, rank, local, dev
+
+
+def train_arm(args):
+    """One DRT-16K training step (forward + backward, bf16 autocast-free: parameters and activations
+    in bf16) of the gpt2-small-scale DRT: 12 layers (6 lower + one group of 6 upper with GCA), 2 encoder
+    layers, 768 wide, 12 heads, vocabulary 50,265, 8 sequences x 16,380 tokens (260 chunks of 63 tokens
+    + landmark = 16,640 positions) per GPU, uniform random token ids.  Data-parallel over ranks: the
+    gradient all-reduce of DDP is part of the step at N > 1."""
+    dist, world, rank, local, dev = _init_dist()
+    from long_context_modeling_b200 import drt_minimal as D
+    import long_context_modeling_b200 as lcm
+    torch.manual_seed(0)
+    cfg = D.DRTConfig()
+    model = D.DRTMinimal(cfg).to(dev).bfloat16().train()
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    n_seq, tokens = args.n_seq, 260 * 63
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    batches = [torch.randint(0, 50257, (n_seq, tokens), generator=g, device=dev) for _ in range(2)]
+
+    def step(i):
+        tok = batches[i % 2]
+        net.zero_grad(set_to_none=True)
+        loss = net(tok, labels=tok)
+        loss.backward()
+        return loss
+
+    steps, warmup = max(3, min(args.steps, 10)), max(3, min(args.warmup, 3))
+    for i in range(warmup):
+        step(i)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        loss = step(i)
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    tok_s = world * n_seq * tokens / (ms * 1e-3)
+    line = {"metric": "drt16k_train_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "one training step (fwd+bwd, no optimizer) of the minimal DRT body, gpt2-small scale: 6 lower + 6 "
+                                   "upper layers with GCA, 2 encoder layers, d_model 768, 12 heads, vocab 50,265, "
+                                   f"{n_seq} x 16,380 tokens per GPU, chunk 63 + landmark, top-k 8, sliding window 512 + ALiBi",
+                       "n_seq_per_gpu": n_seq, "tokens_per_seq": tokens, "parameters": sum(p.numel() for p in model.parameters()),
+                       "cache_policy": "activations of a step (GBs) exceed the 126 MB L2; two token batches alternate",
+                       "parallelism": "data-parallel over ranks (DDP gradient all-reduce inside the step at N > 1)",
+                       "note": "dense projections, MLPs and the windowed self-attention are torch ops (cuBLAS / SDPA); GCA, "
+                               "retrieval and the chunk cache are this repository's kernels"},
+            "clocks": clocks, "loss": float(loss), "device_status": lcm.read_status(),
+            "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
+                    "note": "token ids are generated on the device; the loss is read back after the timed region"},
+            "gpu_launches": None, "max_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def generate_arm(args):
+    """Greedy generation with a long chunk cache: 32 sequences (split over the ranks), each with
+    `--cache-chunks` cached chunks (16,384 = a 1M-token context; K/V 3.2 GB + 25 MB of landmarks per
+    sequence), 256 new tokens.  The caches are filled with random bf16 values (with a random-init model
+    their contents are noise anyway); every decoded token runs the full minimal DRT body: 6 lower layers,
+    6 upper layers with one-row GCA over the 8 retrieved chunks, and at every chunk boundary the chunk
+    encoder, the cache append and the landmark retrieval over all cached chunks."""
+    dist, world, rank, local, dev = _init_dist()
+    from long_context_modeling_b200 import drt_minimal as D
+    import long_context_modeling_b200 as lcm
+    torch.manual_seed(0)
+    cfg = D.DRTConfig()
+    model = D.DRTMinimal(cfg).to(dev).bfloat16().eval()
+    n_seq = max(1, 32 // world)
+    c = args.cache_chunks
+    new_tokens = 256
+    state = D.DecodeState(cfg)
+    state.chunks = lcm.ChunkKVManager(group_size=1, capacity=c + 8, zero_landmark=True)
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+    piece = 512
+    with torch.no_grad():
+        for c0 in range(0, c, piece):
+            m = min(piece, c - c0)
+            kv = torch.empty(n_seq, m, 64, cfg.hidden_size, dtype=torch.bfloat16, device=dev)
+            kk = kv.normal_(generator=g)
+            state.chunks.append(kk, kv.clone().normal_(generator=g),
+                                torch.empty(n_seq, m, cfg.hidden_size, dtype=torch.bfloat16, device=dev).normal_(std=0.125, generator=g))
+        nl = cfg.decoder_layers[0] + sum(cfg.decoder_layers[1:])
+        w = cfg.slide_window + 1
+        state.self_attn = [(torch.randn(n_seq, cfg.num_attention_heads, w, cfg.head_dim, device=dev, dtype=torch.bfloat16),
+                            torch.randn(n_seq, cfg.num_attention_heads, w, cfg.head_dim, device=dev, dtype=torch.bfloat16)) for _ in range(nl)]
+        state.position = c * 64
+        idx0 = torch.stack([torch.randperm(c, device=dev)[:cfg.chunk_topk] for _ in range(n_seq)]).int()
+        state.chunks.update_current_retrieved_chunk(idx0, torch.softmax(torch.randn(n_seq, 1, cfg.chunk_topk, device=dev), -1), 0)
+        tok = torch.randint(0, 50257, (n_seq,), device=dev)
+        for _ in range(8):                                  # warm-up steps (not counted)
+            tok = model.decode_step(tok, state).argmax(-1)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(physical_gpu_index(local))
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(new_tokens):
+            tok = model.decode_step(tok, state).argmax(-1)
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    tok_s = world * n_seq * new_tokens / (ms * 1e-3)
+    line = {"metric": "drt_1m_ctx_decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": new_tokens,
+            "warmup": 8, "ms_per_step": ms / new_tokens, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"greedy generation of 256 tokens, {32} sequences in total ({n_seq} per GPU), minimal DRT body at "
+                                   f"gpt2-small scale, {c} cached chunks per sequence ({c * 64} positions), top-k 8",
+                       "sequences_per_gpu": n_seq, "cache_chunks": c, "new_tokens": new_tokens,
+                       "cache_gb_per_gpu": n_seq * c * 64 * cfg.hidden_size * 2 * 2 / 1e9,
+                       "cache_policy": "the chunk cache (GBs per sequence) exceeds the 126 MB L2; every boundary step scans all landmarks",
+                       "parallelism": "sequences split over ranks, no collective per token",
+                       "note": "eager PyTorch around the kernels: the step is bound by launch overhead of the ~12 layers' small ops"},
+            "clocks": clocks, "device_status": lcm.read_status(),
+            "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "tokens stay on the device between steps (greedy argmax on the device)"},
+            "gpu_launches": None, "max_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -670,12 +830,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="gca", choices=["gca", "retrieval", "decode", "triton-ref"],
+    ap.add_argument("--workload", default="gca", choices=["gca", "retrieval", "decode", "triton-ref", "train16k", "generate"],
                     help="gca (default, the headline): GCA fwd+bwd at the DRT-16K shape; retrieval: landmark top-k over "
-                         "a 16M-token cache; decode: one-row GCA for 32 sequences")
+                         "a 16M-token cache; decode: one-row GCA for 32 sequences; train16k: one training step of the minimal "
+                         "DRT body at the DRT-16K shape; generate: greedy generation with a 1M-token chunk cache")
     ap.add_argument("--triton-ref", action="store_true",
                     help="gca workload, 1 GPU: also time the reference's own Triton kernels (staged under oracle/_ref) "
                          "in a subprocess and add the result as `reference_triton_gpu`")
+    ap.add_argument("--cache-chunks", type=int, default=16384,
+                    help="generate workload: cached chunks per sequence (16,384 = a 1M-token context)")
     ap.add_argument("--per-head", action="store_true", help="retrieval workload: one 64-d score and top-k per head")
     ap.add_argument("--n-seq", type=int, default=N_SEQ,
                     help="sequences per GPU (default: the DRT-16K batch of 8; smaller values are for profiling captures)")
@@ -689,6 +852,10 @@ def main():
         decode_arm(args)
     elif args.workload == "triton-ref":
         triton_ref_arm(args)
+    elif args.workload == "train16k":
+        train_arm(args)
+    elif args.workload == "generate":
+        generate_arm(args)
     else:
         gpu_arm(args)
 
