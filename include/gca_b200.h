@@ -338,10 +338,41 @@ typedef struct CacheAppendArgs {
 
 int gca_cache_append(const CacheAppendArgs* args, void* stream);
 
+/*
+ * Chunk K/V projection with the cache append as its epilogue.  Stands in for
+ * model/DRT.py:766-784 -- `lmk_embs = enc[:, :, -1]`, `chunk_k = chunk_k_proj(enc)`,
+ * `chunk_v = chunk_v_proj(enc)`, the landmark row of both cleared, then
+ * `ChunkKVManager.append` (:87-133) -- as ONE tensor-core GEMM whose epilogue writes K and V in
+ * bf16 straight into the cache at chunk position `pos` (no intermediate tensors, no copy of the
+ * existing cache), plus a copy of the landmark rows of `x` into the landmark cache.
+ *
+ *   x        (N, count, 64, D) bf16, contiguous: the chunk encoder's output
+ *   wk, wv   (D, D) bf16, contiguous, nn.Linear layout (out_features, in_features), no bias
+ *   k_cache, v_cache (N, capacity, 64, D) bf16, sequence stride cache_batch_stride elements
+ *   lmk_cache (N, lmk_capacity, D) bf16 or NULL
+ *   D must be a multiple of 256 (the model: 768).
+ */
+typedef struct KvProjectArgs {
+  const void* x;
+  const void* wk;
+  const void* wv;
+  void* k_cache;
+  void* v_cache;
+  void* lmk_cache;            /* may be NULL */
+  int32_t* status;            /* device status word, or NULL */
+  int64_t cache_batch_stride;
+  int64_t lmk_cache_batch_stride;
+  int32_t N, count, pos, D;
+  int32_t capacity, lmk_capacity;
+  int32_t zero_landmark;
+} KvProjectArgs;
+
+int gca_kv_project_append(const KvProjectArgs* args, void* stream);
+
 const char* gca_strerror(int code);
 int gca_abi_version(void);
 /* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,
- * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs): lets a foreign-language binding verify
+ * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs): lets a foreign-language binding verify
  * its struct layout before the first call. */
 size_t gca_sizeof(int which);
 

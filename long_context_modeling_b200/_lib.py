@@ -93,6 +93,16 @@ class LmkExchangeArgs(C.Structure):
     ]
 
 
+class KvProjectArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("wk", C.c_void_p), ("wv", C.c_void_p),
+        ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("lmk_cache", C.c_void_p), ("status", C.c_void_p),
+        ("cache_batch_stride", C.c_int64), ("lmk_cache_batch_stride", C.c_int64),
+        ("N", C.c_int32), ("count", C.c_int32), ("pos", C.c_int32), ("D", C.c_int32),
+        ("capacity", C.c_int32), ("lmk_capacity", C.c_int32), ("zero_landmark", C.c_int32),
+    ]
+
+
 EXPORTS = {
     "gca_fwd": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
     "gca_decode": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
@@ -104,6 +114,7 @@ EXPORTS = {
     "lmk_score_topk_static": (C.c_int, [C.POINTER(LmkTopkArgs), C.c_void_p]),
     "lmk_topk_merge": (C.c_int, [C.POINTER(LmkMergeArgs), C.c_void_p]),
     "gca_cache_append": (C.c_int, [C.POINTER(CacheAppendArgs), C.c_void_p]),
+    "gca_kv_project_append": (C.c_int, [C.POINTER(KvProjectArgs), C.c_void_p]),
     "lmk_exchange_mailbox_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "lmk_exchange_mailbox_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p]),
     "lmk_exchange_mailbox_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
@@ -134,7 +145,8 @@ def lib() -> C.CDLL:
             fn.argtypes = argtypes
         if handle.gca_abi_version() != ABI_VERSION:
             raise RuntimeError("libgca_b200.so has an unexpected ABI version")
-        for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs, LmkExchangeArgs)):
+        for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs, LmkExchangeArgs,
+                                       KvProjectArgs)):
             if handle.gca_sizeof(which) != C.sizeof(struct):
                 raise RuntimeError(f"struct layout mismatch for {struct.__name__}: "
                                    f"library {handle.gca_sizeof(which)} vs binding {C.sizeof(struct)}")

@@ -156,6 +156,39 @@ class ChunkKVManager:
                        "gca_cache_append")
         self._len += count
 
+    def append_projected(self, enc_out: torch.Tensor, k_weight: torch.Tensor, v_weight: torch.Tensor) -> None:
+        """The reference's ``chunk_k_proj`` / ``chunk_v_proj`` + landmark extraction + ``append``
+        (``model/DRT.py:766-784``) as ONE tensor-core GEMM whose epilogue writes K and V straight into
+        the cache (landmark rows cleared when the manager was built with ``zero_landmark``) and the
+        landmark rows of ``enc_out`` into the landmark cache.  enc_out (N, D, 64, dim) bf16; the weights
+        are the two ``nn.Linear.weight`` tensors (dim, dim), no bias.  Inference path: when the inputs
+        require grad the projections are done with torch and ``append`` keeps the graph."""
+        if (torch.is_grad_enabled() and (enc_out.requires_grad or k_weight.requires_grad or v_weight.requires_grad)) or \
+                self._grad_mode or enc_out.dtype != torch.bfloat16 or enc_out.shape[-1] % 256 != 0 or enc_out.shape[-2] != 64:
+            x = enc_out
+            self.append(torch.nn.functional.linear(x, k_weight), torch.nn.functional.linear(x, v_weight), x[:, :, -1])
+            return
+        if not enc_out.is_cuda:
+            raise RuntimeError("ChunkKVManager holds device memory only (there is no CPU path)")
+        x = enc_out.contiguous()
+        n, count, l, dim = x.shape
+        self._reserve(self._len + count, x, x[:, :, -1])
+        if self._k.dtype != torch.bfloat16 or self._lmk.dtype != torch.bfloat16:
+            raise ValueError("append_projected writes a bf16 cache")
+        a = _lib.KvProjectArgs()
+        a.x, a.wk, a.wv = x.data_ptr(), k_weight.contiguous().data_ptr(), v_weight.contiguous().data_ptr()
+        a.k_cache, a.v_cache, a.lmk_cache = self._k.data_ptr(), self._v.data_ptr(), self._lmk.data_ptr()
+        from .gca import _status
+        a.status = _status(x.device).data_ptr()
+        a.cache_batch_stride, a.lmk_cache_batch_stride = self._k.stride(0), self._lmk.stride(0)
+        a.N, a.count, a.pos, a.D = n, count, self._len, dim
+        a.capacity, a.lmk_capacity = self._k.shape[1], self._lmk.shape[1]
+        a.zero_landmark = 1 if self._zero_landmark else 0
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib().gca_kv_project_append(C.byref(a), torch.cuda.current_stream().cuda_stream),
+                       "gca_kv_project_append")
+        self._len += count
+
     # ------------------------------------------------------------------ retrieval state
     def retrieve_chunks(self, indices: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """indices (N, M) -> gathered k, v (N, M, S, dim)  (``model/DRT.py:193-199``).

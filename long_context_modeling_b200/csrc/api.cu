@@ -12,6 +12,7 @@ size_t lmk_topk_workspace_bytes_impl(const LmkTopkArgs& a, int sms);
 bool bwd_tc_available();
 void set_fwd_profile_buffer(void* device_ptr);
 int launch_cache_append(const CacheAppendArgs& a, cudaStream_t stream);
+int launch_kv_project_append(const KvProjectArgs& a, int sms, cudaStream_t stream);
 
 DeviceScope::DeviceScope(const void* device_ptr) {
   cudaPointerAttributes at;
@@ -109,6 +110,7 @@ size_t gca_sizeof(int which) {
     case 3: return sizeof(LmkMergeArgs);
     case 4: return sizeof(CacheAppendArgs);
     case 5: return sizeof(LmkExchangeArgs);
+    case 6: return sizeof(KvProjectArgs);
     default: return 0;
   }
 }
@@ -299,6 +301,23 @@ int gca_cache_append(const CacheAppendArgs* a, void* stream) {
   gca::DeviceScope scope(a->k_cache);
   if (scope.rc) return scope.rc;
   return gca::launch_cache_append(*a, (cudaStream_t)stream);
+}
+
+int gca_kv_project_append(const KvProjectArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->x || !a->wk || !a->wv || !a->k_cache || !a->v_cache) return GCA_ERR_NULL;
+  if (a->N < 0 || a->count < 0 || a->pos < 0 || a->D < 256 || a->D % 256 != 0) return GCA_ERR_SHAPE;
+  if ((long long)a->pos + a->count > a->capacity) return GCA_ERR_SHAPE;
+  if (a->lmk_cache && (long long)a->pos + a->count > a->lmk_capacity) return GCA_ERR_SHAPE;
+  if (a->cache_batch_stride % 16 || (a->lmk_cache && a->lmk_cache_batch_stride % 8)) return GCA_ERR_STRIDE;
+  if ((reinterpret_cast<uintptr_t>(a->k_cache) & 31u) || (reinterpret_cast<uintptr_t>(a->v_cache) & 31u) || !aligned16(a->x) ||
+      !aligned16(a->wk) || !aligned16(a->wv) || (a->lmk_cache && !aligned16(a->lmk_cache)))
+    return GCA_ERR_ALIGN;
+  if ((long long)a->N * a->count * 64 >= (1ll << 31)) return GCA_ERR_TOO_LARGE;
+  if (a->N == 0 || a->count == 0) return 0;
+  gca::DeviceScope scope(a->k_cache);
+  if (scope.rc) return scope.rc;
+  return gca::launch_kv_project_append(*a, gca::sm_count(scope.dev), (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -142,7 +142,14 @@ class SelfAttention(nn.Module):
         if self.bidirectional:
             o = F.scaled_dot_product_attention(rotary(q), rotary(k), v)
             return self.o_proj(o.transpose(1, 2).reshape(n, l, -1)), None
-        if cache is None:
+        if cache is not None and l > 2:
+            # a later SEGMENT of a long prompt: the cached window of the previous segment goes in front
+            # (window and ALiBi bias are relative, so positions need no offset)
+            kc, vc = torch.cat([cache[0], k], 2), torch.cat([cache[1], v], 2)
+            qc = torch.cat([torch.zeros_like(cache[0]), q], 2)
+            o = windowed_alibi_attention(qc, kc, vc, self.window, self.slopes)[:, :, -l:]
+            new_cache = (kc[:, :, -(self.window + 1):], vc[:, :, -(self.window + 1):])
+        elif cache is None:
             if torch.is_grad_enabled() and q.requires_grad:
                 # SDPA with an explicit bias keeps the (window x 2 window) score blocks for its backward:
                 # ~10 GB per layer at 8 x 16,640 positions.  Recompute them in the backward instead.
@@ -190,7 +197,7 @@ class UpperDecoderLayer(nn.Module):
         self.mlp = MLP(cfg)
         self.chunk = cfg.enc_chunk_size + 1
 
-    def forward(self, x, k_cache, v_cache, indices, weights, cache=None, use_cache=False):
+    def forward(self, x, k_cache, v_cache, indices, weights, cache=None, use_cache=False, first_chunk_retrieves=False):
         a, cache = self.self_attn(self.input_layernorm(x), cache, use_cache)
         r = x + a
         n, l, dim = r.shape
@@ -198,7 +205,7 @@ class UpperDecoderLayer(nn.Module):
         if indices is None:                                       # nothing retrieved yet
             g = torch.zeros_like(r)
         else:
-            g = self.gca.forward_indexed(hs4, k_cache, v_cache, indices, weights)
+            g = self.gca.forward_indexed(hs4, k_cache, v_cache, indices, weights, first_chunk_retrieves)
         return r + self.mlp(self.post_attention_layernorm(r + g)), cache
 
 
@@ -240,15 +247,17 @@ class DRTMinimal(nn.Module):
         lmk = torch.full((n, c, 1), self.cfg.chunk_id, dtype=tokens.dtype, device=tokens.device)
         return torch.cat([tokens.view(n, c, -1), lmk], dim=2).view(n, c * self.chunk)
 
-    def encode_chunks(self, hidden: torch.Tensor):
-        """hidden (N, C, 64, dim) lower-stack states of complete chunks -> (chunk_k, chunk_v (N, C, 64, dim),
-        landmark embeddings (N, C, dim)).  The landmark rows are zeroed by the cache manager."""
+    def encode_chunks(self, hidden: torch.Tensor, chunks: ChunkKVManager) -> None:
+        """hidden (N, C, 64, dim) lower-stack states of complete chunks: encode them and append K, V
+        (projections of the encoder output, landmark rows zeroed) and the landmark embeddings (the encoder
+        output's last row) to ``chunks`` -- one GEMM with the append as its epilogue when no gradient is
+        needed (``ChunkKVManager.append_projected``)."""
         n, c, s, dim = hidden.shape
         x = self.enc_prenorm(hidden.reshape(n * c, s, dim))
         for layer in self.encoder:
             x, _ = layer(x)
         x = self.encoder_norm(x).view(n, c, s, dim)
-        return self.chunk_k_proj(x), self.chunk_v_proj(x), x[:, :, -1]
+        chunks.append_projected(x, self.chunk_k_proj.weight, self.chunk_v_proj.weight)
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         return F.linear(self.norm(hidden), self.embed_tokens.weight)          # tied LM head
@@ -256,31 +265,42 @@ class DRTMinimal(nn.Module):
     # ------------------------------------------------------------------ full-sequence forward (training, prefill)
     def forward(self, tokens: torch.Tensor, labels: Optional[torch.Tensor] = None, state: Optional[DecodeState] = None):
         """tokens (N, T), T % 63 == 0.  Returns logits at token positions (N, T, vocab) -- or the loss when
-        ``labels`` (N, T) are given (next-token targets are ``labels`` shifted left) -- and fills ``state``."""
+        ``labels`` (N, T) are given (next-token targets are ``labels`` shifted left) -- and fills ``state``.
+        A ``state`` that already holds earlier positions makes this call the NEXT SEGMENT of a long prompt
+        (``model/DRT.py:1018-1050``): self-attention continues from the cached window, the chunk cache and
+        landmarks grow, and the segment's first chunk uses the retrieval made at the end of the previous one."""
         cfg = self.cfg
         ids = self.insert_landmarks(tokens)
         n, l = ids.shape
         c = l // self.chunk
         x = self.embed_tokens(ids)
         use_cache = state is not None
+        later = use_cache and state.position > 0
+        old = state.self_attn if later else None
         caches = []
         for layer in self.lower_layers:
-            x, kv = layer(x, use_cache=use_cache)
+            x, kv = layer(x, old[len(caches)] if later else None, use_cache=use_cache)
             caches.append(kv)
         chunks = state.chunks if use_cache else ChunkKVManager(group_size=len(self.upper_layers), zero_landmark=True)
-        ck, cv, lmk = self.encode_chunks(x.view(n, c, self.chunk, -1))
-        chunks.append(ck, cv, lmk)
+        self.encode_chunks(x.view(n, c, self.chunk, -1), chunks)
         for g, layers in enumerate(self.upper_layers):
             q_lmk = self.lmk_norms[g](x.view(n, c, self.chunk, -1)[:, :, -1])
             k = min(len(chunks), cfg.chunk_topk)
             idx, w, full = retrieve(q_lmk, chunks, k, training=self.training)
+            if later:                                            # chunk 0 of this segment: the previous segment's last retrieval
+                pidx, pw = chunks.current_retrieved_indices(g)
+                pad = k - pidx.shape[-1]
+                idx = torch.cat([F.pad(pidx, (0, pad), value=-1).unsqueeze(1), idx], dim=1)
+                w = torch.cat([F.pad(pw, (0, pad)), w], dim=1)
             if use_cache:
                 chunks.update_current_retrieved_chunk(full.indices, full.weights, g)
+            have = later or c > 1
             for layer in layers:
-                x, kv = layer(x, chunks.chunk_k, chunks.chunk_v, idx if c > 1 else None, w if c > 1 else None, use_cache=use_cache)
+                x, kv = layer(x, chunks.chunk_k, chunks.chunk_v, idx if have else None, w if have else None,
+                              old[len(caches)] if later else None, use_cache=use_cache, first_chunk_retrieves=later)
                 caches.append(kv)
         if use_cache:
-            state.self_attn, state.position = caches, l
+            state.self_attn, state.position = caches, (state.position if later else 0) + l
         x = x.view(n, c, self.chunk, -1)[:, :, :-1].reshape(n, c * cfg.enc_chunk_size, -1)   # drop landmark positions
         if labels is None:
             return self.logits(x)
@@ -320,8 +340,7 @@ class DRTMinimal(nn.Module):
         if boundary:
             staged = chunks.lower_hidden_states                      # (N, 64, dim): the chunk is complete
             chunks.clear_lower_hidden_states()
-            ck, cv, lmk = self.encode_chunks(staged.unsqueeze(1))
-            chunks.append(ck, cv, lmk)
+            self.encode_chunks(staged.unsqueeze(1), chunks)
         for g, layers in enumerate(self.upper_layers):
             idx, w = chunks.current_retrieved_indices(g)             # fetched BEFORE this step's retrieval
             if boundary:
@@ -337,6 +356,19 @@ class DRTMinimal(nn.Module):
                 chunks.update_current_retrieved_chunk(new_idx, new_w, g)
         state.position += s
         return self.logits(x[:, 0])
+
+    @torch.no_grad()
+    def prefill_segmented(self, prompt: torch.Tensor, segment_tokens: int, state: Optional[DecodeState] = None):
+        """Prefill a long prompt segment by segment (``segment_tokens`` a multiple of 63), carrying the
+        self-attention window and the growing chunk cache between segments, so that activation memory is
+        bounded by the segment and not by the prompt (``model/DRT.py:1018-1050``,
+        ``eval/slidewin_eval.py:115``; the reference parks the cache on the host meanwhile, here it stays
+        in HBM).  Returns (logits of all token positions, state)."""
+        if segment_tokens % self.cfg.enc_chunk_size:
+            raise ValueError(f"segment length must be a multiple of {self.cfg.enc_chunk_size}")
+        state = state or DecodeState(self.cfg)
+        outs = [self.forward(prompt[:, t0:t0 + segment_tokens], state=state) for t0 in range(0, prompt.shape[1], segment_tokens)]
+        return torch.cat(outs, dim=1), state
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, new_tokens: int) -> torch.Tensor:

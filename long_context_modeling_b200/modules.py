@@ -117,10 +117,12 @@ class TritonGroupCrossAttention(nn.Module):
         return self._pad_first_chunk(hidden_states, o) if chunk_size > 1 else o
 
     def forward_indexed(self, hidden_states: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                        indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+                        indices: torch.Tensor, weights: torch.Tensor, first_chunk_retrieves: bool = False) -> torch.Tensor:
         """hidden_states (N, D, S, dim); caches (N, C, L, h*d); indices / weights (N, D', K)
         where D' = D-1 for D > 1 (query chunk j uses the retrieval made by chunk j-1) and
-        D' = D = 1 while decoding."""
+        D' = D = 1 while decoding.  ``first_chunk_retrieves``: the chunks are a later SEGMENT of a
+        long prompt whose first chunk uses the retrieval made at the end of the previous segment:
+        D' = D and no chunk is skipped."""
         hs = self.pre_norm(hidden_states)
         chunk_size = hs.shape[1]
         q = self.q_proj(hs)
@@ -128,7 +130,8 @@ class TritonGroupCrossAttention(nn.Module):
         if indices.shape[1] * indices.shape[2] == 0:
             return self._zeros(hidden_states)
         q5 = q.view(n, dd, s, self.num_heads, self.head_dim).permute(0, 1, 3, 2, 4)  # strided view, no copy
-        if chunk_size > 1:
+        skip_first = chunk_size > 1 and not first_chunk_retrieves
+        if skip_first:
             q5 = q5[:, 1:]
         scale = 1.0 / math.sqrt(self.head_dim)
         if torch.is_grad_enabled() and (q5.requires_grad or k_cache.requires_grad or weights.requires_grad):
@@ -137,7 +140,7 @@ class TritonGroupCrossAttention(nn.Module):
             vals = gca.gca_indexed_nograd(q5, k_cache, v_cache, indices, weights, scale, self.sm_n)
         vals = vals.permute(0, 1, 3, 2, 4).reshape(n, -1, self.hidden_size)
         o = self.o_proj(vals)
-        return self._pad_first_chunk(hidden_states, o) if chunk_size > 1 else o
+        return self._pad_first_chunk(hidden_states, o) if skip_first else o
 
 
 class GroupCrossAttention(TritonGroupCrossAttention):

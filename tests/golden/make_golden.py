@@ -159,6 +159,17 @@ def lift_reference_modules(ref_root: str, einsum_block: str):
     return ns["TritonGroupCrossAttention"], ns["GroupCrossAttention"]
 
 
+def projection_case(seed: int):
+    """Encoder outputs of an earlier append (1 chunk) and of the append under test (2 chunks), 2 sequences,
+    256 wide, and the two projection matrices: all bf16-representable."""
+    g = torch.Generator().manual_seed(seed)
+    enc_prev = torch.randn(2, 1, 64, 256, generator=g).bfloat16().float()
+    enc_new = torch.randn(2, 2, 64, 256, generator=g).bfloat16().float()
+    wk = (torch.randn(256, 256, generator=g) / 16).bfloat16().float()
+    wv = (torch.randn(256, 256, generator=g) / 16).bfloat16().float()
+    return enc_prev, enc_new, wk, wv
+
+
 class ModuleConfig:
     hidden_size, num_attention_heads, enc_chunk_size, chunk_topk = 128, 2, 63, 3
     rms_norm_eps, attention_bias, enable_softmax_one = 1e-5, False, False
@@ -262,6 +273,26 @@ def main(ref_root: str):
         out[f"{tag}_decode_o"] = o1.numpy()
     np.savez_compressed(os.path.join(HERE, "module_ref.npz"), **out)
     print("module_ref ok", {k2: v2.shape for k2, v2 in out.items() if hasattr(v2, "shape") and v2.ndim > 0 and "train_o" in k2})
+
+    # ---- 6. chunk K/V projection + landmark clearing + append (DRT.py:766-784), after an earlier append ----
+    import torch.nn as nn
+    src_drt = open(os.path.join(ref_root, "model", "DRT.py")).read()
+    proj_block = _slice_between(src_drt, "lmk_embs = chunk_hidden_states[:, :, -1, :]", "chunk_kvs.append(chunk_k, chunk_v, lmk_embs)")
+    enc_prev, enc_new, wk, wv = projection_case(61)
+
+    class ProjSelf:
+        chunk_k_proj = nn.Linear(256, 256, bias=False)
+        chunk_v_proj = nn.Linear(256, 256, bias=False)
+    with torch.no_grad():
+        ProjSelf.chunk_k_proj.weight.copy_(wk)
+        ProjSelf.chunk_v_proj.weight.copy_(wv)
+        mgr6 = Manager(False, 1)
+        for enc in (enc_prev, enc_new):
+            exec(proj_block, dict(torch=torch, self=ProjSelf, chunk_hidden_states=enc.clone(), chunk_kvs=mgr6))
+    np.savez_compressed(os.path.join(HERE, "projection_ref.npz"), in_checksum=cases.checksum(enc_prev, enc_new, wk, wv),
+                        chunk_k=mgr6.chunk_k.numpy().astype(np.float16), chunk_v=mgr6.chunk_v.numpy().astype(np.float16),
+                        lmk=mgr6.past_lmk_embeds.numpy())
+    print("projection_ref ok", tuple(mgr6.chunk_k.shape))
 
     # ---- 4. mask (DRT.py:590-607) for a few shapes ----
     masks = {}

@@ -58,6 +58,35 @@ def test_incremental_decoding_equals_teacher_forced_argmax():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("segment_chunks", [1, 2, 3])
+def test_segmented_prefill_equals_monolithic(segment_chunks):
+    """A long prompt prefilled segment by segment (self-attention window and chunk cache carried over,
+    ``model/DRT.py:1018-1050``) gives the logits, the retrieved chunks and the next decoded tokens of the
+    one-pass prefill."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    torch.manual_seed(3)
+    cfg = tiny_config()
+    cfg.slide_window = 40                                      # shorter than a chunk: the window crosses segments
+    model = D.DRTMinimal(cfg).cuda().eval()
+    prompt = torch.randint(0, 99, (2, 63 * 6), device="cuda")
+    with torch.no_grad():
+        s_mono = D.DecodeState(cfg)
+        mono = model(prompt, state=s_mono)
+        seg, s_seg = model.prefill_segmented(prompt, 63 * segment_chunks)
+    assert (mono - seg).abs().max().item() <= 2e-4 * mono.abs().max().item()
+    assert len(s_seg.chunks) == len(s_mono.chunks) == 6 and s_seg.position == s_mono.position
+    for g in range(2):
+        a, b = s_mono.chunks.current_retrieved_indices(g), s_seg.chunks.current_retrieved_indices(g)
+        assert torch.equal(a[0][:, :b[0].shape[1]], b[0][:, :a[0].shape[1]])
+    tok = mono[:, -1].argmax(-1)
+    for _ in range(70):                                        # across one chunk boundary
+        la, lb = model.decode_step(tok, s_mono), model.decode_step(tok, s_seg)
+        assert torch.equal(la.argmax(-1), lb.argmax(-1))
+        tok = la.argmax(-1)
+
+
+@pytest.mark.gpu
 def test_training_step_reaches_every_parameter():
     """One bf16 training step at a small shape: the loss is finite and every parameter -- the
     chunk encoder and the K/V projections included, which only the chunk cache connects to the

@@ -244,3 +244,37 @@ def test_differentiable_weights_match_reference_autograd(lcm):
     assert torch.allclose(w.detach().cpu(), tw.detach(), atol=1e-5)
     assert torch.allclose(lqg.grad.cpu(), a.grad, atol=1e-4)
     assert torch.allclose(lkg.grad.cpu(), b.grad, atol=1e-4)
+
+
+def test_projection_with_append_epilogue_matches_reference_statements(lcm, golden_dir):
+    """``ChunkKVManager.append_projected`` (one tensor-core GEMM whose epilogue writes K and V into the
+    cache, landmark rows cleared, landmark embeddings extracted) against the reference's own statements
+    ``model/DRT.py:766-784`` run on the reference's own manager, for an append that follows an earlier
+    one (non-zero position, cache growth)."""
+    import make_golden as MG
+    g = np.load(os.path.join(golden_dir, "projection_ref.npz"))
+    enc_prev, enc_new, wk, wv = MG.projection_case(61)
+    assert abs(cases.checksum(enc_prev, enc_new, wk, wv) - float(g["in_checksum"])) < 1e-6
+    mgr = lcm.ChunkKVManager(zero_landmark=True, capacity=2)          # capacity 2 < 3 chunks: the buffer also grows
+    wk_d, wv_d = wk.cuda().bfloat16(), wv.cuda().bfloat16()
+    with torch.no_grad():
+        for enc in (enc_prev, enc_new):
+            mgr.append_projected(enc.cuda().bfloat16(), wk_d, wv_d)
+    torch.cuda.synchronize()
+    assert lcm.read_status() == 0 and len(mgr) == 3 and not mgr.tracks_gradients
+    for name, got in (("chunk_k", mgr.chunk_k), ("chunk_v", mgr.chunk_v), ("lmk", mgr.past_lmk_embeds)):
+        ref = torch.from_numpy(g[name].astype(np.float32))
+        assert got.shape == ref.shape, name
+        err = (got.float().cpu() - ref).abs().max().item() / (ref.abs().max().item() + 1e-12)
+        assert err <= 1e-2, (name, err)
+    assert mgr.chunk_k[:, :, -1].abs().max().item() == 0 and mgr.chunk_v[:, :, -1].abs().max().item() == 0
+    # more row tiles than CTAs, and a row count that is not a multiple of the 128-row tile
+    gen = torch.Generator().manual_seed(62)
+    enc = torch.randn(3, 101, 64, 256, generator=gen).bfloat16()
+    big = lcm.ChunkKVManager(zero_landmark=False)
+    with torch.no_grad():
+        big.append_projected(enc.cuda(), wk_d, wv_d)
+    want_k = (enc.float() @ wk.t())
+    err = (big.chunk_k.float().cpu() - want_k).abs().max().item() / want_k.abs().max().item()
+    assert err <= 1e-2, err
+    assert lcm.read_status() == 0
