@@ -115,6 +115,29 @@ def physical_gpu_index(local: int) -> int:
     return local
 
 
+def bind_to_gpu_cpus(index: int) -> dict:
+    """Restrict this process to the CPU cores that are local to GPU `index` (NVML's affinity mask,
+    intersected with what the process may use), BEFORE any pinned host memory is allocated, so that
+    the staging buffers land on the GPU's NUMA node.  Returns what was done, for the JSON line."""
+    info = {"bound": False, "cpus": len(os.sched_getaffinity(0))}
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        local = {64 * i + b for i, wd in enumerate(words) for b in range(64) if (int(wd) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        want = local & allowed
+        if want and want != allowed:
+            os.sched_setaffinity(0, want)
+            info = {"bound": True, "cpus": len(want), "of": len(allowed)}
+        elif want:
+            info["note"] = "every allowed core is local to the GPU"
+    except Exception as e:                       # no NVML, no affinity call: run unbound and say so
+        info["note"] = f"not bound: {type(e).__name__}"
+    return info
+
+
 # --------------------------------------------------------------------------------------------
 # CPU arms (the oracle is only ever the thing measured here as the *baseline*, never the product)
 # --------------------------------------------------------------------------------------------
@@ -178,6 +201,7 @@ def gpu_arm(args):
         raise RuntimeError("bench.py needs a CUDA device: the GCA path has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    binding = bind_to_gpu_cpus(physical_gpu_index(local))      # before the pinned buffers exist
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
@@ -241,6 +265,31 @@ def gpu_arm(args):
     ms_dev, clocks = timed(device_step, dev_sets, steps, warmup)
     ms_e2e, _ = timed(e2e_step, host_sets, max(6, steps // 2), 4, finish=pipe.drain)
 
+    # The host ceiling of the end-to-end step: one step's upload and download bytes moved with no
+    # kernel at all, every rank at the same time (the ranks share the host's memory and PCIe root
+    # complexes): upload alone, download alone, both directions at once.
+    up_dst = [torch.empty_like(t, device=dev) for t in host_sets[0]]
+    dn_src = torch.empty(pipe.d2h_bytes, dtype=torch.uint8, device=dev)
+    dn_dst = torch.empty(pipe.d2h_bytes, dtype=torch.uint8).pin_memory()
+    s_up, s_dn = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def copies(up, down):
+        def run(_):
+            if up:
+                with torch.cuda.stream(s_up):
+                    for d, h in zip(up_dst, host_sets[0]):
+                        d.copy_(h, non_blocking=True)
+            if down:
+                with torch.cuda.stream(s_dn):
+                    dn_dst.copy_(dn_src, non_blocking=True)
+            torch.cuda.current_stream().wait_stream(s_up)
+            torch.cuda.current_stream().wait_stream(s_dn)
+        return run
+    ms_up = timed(copies(True, False), host_sets, 5, 3)[0]
+    ms_dn = timed(copies(False, True), host_sets, 5, 3)[0]
+    ms_both = timed(copies(True, True), host_sets, 5, 3)[0]
+    del up_dst, dn_src, dn_dst
+
     # the three tensor-core kernels one at a time (one launch per call), for the roofline
     def time_calls(fn, reps):
         for i in range(3):
@@ -295,7 +344,14 @@ def gpu_arm(args):
         "dtype": "bf16", "data": "synthetic", "config": config_dict(), "clocks": clocks,
         "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": pipe.h2d_bytes,
                 "d2h_bytes_per_step": pipe.d2h_bytes, "ms_per_step": ms_e2e,
-                "how": "HostGcaPipeline, 3 steps in flight: upload, kernels and download of consecutive steps overlap"},
+                "how": "HostGcaPipeline, 3 steps in flight: upload, kernels and download of consecutive steps overlap",
+                "host_ceiling": {"what": "one step's bytes copied with no kernel running, all ranks at once, max over ranks",
+                                 "h2d_gbs_per_gpu": pipe.h2d_bytes / (ms_up * 1e-3) / 1e9,
+                                 "d2h_gbs_per_gpu": pipe.d2h_bytes / (ms_dn * 1e-3) / 1e9,
+                                 "both_directions_ms": ms_both,
+                                 "ceiling_value": flops_step * world / (ms_both * 1e-3) / 1e12,
+                                 "e2e_frac_of_ceiling": ms_both / ms_e2e},
+                "host_binding": binding},
         "gpu_launches": 5 * steps,      # fwd_tc, csr_small, bwd_kv_tc, bwd_q_tc, dw_reduce
         "kernels": kernels,
         "roofline": {"kernel": top, "bound": "tensor", "achieved": kernels[top]["achieved_tflops"],
@@ -679,8 +735,8 @@ def _init_dist():
 
 
 def train_arm(args):
-    """One DRT-16K training step (forward + backward, bf16 autocast-free: parameters and activations
-    in bf16) of the gpt2-small-scale DRT: 12 layers (6 lower + one group of 6 upper with GCA), 2 encoder
+    """One DRT-16K training step (forward + backward + fused AdamW update, autocast-free: parameters,
+    activations and optimizer states in bf16) of the gpt2-small-scale DRT: 12 layers (6 lower + one group of 6 upper with GCA), 2 encoder
     layers, 768 wide, 12 heads, vocabulary 50,265, 8 sequences x 16,380 tokens (260 chunks of 63 tokens
     + landmark = 16,640 positions) per GPU, uniform random token ids.  Data-parallel over ranks: the
     gradient all-reduce of DDP is part of the step at N > 1."""
@@ -695,11 +751,14 @@ def train_arm(args):
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     batches = [torch.randint(0, 50257, (n_seq, tokens), generator=g, device=dev) for _ in range(2)]
 
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01, fused=True)
+
     def step(i):
         tok = batches[i % 2]
-        net.zero_grad(set_to_none=True)
+        opt.zero_grad(set_to_none=True)
         loss = net(tok, labels=tok)
         loss.backward()
+        opt.step()
         return loss
 
     steps, warmup = max(3, min(args.steps, 10)), max(3, min(args.warmup, 3))
@@ -728,7 +787,7 @@ def train_arm(args):
     line = {"metric": "drt16k_train_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "one training step (fwd+bwd, no optimizer) of the minimal DRT body, gpt2-small scale: 6 lower + 6 "
+            "config": {"workload": "one training step (forward + backward + fused AdamW update) of the minimal DRT body, gpt2-small scale: 6 lower + 6 "
                                    "upper layers with GCA, 2 encoder layers, d_model 768, 12 heads, vocab 50,265, "
                                    f"{n_seq} x 16,380 tokens per GPU, chunk 63 + landmark, top-k 8, sliding window 512 + ALiBi",
                        "n_seq_per_gpu": n_seq, "tokens_per_seq": tokens, "parameters": sum(p.numel() for p in model.parameters()),

@@ -369,10 +369,46 @@ typedef struct KvProjectArgs {
 
 int gca_kv_project_append(const KvProjectArgs* args, void* stream);
 
+/* ---- projections either side of GCA (reference: model/DRT.py:352-355 pre_norm + q_proj, :385 o_proj
+ * and the residual add of the decoder layer, :476-484; the reference's RMSNorm is LlamaRMSNorm) ----
+ *
+ *   gca_row_rms:  row_scale[m] = rsqrt(mean(x[m, :]^2) + eps)                      (float32, M values)
+ *   gca_linear:   out[m, :] = row_scale[m] * (x[m, :] . w^T) + residual[m, :]      (bf16 in / out, f32 accumulate)
+ *
+ * x (M, K) bf16, w (N, K) bf16 in nn.Linear layout, out / residual (M, N) bf16; strides in elements
+ * between rows; row_scale and residual may be NULL.  K a multiple of 64, N a multiple of 16, row
+ * strides multiples of 8 elements, every pointer 16-byte aligned.  With row_scale from gca_row_rms
+ * and the norm's gain folded into w's columns (w' = w * gain[None, :]) this is RMSNorm + projection
+ * without writing the normalised activations; with residual it is projection + residual add.
+ * One tcgen05 GEMM launch (128 x 256 tiles, TMA ring, accumulators in tensor memory). */
+typedef struct RowRmsArgs {
+  const void* x;
+  float* row_scale;
+  int64_t M;
+  int64_t x_stride;
+  int32_t D;
+  float eps;
+} RowRmsArgs;
+
+typedef struct LinearArgs {
+  const void* x;
+  const void* w;
+  void* out;
+  const void* residual;       /* may be NULL */
+  const float* row_scale;     /* may be NULL */
+  int32_t* status;            /* device status word, or NULL */
+  int64_t M;
+  int64_t x_stride, w_stride, out_stride, residual_stride;
+  int32_t N, K;
+} LinearArgs;
+
+int gca_row_rms(const RowRmsArgs* args, void* stream);
+int gca_linear(const LinearArgs* args, void* stream);
+
 const char* gca_strerror(int code);
 int gca_abi_version(void);
 /* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,
- * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs): lets a foreign-language binding verify
+ * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs, 7 RowRmsArgs, 8 LinearArgs): lets a foreign-language binding verify
  * its struct layout before the first call. */
 size_t gca_sizeof(int which);
 

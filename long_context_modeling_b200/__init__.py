@@ -11,3 +11,4 @@ from .retrieval import (lmk_score_topk, merge_topk, retrieve, perform_batch_retr
 from .chunk_cache import ChunkKVManager  # noqa: F401
 from .host_pipeline import HostGcaPipeline  # noqa: F401
 from .modules import TritonGroupCrossAttention, GroupCrossAttention, preprocess_chunk_kv_cache  # noqa: F401
+from . import fused_ops  # noqa: F401

@@ -103,6 +103,19 @@ class KvProjectArgs(C.Structure):
     ]
 
 
+class RowRmsArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("row_scale", C.c_void_p), ("M", C.c_int64), ("x_stride", C.c_int64),
+                ("D", C.c_int32), ("eps", C.c_float)]
+
+
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p), ("residual", C.c_void_p), ("row_scale", C.c_void_p),
+        ("status", C.c_void_p), ("M", C.c_int64),
+        ("x_stride", C.c_int64), ("w_stride", C.c_int64), ("out_stride", C.c_int64), ("residual_stride", C.c_int64),
+        ("N", C.c_int32), ("K", C.c_int32),
+    ]
+
 EXPORTS = {
     "gca_fwd": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
     "gca_decode": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
@@ -115,6 +128,8 @@ EXPORTS = {
     "lmk_topk_merge": (C.c_int, [C.POINTER(LmkMergeArgs), C.c_void_p]),
     "gca_cache_append": (C.c_int, [C.POINTER(CacheAppendArgs), C.c_void_p]),
     "gca_kv_project_append": (C.c_int, [C.POINTER(KvProjectArgs), C.c_void_p]),
+    "gca_row_rms": (C.c_int, [C.POINTER(RowRmsArgs), C.c_void_p]),
+    "gca_linear": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "lmk_exchange_mailbox_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "lmk_exchange_mailbox_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p]),
     "lmk_exchange_mailbox_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
@@ -146,7 +161,7 @@ def lib() -> C.CDLL:
         if handle.gca_abi_version() != ABI_VERSION:
             raise RuntimeError("libgca_b200.so has an unexpected ABI version")
         for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs, LmkExchangeArgs,
-                                       KvProjectArgs)):
+                                       KvProjectArgs, RowRmsArgs, LinearArgs)):
             if handle.gca_sizeof(which) != C.sizeof(struct):
                 raise RuntimeError(f"struct layout mismatch for {struct.__name__}: "
                                    f"library {handle.gca_sizeof(which)} vs binding {C.sizeof(struct)}")

@@ -13,6 +13,8 @@ bool bwd_tc_available();
 void set_fwd_profile_buffer(void* device_ptr);
 int launch_cache_append(const CacheAppendArgs& a, cudaStream_t stream);
 int launch_kv_project_append(const KvProjectArgs& a, int sms, cudaStream_t stream);
+int launch_row_rms(const RowRmsArgs& a, cudaStream_t stream);
+int launch_linear(const LinearArgs& a, int sms, cudaStream_t stream);
 
 DeviceScope::DeviceScope(const void* device_ptr) {
   cudaPointerAttributes at;
@@ -111,6 +113,8 @@ size_t gca_sizeof(int which) {
     case 4: return sizeof(CacheAppendArgs);
     case 5: return sizeof(LmkExchangeArgs);
     case 6: return sizeof(KvProjectArgs);
+    case 7: return sizeof(RowRmsArgs);
+    case 8: return sizeof(LinearArgs);
     default: return 0;
   }
 }
@@ -173,7 +177,7 @@ int gca_decode(const GcaFwdArgs* a, void* stream) {
 }
 
 static size_t dw_part_bytes(const GcaBwdArgs* a) {
-  return gca::align_up((size_t)2 * a->N * a->J * a->Hq * a->K * sizeof(float), 256);   // two partials per (row block, head, slot)
+  return gca::align_up((size_t)4 * a->N * a->J * a->Hq * a->K * sizeof(float), 256);   // up to four partials per (row block, head, slot)
 }
 
 // 16 bytes per (row block, head, slot, row): written by the q-major pass, read by the kv-major pass
@@ -232,7 +236,7 @@ int gca_bwd_stages(const GcaBwdArgs* a, unsigned stages, void* stream) {
   else rc = GCA_ERR_ALGO;
   if (rc) return rc;
   if (!(stages & GCA_BWD_STAGE_Q)) return 0;
-  return gca::launch_dw_reduce(dw_part, a->dw, a->N * a->J, a->Hq, a->K, algo == GCA_ALGO_TC ? 2 : 1, s);
+  return gca::launch_dw_reduce(dw_part, a->dw, a->N * a->J, a->Hq, a->K, algo == GCA_ALGO_TC ? gca::bwd_tc_dw_parts() : 1, s);
 }
 
 }  // extern "C"
@@ -318,6 +322,32 @@ int gca_kv_project_append(const KvProjectArgs* a, void* stream) {
   gca::DeviceScope scope(a->k_cache);
   if (scope.rc) return scope.rc;
   return gca::launch_kv_project_append(*a, gca::sm_count(scope.dev), (cudaStream_t)stream);
+}
+
+int gca_row_rms(const RowRmsArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->x || !a->row_scale) return GCA_ERR_NULL;
+  if (a->M < 0 || a->D < 8 || a->D % 8 != 0) return GCA_ERR_SHAPE;
+  if (a->x_stride % 8 != 0 || a->x_stride < a->D) return GCA_ERR_STRIDE;
+  if (!aligned16(a->x)) return GCA_ERR_ALIGN;
+  if (a->M == 0) return 0;
+  gca::DeviceScope scope(a->x);
+  if (scope.rc) return scope.rc;
+  return gca::launch_row_rms(*a, (cudaStream_t)stream);
+}
+
+int gca_linear(const LinearArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->x || !a->w || !a->out) return GCA_ERR_NULL;
+  if (a->M < 0 || a->N < 16 || a->N % 16 != 0 || a->K < 64 || a->K % 64 != 0) return GCA_ERR_SHAPE;
+  if (a->x_stride % 8 || a->w_stride % 8 || a->out_stride % 8 || (a->residual && a->residual_stride % 8) ||
+      a->x_stride < a->K || a->w_stride < a->K || a->out_stride < a->N || (a->residual && a->residual_stride < a->N))
+    return GCA_ERR_STRIDE;
+  if (!aligned16(a->x) || !aligned16(a->w) || !aligned16(a->out) || (a->residual && !aligned16(a->residual))) return GCA_ERR_ALIGN;
+  if (a->M == 0) return 0;
+  gca::DeviceScope scope(a->out);
+  if (scope.rc) return scope.rc;
+  return gca::launch_linear(*a, gca::sm_count(scope.dev), (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -500,6 +500,13 @@ static bool rows_32b_aligned(const void* base, const int64_t* stride) {
 }
 
 int launch_bwd_kv_tc(const GcaBwdArgs& a, const Csr& csr, const uint4* rowterm, int sms, cudaStream_t stream);
+int launch_bwd_q_tc(const GcaBwdArgs& a, float* dw_part, uint4* rowterm, int sms, cudaStream_t stream);
+
+#ifdef GCA_Q_STACKED
+int bwd_tc_dw_parts() { return 2; }
+#else
+int bwd_tc_dw_parts() { return 4; }
+#endif
 
 // Stage order inside one call: the q-major pass first (it writes the per-row terms), then the
 // kv-major pass, which reads them.  A caller that runs the stages in separate calls must keep
@@ -514,6 +521,11 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, uint4* ro
   auto kmap = [&](CUtensorMap* m, const void* base, const int64_t* st, int box) {
     return make_tile_map_5d(m, base, 64, 64, a.Hkv, a.C, a.N, st[2], st[3], st[1], st[0], box);
   };
+#ifndef GCA_Q_STACKED
+  if (stages & GCA_BWD_STAGE_Q) {
+    if ((rc = launch_bwd_q_tc(a, dw_part, rowterm, sms, stream))) return rc;
+  }
+#else
   if (stages & GCA_BWD_STAGE_Q) {
     BwdQParams p;
     if ((rc = qmap(&p.tm_q, a.q, a.q_stride, 2)) || (rc = qmap(&p.tm_do, a.dout, a.do_stride, 2)) ||
@@ -538,6 +550,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, uint4* ro
       GCA_CUDA_CHECK(cudaGetLastError());
     }
   }
+#endif
   if (stages & GCA_BWD_STAGE_KV) {
     if ((rc = launch_bwd_kv_tc(a, csr, rowterm, sms, stream))) return rc;
   }

@@ -72,6 +72,7 @@ int launch_bwd_tc(const GcaBwdArgs& a, const Csr& csr, float* dw_part, uint4* ro
 
 // dw[zj, k] = sum over heads and `parts` partials of dw_part[zj, h, k, part], in a fixed order
 int launch_dw_reduce(const float* dw_part, float* dw, int ZJ, int Hq, int K, int parts, cudaStream_t stream);
+int bwd_tc_dw_parts();   // partials per (row block, head, slot) that the tensor-core q-major pass writes
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 

@@ -15,6 +15,12 @@
 // 128 x 256 x 16 MMAs into one of two 256-column accumulators in tensor memory, warps 2-5 turn a
 // finished accumulator into bf16 rows of the cache while the next tile is being multiplied.
 // Every wait is bounded (GCA_STATUS_TIMEOUT on expiry).
+//
+// The same kernel in LINEAR mode is the projection either side of GCA (model/DRT.py:352-355,385):
+//   out[m, :] = row_scale[m] * (x[m, :] W^T) + residual[m, :]
+// row_scale = 1 / rms(x) from `row_rms_kernel` turns it into pre-norm RMSNorm + q_proj (the norm's
+// gain is folded into W's columns by the caller: RMSNorm(x) W^T = diag(1 / rms) x (W diag(g))^T, so
+// the normalised activations are never written), residual makes it o_proj + residual add.
 #include "gca_common.cuh"
 #include "sm100_ptx.cuh"
 #include "tc_common.cuh"
@@ -41,10 +47,17 @@ struct ProjParams {
   __nv_bfloat16* v_cache;
   int32_t* status;
   long long cache_bs;       // elements between sequences in the caches
-  int M, D, rows_per_seq;   // rows_per_seq = count * 64
+  int M, D, rows_per_seq;   // D = contraction length; rows_per_seq = count * 64
   int pos;                  // first chunk position written
   int zero_landmark;
-  int tiles_m, tiles_n;     // tiles_n = D / BN
+  int tiles_m, tiles_n;     // tiles_n = ceil(output columns / BN)
+  int nmat;                 // 2: K and V projection with append epilogue; 1: linear mode
+  // linear mode
+  __nv_bfloat16* out;
+  const __nv_bfloat16* residual;      // or nullptr
+  const float* row_scale;             // or nullptr
+  long long out_stride, res_stride;   // elements between rows
+  int ncols;                          // output columns (multiple of 16)
 };
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1) {
@@ -57,8 +70,8 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
 __device__ __forceinline__ void tile_of(const ProjParams& p, int t, int& which, int& tm, int& tn) {
   tn = t % p.tiles_n;
   const int r = t / p.tiles_n;
-  which = r & 1;
-  tm = r >> 1;
+  if (p.nmat == 2) { which = r & 1; tm = r >> 1; }
+  else { which = 0; tm = r; }
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -69,7 +82,7 @@ kv_project_append_kernel(const __grid_constant__ ProjParams p) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + NUM_BARS + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total = p.tiles_m * p.tiles_n * 2;
+  const int total = p.tiles_m * p.tiles_n * p.nmat;
   const int ksteps = p.D / BK;
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&bars[FULL + i], 1); mbar_init(&bars[EMPTY + i], 1); }
@@ -149,6 +162,38 @@ kv_project_append_kernel(const __grid_constant__ ProjParams p) {
       tc_fence_after();
       const long long m = (long long)tm * BM + row_in_tile;
       const bool live = m < p.M;
+      if (p.nmat == 1) {
+        // linear mode: out = row_scale * acc + residual, 16 columns per pass
+        const float sc = (live && p.row_scale) ? p.row_scale[m] : 1.0f;
+        __nv_bfloat16* orow = p.out + m * p.out_stride + tn * BN;
+        const __nv_bfloat16* rrow = p.residual ? p.residual + m * p.res_stride + tn * BN : nullptr;
+        const int cols = min(BN, p.ncols - tn * BN);
+#pragma unroll 1
+        for (int c0 = 0; c0 < cols; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld_32x32b_x16(tlane + ab * BN + c0, v);
+          tmem_ld_wait();
+          if (live) {
+            uint32_t w[8];
+            if (rrow) {
+              const uint4 r0 = *reinterpret_cast<const uint4*>(rrow + c0), r1 = *reinterpret_cast<const uint4*>(rrow + c0 + 8);
+              const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                w[i] = pack_bf16x2(fmaf(__uint_as_float(v[2 * i]), sc, __uint_as_float(rr[i] << 16)),
+                                   fmaf(__uint_as_float(v[2 * i + 1]), sc, __uint_as_float(rr[i] & 0xffff0000u)));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) w[i] = pack_bf16x2(__uint_as_float(v[2 * i]) * sc, __uint_as_float(v[2 * i + 1]) * sc);
+            }
+            reinterpret_cast<uint4*>(orow + c0)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            reinterpret_cast<uint4*>(orow + c0)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&bars[ACC_EMPTY + ab]);
+        continue;
+      }
       const int n = live ? (int)(m / p.rows_per_seq) : 0;
       const int r = live ? (int)(m - (long long)n * p.rows_per_seq) : 0;       // (chunk, row) inside the appended block
       const bool zero = p.zero_landmark && (r & 63) == 63;
@@ -201,7 +246,58 @@ __global__ void lmk_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__
   lmk[n * lmk_bs + (long long)(pos + c) * row_vecs + v] = x[(cn * 64 + 63) * row_vecs + v];
 }
 
+// row_scale[m] = rsqrt(mean(x[m, :]^2) + eps): one warp per row, 16-byte loads.
+__global__ void row_rms_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ row_scale, long long M, int D,
+                               long long stride, float eps) {
+  const long long m = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (m >= M) return;
+  const int lane = threadIdx.x & 31;
+  const uint4* row = reinterpret_cast<const uint4*>(x + m * stride);
+  float acc = 0.f;
+  for (int i = lane; i < D / 8; i += 32) {
+    const uint4 v = row[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xffff0000u);
+      acc = fmaf(a, a, acc); acc = fmaf(b, b, acc);
+    }
+  }
+#pragma unroll
+  for (int of = 16; of > 0; of >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, of);
+  if (lane == 0) row_scale[m] = rsqrtf(acc / (float)D + eps);
+}
+
 }  // namespace
+
+int launch_row_rms(const RowRmsArgs& a, cudaStream_t stream) {
+  if (a.M == 0) return 0;
+  const int warps = 8;
+  row_rms_kernel<<<(unsigned)((a.M + warps - 1) / warps), warps * 32, 0, stream>>>(
+      (const __nv_bfloat16*)a.x, a.row_scale, a.M, a.D, a.x_stride, a.eps);
+  return (int)cudaGetLastError();
+}
+
+int launch_linear(const LinearArgs& a, int sms, cudaStream_t stream) {
+  ProjParams p;
+  int rc;
+  if ((rc = make_matrix_map(&p.tm_x, a.x, a.M, a.K, a.x_stride, BM)) || (rc = make_matrix_map(&p.tm_wk, a.w, a.N, a.K, a.w_stride, BN)))
+    return rc;
+  p.tm_wv = p.tm_wk;
+  p.k_cache = p.v_cache = nullptr; p.status = a.status; p.cache_bs = 0;
+  p.M = (int)a.M; p.D = a.K; p.rows_per_seq = 1; p.pos = 0; p.zero_landmark = 0;
+  p.tiles_m = (int)((a.M + BM - 1) / BM); p.tiles_n = (a.N + BN - 1) / BN; p.nmat = 1;
+  p.out = (__nv_bfloat16*)a.out; p.residual = (const __nv_bfloat16*)a.residual; p.row_scale = a.row_scale;
+  p.out_stride = a.out_stride; p.res_stride = a.residual_stride; p.ncols = a.N;
+  const long long total = (long long)p.tiles_m * p.tiles_n;
+  if (total >= (1ll << 31) || a.M >= (1ll << 31)) return GCA_ERR_TOO_LARGE;
+  if (total == 0) return 0;
+  GCA_CUDA_CHECK(cudaFuncSetAttribute(kv_project_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  const unsigned grid = (unsigned)(total < sms ? total : sms);
+  kv_project_append_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(p);
+  GCA_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 int launch_kv_project_append(const KvProjectArgs& a, int sms, cudaStream_t stream) {
   ProjParams p;
@@ -213,7 +309,8 @@ int launch_kv_project_append(const KvProjectArgs& a, int sms, cudaStream_t strea
   p.k_cache = (__nv_bfloat16*)a.k_cache; p.v_cache = (__nv_bfloat16*)a.v_cache; p.status = a.status;
   p.cache_bs = a.cache_batch_stride; p.M = (int)M; p.D = a.D; p.rows_per_seq = a.count * 64; p.pos = a.pos;
   p.zero_landmark = a.zero_landmark;
-  p.tiles_m = (int)((M + BM - 1) / BM); p.tiles_n = a.D / BN;
+  p.tiles_m = (int)((M + BM - 1) / BM); p.tiles_n = a.D / BN; p.nmat = 2;
+  p.out = nullptr; p.residual = nullptr; p.row_scale = nullptr; p.out_stride = p.res_stride = 0; p.ncols = a.D;
   const long long total = (long long)p.tiles_m * p.tiles_n * 2;
   if (total >= (1ll << 31)) return GCA_ERR_TOO_LARGE;
   GCA_CUDA_CHECK(cudaFuncSetAttribute(kv_project_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));

@@ -1,0 +1,88 @@
+"""The projections either side of GCA as tensor-core GEMMs with fused prologue / epilogue work
+(inference: no autograd): pre-norm RMSNorm + ``q_proj`` (``model/DRT.py:352-355``) and ``o_proj`` +
+residual add (``model/DRT.py:385`` and the decoder layer's ``residual + hidden_states``, ``:484``).
+
+``RMSNorm(x) W^T = diag(1 / rms(x)) . x . (W diag(g))^T``: the norm's gain ``g`` is folded into the
+weight's columns once, the GEMM reads the raw activations, and its epilogue scales each output row
+by ``1 / rms`` -- the normalised activations are never written or re-read.  The reference gets the
+same effect from third-party fused kernels (flash-attn's RMSNorm, xformers); here it is the
+library's own tcgen05 GEMM (``gca_linear``) plus a one-pass row reduction (``gca_row_rms``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .gca import _status, _stream
+
+
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    """(..., D) -> a 2-D view (M, D) with one row stride; copies only if no such view exists."""
+    if t.dim() == 2 and t.stride(1) == 1:
+        return t
+    if t.is_contiguous():
+        return t.view(-1, t.shape[-1])
+    return t.reshape(-1, t.shape[-1]).contiguous()
+
+
+def _require(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name}: the fused projections run on a CUDA device only (no CPU fallback)")
+    if t.dtype != torch.bfloat16:
+        raise ValueError(f"{name}: expected bfloat16, got {t.dtype}")
+
+
+def row_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
+    """1 / sqrt(mean(x^2, -1) + eps) per row of x (..., D) bf16 -> float32 (M,)."""
+    _require(x, "row_rms")
+    x2 = _rows(x)
+    out = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+    a = _lib.RowRmsArgs()
+    a.x, a.row_scale, a.M, a.x_stride, a.D, a.eps = x2.data_ptr(), out.data_ptr(), x2.shape[0], x2.stride(0), x2.shape[1], eps
+    _lib.check(_lib.lib().gca_row_rms(C.byref(a), _stream()), "gca_row_rms")
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, row_scale: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[m] = row_scale[m] * (x[m] @ weight.T) + residual[m]; x (..., K), weight (N, K), bf16."""
+    _require(x, "linear")
+    _require(weight, "linear weight")
+    x2, n = _rows(x), weight.shape[0]
+    shape = x.shape[:-1] + (n,)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.bfloat16, device=x.device)
+    o2 = _rows(out)
+    if o2.data_ptr() != out.data_ptr():
+        raise ValueError("linear: `out` must be viewable as (M, N) rows")
+    a = _lib.LinearArgs()
+    a.x, a.w, a.out = x2.data_ptr(), weight.data_ptr(), o2.data_ptr()
+    a.M, a.N, a.K = x2.shape[0], n, x2.shape[1]
+    a.x_stride, a.w_stride, a.out_stride = x2.stride(0), weight.stride(0), o2.stride(0)
+    if residual is not None:
+        _require(residual, "linear residual")
+        r2 = _rows(residual)
+        if r2.shape != o2.shape:
+            raise ValueError(f"linear: residual {tuple(residual.shape)} does not match the output {tuple(shape)}")
+        a.residual, a.residual_stride = r2.data_ptr(), r2.stride(0)
+    if row_scale is not None:
+        if row_scale.dtype != torch.float32 or row_scale.numel() != x2.shape[0] or not row_scale.is_contiguous():
+            raise ValueError("linear: row_scale must be contiguous float32 with one value per row")
+        a.row_scale = row_scale.data_ptr()
+    a.status = _status(x.device).data_ptr()
+    _lib.check(_lib.lib().gca_linear(C.byref(a), _stream()), "gca_linear")
+    return out
+
+
+def fold_gain(weight: torch.Tensor, gain: torch.Tensor) -> torch.Tensor:
+    """W diag(g) as bf16: the projection weight with the preceding RMSNorm's gain folded in."""
+    return (weight.float() * gain.float()[None, :]).to(torch.bfloat16).contiguous()
+
+
+def rmsnorm_linear(x: torch.Tensor, folded_weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm(x) @ W.T with ``folded_weight = fold_gain(W, norm.weight)``: one row reduction over x
+    and one GEMM over the raw x whose epilogue applies 1 / rms."""
+    return linear(x, folded_weight, row_scale=row_rms(x, eps))

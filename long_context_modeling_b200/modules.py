@@ -16,7 +16,7 @@ import math
 import torch
 import torch.nn as nn
 
-from . import gca
+from . import fused_ops, gca
 
 
 class RMSNorm(nn.Module):
@@ -115,6 +115,48 @@ class TritonGroupCrossAttention(nn.Module):
         vals = vals.view(n, -1, self.num_heads, s, self.head_dim).permute(0, 1, 3, 2, 4).reshape(n, -1, self.hidden_size)
         o = self.o_proj(vals)
         return self._pad_first_chunk(hidden_states, o) if chunk_size > 1 else o
+
+    def _folded_q_weight(self) -> torch.Tensor:
+        """q_proj.weight with pre_norm's gain folded in, cached until either parameter changes."""
+        key = (self.q_proj.weight._version, self.pre_norm.weight._version, self.q_proj.weight.data_ptr())
+        if getattr(self, "_folded_key", None) != key:
+            self._folded_w = fused_ops.fold_gain(self.q_proj.weight.detach(), self.pre_norm.weight.detach())
+            self._folded_key = key
+        return self._folded_w
+
+    def forward_fused(self, hidden_states: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      indices: torch.Tensor, weights: torch.Tensor, residual: torch.Tensor = None,
+                      first_chunk_retrieves: bool = False) -> torch.Tensor:
+        """Inference form of ``forward_indexed`` (bf16, no autograd, no projection bias) with the small
+        operations fused into the two projections: RMSNorm's row scale is the q_proj GEMM's epilogue
+        (gain folded into the weight), and ``residual`` -- the decoder layer's ``residual +
+        gca(...)`` (``model/DRT.py:484``), shape (N, D*S, dim) -- is added by the o_proj GEMM's
+        epilogue.  Rows of a skipped first chunk come back as the residual alone (zeros without one),
+        as in ``model/DRT.py:387-394``."""
+        if self.q_proj.bias is not None or self.o_proj.bias is not None:
+            raise ValueError("forward_fused: projection biases are not supported")
+        n, dd, s, dim = hidden_states.shape
+        q = fused_ops.rmsnorm_linear(hidden_states, self._folded_q_weight(), self.pre_norm.eps)
+        skip_first = dd > 1 and not first_chunk_retrieves
+        out = torch.empty((n, dd * s, dim), dtype=torch.bfloat16, device=hidden_states.device)
+        if skip_first or indices.shape[1] * indices.shape[2] == 0:
+            lead = s if indices.shape[1] * indices.shape[2] else dd * s
+            if residual is None:
+                out[:, :lead].zero_()
+            else:
+                out[:, :lead] = residual[:, :lead]
+            if lead == dd * s:
+                return out
+        q5 = q.view(n, dd, s, self.num_heads, self.head_dim).permute(0, 1, 3, 2, 4)
+        if skip_first:
+            q5 = q5[:, 1:]
+        vals = gca.gca_indexed_nograd(q5, k_cache, v_cache, indices, weights, 1.0 / math.sqrt(self.head_dim), self.sm_n)
+        vals = vals.permute(0, 1, 3, 2, 4).reshape(n, -1, self.hidden_size)
+        first = s if skip_first else 0
+        w = self.o_proj.weight.detach()
+        for b in range(n):                       # one GEMM per sequence: a sequence's rows share one row stride
+            fused_ops.linear(vals[b], w, residual=None if residual is None else residual[b, first:], out=out[b, first:])
+        return out
 
     def forward_indexed(self, hidden_states: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                         indices: torch.Tensor, weights: torch.Tensor, first_chunk_retrieves: bool = False) -> torch.Tensor:

@@ -1,0 +1,140 @@
+"""The projections either side of GCA with their small operations fused in (inference path):
+``gca_row_rms`` + ``gca_linear`` through the C ABI, against plain float32 PyTorch on the same bf16
+inputs, and ``TritonGroupCrossAttention.forward_fused`` against the fixture produced by the
+REFERENCE's module class (``tests/golden/module_ref.npz``, ``model/DRT.py:345-398``) and against
+this repository's unfused ``forward_indexed``.  bf16 data, float32 accumulation: per element
+|a - b| <= 1e-2 * scale + 2e-2 * |b| with scale = max |b|.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import make_golden as MG
+
+pytestmark = pytest.mark.gpu
+
+
+def close(a, b, what=""):
+    a, b = a.detach().float().cpu(), torch.as_tensor(b).float().cpu()
+    scale = b.abs().max().item() + 1e-12
+    bad = (a - b).abs() > 1e-2 * scale + 2e-2 * b.abs()
+    assert not bad.any(), (what, int(bad.sum()), ((a - b).abs().max() / scale).item())
+
+
+def need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+
+
+@pytest.mark.parametrize("m,d", [(1, 768), (37, 128), (4100, 768)])
+def test_row_rms(m, d):
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    x = (torch.randn(m, d, generator=torch.Generator().manual_seed(m)) * 3).bfloat16().cuda()
+    got = F.row_rms(x, 1e-5)
+    ref = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-5)
+    assert torch.allclose(got, ref, rtol=1e-5, atol=0)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 768, 768), (300, 768, 768), (129, 48, 128), (1000, 1024, 3072), (64, 272, 64)])
+@pytest.mark.parametrize("with_scale,with_res", [(False, False), (True, False), (False, True), (True, True)])
+def test_linear_against_float32(m, n, k, with_scale, with_res):
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    import long_context_modeling_b200 as lcm
+    g = torch.Generator().manual_seed(m * 7 + n)
+    x = torch.randn(m, k, generator=g).bfloat16().cuda()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).bfloat16().cuda()
+    sc = (torch.rand(m, generator=g) + 0.5).cuda() if with_scale else None
+    res = torch.randn(m, n, generator=g).bfloat16().cuda() if with_res else None
+    out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    F.linear(x, w, row_scale=sc, residual=res, out=out)
+    ref = x.float() @ w.float().T
+    if with_scale:
+        ref = ref * sc[:, None]
+    if with_res:
+        ref = ref + res.float()
+    close(out, ref, (m, n, k))
+    assert lcm.read_status() == 0
+
+
+def test_linear_writes_only_its_rows_and_columns():
+    """Strided output (a column block of a wider matrix, a row block of a taller one): nothing outside
+    the (M, N) window changes."""
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(200, 128, generator=g).bfloat16().cuda()
+    w = (torch.randn(64, 128, generator=g) / 11).bfloat16().cuda()
+    big = torch.full((260, 256), -5.0, dtype=torch.bfloat16, device="cuda")
+    F.linear(x, w, out=big[30:230, 64:128])
+    close(big[30:230, 64:128], x.float() @ w.float().T)
+    mask = torch.ones_like(big, dtype=torch.bool)
+    mask[30:230, 64:128] = False
+    assert (big[mask] == -5.0).all()
+
+
+def test_linear_rejects_bad_arguments():
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    x = torch.zeros(8, 96, dtype=torch.bfloat16, device="cuda")            # K not a multiple of 64
+    w = torch.zeros(64, 96, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        F.linear(x, w)
+    with pytest.raises(ValueError):
+        F.linear(torch.zeros(8, 128, device="cuda"), torch.zeros(64, 128, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(RuntimeError):
+        F.linear(torch.zeros(8, 128, dtype=torch.bfloat16), torch.zeros(64, 128, dtype=torch.bfloat16))
+
+
+def test_rmsnorm_linear_matches_norm_then_projection():
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(2, 5, 64, 768, generator=g) * 2).bfloat16().cuda()
+    gain = (1 + 0.2 * torch.randn(768, generator=g)).cuda()
+    w = (torch.randn(768, 768, generator=g) / 28).bfloat16().cuda()
+    got = F.rmsnorm_linear(x, F.fold_gain(w, gain), 1e-5)
+    xf = x.float()
+    normed = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * gain
+    close(got, normed @ w.float().T)
+    assert got.shape == (2, 5, 64, 768)
+
+
+def _fixture_module(golden_dir):
+    import long_context_modeling_b200 as lcm
+    g = np.load(os.path.join(golden_dir, "module_ref.npz"))
+    cfg = MG.ModuleConfig()
+    n, c, k = 1, 3, cfg.chunk_topk
+    hidden, gk, gv, w, dout, params = MG.module_case(51, n, c, cfg.num_attention_heads, k, cfg.hidden_size)
+    mod = lcm.TritonGroupCrossAttention(cfg).cuda()
+    mod.load_state_dict({k_: v_.cuda() for k_, v_ in params.items()})
+    return g, cfg, mod.bfloat16().eval(), hidden, gk, gv, w
+
+
+def test_fused_module_path_matches_reference_class(golden_dir):
+    """forward_fused (RMSNorm folded into q_proj's GEMM, o_proj with residual epilogue) in bf16 against
+    the reference class's float32 output for the same parameters and inputs; the gathered chunks of
+    the fixture serve as the cache, read through an identity index."""
+    need_gpu()
+    g, cfg, mod, hidden, gk, gv, w = _fixture_module(golden_dir)
+    k = cfg.chunk_topk
+    n, dk = gk.shape[:2]
+    idx = torch.arange(dk, dtype=torch.int32).view(1, dk // k, k).expand(n, -1, -1).contiguous().cuda()
+    hs = hidden.bfloat16().cuda()
+    kc, vc = gk.bfloat16().cuda(), gv.bfloat16().cuda()
+    with torch.no_grad():
+        o = mod.forward_fused(hs, kc, vc, idx, w.cuda())
+        close(o, g["triton_eval_o"], "no residual")
+        assert o[:, :64].abs().max().item() == 0            # the first chunk retrieves nothing
+        res = torch.randn(o.shape, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+        o2 = mod.forward_fused(hs, kc, vc, idx, w.cuda(), residual=res)
+        close(o2, torch.as_tensor(g["triton_eval_o"]) + res.float().cpu(), "with residual")
+        assert torch.equal(o2[:, :64], res[:, :64])
+        # and against the unfused path of this repository
+        close(o2, (mod.forward_indexed(hs, kc, vc, idx, w.cuda()).float() + res.float()), "vs forward_indexed")
+        # one-row decode step (chunk_size == 1: nothing is skipped)
+        o1 = mod.forward_fused(hs[:, 1:2, :1], kc[:, :k], vc[:, :k], idx[:, :1], w[:, :1].cuda())
+        close(o1, g["triton_decode_o"], "decode")
