@@ -405,10 +405,31 @@ typedef struct LinearArgs {
 int gca_row_rms(const RowRmsArgs* args, void* stream);
 int gca_linear(const LinearArgs* args, void* stream);
 
+/* ---- sliding-window causal self-attention with ALiBi, decode form (reference call site:
+ * model/llama.py:684-688, flash_attn_with_kvcache(..., causal=True, window_size=(W, 0), alibi_slopes=m)) ----
+ *
+ *   q, out (N, Hq, Sq, 64) bf16 by strides (n, head, row), k, v (N, Hkv, T, 64) bf16 by strides
+ *   (n, kv head, position); the 64 head dimensions contiguous, rows 16-byte aligned.
+ *   Query row i stands at position T - Sq + i and sees keys j with  pos - window <= j <= pos;
+ *   score = sm_scale * q.k - slope[head] * (pos - j);  alibi_slopes (Hq) float32 or NULL.
+ *   (Hq / Hkv) * Sq <= 4 rows per kv head.  HBM-bound: 2 * (window + 1) * 128 bytes per (n, kv head). */
+typedef struct WindowDecodeArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* alibi_slopes;  /* may be NULL */
+  void* out;
+  int64_t q_stride[3], o_stride[3], k_stride[3], v_stride[3];
+  int32_t N, Hq, Hkv, Sq, T, window;
+  float sm_scale;
+} WindowDecodeArgs;
+
+int gca_window_decode(const WindowDecodeArgs* args, void* stream);
+
 const char* gca_strerror(int code);
 int gca_abi_version(void);
 /* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,
- * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs, 7 RowRmsArgs, 8 LinearArgs): lets a foreign-language binding verify
+ * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs, 7 RowRmsArgs, 8 LinearArgs, 9 WindowDecodeArgs): lets a foreign-language binding verify
  * its struct layout before the first call. */
 size_t gca_sizeof(int which);
 

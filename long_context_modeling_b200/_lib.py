@@ -116,6 +116,15 @@ class LinearArgs(C.Structure):
         ("N", C.c_int32), ("K", C.c_int32),
     ]
 
+
+class WindowDecodeArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("alibi_slopes", C.c_void_p), ("out", C.c_void_p),
+        ("q_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3),
+        ("N", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Sq", C.c_int32), ("T", C.c_int32), ("window", C.c_int32),
+        ("sm_scale", C.c_float),
+    ]
+
 EXPORTS = {
     "gca_fwd": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
     "gca_decode": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
@@ -130,6 +139,7 @@ EXPORTS = {
     "gca_kv_project_append": (C.c_int, [C.POINTER(KvProjectArgs), C.c_void_p]),
     "gca_row_rms": (C.c_int, [C.POINTER(RowRmsArgs), C.c_void_p]),
     "gca_linear": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
+    "gca_window_decode": (C.c_int, [C.POINTER(WindowDecodeArgs), C.c_void_p]),
     "lmk_exchange_mailbox_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "lmk_exchange_mailbox_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p]),
     "lmk_exchange_mailbox_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
@@ -161,7 +171,7 @@ def lib() -> C.CDLL:
         if handle.gca_abi_version() != ABI_VERSION:
             raise RuntimeError("libgca_b200.so has an unexpected ABI version")
         for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs, LmkExchangeArgs,
-                                       KvProjectArgs, RowRmsArgs, LinearArgs)):
+                                       KvProjectArgs, RowRmsArgs, LinearArgs, WindowDecodeArgs)):
             if handle.gca_sizeof(which) != C.sizeof(struct):
                 raise RuntimeError(f"struct layout mismatch for {struct.__name__}: "
                                    f"library {handle.gca_sizeof(which)} vs binding {C.sizeof(struct)}")

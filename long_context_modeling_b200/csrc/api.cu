@@ -15,6 +15,7 @@ int launch_cache_append(const CacheAppendArgs& a, cudaStream_t stream);
 int launch_kv_project_append(const KvProjectArgs& a, int sms, cudaStream_t stream);
 int launch_row_rms(const RowRmsArgs& a, cudaStream_t stream);
 int launch_linear(const LinearArgs& a, int sms, cudaStream_t stream);
+int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream);
 
 DeviceScope::DeviceScope(const void* device_ptr) {
   cudaPointerAttributes at;
@@ -115,6 +116,7 @@ size_t gca_sizeof(int which) {
     case 6: return sizeof(KvProjectArgs);
     case 7: return sizeof(RowRmsArgs);
     case 8: return sizeof(LinearArgs);
+    case 9: return sizeof(WindowDecodeArgs);
     default: return 0;
   }
 }
@@ -334,6 +336,20 @@ int gca_row_rms(const RowRmsArgs* a, void* stream) {
   gca::DeviceScope scope(a->x);
   if (scope.rc) return scope.rc;
   return gca::launch_row_rms(*a, (cudaStream_t)stream);
+}
+
+int gca_window_decode(const WindowDecodeArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->q || !a->k || !a->v || !a->out) return GCA_ERR_NULL;
+  if (a->N < 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Hq % a->Hkv || a->Sq <= 0 || a->T < a->Sq || a->window < 0) return GCA_ERR_SHAPE;
+  if ((a->Hq / a->Hkv) * a->Sq > 4) return GCA_ERR_SHAPE;
+  for (int i = 0; i < 3; ++i)
+    if (a->q_stride[i] % 8 || a->o_stride[i] % 8 || a->k_stride[i] % 8 || a->v_stride[i] % 8) return GCA_ERR_STRIDE;
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out)) return GCA_ERR_ALIGN;
+  if (a->N == 0) return 0;
+  gca::DeviceScope scope(a->out);
+  if (scope.rc) return scope.rc;
+  return gca::launch_window_decode(*a, (cudaStream_t)stream);
 }
 
 int gca_linear(const LinearArgs* a, void* stream) {

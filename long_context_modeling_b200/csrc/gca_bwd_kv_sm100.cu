@@ -68,9 +68,15 @@ constexpr uint32_t PAIR16 = PAIR_BYTES >> 4, TILE16 = TILE_BYTES >> 4;
 constexpr int NBUF = GCA_KV_NBUF, SPLIT = GCA_KV_SPLIT, NG = NBUF * SPLIT;
 constexpr int GRAD_ISSUERS = GCA_KV_GRAD2 ? 2 : 1;       // dV and dK from one warp, or from a warp each
 static_assert(NBUF == 2 || NBUF == 3, "score buffers");
-constexpr int PROD_WARP = 4 * NG, ISSUE_S = PROD_WARP + 1, ISSUE_DP = PROD_WARP + 2, ISSUE_DV = PROD_WARP + 3,
-              ISSUE_DK = PROD_WARP + 4;
-constexpr int NTHREADS = (4 * NG + 3 + GRAD_ISSUERS) * 32;
+// One issuing warp per product (two for the gradients with GRAD2).  Measured slower: one issuing
+// warp per HEAD (0.955 against 0.615 ms: both heads of an iteration share the buffer's columns, and
+// every extra polling warp loads the shared-memory path); a warpgroup of its own that writes dK /
+// dV so that no worker group is held up by a unit's output (0.668 ms, 0.70-0.81 with sleeping
+// waits: with single accumulators the gradient issuers wait for the writer either way, and four
+// more resident warps cost more than the freed worker group gains).
+constexpr int PROD_WARP = 4 * NG, ISSUE_S = PROD_WARP + 1, ISSUE_DP = ISSUE_S + 1, ISSUE_DV = ISSUE_DP + 1,
+              ISSUE_DK = ISSUE_DV + 1;
+constexpr int NTHREADS = (ISSUE_DV + GRAD_ISSUERS) * 32;
 constexpr int WCOLS = 64 / SPLIT;                        // query columns of a key row that one group handles
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t LANE16 = 16u << 16;            // TMEM lane offset of head B's 64-row tile
@@ -242,10 +248,10 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
       const uint64_t stage = ring.st * 2 * PAIR16;
       const uint32_t tbuf = tmem_base + b * BUF_COLS;
       if (ROLE < 2) {
-        ok = mbar_wait_warp(&bars[QDO_FULL + ring.st], ring.ph, abort_flag, lane);
-        // the buffer's previous contents (the packed A operands of iteration g - NBUF) have been consumed
+        // the tiles have landed AND the buffer's previous contents (the packed A operands of iteration
+        // g - NBUF) have been consumed: both barriers are probed at once (one shared-memory round trip)
         if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 1, g);
-        if (ok) ok = mbar_wait_warp(&bars[BUF_FREE + b], bph ^ 1, abort_flag, lane);
+        ok = mbar_wait_warp2(&bars[QDO_FULL + ring.st], ring.ph, &bars[BUF_FREE + b], bph ^ 1, abort_flag, lane);
         if (!ok) break;
         if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 2, g);
         tc_fence_after();
@@ -276,19 +282,21 @@ __device__ void kv_issuer(const BwdKvParams& p, uint8_t* smem, uint64_t* bars, v
         // per K step of 16 query rows), B = the head's dO / Q tile read N-contiguous (MN-major)
         if (ROLE == 2) {
 #pragma unroll
-          for (int tl = 0; tl < 2; ++tl)
-#pragma unroll
+          for (int tl = 0; tl < 2; ++tl) {
+  #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
               umma_bf16_ts_elect(tmem_base + COL_DV + (tl ? LANE16 : 0u), tbuf + (tl ? LANE16 : 0u) + packed_col(kk),
                                  dQDOmn + stage + PAIR16 + tl * TILE16 + kk * STEP_MN, idesc, (uint32_t)(i > 0 || kk > 0));
+          }
         }
         if (ROLE == 3 || GRAD_ISSUERS == 1) {
 #pragma unroll
-          for (int tl = 0; tl < 2; ++tl)
-#pragma unroll
+          for (int tl = 0; tl < 2; ++tl) {
+  #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
               umma_bf16_ts_elect(tmem_base + COL_DK + (tl ? LANE16 : 0u), tbuf + COL_DPT + (tl ? LANE16 : 0u) + packed_col(kk),
                                  dQDOmn + stage + tl * TILE16 + kk * STEP_MN, idesc, (uint32_t)(i > 0 || kk > 0));
+          }
         }
         umma_commit_elect(&bars[BUF_FREE + b]);
         umma_commit_elect(&bars[QDO_EMPTY + ring.st]);   // Q / dO of this iteration are free once dV, dK are done
@@ -452,7 +460,7 @@ bwd_kv_tc_kernel(const __grid_constant__ BwdKvParams p) {
     for (int i = 0; i < NBUF; ++i) {
       mbar_init(&bars[SP_FULL + i], 2);                              // S^T commit + dP^T commit
       mbar_init(&bars[PDS_FULL + i], 128 * SPLIT);
-      mbar_init(&bars[BUF_FREE + i], GRAD_ISSUERS);                  // one commit per gradient issuer
+      mbar_init(&bars[BUF_FREE + i], GRAD_ISSUERS);             // one commit per gradient issuer
       mbar_init(&bars[ACC_FULL + i], GRAD_ISSUERS);
     }
     mbar_init(&bars[ACC_EMPTY], 128 * SPLIT);

@@ -27,10 +27,11 @@
 // 16 columns.  Pass 1 reads S and dP, accumulates Di and writes P as packed bf16 over the S
 // columns it has already read; pass 2 reads P and dP back and writes dS = P (w dP - w Di) as
 // packed bf16 over the dP columns, from where the dQ product takes it as its A operand (lane =
-// row of A = query row).  ~70 registers instead of 161, which is what lets three worker groups
-// and sixteen warps fit.  Shared memory sees only the TMA copies and the MMAs' operand reads.
+// row of A = query row).  82 registers instead of 161, which is what lets three worker groups
+// and twenty warps fit.  Shared memory sees only the TMA copies and the MMAs' operand reads.
 //
-// CTA = 16 warps: three worker warpgroups, one TMA producer, three MMA issuers (S, dP, dQ).  No
+// CTA = 20 warps: three worker warpgroups, one TMA producer, three MMA issuers (S, dP, dQ), and a
+// warpgroup that writes the finished dQ tiles.  No
 // atomics: gradients are bit-reproducible.  Every wait is bounded (GCA_STATUS_TIMEOUT on expiry).
 #include "gca_common.cuh"
 #include "sm100_ptx.cuh"
@@ -53,8 +54,15 @@ constexpr uint32_t PAIR16 = PAIR_BYTES >> 4, TILE16 = TILE_BYTES >> 4;
 #endif
 constexpr int NBUF = GCA_Q_NBUF;
 static_assert(NBUF == 2 || NBUF == 3, "score buffers");
-constexpr int PROD_WARP = 4 * NBUF, ISSUE_S = PROD_WARP + 1, ISSUE_DP = PROD_WARP + 2, ISSUE_DQ = PROD_WARP + 3;
-constexpr int NTHREADS = (4 * NBUF + 4) * 32;
+// One issuing warp per product.  An issuer needs ~1,300 cycles per slot (probe of its two barriers
+// ~330, eight 64-row MMAs and the commits ~600, loop bookkeeping ~300: event traces), which is what
+// bounds the kernel today; yet more issuing warps were measured SLOWER, both ways tried: one warp
+// per head (the heads of a slot share the buffer's columns) 0.835 against 0.567 ms, one warp per
+// slot parity for S and dP 1,640 against 1,390 cycles per slot -- every extra polling warp slows
+// the shared-memory path that the MMAs' operand reads already load to ~875 of those cycles.
+constexpr int PROD_WARP = 4 * NBUF, ISSUE_S = PROD_WARP + 1, ISSUE_DP = ISSUE_S + 1, ISSUE_DQ = ISSUE_DP + 1;
+constexpr int WRITER_WARP = (ISSUE_DQ + 1 + 3) / 4 * 4;   // a multiple of 4: warp % 4 = its TMEM lane quarter
+constexpr int NTHREADS = (WRITER_WARP + 4) * 32;
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t LANE16 = 16u << 16;            // TMEM lane offset of head B's 64-row tile
 constexpr uint32_t IDESC_64 = umma_idesc_bf16(64, 64, 0, 0);
@@ -241,9 +249,11 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     for (int i = 0; i < nv && ok; ++i, ++g) {
       const uint32_t tbuf = tmem_base + b * BUF_COLS;
       if (ROLE != 2) {
-        ok = mbar_wait_warp(&bars[(ROLE == 0 ? K_FULL : V_FULL) + ring.st], ring.ph, abort_flag, lane);
-        // the buffer's previous contents (the packed dS of slot g - NBUF) have been consumed
-        if (ok) ok = mbar_wait_warp(&bars[BUF_FREE + b], bph ^ 1, abort_flag, lane);
+        if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 0, g);
+        // the tile has landed AND the buffer's previous contents (the packed dS of slot g - NBUF)
+        // have been consumed: both barriers are probed at once (one shared-memory round trip)
+        ok = mbar_wait_warp2(&bars[(ROLE == 0 ? K_FULL : V_FULL) + ring.st], ring.ph, &bars[BUF_FREE + b], bph ^ 1, abort_flag, lane);
+        if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 3, g);
         if (!ok) break;
         if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 1, g);
         tc_fence_after();
@@ -251,11 +261,12 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
         const uint64_t bt = (ROLE == 0 ? dK : dV) + ring.st * PAIR16;
         const uint32_t d = tbuf + (ROLE == 0 ? 0u : COL_DPT);
 #pragma unroll
-        for (int tl = 0; tl < 2; ++tl)
+        for (int tl = 0; tl < 2; ++tl) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_bf16_ss_elect(d + (tl ? LANE16 : 0u), a + tl * TILE16 + kk * STEP_K, bt + (tl ? kt1 : 0u) + kk * STEP_K,
                                IDESC_64, (uint32_t)(kk > 0));
+        }
         umma_commit_elect(&bars[SP_FULL + b]);            // the barrier expects both the S and the dP commit
         if (ROLE == 1) umma_commit_elect(&bars[V_EMPTY + ring.st]);
         if (i == nv - 1) umma_commit_elect(&bars[QDO_EMPTY + ub]);    // expects both issuers' commits
@@ -270,11 +281,12 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
         const uint32_t acc = tmem_base + COL_DQ + ub * 64;
         const uint64_t bk = dKmn + ring.st * PAIR16;
 #pragma unroll
-        for (int tl = 0; tl < 2; ++tl)
+        for (int tl = 0; tl < 2; ++tl) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_bf16_ts_elect(acc + (tl ? LANE16 : 0u), tbuf + COL_DPT + (tl ? LANE16 : 0u) + kk * 8,
                                bk + (tl ? kt1 : 0u) + kk * STEP_MN, IDESC_DQ, (uint32_t)(i > 0 || kk > 0));
+        }
         umma_commit_elect(&bars[BUF_FREE + b]);
         umma_commit_elect(&bars[K_EMPTY + ring.st]);      // the K tiles of this slot are free once dQ is done
         if (i == nv - 1) umma_commit_elect(&bars[ACC_FULL + ub]);     // written out by the last slot's worker group
@@ -287,6 +299,32 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
 }
 
 constexpr int CW = 16;                               // key columns per pass of the worker loops
+
+// Pass 1 for 16 keys of one query row:  P = exp2(S c - LSE),  Di += P dP,  P -> packed bf16 into
+// tensor memory at `dst` (8 columns of the S region that have already been read).
+__device__ __forceinline__ void pass1_cols(const uint32_t* s, const uint32_t* dp, float2 c2v, float2 nl, float2& dacc, uint32_t dst) {
+  uint32_t pw[CW / 2];
+#pragma unroll
+  for (int q = 0; q < CW; q += 2) {
+    float2 a = __ffma2_rn(f2(s[q], s[q + 1]), c2v, nl);
+    a.x = ex2_approx(a.x); a.y = ex2_approx(a.y);
+    dacc = __ffma2_rn(a, f2(dp[q], dp[q + 1]), dacc);
+    pw[q / 2] = pack_bf16x2(a.x, a.y);
+  }
+  tmem_st_32x32b_x8(dst, pw);
+}
+// Pass 2 for the same 16 keys:  dS = P (w dP - w Di)  -> packed bf16 at `dst` (8 columns of the dP
+// region that have already been read).  pk: the 8 packed words of P.
+__device__ __forceinline__ void pass2_cols(const uint32_t* pk, const uint32_t* dp, float2 wv, float2 nwd, uint32_t dst) {
+  uint32_t ds[CW / 2];
+#pragma unroll
+  for (int q = 0; q < CW; q += 2) {
+    const float2 pf = f2(pk[q / 2] << 16, pk[q / 2] & 0xffff0000u);
+    const float2 e = __fmul2_rn(pf, __ffma2_rn(f2(dp[q], dp[q + 1]), wv, nwd));
+    ds[q / 2] = pack_bf16x2(e.x, e.y);
+  }
+  tmem_st_32x32b_x8(dst, ds);
+}
 constexpr int OUT_COLS = 16, OUT_PASSES = 64 / OUT_COLS;
 
 __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int wg,
@@ -336,16 +374,13 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     }
     if (mask == 0) continue;
     const uint32_t un = ucnt++;
-    const uint32_t ub = un & 1;
     const long long row_off = ((long long)c.outer * p.Hq + (live ? h : t.h0)) * p.K * 64 + row;
     const float* lse_base = p.lse + row_off;
     uint4* rt_base = p.rowterm + row_off;
-    bool my_unit = false;                       // this group owns the unit's last slot: it writes dQ
     for (unsigned m = mask; m; m &= m - 1, ++g) {
       const uint32_t bb = b, pp = bph;
       if (++b == NBUF) { b = 0; bph ^= 1; }
-      my_unit = (int)bb == wg;
-      if (!my_unit) continue;
+      if ((int)bb != wg) continue;
       const int k = __ffs(m) - 1;
       const float w = __shfl_sync(0xffffffffu, my_w, k);
       const float lse = lse_base[k * 64];
@@ -361,37 +396,27 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       float2 dacc = make_float2(0.f, 0.f);
 #pragma unroll 1
       for (int cpos = 0; cpos < 64; cpos += CW) {
-        uint32_t s[CW], dp[CW], pw[CW / 2];
+        uint32_t s[CW], dp[CW];
         tmem_ld_32x32b_x16(tb + cpos, s);
         tmem_ld_32x32b_x16(tb + COL_DPT + cpos, dp);
         tmem_ld_wait();
-#pragma unroll
-        for (int q = 0; q < CW; q += 2) {
-          float2 a = __ffma2_rn(f2(s[q], s[q + 1]), c2v, nl);
-          a.x = ex2_approx(a.x); a.y = ex2_approx(a.y);
-          dacc = __ffma2_rn(a, f2(dp[q], dp[q + 1]), dacc);
-          pw[q / 2] = pack_bf16x2(a.x, a.y);
-        }
-        tmem_st_32x32b_x8(tb + cpos / 2, pw);
+        pass1_cols(s, dp, c2v, nl, dacc, tb + cpos / 2);
       }
       const float di = dacc.x + dacc.y;
       tmem_st_wait();
       if (elected) GCA_TRACE_BUF(p.prof, 8, g);
-      // Pass 2:  dS = P (w dP - w Di)  -> packed bf16 over the dP columns already read
+      // Pass 2:  dS = P (w dP - w Di)  -> packed bf16 over the dP columns already read.  (Issuing the
+      // tensor-memory read of the next 16 columns before computing the current ones was measured
+      // slower, 0.603 against 0.562 ms; so was writing dS into two regions of its own, which frees
+      // the score buffer before the dQ product has run: 0.602 against 0.558 ms.)
       const float2 wv = make_float2(w, w), nwd = make_float2(-w * di, -w * di);
 #pragma unroll 1
       for (int cpos = 0; cpos < 64; cpos += CW) {
-        uint32_t pk[CW / 2], dp[CW], ds[CW / 2];
+        uint32_t pk[CW / 2], dp[CW];
         tmem_ld_32x32b_x8(tb + cpos / 2, pk);
         tmem_ld_32x32b_x16(tb + COL_DPT + cpos, dp);
         tmem_ld_wait();
-#pragma unroll
-        for (int q = 0; q < CW; q += 2) {
-          const float2 pf = f2(pk[q / 2] << 16, pk[q / 2] & 0xffff0000u);
-          const float2 e = __fmul2_rn(pf, __ffma2_rn(f2(dp[q], dp[q + 1]), wv, nwd));
-          ds[q / 2] = pack_bf16x2(e.x, e.y);
-        }
-        tmem_st_32x32b_x8(tb + COL_DPT + cpos / 2, ds);
+        pass2_cols(pk, dp, wv, nwd, tb + COL_DPT + cpos / 2);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -406,24 +431,52 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
       if ((lane & 15) == 0 && live) dwp[(tile * p.K + k) * 4 + quad] = dsum;
     }
     if (!ok) break;
-    if (my_unit) {
-      ok = mbar_wait_bounded(&bars[ACC_FULL + ub], (un >> 1) & 1, abort_flag);
-      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-      if (elected) GCA_TRACE_BUF(p.prof, 10, un);
-      tc_fence_after();
-      // dQ leaves in four passes of one small loop body (16 columns: TMEM -> bf16 -> one 32-byte
-      // store per row)
+  }
+}
+
+// The dQ writer: a warpgroup of its own, so that no worker group is held up by a unit's output (a
+// worker group is tied to every NBUF-th slot; while it waited for the unit's last dQ product and
+// stored the tile, ~2,000-2,800 cycles, its next slot and with it the whole ring stood still once
+// per unit: 0.571 -> 0.544 ms).  Its wait is the ordinary suspending try_wait: polling with a sleep
+// between probes (20 / 100 / 400 ns) was measured slower (0.584 / 0.574 / 0.558 ms).  Thread = TMEM
+// lane = (head tile, query row) as in the workers.
+__device__ void q_writer(const BwdQParams& p, uint64_t* bars, volatile int* abort_flag, int quad, int lane, uint32_t tmem_base) {
+  const int tile = lane >> 4;
+  const int row = quad * 16 + (lane & 15);
+  const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16);
+  const bool elected = quad == 0 && lane == 0;
+  PairCursor c;
+  c.init(p.HP);
+  uint32_t ucnt = 0;
+  bool ok = true;
+  int next_idx = q_load_row(p, c.u, c.outer, lane);
+  for (; c.u < p.units && ok; c.advance()) {
+    const int my_idx = next_idx;
+    next_idx = q_load_row(p, c.u + gridDim.x, c.next_outer(), lane);
+    if (q_valid(p, my_idx) == 0) continue;           // the workers zero-fill units without valid slots
+    const uint32_t un = ucnt++;
+    const uint32_t ub = un & 1;
+    const QInfo t = q_info(p, c.inner);
+    const int h = t.h0 + tile;
+    const bool live = (tile == 0 || t.two) && h < p.Hq;
+    const int n = c.outer / p.J, j = c.outer - n * p.J;
+    __nv_bfloat16* dq_row = p.dq + n * p.dqs[0] + j * p.dqs[1] + h * p.dqs[2] + row * p.dqs[3];
+    ok = mbar_wait_bounded(&bars[ACC_FULL + ub], (un >> 1) & 1, abort_flag);
+    if (!__all_sync(0xffffffffu, ok)) break;
+    if (elected) GCA_TRACE_BUF(p.prof, 10, un);
+    tc_fence_after();
+    // dQ leaves in four passes of one small loop body (16 columns: TMEM -> bf16 -> one 32-byte
+    // store per row)
 #pragma unroll 1
-      for (int part = 0; part < OUT_PASSES; ++part) {
-        uint32_t v[OUT_COLS];
-        tmem_ld_32x32b_x16(tlane + COL_DQ + ub * 64 + part * OUT_COLS, v);
-        tmem_ld_wait();
-        if (live) store16_bf16(reinterpret_cast<uint8_t*>(dq_row) + part * OUT_COLS * 2, v, p.sm_scale, p.wide_store);
-      }
-      tc_fence_before();
-      mbar_arrive(&bars[ACC_EMPTY + ub]);
-      if (elected) GCA_TRACE_BUF(p.prof, 11, un);
+    for (int part = 0; part < OUT_PASSES; ++part) {
+      uint32_t v[OUT_COLS];
+      tmem_ld_32x32b_x16(tlane + COL_DQ + ub * 64 + part * OUT_COLS, v);
+      tmem_ld_wait();
+      if (live) store16_bf16(reinterpret_cast<uint8_t*>(dq_row) + part * OUT_COLS * 2, v, p.sm_scale, p.wide_store);
     }
+    tc_fence_before();
+    mbar_arrive(&bars[ACC_EMPTY + ub]);
+    if (elected) GCA_TRACE_BUF(p.prof, 11, un);
   }
 }
 
@@ -438,12 +491,12 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[QDO_FULL + i], 1);
-      mbar_init(&bars[QDO_EMPTY + i], 2);                            // S issuer + dP issuer
+      mbar_init(&bars[QDO_EMPTY + i], 2);                  // S issuers + dP issuers
       mbar_init(&bars[ACC_FULL + i], 1);
       mbar_init(&bars[ACC_EMPTY + i], 128);
     }
     for (int i = 0; i < NBUF; ++i) {
-      mbar_init(&bars[SP_FULL + i], 2);                              // S commit + dP commit
+      mbar_init(&bars[SP_FULL + i], 2);                    // S commits + dP commits
       mbar_init(&bars[PDS_FULL + i], 128);
       mbar_init(&bars[BUF_FREE + i], 1);
     }
@@ -462,6 +515,7 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
   const uint32_t tmem_base = *tmem_slot;
   if (warp < 4 * NBUF) q_worker(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
   else if (warp == PROD_WARP) q_producer(p, smem, bars, abort_flag, lane);
+  else if (warp >= WRITER_WARP) q_writer(p, bars, abort_flag, warp & 3, lane, tmem_base);
   else if (warp == ISSUE_S) q_issuer<0>(p, smem, bars, abort_flag, lane, tmem_base);
   else if (warp == ISSUE_DP) q_issuer<1>(p, smem, bars, abort_flag, lane, tmem_base);
   else if (warp == ISSUE_DQ) q_issuer<2>(p, smem, bars, abort_flag, lane, tmem_base);

@@ -101,6 +101,18 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
   // that follows (tcgen05.mma issue in particular) on the uniform path
   return __all_sync(0xffffffffu, ok);
 }
+// Two barriers at once: both are probed before either result is used, so that a wait whose
+// barriers are already complete (the usual case for an MMA-issuing warp) costs one shared-memory
+// round trip, not two.
+__device__ __forceinline__ bool mbar_wait_warp2(uint64_t* bar_a, uint32_t parity_a, uint64_t* bar_b, uint32_t parity_b,
+                                                volatile int* abort_flag, int lane) {
+  (void)lane;
+  const bool ra = mbar_test_wait(bar_a, parity_a), rb = mbar_test_wait(bar_b, parity_b);
+  bool ok = true;
+  if (!ra) ok = mbar_wait_bounded(bar_a, parity_a, abort_flag);
+  if (ok && !rb) ok = mbar_wait_bounded(bar_b, parity_b, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
 __device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);

@@ -1,0 +1,199 @@
+// Sliding-window causal self-attention with ALiBi for a handful of new positions against the
+// cached window (autoregressive decode): what the reference gets from flash-attn's
+// flash_attn_with_kvcache(q, k, v, causal=True, window_size=(W, 0), alibi_slopes=m) at
+// model/llama.py:684-688.  Per decoded token this reads 2 x (W + 1) x 128 bytes per (sequence, kv
+// head) and layer: HBM-bound, no tensor cores.
+//
+//   s[i, j] = scale * q_i . k_j  -  slope_h * (pos_i - j),   pos_i = T - Sq + i  (bottom-right aligned)
+//   visible: pos_i - W <= j <= pos_i;   out_i = softmax_j(s[i, :]) V
+//
+// One CTA per (sequence, kv head), 8 warps.  A warp load covers FOUR key rows: 8 lanes x 16 bytes
+// per 128-byte row, fully coalesced; each 8-lane group owns a stream of keys (j = 4 * step + group)
+// with its own online-softmax state (running maximum, sum, 8 output columns per lane), so the loop
+// has no cross-lane traffic except the 3-step dot-product reduction inside a group.  Loads run
+// PREFETCH steps ahead of the arithmetic (registers), which keeps ~64 KB per SM in flight.  At the
+// end the 4 streams of a warp and the 8 warps are merged in a fixed order: the result does not
+// depend on scheduling.
+#include "gca_common.cuh"
+
+namespace gca {
+
+namespace {
+
+constexpr int NWARPS = 8, PREFETCH = 4;
+
+__device__ __forceinline__ float lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct WinParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const float* slopes;        // (Hq) or nullptr
+  __nv_bfloat16* out;
+  long long qs[3], os[3];     // strides of (n, head, row) in elements; the 64 head dims are contiguous
+  long long ks[3], vs[3];     // strides of (n, kv head, position)
+  int N, Hq, Hkv, G, Sq, T, window;
+  float c2;                   // scale * log2(e)
+};
+
+struct State { float m, l, acc[8]; };
+
+__device__ __forceinline__ void merge(State& a, float m2, float l2, const float* acc2) {
+  const float m = fmaxf(a.m, m2);
+  const float ca = (a.m == -INFINITY) ? 0.f : ex2(a.m - m), cb = (m2 == -INFINITY) ? 0.f : ex2(m2 - m);
+  a.l = a.l * ca + l2 * cb;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a.acc[i] = a.acc[i] * ca + acc2[i] * cb;
+  a.m = m;
+}
+
+template <int R>
+__global__ void __launch_bounds__(NWARPS * 32)
+win_decode_kernel(const WinParams p) {
+  __shared__ float part[NWARPS][R][2 + 64];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
+  const int n = blockIdx.x / p.Hkv, hk = blockIdx.x - n * p.Hkv;
+  const int rows = p.G * p.Sq;                       // <= R
+  // this lane's 8 query values of every row, pre-scaled; the row's ALiBi slope (in log2 units) and position
+  float qv[R][8], slope[R];
+  int pos[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int gi = r / p.Sq, i = r - gi * p.Sq, h = hk * p.G + gi;
+    pos[r] = p.T - p.Sq + i;
+    slope[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qv[r][e] = 0.f;
+    if (r < rows) {
+      slope[r] = p.slopes ? p.slopes[h] * GCA_LOG2E : 0.f;
+      const uint4 t = *reinterpret_cast<const uint4*>(p.q + n * p.qs[0] + h * p.qs[1] + i * p.qs[2] + sub * 8);
+      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { qv[r][2 * e] = lo(w[e]) * p.c2; qv[r][2 * e + 1] = hi(w[e]) * p.c2; }
+    }
+  }
+  State st[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    st[r].m = -INFINITY; st[r].l = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) st[r].acc[e] = 0.f;
+  }
+  // keys any row can see: [first, T)
+  const int first = max(0, p.T - p.Sq - p.window);
+  const __nv_bfloat16* kb = p.k + n * p.ks[0] + hk * p.ks[1] + sub * 8;
+  const __nv_bfloat16* vb = p.v + n * p.vs[0] + hk * p.vs[1] + sub * 8;
+  const int stride = NWARPS * 4;                     // keys per CTA step
+  const int base = first + warp * 4;                 // warp-uniform: every lane runs the same steps
+  uint4 kq[PREFETCH], vq[PREFETCH];
+#pragma unroll
+  for (int s = 0; s < PREFETCH; ++s) {
+    const int j = base + grp + s * stride;
+    kq[s] = vq[s] = make_uint4(0, 0, 0, 0);
+    if (j < p.T) {
+      kq[s] = *reinterpret_cast<const uint4*>(kb + j * p.ks[2]);
+      vq[s] = *reinterpret_cast<const uint4*>(vb + j * p.vs[2]);
+    }
+  }
+  for (int jb = base; jb < p.T; jb += PREFETCH * stride) {
+#pragma unroll
+    for (int s = 0; s < PREFETCH; ++s) {
+      const int j = jb + grp + s * stride;
+      const uint4 kc = kq[s], vc = vq[s];
+      const int jn = j + PREFETCH * stride;             // refill this register slot
+      if (jn < p.T) {
+        kq[s] = *reinterpret_cast<const uint4*>(kb + jn * p.ks[2]);
+        vq[s] = *reinterpret_cast<const uint4*>(vb + jn * p.vs[2]);
+      }
+      // every lane of a warp runs the same number of steps (the reduction below uses shuffles);
+      // keys past the end are masked
+      const bool in_range = j < p.T;
+      const uint32_t kw[4] = {kc.x, kc.y, kc.z, kc.w}, vw[4] = {vc.x, vc.y, vc.z, vc.w};
+      float kf[8], vf[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { kf[2 * e] = lo(kw[e]); kf[2 * e + 1] = hi(kw[e]); vf[2 * e] = lo(vw[e]); vf[2 * e + 1] = hi(vw[e]); }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float sc = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sc = fmaf(qv[r][e], kf[e], sc);
+        sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+        sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+        sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+        const int dist = pos[r] - j;
+        if (r < rows && in_range && dist >= 0 && dist <= p.window) {
+          sc -= slope[r] * (float)dist;
+          const float m = fmaxf(st[r].m, sc);
+          const float corr = ex2(st[r].m - m), pr = ex2(sc - m);       // ex2(-inf) = 0 on the first key
+          st[r].l = st[r].l * corr + pr;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) st[r].acc[e] = fmaf(pr, vf[e], st[r].acc[e] * corr);
+          st[r].m = m;
+        }
+      }
+    }
+  }
+  // merge the 4 key streams of the warp (groups 8 and 16 lanes apart), then the warps
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int of = 8; of <= 16; of <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, st[r].m, of), l2 = __shfl_xor_sync(0xffffffffu, st[r].l, of);
+      float a2[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a2[e] = __shfl_xor_sync(0xffffffffu, st[r].acc[e], of);
+      merge(st[r], m2, l2, a2);
+    }
+    if (grp == 0) {
+      if (sub == 0) { part[warp][r][0] = st[r].m; part[warp][r][1] = st[r].l; }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part[warp][r][2 + sub * 8 + e] = st[r].acc[e];
+    }
+  }
+  __syncthreads();
+  // thread t < rows * 8 finishes 8 output columns of one row
+  if (threadIdx.x < rows * 8) {
+    const int r = threadIdx.x >> 3, s8 = threadIdx.x & 7;
+    State t;
+    t.m = -INFINITY; t.l = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) t.acc[e] = 0.f;
+    for (int w = 0; w < NWARPS; ++w) merge(t, part[w][r][0], part[w][r][1], &part[w][r][2 + s8 * 8]);
+    const float inv = t.l > 0.f ? 1.0f / t.l : 0.f;
+    const int gi = r / p.Sq, i = r - gi * p.Sq, h = hk * p.G + gi;
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 b = __floats2bfloat162_rn(t.acc[2 * e] * inv, t.acc[2 * e + 1] * inv);
+      o[e] = *reinterpret_cast<const uint32_t*>(&b);
+    }
+    *reinterpret_cast<uint4*>(p.out + n * p.os[0] + h * p.os[1] + i * p.os[2] + s8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+}  // namespace
+
+int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream) {
+  WinParams p;
+  p.q = (const __nv_bfloat16*)a.q; p.k = (const __nv_bfloat16*)a.k; p.v = (const __nv_bfloat16*)a.v;
+  p.slopes = a.alibi_slopes; p.out = (__nv_bfloat16*)a.out;
+  for (int i = 0; i < 3; ++i) { p.qs[i] = a.q_stride[i]; p.os[i] = a.o_stride[i]; p.ks[i] = a.k_stride[i]; p.vs[i] = a.v_stride[i]; }
+  p.N = a.N; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = a.Hq / a.Hkv; p.Sq = a.Sq; p.T = a.T; p.window = a.window;
+  p.c2 = a.sm_scale * GCA_LOG2E;
+  const int rows = p.G * a.Sq;
+  const unsigned grid = (unsigned)(a.N * a.Hkv);
+  if (grid == 0) return 0;
+  if (rows <= 1) win_decode_kernel<1><<<grid, NWARPS * 32, 0, stream>>>(p);
+  else if (rows <= 2) win_decode_kernel<2><<<grid, NWARPS * 32, 0, stream>>>(p);
+  else if (rows <= 4) win_decode_kernel<4><<<grid, NWARPS * 32, 0, stream>>>(p);
+  else return GCA_ERR_SHAPE;
+  return (int)cudaGetLastError();
+}
+
+}  // namespace gca

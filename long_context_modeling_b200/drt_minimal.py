@@ -161,6 +161,12 @@ class SelfAttention(nn.Module):
         else:                                                    # a few new positions against the cached window
             kc, vc = torch.cat([cache[0], k], 2), torch.cat([cache[1], v], 2)
             t = kc.shape[2]
+            if q.dtype == torch.bfloat16 and q.is_cuda and l <= 4 and self.d == 64 and not torch.is_grad_enabled():
+                # the library's decode kernel for windowed ALiBi attention (flash_attn_with_kvcache in the reference)
+                from . import fused_ops
+                o = fused_ops.window_decode(q, kc, vc, self.window, self.slopes.float().contiguous(), 1.0 / math.sqrt(self.d))
+                new_cache = (kc[:, :, -(self.window + 1):], vc[:, :, -(self.window + 1):])
+                return self.o_proj(o.transpose(1, 2).reshape(n, l, -1)), new_cache
             qi = torch.arange(t - l, t, device=x.device).view(l, 1)
             kj = torch.arange(t, device=x.device).view(1, t)
             dist = (qi - kj).float()

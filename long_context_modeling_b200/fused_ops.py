@@ -86,3 +86,30 @@ def rmsnorm_linear(x: torch.Tensor, folded_weight: torch.Tensor, eps: float) -> 
     """RMSNorm(x) @ W.T with ``folded_weight = fold_gain(W, norm.weight)``: one row reduction over x
     and one GEMM over the raw x whose epilogue applies 1 / rms."""
     return linear(x, folded_weight, row_scale=row_rms(x, eps))
+
+
+def window_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int, slopes: Optional[torch.Tensor] = None,
+                  sm_scale: Optional[float] = None) -> torch.Tensor:
+    """Sliding-window causal attention with ALiBi for a few new positions against the cached window
+    (``flash_attn_with_kvcache(..., causal=True, window_size=(window, 0), alibi_slopes=slopes)``,
+    ``model/llama.py:684-688``).  q (N, Hq, Sq, 64), k / v (N, Hkv, T, 64) bf16 -- any strides with the
+    head dimension contiguous; the query rows stand at positions T - Sq .. T - 1.  Returns (N, Hq, Sq, 64)."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _require(t, f"window_decode {name}")
+        if t.dim() != 4 or t.shape[-1] != 64 or t.stride(-1) != 1:
+            raise ValueError(f"window_decode: {name} must be (N, H, L, 64) with contiguous head dimension")
+    n, hq, sq, _ = q.shape
+    hkv, t_len = k.shape[1], k.shape[2]
+    out = torch.empty((n, hq, sq, 64), dtype=torch.bfloat16, device=q.device)
+    a = _lib.WindowDecodeArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    if slopes is not None:
+        if slopes.dtype != torch.float32 or slopes.numel() != hq or not slopes.is_contiguous() or not slopes.is_cuda:
+            raise ValueError("window_decode: slopes must be contiguous float32 (Hq,) on the device")
+        a.alibi_slopes = slopes.data_ptr()
+    for i in range(3):
+        a.q_stride[i], a.o_stride[i], a.k_stride[i], a.v_stride[i] = q.stride(i), out.stride(i), k.stride(i), v.stride(i)
+    a.N, a.Hq, a.Hkv, a.Sq, a.T, a.window = n, hq, hkv, sq, t_len, int(window)
+    a.sm_scale = float(sm_scale) if sm_scale is not None else 0.125
+    _lib.check(_lib.lib().gca_window_decode(C.byref(a), _stream()), "gca_window_decode")
+    return out

@@ -138,3 +138,53 @@ def test_fused_module_path_matches_reference_class(golden_dir):
         # one-row decode step (chunk_size == 1: nothing is skipped)
         o1 = mod.forward_fused(hs[:, 1:2, :1], kc[:, :k], vc[:, :k], idx[:, :1], w[:, :1].cuda())
         close(o1, g["triton_decode_o"], "decode")
+
+
+def _window_reference(q, k, v, window, slopes, scale):
+    """float32: explicit scores, ALiBi bias, window + causal mask, softmax (model/llama.py:684-688 semantics)."""
+    n, hq, sq, d = q.shape
+    hkv, t = k.shape[1], k.shape[2]
+    g = hq // hkv
+    kf = k.float().repeat_interleave(g, 1)
+    vf = v.float().repeat_interleave(g, 1)
+    s = torch.einsum("nhid,nhjd->nhij", q.float(), kf) * scale
+    pos = torch.arange(t - sq, t).view(sq, 1)
+    j = torch.arange(t).view(1, t)
+    dist = (pos - j).float()
+    bias = torch.zeros(hq, sq, t) if slopes is None else -slopes.view(hq, 1, 1).cpu() * dist
+    bias = bias.masked_fill((dist < 0) | (dist > window), float("-inf"))
+    p = torch.softmax(s.cpu() + bias, -1)
+    return torch.einsum("nhij,nhjd->nhid", p, vf.cpu())
+
+
+@pytest.mark.parametrize("n,hq,hkv,sq,t,window,alibi", [
+    (2, 12, 12, 1, 513, 512, True),       # the model's decode step: one new position, full window
+    (3, 4, 4, 2, 300, 512, True),         # two new positions, fewer keys than the window
+    (2, 8, 4, 2, 700, 128, True),         # grouped-query heads, keys older than the window are skipped
+    (1, 2, 2, 1, 1, 16, False),           # a single key, no ALiBi
+    (2, 4, 1, 1, 97, 40, True),           # four q heads on one kv head
+    (1, 12, 12, 3, 1030, 512, True),      # three rows
+])
+def test_window_decode_against_float32(n, hq, hkv, sq, t, window, alibi):
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    g = torch.Generator().manual_seed(t + sq)
+    q = torch.randn(n, hq, sq, 64, generator=g).bfloat16().cuda()
+    k = torch.randn(n, hkv, t, 64, generator=g).bfloat16().cuda()
+    v = torch.randn(n, hkv, t, 64, generator=g).bfloat16().cuda()
+    slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / hq) for i in range(hq)]).cuda() if alibi else None
+    got = F.window_decode(q, k, v, window, slopes, 0.125)
+    ref = _window_reference(q, k, v, window, slopes, 0.125)
+    close(got, ref, (n, hq, hkv, sq, t, window))
+
+
+def test_window_decode_reads_strided_caches():
+    """k / v as (N, T, H, 64) token-major storage viewed as (N, H, T, 64): the reference's cache layout."""
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(2, 1, 6, 64, generator=g).bfloat16().cuda().transpose(1, 2)          # (N, H, 1, 64) view
+    k = torch.randn(2, 200, 6, 64, generator=g).bfloat16().cuda().transpose(1, 2)
+    v = torch.randn(2, 200, 6, 64, generator=g).bfloat16().cuda().transpose(1, 2)
+    slopes = torch.full((6,), 0.05).cuda()
+    close(F.window_decode(q, k, v, 64, slopes, 0.125), _window_reference(q, k, v, 64, slopes, 0.125))
