@@ -172,11 +172,13 @@ kv_project_append_kernel(const __grid_constant__ ProjParams p) {
         for (int c0 = 0; c0 < cols; c0 += 16) {
           uint32_t v[16];
           tmem_ld_32x32b_x16(tlane + ab * BN + c0, v);
+          // the residual's 32 bytes are requested before the accumulator read is waited for
+          uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
+          if (live && rrow) { r0 = *reinterpret_cast<const uint4*>(rrow + c0); r1 = *reinterpret_cast<const uint4*>(rrow + c0 + 8); }
           tmem_ld_wait();
           if (live) {
             uint32_t w[8];
             if (rrow) {
-              const uint4 r0 = *reinterpret_cast<const uint4*>(rrow + c0), r1 = *reinterpret_cast<const uint4*>(rrow + c0 + 8);
               const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
               for (int i = 0; i < 8; ++i)
