@@ -34,7 +34,7 @@ N_SEQ, CHUNKS, HEADS, TOPK, HEAD_DIM, CHUNK = 8, 256, 12, 8, 64, 64
 FWD_FLOP_PER_SLOT = 4 * CHUNK * CHUNK * HEAD_DIM          # QK^T + PV for one (query chunk, head, slot)
 FWD_BWD_FACTOR = 3.5                                      # backward counted as 2.5 x forward (ltriton/gca.py:1091-1092)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, ncu capture of `--n-seq 2` (see profiles/)
-TRAFFIC_2SEQ = {"fwd": 140.4e6 + 47.5e6, "bwd_kv": 219.4e6 + 71.8e6, "bwd_q": 205.5e6 + 41.2e6}
+TRAFFIC_2SEQ = {"fwd": 140.5e6 + 48.4e6, "bwd_kv": 265.2e6 + 71.5e6, "bwd_q": 211.6e6 + 83.0e6}
 
 
 def valid_slots(chunks: int, topk: int) -> int:
