@@ -719,6 +719,141 @@ def decode_arm(args):
         dist.destroy_process_group()
 
 
+def window_decode_arm(args):
+    """Sliding-window ALiBi attention of one decode step (the reference's flash_attn_with_kvcache call,
+    model/llama.py:684-688): 32 sequences x 12 heads, one new position against 513 cached keys per
+    head, one layer.  HBM-bound; ten caches in turn and an L2 flush between graph replays."""
+    import long_context_modeling_b200 as lcm
+    from long_context_modeling_b200 import fused_ops as F
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    n, h, t, window = 32, 12, 513, 512
+    g = torch.Generator(device=dev).manual_seed(3)
+    ks = [torch.randn(n, h, t, 64, generator=g, device=dev).bfloat16() for _ in range(10)]
+    vs = [torch.randn(n, h, t, 64, generator=g, device=dev).bfloat16() for _ in range(10)]
+    q = torch.randn(n, h, 1, 64, generator=g, device=dev).bfloat16()
+    q_host = q.cpu().pin_memory()
+    slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / h) for i in range(h)], device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    calls = [0]
+
+    def step():
+        calls[0] += 1
+        return F.window_decode(q, ks[calls[0] % 10], vs[calls[0] % 10], window, slopes, 0.125)
+
+    def e2e_step():
+        calls[0] += 1
+        return F.window_decode(q_host.to(dev, non_blocking=True), ks[calls[0] % 10], vs[calls[0] % 10], window, slopes, 0.125).cpu()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(physical_gpu_index(0))
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps, sampler.stop()
+
+    steps, warmup = max(args.steps, 100), max(5, args.warmup)
+    ms, clocks = timed(step, steps, warmup)
+    ms_e2e, _ = timed(e2e_step, steps, warmup)
+    ms_k = _graph_time([(lambda i=i: F.window_decode(q, ks[i], vs[i], window, slopes, 0.125)) for i in range(10)], flush)
+    nbytes = 2 * n * h * t * 128
+    achieved = nbytes / (ms_k * 1e-3) / 1e9
+    line = {"metric": "window_decode_gbs", "value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "sliding-window (512) causal attention with ALiBi, one new position: 32 sequences x 12 heads "
+                                   "x 513 cached keys (50.4 MB of K/V per call), one layer", "sequences": n, "heads": h, "keys": t,
+                       "cache_policy": "ten caches in turn (504 MB, 4 x the L2) and an L2 flush between graph replays"},
+            "clocks": clocks,
+            "e2e": {"value": nbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": q_host.numel() * 2,
+                    "d2h_bytes_per_step": q_host.numel() * 2, "ms_per_step": ms_e2e},
+            "gpu_launches": steps,
+            "roofline": {"kernel": "win_decode_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy bandwidth", "traffic": None,
+                         "algorithmic_bytes_per_launch": nbytes, "us_per_launch": ms_k * 1e3},
+            "device_status": lcm.read_status()}
+    print(json.dumps(line), flush=True)
+
+
+def projection_arm(args):
+    """The tensor-core GEMM of the library at the training shape (8 x 16,640 rows, 768 wide): chunk K/V
+    projection with the cache append as its epilogue, and its linear mode with the RMSNorm row scale
+    (pre-norm + q_proj) and with the residual epilogue (o_proj + residual)."""
+    import long_context_modeling_b200 as lcm
+    from long_context_modeling_b200 import fused_ops as F
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    n, c, dim = 8, 260, 768
+    m = n * c * 64
+    g = torch.Generator(device=dev).manual_seed(5)
+    xs = [torch.randn(n, c, 64, dim, generator=g, device=dev).bfloat16() for _ in range(2)]       # 2 x 204 MB: above the L2
+    wk, wv, wq = ((torch.randn(dim, dim, generator=g, device=dev) / 28).bfloat16() for _ in range(3))
+    res = torch.randn(m, dim, generator=g, device=dev).bfloat16()
+    out = torch.empty(m, dim, dtype=torch.bfloat16, device=dev)
+    x_host = xs[0].cpu().pin_memory()
+    calls = [0]
+
+    def append_step():
+        calls[0] += 1
+        m2 = lcm.ChunkKVManager(zero_landmark=True, capacity=c)
+        m2.append_projected(xs[calls[0] % 2], wk, wv)
+        return m2
+
+    def ev(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(physical_gpu_index(0))
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps, sampler.stop()
+
+    steps, warmup = max(args.steps, 20), max(3, args.warmup)
+    with torch.no_grad():
+        ms, clocks = ev(append_step, steps, warmup)
+        ms_lin, _ = ev(lambda: F.linear(xs[0], wq, out=out), steps, warmup)
+        ms_res, _ = ev(lambda: F.linear(xs[0], wq, residual=res, out=out), steps, warmup)
+        ms_rms, _ = ev(lambda: F.linear(xs[0], wq, row_scale=F.row_rms(xs[0], 1e-5), out=out), steps, warmup)
+
+        def e2e_step():
+            m2 = lcm.ChunkKVManager(zero_landmark=True, capacity=c)
+            m2.append_projected(x_host.to(dev, non_blocking=True), wk, wv)
+            return m2.past_lmk_embeds[:, :1].cpu()
+        ms_e2e, _ = ev(e2e_step, 5, 3)
+    fl = 2 * 2 * m * dim * dim
+    tf = fl / (ms * 1e-3) / 1e12
+    line = {"metric": "kv_projection_append_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"chunk K/V projection with cache-append epilogue: {n} x {c} chunks x 64 rows, {dim} -> 2 x {dim} "
+                                   "(cache allocation inside the step)", "rows": m, "hidden": dim,
+                       "cache_policy": "two input sets of 204 MB alternate (above the 126 MB L2)"},
+            "clocks": clocks,
+            "e2e": {"value": fl / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": n * dim * 2, "ms_per_step": ms_e2e},
+            "gpu_launches": 2 * steps,
+            "linear_mode": {"rows": m, "gemm_ms": ms_lin, "gemm_tflops": fl / 2 / (ms_lin * 1e-3) / 1e12,
+                            "with_residual_ms": ms_res, "rmsnorm_row_scale_ms": ms_rms},
+            "roofline": {"kernel": "kv_project_append_kernel", "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " burst dense bf16",
+                         "traffic": None, "algorithmic_flops_per_launch": fl},
+            "device_status": lcm.read_status()}
+    print(json.dumps(line), flush=True)
+
+
 # --------------------------------------------------------------------------------------------
 # Whole-model legs of the metric: the minimal DRT body with the kernels plugged in
 # --------------------------------------------------------------------------------------------
@@ -889,7 +1024,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="gca", choices=["gca", "retrieval", "decode", "triton-ref", "train16k", "generate"],
+    ap.add_argument("--workload", default="gca", choices=["gca", "retrieval", "decode", "triton-ref", "train16k", "generate", "window-decode", "projection"],
                     help="gca (default, the headline): GCA fwd+bwd at the DRT-16K shape; retrieval: landmark top-k over "
                          "a 16M-token cache; decode: one-row GCA for 32 sequences; train16k: one training step of the minimal "
                          "DRT body at the DRT-16K shape; generate: greedy generation with a 1M-token chunk cache")
@@ -913,6 +1048,10 @@ def main():
         triton_ref_arm(args)
     elif args.workload == "train16k":
         train_arm(args)
+    elif args.workload == "window-decode":
+        window_decode_arm(args)
+    elif args.workload == "projection":
+        projection_arm(args)
     elif args.workload == "generate":
         generate_arm(args)
     else:

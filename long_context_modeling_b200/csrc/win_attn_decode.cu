@@ -53,8 +53,11 @@ __device__ __forceinline__ void merge(State& a, float m2, float l2, const float*
   a.m = m;
 }
 
+// Registers are capped so that three CTAs of the one-row kernel share an SM: 32 sequences x 12
+// heads = 384 CTAs then run as ONE wave on 148 SMs (with two per SM a second wave of 88 CTAs
+// doubled the kernel's duration).
 template <int R>
-__global__ void __launch_bounds__(NWARPS * 32)
+__global__ void __launch_bounds__(NWARPS * 32, R == 1 ? 3 : (R == 2 ? 2 : 1))
 win_decode_kernel(const WinParams p) {
   __shared__ float part[NWARPS][R][2 + 64];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
