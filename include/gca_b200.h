@@ -405,6 +405,33 @@ typedef struct LinearArgs {
 int gca_row_rms(const RowRmsArgs* args, void* stream);
 int gca_linear(const LinearArgs* args, void* stream);
 
+/* ---- LM head fused with the cross-entropy loss, forward only (reference: model/DRT.py:1055-1064,
+ * `logits = lm_head(hidden)` followed by CrossEntropyLoss(ignore_index=-100); evaluation / perplexity) ----
+ *
+ *   loss[m] = logsumexp_j(row_scale[m] * x[m, :] . w[j, :]) - (row_scale[m] * x[m, :] . w[targets[m], :])
+ *
+ * x (M, K) bf16, w (N, K) bf16 (N = vocabulary, any size), targets (M) int64 (negative: the row is
+ * ignored, loss 0; a target >= N gives NaN), loss (M) float32, lse (M) float32 or NULL (natural log).
+ * The (M, N) logits stay in tensor memory.  workspace: gca_linear_ce_workspace_bytes(M, N) bytes,
+ * 16-byte aligned, caller-owned. */
+typedef struct LinearCeArgs {
+  const void* x;
+  const void* w;
+  const void* targets;
+  const float* row_scale;     /* may be NULL */
+  float* loss;
+  float* lse;                 /* may be NULL */
+  void* workspace;
+  int32_t* status;            /* device status word, or NULL */
+  int64_t M;
+  int64_t x_stride, w_stride;
+  int64_t workspace_bytes;
+  int32_t N, K;
+} LinearCeArgs;
+
+size_t gca_linear_ce_workspace_bytes(int64_t M, int32_t N);
+int gca_linear_cross_entropy(const LinearCeArgs* args, void* stream);
+
 /* ---- sliding-window causal self-attention with ALiBi, decode form (reference call site:
  * model/llama.py:684-688, flash_attn_with_kvcache(..., causal=True, window_size=(W, 0), alibi_slopes=m)) ----
  *
@@ -429,7 +456,7 @@ int gca_window_decode(const WindowDecodeArgs* args, void* stream);
 const char* gca_strerror(int code);
 int gca_abi_version(void);
 /* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,
- * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs, 7 RowRmsArgs, 8 LinearArgs, 9 WindowDecodeArgs): lets a foreign-language binding verify
+ * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs, 7 RowRmsArgs, 8 LinearArgs, 9 WindowDecodeArgs, 10 LinearCeArgs): lets a foreign-language binding verify
  * its struct layout before the first call. */
 size_t gca_sizeof(int which);
 

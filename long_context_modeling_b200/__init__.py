@@ -5,7 +5,7 @@ Host layer (this package) = views, strides, autograd bookkeeping; all arithmetic
 """
 from .gca import (attention, gca_kv_cache, gca_indexed, gca_indexed_nograd, read_status, check_status,  # noqa: F401
                   set_status_checks)
-from ._lib import GcaError  # noqa: F401
+from ._lib import GcaError, set_nvtx  # noqa: F401
 from .retrieval import (lmk_score_topk, merge_topk, retrieve, perform_batch_retrieval,  # noqa: F401
                         decode_retrieval, differentiable_weights, Retrieval)
 from .chunk_cache import ChunkKVManager  # noqa: F401

@@ -125,6 +125,14 @@ class WindowDecodeArgs(C.Structure):
         ("sm_scale", C.c_float),
     ]
 
+
+class LinearCeArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("targets", C.c_void_p), ("row_scale", C.c_void_p), ("loss", C.c_void_p),
+        ("lse", C.c_void_p), ("workspace", C.c_void_p), ("status", C.c_void_p), ("M", C.c_int64),
+        ("x_stride", C.c_int64), ("w_stride", C.c_int64), ("workspace_bytes", C.c_int64), ("N", C.c_int32), ("K", C.c_int32),
+    ]
+
 EXPORTS = {
     "gca_fwd": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
     "gca_decode": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
@@ -140,6 +148,8 @@ EXPORTS = {
     "gca_row_rms": (C.c_int, [C.POINTER(RowRmsArgs), C.c_void_p]),
     "gca_linear": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "gca_window_decode": (C.c_int, [C.POINTER(WindowDecodeArgs), C.c_void_p]),
+    "gca_linear_ce_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
+    "gca_linear_cross_entropy": (C.c_int, [C.POINTER(LinearCeArgs), C.c_void_p]),
     "lmk_exchange_mailbox_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "lmk_exchange_mailbox_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_void_p]),
     "lmk_exchange_mailbox_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
@@ -171,7 +181,7 @@ def lib() -> C.CDLL:
         if handle.gca_abi_version() != ABI_VERSION:
             raise RuntimeError("libgca_b200.so has an unexpected ABI version")
         for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs, LmkExchangeArgs,
-                                       KvProjectArgs, RowRmsArgs, LinearArgs, WindowDecodeArgs)):
+                                       KvProjectArgs, RowRmsArgs, LinearArgs, WindowDecodeArgs, LinearCeArgs)):
             if handle.gca_sizeof(which) != C.sizeof(struct):
                 raise RuntimeError(f"struct layout mismatch for {struct.__name__}: "
                                    f"library {handle.gca_sizeof(which)} vs binding {C.sizeof(struct)}")
@@ -181,6 +191,31 @@ def lib() -> C.CDLL:
 
 class GcaError(RuntimeError):
     pass
+
+
+_nvtx = False
+
+
+def set_nvtx(enabled: bool) -> None:
+    """Wrap every call into the library in an NVTX range named after the entry point (for timelines of
+    a host program; off by default)."""
+    global _nvtx
+    _nvtx = bool(enabled)
+
+
+def call(name: str, *args) -> None:
+    """``check(lib().<name>(*args), name)`` with the optional NVTX range around the launch."""
+    fn = getattr(lib(), name)
+    if _nvtx:
+        import torch
+        torch.cuda.nvtx.range_push(name)
+        try:
+            code = fn(*args)
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        code = fn(*args)
+    check(code, name)
 
 
 def check(code: int, what: str) -> None:

@@ -152,8 +152,7 @@ class ChunkKVManager:
         a.zero_landmark = 1 if self._zero_landmark else 0
         a.capacity, a.lmk_capacity = self._k.shape[1], self._lmk.shape[1]
         with torch.cuda.device(chunk_k.device):
-            _lib.check(_lib.lib().gca_cache_append(C.byref(a), torch.cuda.current_stream().cuda_stream),
-                       "gca_cache_append")
+            _lib.call("gca_cache_append", C.byref(a), torch.cuda.current_stream().cuda_stream)
         self._len += count
 
     def append_projected(self, enc_out: torch.Tensor, k_weight: torch.Tensor, v_weight: torch.Tensor) -> None:
@@ -185,8 +184,7 @@ class ChunkKVManager:
         a.capacity, a.lmk_capacity = self._k.shape[1], self._lmk.shape[1]
         a.zero_landmark = 1 if self._zero_landmark else 0
         with torch.cuda.device(x.device):
-            _lib.check(_lib.lib().gca_kv_project_append(C.byref(a), torch.cuda.current_stream().cuda_stream),
-                       "gca_kv_project_append")
+            _lib.call("gca_kv_project_append", C.byref(a), torch.cuda.current_stream().cuda_stream)
         self._len += count
 
     # ------------------------------------------------------------------ retrieval state

@@ -16,6 +16,7 @@ int launch_kv_project_append(const KvProjectArgs& a, int sms, cudaStream_t strea
 int launch_row_rms(const RowRmsArgs& a, cudaStream_t stream);
 int launch_linear(const LinearArgs& a, int sms, cudaStream_t stream);
 int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream);
+int launch_linear_ce(const LinearCeArgs& a, int sms, cudaStream_t stream);
 
 DeviceScope::DeviceScope(const void* device_ptr) {
   cudaPointerAttributes at;
@@ -117,6 +118,7 @@ size_t gca_sizeof(int which) {
     case 7: return sizeof(RowRmsArgs);
     case 8: return sizeof(LinearArgs);
     case 9: return sizeof(WindowDecodeArgs);
+    case 10: return sizeof(LinearCeArgs);
     default: return 0;
   }
 }
@@ -336,6 +338,31 @@ int gca_row_rms(const RowRmsArgs* a, void* stream) {
   gca::DeviceScope scope(a->x);
   if (scope.rc) return scope.rc;
   return gca::launch_row_rms(*a, (cudaStream_t)stream);
+}
+
+size_t gca_linear_ce_workspace_bytes(int64_t M, int32_t N) {
+  if (M <= 0 || N <= 0) return 0;
+  const size_t tiles = ((size_t)N + 255) / 256;
+  return gca::align_up((size_t)M * tiles * sizeof(float) * 2 + (size_t)M * sizeof(float), 256);
+}
+
+int gca_linear_cross_entropy(const LinearCeArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->x || !a->w || !a->targets || !a->loss) return GCA_ERR_NULL;
+  if (a->M < 0 || a->N < 1 || a->K < 64 || a->K % 64 != 0) return GCA_ERR_SHAPE;
+  if (a->x_stride % 8 || a->w_stride % 8 || a->x_stride < a->K || a->w_stride < a->K) return GCA_ERR_STRIDE;
+  if (!aligned16(a->x) || !aligned16(a->w) || (reinterpret_cast<uintptr_t>(a->targets) & 7u)) return GCA_ERR_ALIGN;
+  if (a->M == 0) return 0;
+  if (!a->workspace || !aligned16(a->workspace)) return GCA_ERR_NULL;
+  if ((size_t)a->workspace_bytes < gca_linear_ce_workspace_bytes(a->M, a->N)) return GCA_ERR_WORKSPACE;
+  gca::DeviceScope scope(a->loss);
+  if (scope.rc) return scope.rc;
+  // a target outside [0, N) never gets its logit written: start from NaN so that the loss says so
+  const size_t tiles = ((size_t)a->N + 255) / 256;
+  cudaError_t e = cudaMemsetAsync(static_cast<char*>(a->workspace) + (size_t)a->M * tiles * sizeof(float) * 2, 0xFF,
+                                  (size_t)a->M * sizeof(float), (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return gca::launch_linear_ce(*a, gca::sm_count(scope.dev), (cudaStream_t)stream);
 }
 
 int gca_window_decode(const WindowDecodeArgs* a, void* stream) {

@@ -60,7 +60,12 @@ static_assert(NBUF == 2 || NBUF == 3, "score buffers");
 // per head (the heads of a slot share the buffer's columns) 0.835 against 0.567 ms, one warp per
 // slot parity for S and dP 1,640 against 1,390 cycles per slot -- every extra polling warp slows
 // the shared-memory path that the MMAs' operand reads already load to ~875 of those cycles.
-constexpr int PROD_WARP = 4 * NBUF, ISSUE_S = PROD_WARP + 1, ISSUE_DP = ISSUE_S + 1, ISSUE_DQ = ISSUE_DP + 1;
+// Worker warpgroups: slot g goes to group g % NWG (and to buffer g % NBUF).
+#ifndef GCA_Q_NWG
+#define GCA_Q_NWG GCA_Q_NBUF
+#endif
+constexpr int NWG = GCA_Q_NWG;
+constexpr int PROD_WARP = 4 * NWG, ISSUE_S = PROD_WARP + 1, ISSUE_DP = ISSUE_S + 1, ISSUE_DQ = ISSUE_DP + 1;
 constexpr int WRITER_WARP = (ISSUE_DQ + 1 + 3) / 4 * 4;   // a multiple of 4: warp % 4 = its TMEM lane quarter
 constexpr int NTHREADS = (WRITER_WARP + 4) * 32;
 constexpr int TMEM_COLS = 512;
@@ -380,7 +385,7 @@ __device__ void q_worker(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     for (unsigned m = mask; m; m &= m - 1, ++g) {
       const uint32_t bb = b, pp = bph;
       if (++b == NBUF) { b = 0; bph ^= 1; }
-      if ((int)bb != wg) continue;
+      if ((int)(g % NWG) != wg) continue;
       const int k = __ffs(m) - 1;
       const float w = __shfl_sync(0xffffffffu, my_w, k);
       const float lse = lse_base[k * 64];
@@ -513,7 +518,7 @@ bwd_q_tc_kernel(const __grid_constant__ BwdQParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (warp < 4 * NBUF) q_worker(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
+  if (warp < 4 * NWG) q_worker(p, smem, bars, abort_flag, warp >> 2, warp & 3, lane, tmem_base);
   else if (warp == PROD_WARP) q_producer(p, smem, bars, abort_flag, lane);
   else if (warp >= WRITER_WARP) q_writer(p, bars, abort_flag, warp & 3, lane, tmem_base);
   else if (warp == ISSUE_S) q_issuer<0>(p, smem, bars, abort_flag, lane, tmem_base);

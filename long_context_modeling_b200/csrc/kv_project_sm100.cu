@@ -21,6 +21,12 @@
 // row_scale = 1 / rms(x) from `row_rms_kernel` turns it into pre-norm RMSNorm + q_proj (the norm's
 // gain is folded into W's columns by the caller: RMSNorm(x) W^T = diag(1 / rms) x (W diag(g))^T, so
 // the normalised activations are never written), residual makes it o_proj + residual add.
+//
+// CROSS-ENTROPY mode is the LM head fused with the loss (model/DRT.py:1055-1064, inference /
+// evaluation): the 128 x 256 logit tiles stay in tensor memory, the epilogue reduces each row's tile
+// to (maximum, sum of exponentials) and picks out the target's logit, and `ce_combine_kernel`
+// merges a row's column tiles into  loss = logsumexp - logit[target].  The (rows x 50,265) logits
+// -- 13 GB in bf16 at 8 x 16K tokens -- are never written.
 #include "gca_common.cuh"
 #include "sm100_ptx.cuh"
 #include "tc_common.cuh"
@@ -57,7 +63,11 @@ struct ProjParams {
   const __nv_bfloat16* residual;      // or nullptr
   const float* row_scale;             // or nullptr
   long long out_stride, res_stride;   // elements between rows
-  int ncols;                          // output columns (multiple of 16)
+  int ncols;                          // output columns (multiple of 16; any number in cross-entropy mode)
+  // cross-entropy mode (linear mode with ce_part != nullptr): the logits never leave tensor memory
+  float2* ce_part;                    // (M, tiles_n): running maximum and sum of exp2 of the row's logits in that column tile
+  float* ce_target;                   // (M): the target's logit, scaled by log2(e)
+  const long long* targets;           // (M) class ids; negative = ignored row
 };
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1) {
@@ -162,6 +172,42 @@ kv_project_append_kernel(const __grid_constant__ ProjParams p) {
       tc_fence_after();
       const long long m = (long long)tm * BM + row_in_tile;
       const bool live = m < p.M;
+      if (p.nmat == 1 && p.ce_part) {
+        // cross-entropy mode: per row, the maximum and the sum of exponentials of this column
+        // tile's logits (base 2, logits scaled by log2 e) and the target's logit if it lies here
+        const float sc = ((live && p.row_scale) ? p.row_scale[m] : 1.0f) * GCA_LOG2E;
+        const int cols = min(BN, p.ncols - tn * BN);
+        const long long tgt = live ? p.targets[m] - (long long)tn * BN : -1;
+        float mx = -INFINITY, sum = 0.f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < cols; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld_32x32b_x16(tlane + ab * BN + c0, v);
+          tmem_ld_wait();
+          float x[16];
+          float pm = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            x[i] = (c0 + i < cols) ? __uint_as_float(v[i]) * sc : -INFINITY;
+            pm = fmaxf(pm, x[i]);
+          }
+          if (tgt >= c0 && tgt < c0 + 16) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (tgt == c0 + i) p.ce_target[m] = x[i];
+          }
+          const float nm = fmaxf(mx, pm);
+          float ps = 0.f;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) ps += ex2_approx(x[i] - nm);
+          sum = sum * ex2_approx(mx - nm) + ps;
+          mx = nm;
+        }
+        if (live) p.ce_part[m * p.tiles_n + tn] = make_float2(mx, sum);
+        tc_fence_before();
+        mbar_arrive(&bars[ACC_EMPTY + ab]);
+        continue;
+      }
       if (p.nmat == 1) {
         // linear mode: out = row_scale * acc + residual, 16 columns per pass
         const float sc = (live && p.row_scale) ? p.row_scale[m] : 1.0f;
@@ -270,7 +316,62 @@ __global__ void row_rms_kernel(const __nv_bfloat16* __restrict__ x, float* __res
   if (lane == 0) row_scale[m] = rsqrtf(acc / (float)D + eps);
 }
 
+// loss[m] = ln(sum_j exp(logit_j)) - logit_target from the per-tile partials (base 2 inside); ignored rows: 0.
+__global__ void ce_combine_kernel(const float2* __restrict__ part, const float* __restrict__ tlogit, const long long* __restrict__ targets,
+                                  float* __restrict__ loss, float* __restrict__ lse_out, long long M, int tiles) {
+  const long long m = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (m >= M) return;
+  const int lane = threadIdx.x & 31;
+  float mx = -INFINITY, sum = 0.f;
+  for (int t = lane; t < tiles; t += 32) {
+    const float2 v = part[m * tiles + t];
+    const float nm = fmaxf(mx, v.x);
+    sum = sum * (mx == -INFINITY ? 0.f : exp2f(mx - nm)) + v.y * (v.x == -INFINITY ? 0.f : exp2f(v.x - nm));
+    mx = nm;
+  }
+#pragma unroll
+  for (int of = 16; of > 0; of >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, mx, of), os = __shfl_xor_sync(0xffffffffu, sum, of);
+    const float nm = fmaxf(mx, om);
+    sum = sum * (mx == -INFINITY ? 0.f : exp2f(mx - nm)) + os * (om == -INFINITY ? 0.f : exp2f(om - nm));
+    mx = nm;
+  }
+  if (lane == 0) {
+    const float lse2 = mx + log2f(sum);                        // base-2 log-sum-exp of the scaled logits
+    const float ln2 = 0.6931471805599453f;
+    if (lse_out) lse_out[m] = lse2 * ln2;
+    loss[m] = targets[m] >= 0 ? (lse2 - tlogit[m]) * ln2 : 0.f;
+  }
+}
+
 }  // namespace
+
+int launch_linear_ce(const LinearCeArgs& a, int sms, cudaStream_t stream) {
+  ProjParams p;
+  int rc;
+  if ((rc = make_matrix_map(&p.tm_x, a.x, a.M, a.K, a.x_stride, BM)) || (rc = make_matrix_map(&p.tm_wk, a.w, a.N, a.K, a.w_stride, BN)))
+    return rc;
+  p.tm_wv = p.tm_wk;
+  p.k_cache = p.v_cache = nullptr; p.status = a.status; p.cache_bs = 0;
+  p.M = (int)a.M; p.D = a.K; p.rows_per_seq = 1; p.pos = 0; p.zero_landmark = 0;
+  p.tiles_m = (int)((a.M + BM - 1) / BM); p.tiles_n = (a.N + BN - 1) / BN; p.nmat = 1;
+  p.out = nullptr; p.residual = nullptr; p.row_scale = a.row_scale; p.out_stride = p.res_stride = 0; p.ncols = a.N;
+  // workspace: partials (M, tiles_n) float2, then the target logits (M) float
+  p.ce_part = reinterpret_cast<float2*>(a.workspace);
+  p.ce_target = reinterpret_cast<float*>(p.ce_part + a.M * p.tiles_n);
+  p.targets = reinterpret_cast<const long long*>(a.targets);
+  const long long total = (long long)p.tiles_m * p.tiles_n;
+  if (total >= (1ll << 31) || a.M >= (1ll << 31)) return GCA_ERR_TOO_LARGE;
+  if (total == 0) return 0;
+  GCA_CUDA_CHECK(cudaFuncSetAttribute(kv_project_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  const unsigned grid = (unsigned)(total < sms ? total : sms);
+  kv_project_append_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(p);
+  GCA_CUDA_CHECK(cudaGetLastError());
+  const int warps = 8;
+  ce_combine_kernel<<<(unsigned)((a.M + warps - 1) / warps), warps * 32, 0, stream>>>(p.ce_part, p.ce_target, p.targets, a.loss, a.lse, a.M,
+                                                                                    p.tiles_n);
+  return (int)cudaGetLastError();
+}
 
 int launch_row_rms(const RowRmsArgs& a, cudaStream_t stream) {
   if (a.M == 0) return 0;
@@ -291,6 +392,7 @@ int launch_linear(const LinearArgs& a, int sms, cudaStream_t stream) {
   p.tiles_m = (int)((a.M + BM - 1) / BM); p.tiles_n = (a.N + BN - 1) / BN; p.nmat = 1;
   p.out = (__nv_bfloat16*)a.out; p.residual = (const __nv_bfloat16*)a.residual; p.row_scale = a.row_scale;
   p.out_stride = a.out_stride; p.res_stride = a.residual_stride; p.ncols = a.N;
+  p.ce_part = nullptr; p.ce_target = nullptr; p.targets = nullptr;
   const long long total = (long long)p.tiles_m * p.tiles_n;
   if (total >= (1ll << 31) || a.M >= (1ll << 31)) return GCA_ERR_TOO_LARGE;
   if (total == 0) return 0;
@@ -313,6 +415,7 @@ int launch_kv_project_append(const KvProjectArgs& a, int sms, cudaStream_t strea
   p.zero_landmark = a.zero_landmark;
   p.tiles_m = (int)((M + BM - 1) / BM); p.tiles_n = a.D / BN; p.nmat = 2;
   p.out = nullptr; p.residual = nullptr; p.row_scale = nullptr; p.out_stride = p.res_stride = 0; p.ncols = a.D;
+  p.ce_part = nullptr; p.ce_target = nullptr; p.targets = nullptr;
   const long long total = (long long)p.tiles_m * p.tiles_n * 2;
   if (total >= (1ll << 31)) return GCA_ERR_TOO_LARGE;
   GCA_CUDA_CHECK(cudaFuncSetAttribute(kv_project_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));

@@ -315,6 +315,13 @@ class DRTMinimal(nn.Module):
         # pieces of 8,192 rows whose logits are recomputed in the backward instead of being kept.
         from torch.utils.checkpoint import checkpoint
         x = x.reshape(-1, x.shape[-1])
+        if not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 64 == 0:
+            # evaluation: final norm + LM head + cross-entropy as one GEMM whose logits never leave tensor
+            # memory (the norm's gain folded into the tied embedding matrix, 1 / rms applied per row)
+            from . import fused_ops
+            w = fused_ops.fold_gain(self.embed_tokens.weight.detach(), self.norm.weight.detach())
+            losses = fused_ops.linear_cross_entropy(x, w, target, row_scale=fused_ops.row_rms(x, self.norm.eps))
+            return losses.sum() / (target != -100).sum().clamp(min=1)
 
         def piece(xp, tp):
             return F.cross_entropy(self.logits(xp).float(), tp, ignore_index=-100, reduction="sum")

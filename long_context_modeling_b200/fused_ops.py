@@ -42,7 +42,7 @@ def row_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     out = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
     a = _lib.RowRmsArgs()
     a.x, a.row_scale, a.M, a.x_stride, a.D, a.eps = x2.data_ptr(), out.data_ptr(), x2.shape[0], x2.stride(0), x2.shape[1], eps
-    _lib.check(_lib.lib().gca_row_rms(C.byref(a), _stream()), "gca_row_rms")
+    _lib.call("gca_row_rms", C.byref(a), _stream())
     return out
 
 
@@ -73,7 +73,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, row_scale: Optional[torch.Tens
             raise ValueError("linear: row_scale must be contiguous float32 with one value per row")
         a.row_scale = row_scale.data_ptr()
     a.status = _status(x.device).data_ptr()
-    _lib.check(_lib.lib().gca_linear(C.byref(a), _stream()), "gca_linear")
+    _lib.call("gca_linear", C.byref(a), _stream())
     return out
 
 
@@ -111,5 +111,38 @@ def window_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int
         a.q_stride[i], a.o_stride[i], a.k_stride[i], a.v_stride[i] = q.stride(i), out.stride(i), k.stride(i), v.stride(i)
     a.N, a.Hq, a.Hkv, a.Sq, a.T, a.window = n, hq, hkv, sq, t_len, int(window)
     a.sm_scale = float(sm_scale) if sm_scale is not None else 0.125
-    _lib.check(_lib.lib().gca_window_decode(C.byref(a), _stream()), "gca_window_decode")
+    _lib.call("gca_window_decode", C.byref(a), _stream())
     return out
+
+
+def linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor,
+                         row_scale: Optional[torch.Tensor] = None, return_lse: bool = False):
+    """Per-row cross-entropy of ``x @ weight.T`` against ``targets`` without materialising the logits
+    (``lm_head`` + ``CrossEntropyLoss(ignore_index=-100, reduction='none')``, ``model/DRT.py:1055-1064``;
+    forward only).  x (..., K) bf16, weight (V, K) bf16, targets (...) int64 with negative = ignored.
+    Returns float32 losses shaped like ``targets`` (and the natural-log logsumexp when asked)."""
+    _require(x, "linear_cross_entropy")
+    _require(weight, "linear_cross_entropy weight")
+    x2 = _rows(x)
+    t = targets.reshape(-1).to(torch.int64).contiguous()
+    if t.numel() != x2.shape[0] or not t.is_cuda:
+        raise ValueError("linear_cross_entropy: one int64 target per row, on the device")
+    m, v = x2.shape[0], weight.shape[0]
+    loss = torch.empty(m, dtype=torch.float32, device=x.device)
+    lse = torch.empty(m, dtype=torch.float32, device=x.device) if return_lse else None
+    lib = _lib.lib()
+    nbytes = lib.gca_linear_ce_workspace_bytes(m, v)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    a = _lib.LinearCeArgs()
+    a.x, a.w, a.targets, a.loss = x2.data_ptr(), weight.data_ptr(), t.data_ptr(), loss.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+    a.M, a.N, a.K, a.x_stride, a.w_stride = m, v, x2.shape[1], x2.stride(0), weight.stride(0)
+    if row_scale is not None:
+        if row_scale.dtype != torch.float32 or row_scale.numel() != m or not row_scale.is_contiguous():
+            raise ValueError("linear_cross_entropy: row_scale must be contiguous float32 with one value per row")
+        a.row_scale = row_scale.data_ptr()
+    a.status = _status(x.device).data_ptr()
+    _lib.call("gca_linear_cross_entropy", C.byref(a), _stream())
+    loss = loss.view(targets.shape)
+    return (loss, lse.view(targets.shape)) if return_lse else loss

@@ -149,7 +149,7 @@ class _GcaIndexed(torch.autograd.Function):
         lse = torch.empty((n * j, hq, k, s), dtype=torch.float32, device=q5.device)
         with torch.cuda.device(q5.device):
             a = _fwd_args(q5, kc5, vc5, idx32, w32, out, lse, sm_scale, off_by_one, algo)
-            _lib.check(_lib.lib().gca_fwd(C.byref(a), _stream()), "gca_fwd")
+            _lib.call("gca_fwd", C.byref(a), _stream())
         _maybe_check(q5.device)
         ctx.save_for_backward(q5, kc5, vc5, idx32, w32, lse)
         ctx.sm_scale, ctx.off_by_one, ctx.algo = sm_scale, off_by_one, algo
@@ -206,7 +206,7 @@ def _backward_call(q5, kc5, vc5, idx32, w32, dout, lse, sm_scale, off_by_one, al
         a.dv_stride = _lib.strides4(*dv.stride()[:4])
         a.workspace = (ws.data_ptr() + 255) // 256 * 256
         a.workspace_bytes = ws.numel() - 256
-        _lib.check(_lib.lib().gca_bwd_stages(C.byref(a), stages, _stream()), "gca_bwd_stages")
+        _lib.call("gca_bwd_stages", C.byref(a), stages, _stream())
     _maybe_check(q5.device)
     if bufs is None and (stages & BWD_STAGE_ALL) != BWD_STAGE_ALL:
         return dq, dk, dv, dw, ws
@@ -298,11 +298,11 @@ def _forward_nograd(q5, kc5, vc5, idx32, w32, sm_scale, off_by_one, algo) -> tor
     with torch.cuda.device(q5.device):
         a = _fwd_args(q5, kc5, vc5, idx32, w32, out, None, sm_scale, off_by_one, algo)
         if s <= 16:
-            _lib.check(_lib.lib().gca_decode(C.byref(a), _stream()), "gca_decode")
+            _lib.call("gca_decode", C.byref(a), _stream())
         else:
             if s != 64 and algo == ALGO_AUTO:
                 a.algo = ALGO_SIMT
-            _lib.check(_lib.lib().gca_fwd(C.byref(a), _stream()), "gca_fwd")
+            _lib.call("gca_fwd", C.byref(a), _stream())
     _maybe_check(q5.device)
     return out
 
@@ -347,5 +347,5 @@ def gca_forward_with_lse(q, k_cache, v_cache, indices, weights, sm_scale, *, off
     lse = torch.empty((n * j, hq, idx32.shape[-1], s), dtype=torch.float32, device=q5.device)
     with torch.cuda.device(q5.device):
         a = _fwd_args(q5, kc5, vc5, idx32, w32, out, lse, sm_scale, off_by_one, algo)
-        _lib.check(_lib.lib().gca_fwd(C.byref(a), _stream()), "gca_fwd")
+        _lib.call("gca_fwd", C.byref(a), _stream())
     return out, lse

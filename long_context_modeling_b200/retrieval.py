@@ -96,7 +96,7 @@ def lmk_score_topk(lmk_q: torch.Tensor, lmk_k: torch.Tensor, topk: int, *, q_pos
         nbytes = _lib.lib().lmk_topk_workspace_bytes(C.byref(a))
         ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
         a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
-        _lib.check(_lib.lib().lmk_score_topk(C.byref(a), torch.cuda.current_stream().cuda_stream), "lmk_score_topk")
+        _lib.call("lmk_score_topk", C.byref(a), torch.cuda.current_stream().cuda_stream)
     return Retrieval(keys, indices, scores, weights, n_valid)
 
 
@@ -119,7 +119,7 @@ def merge_topk(keys: torch.Tensor, topk: int) -> Retrieval:
     a.out_scores, a.out_weights, a.out_nvalid = scores.data_ptr(), weights.data_ptr(), n_valid.data_ptr()
     a.R, a.P, a.K = r, keys.shape[-1], int(topk)
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().lmk_topk_merge(C.byref(a), torch.cuda.current_stream().cuda_stream), "lmk_topk_merge")
+        _lib.call("lmk_topk_merge", C.byref(a), torch.cuda.current_stream().cuda_stream)
     return Retrieval(out_keys, indices, scores, weights, n_valid)
 
 

@@ -164,7 +164,7 @@ class PeerExchange:
         handle = (C.c_uint8 * 64)()
         own = C.c_void_p()
         with torch.cuda.device(self.device):
-            _lib.check(lib.lmk_exchange_mailbox_create(self.r_max, self.world, C.byref(own), handle), "lmk_exchange_mailbox_create")
+            _lib.call("lmk_exchange_mailbox_create", self.r_max, self.world, C.byref(own), handle)
         self._own = own.value
         handles = [None] * self.world
         dist.all_gather_object(handles, bytes(handle), group=group)          # host-side swap of the 64-byte handles
@@ -177,7 +177,7 @@ class PeerExchange:
                     continue
                 buf = (C.c_uint8 * 64).from_buffer_copy(h)
                 peer = C.c_void_p()
-                _lib.check(lib.lmk_exchange_mailbox_open(buf, C.byref(peer)), "lmk_exchange_mailbox_open")
+                _lib.call("lmk_exchange_mailbox_open", buf, C.byref(peer))
                 self._peers.append(peer.value)
                 ptrs.append(peer.value)
         self._table = torch.tensor(ptrs, dtype=torch.int64, device=self.device)     # the device array of mailbox pointers
@@ -203,7 +203,7 @@ class PeerExchange:
         a.status = _status(dev).data_ptr()
         a.R, a.K, a.world, a.rank, a.R_max, a.wait_ms = rows, int(topk), self.world, self.rank, self.r_max, self.wait_ms
         with torch.cuda.device(dev):
-            _lib.check(_lib.lib().lmk_topk_exchange(C.byref(a), torch.cuda.current_stream().cuda_stream), "lmk_topk_exchange")
+            _lib.call("lmk_topk_exchange", C.byref(a), torch.cuda.current_stream().cuda_stream)
         return Retrieval(out_keys, indices, scores, weights, n_valid)
 
     def reset(self) -> None:
@@ -212,8 +212,8 @@ class PeerExchange:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         with torch.cuda.device(self.device):
-            _lib.check(_lib.lib().lmk_exchange_mailbox_reset(self._own, self.r_max, self.world,
-                                                             torch.cuda.current_stream().cuda_stream), "lmk_exchange_mailbox_reset")
+            _lib.call("lmk_exchange_mailbox_reset", self._own, self.r_max, self.world,
+                                                             torch.cuda.current_stream().cuda_stream)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
 

@@ -105,3 +105,21 @@ def test_training_step_reaches_every_parameter():
     assert missing == [], missing
     assert model.chunk_k_proj.weight.grad.abs().max().item() > 0
     assert model.encoder[0].mlp.down_proj.weight.grad.abs().max().item() > 0
+
+
+@pytest.mark.gpu
+def test_fused_evaluation_loss_matches_the_unfused_loss():
+    """Evaluation (no autograd, bf16) takes the fused norm + LM head + cross-entropy GEMM; the same model
+    with autograd on takes the chunked torch path: the two losses must agree to bf16 accuracy."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from long_context_modeling_b200 import drt_minimal as D
+    torch.manual_seed(3)
+    cfg = D.DRTConfig(hidden_size=128, num_attention_heads=2, intermediate_size=256, decoder_layers=[1, 1], encoder_layers=1,
+                      vocab_size=1000, chunk_topk=2, slide_window=32, chunk_id=999)
+    model = D.DRTMinimal(cfg).cuda().bfloat16().eval()
+    tok = torch.randint(0, 999, (2, 63 * 5), device="cuda")
+    with torch.no_grad():
+        fused = model(tok, labels=tok)
+    unfused = model(tok, labels=tok)                    # autograd on: the chunked torch cross-entropy
+    assert abs(fused.item() - unfused.item()) <= 2e-2 * abs(unfused.item()), (fused.item(), unfused.item())

@@ -188,3 +188,45 @@ def test_window_decode_reads_strided_caches():
     v = torch.randn(2, 200, 6, 64, generator=g).bfloat16().cuda().transpose(1, 2)
     slopes = torch.full((6,), 0.05).cuda()
     close(F.window_decode(q, k, v, 64, slopes, 0.125), _window_reference(q, k, v, 64, slopes, 0.125))
+
+
+@pytest.mark.parametrize("m,v,k", [(300, 50265, 768), (1, 1000, 64), (129, 257, 128), (2000, 4096, 768)])
+def test_linear_cross_entropy_against_float32(m, v, k):
+    """LM head + cross-entropy without logits in memory, against torch on float32 logits of the same
+    bf16 inputs; ignored rows (target -100) give 0."""
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    import long_context_modeling_b200 as lcm
+    g = torch.Generator().manual_seed(m + v)
+    x = torch.randn(m, k, generator=g).bfloat16().cuda()
+    w = (torch.randn(v, k, generator=g) * (3.0 / k ** 0.5)).bfloat16().cuda()
+    t = torch.randint(0, v, (m,), generator=g).cuda()
+    if m > 4:
+        t[3] = -100
+        t[m - 1] = v - 1
+    loss, lse = F.linear_cross_entropy(x, w, t, return_lse=True)
+    logits = x.float() @ w.float().T
+    ref = torch.nn.functional.cross_entropy(logits, t, reduction="none", ignore_index=-100)
+    assert torch.allclose(loss, ref, rtol=2e-4, atol=2e-4), (loss - ref).abs().max().item()
+    assert torch.allclose(lse, torch.logsumexp(logits, -1), rtol=2e-5, atol=2e-4)
+    if m > 4:
+        assert loss[3].item() == 0.0
+    assert lcm.read_status() == 0
+
+
+def test_linear_cross_entropy_with_rmsnorm_scale_and_bad_target():
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(2, 70, 128, generator=g) * 2).bfloat16().cuda()
+    w = (torch.randn(513, 128, generator=g) / 4).bfloat16().cuda()
+    t = torch.randint(0, 513, (2, 70), generator=g).cuda()
+    sc = F.row_rms(x, 1e-5)
+    loss = F.linear_cross_entropy(x, w, t, row_scale=sc)
+    xf = x.float()
+    logits = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)) @ w.float().T
+    ref = torch.nn.functional.cross_entropy(logits.view(-1, 513), t.view(-1), reduction="none").view(2, 70)
+    assert loss.shape == (2, 70)
+    assert torch.allclose(loss, ref, rtol=3e-4, atol=3e-4)
+    t[0, 0] = 513                                   # outside the vocabulary: the loss says so
+    assert torch.isnan(F.linear_cross_entropy(x, w, t)[0, 0])
