@@ -191,7 +191,7 @@ kv_project_append_kernel(const __grid_constant__ ProjParams p) {
             x[i] = (c0 + i < cols) ? __uint_as_float(v[i]) * sc : -INFINITY;
             pm = fmaxf(pm, x[i]);
           }
-          if (tgt >= c0 && tgt < c0 + 16) {
+          if (tgt >= c0 && tgt < c0 + 16 && tgt < cols) {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               if (tgt == c0 + i) p.ce_target[m] = x[i];
