@@ -709,7 +709,7 @@ def decode_arm(args):
                     "h2d_bytes_per_step": q_host.numel() * 2 + idx_host.numel() * 4 + w_host.numel() * 4,
                     "d2h_bytes_per_step": q_host.numel() * 2, "ms_per_step": ms_e2e},
             "gpu_launches": steps,
-            "roofline": {"kernel": "decode_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+            "roofline": {"kernel": "decode_rows_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy bandwidth",
                          "traffic": None, "algorithmic_bytes_per_launch": nbytes, "us_per_launch": ms_k * 1e3},
             "device_status": lcm.read_status()}

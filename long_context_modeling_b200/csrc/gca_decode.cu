@@ -1,6 +1,8 @@
 // GCA forward for a handful of query rows (autoregressive decode: 1 or 2 rows per
 // sequence).  The work is a stream over K retrieved chunks x (K tile + V tile) per
-// (sequence, kv head): HBM-bound, no tensor cores.  Blocks are persistent (one per SM: each
+// (sequence, kv head): HBM-bound, no tensor cores.  Two kernels: up to four rows per kv head (the
+// model's decode step) take `decode_rows_kernel`, which streams the tiles through registers (see
+// its comment); 5-16 rows take `decode_kernel`, described here.  Blocks are persistent (one per SM: each
 // warp keeps a K and a V tile, 128 KB per block) and walk the (n, j, kv head) items; each warp
 // owns whole slots and fetches its slot's two 8 KB tiles with two TMA copies (retrieved chunk
 // index = tensor coordinate) onto two mbarriers of its own, so nothing is staged through
@@ -216,6 +218,154 @@ decode_kernel(const __grid_constant__ DecParams p) {
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, GCA_STATUS_TIMEOUT);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Up to four query rows per kv head (the model's decode step: one row): no shared-memory staging at
+// all.  One CTA per (sequence, query chunk, kv head), one warp per retrieved slot (slots k = warp,
+// warp + 8, ...).  A warp load covers FOUR key rows of the slot's tile (8 lanes x 16 bytes per
+// 128-byte row); every 8-lane group owns a stream of 16 keys with its own online-softmax state, the
+// loads run four steps ahead of the arithmetic in registers, and nothing is waited for except the
+// data itself.  Registers are capped so that three CTAs share an SM: 32 sequences x
+// 12 heads = 384 CTAs run as one wave, where the persistent TMA kernel below needs a ragged third
+// round of its 148 CTAs.  The four streams of a warp, then the slots in slot order, are merged in a
+// fixed order: the result does not depend on scheduling.
+struct RowState { float m, l, acc[8]; };
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void merge_state(RowState& a, float m2, float l2, const float* acc2) {
+  const float m = fmaxf(a.m, m2);
+  const float ca = (a.m == -INFINITY) ? 0.f : ex2f(a.m - m), cb = (m2 == -INFINITY) ? 0.f : ex2f(m2 - m);
+  a.l = a.l * ca + l2 * cb;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a.acc[i] = a.acc[i] * ca + acc2[i] * cb;
+  a.m = m;
+}
+
+template <int R>
+__global__ void __launch_bounds__(NWARPS * 32, R == 1 ? 3 : (R == 2 ? 2 : 1))
+decode_rows_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                   const int32_t* __restrict__ indices, const float* __restrict__ weights, __nv_bfloat16* __restrict__ out,
+                   int32_t* status, const Geom g) {
+  __shared__ float part[NWARPS][R][64];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
+  const int item = blockIdx.x;
+  const int zj = item / g.Hkv, hk = item - zj * g.Hkv;
+  const int n = zj / g.J, j = zj - n * g.J;
+  const int rows = g.G * g.S;                                    // <= R
+  const float c2 = g.sm_scale * GCA_LOG2E;
+  float qv[R][8];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qv[r][e] = 0.f;
+    if (r < rows) {
+      const int gi = r / g.S, s = r - gi * g.S;
+      const uint4 t = *reinterpret_cast<const uint4*>(q + n * g.qs[0] + j * g.qs[1] + (hk * g.G + gi) * g.qs[2] + s * g.qs[3] + sub * 8);
+      const unsigned w4[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { qv[r][2 * e] = bf_lo(w4[e]) * c2; qv[r][2 * e + 1] = bf_hi(w4[e]) * c2; }
+    }
+  }
+  float o[R][8];                                 // this warp's weighted outputs, 8 columns per lane
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[r][e] = 0.f;
+  for (int k = warp; k < g.K; k += NWARPS) {
+    const int idx = indices[(long long)zj * g.K + k];
+    if (idx < 0) continue;                                       // padding slot (warp-uniform)
+    if (idx >= g.C) { if (status && lane == 0) atomicOr(status, GCA_STATUS_BAD_INDEX); continue; }
+    const float w = weights[(long long)zj * g.K + k];
+    const __nv_bfloat16* kb = kc + n * g.ks[0] + idx * g.ks[1] + hk * g.ks[3] + sub * 8;
+    const __nv_bfloat16* vb = vc + n * g.vs[0] + idx * g.vs[1] + hk * g.vs[3] + sub * 8;
+    RowState st[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      st[r].m = -INFINITY; st[r].l = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) st[r].acc[e] = 0.f;
+    }
+    // 16 steps of 4 keys; the loads run four steps ahead of the arithmetic in registers
+    uint4 kq[4], vq[4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      kq[s] = *reinterpret_cast<const uint4*>(kb + (s * 4 + grp) * g.ks[2]);
+      vq[s] = *reinterpret_cast<const uint4*>(vb + (s * 4 + grp) * g.vs[2]);
+    }
+#pragma unroll 1
+    for (int b4 = 0; b4 < 16; b4 += 4) {
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const uint4 kcur = kq[s], vcur = vq[s];
+        if (b4 + 4 < 16) {
+          const int key = (b4 + 4 + s) * 4 + grp;
+          kq[s] = *reinterpret_cast<const uint4*>(kb + key * g.ks[2]);
+          vq[s] = *reinterpret_cast<const uint4*>(vb + key * g.vs[2]);
+        }
+        const unsigned kw[4] = {kcur.x, kcur.y, kcur.z, kcur.w}, vw[4] = {vcur.x, vcur.y, vcur.z, vcur.w};
+        float kf[8], vf[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { kf[2 * e] = bf_lo(kw[e]); kf[2 * e + 1] = bf_hi(kw[e]); vf[2 * e] = bf_lo(vw[e]); vf[2 * e + 1] = bf_hi(vw[e]); }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float sc = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) sc = fmaf(qv[r][e], kf[e], sc);
+          sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+          sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+          sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+          const float m = fmaxf(st[r].m, sc);
+          const float corr = ex2f(st[r].m - m), pr = ex2f(sc - m);
+          st[r].l = st[r].l * corr + pr;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) st[r].acc[e] = fmaf(pr, vf[e], st[r].acc[e] * corr);
+          st[r].m = m;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+      for (int of = 8; of <= 16; of <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, st[r].m, of), l2 = __shfl_xor_sync(0xffffffffu, st[r].l, of);
+        float a2[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a2[e] = __shfl_xor_sync(0xffffffffu, st[r].acc[e], of);
+        merge_state(st[r], m2, l2, a2);
+      }
+      // softmax over this slot's 64 keys (optionally with the off-by-one term), weighted by w
+      float mm = st[r].m, ll = st[r].l;
+      if (g.off_by_one > 0.f) {
+        const float m1 = fmaxf(mm, 0.f);
+        ll = ll * ex2f(mm - m1) + g.off_by_one * ex2f(-m1);
+        const float sc1 = ex2f(mm - m1);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) st[r].acc[e] *= sc1;
+      }
+      const float f = w / ll;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[r][e] = fmaf(st[r].acc[e], f, o[r][e]);
+    }
+  }
+  if (grp == 0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part[warp][r][sub * 8 + e] = o[r][e];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < rows * 64; i += NWARPS * 32) {
+    const int r = i >> 6, d = i & 63;
+    float t = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < NWARPS; ++wv) t += part[wv][r][d];
+    const int gi = r / g.S, s = r - gi * g.S;
+    out[n * g.os[0] + j * g.os[1] + (hk * g.G + gi) * g.os[2] + s * g.os[3] + d] = __float2bfloat16_rn(t);
+  }
+}
+
 template <int R>
 int launch_decode_r(const DecParams& p, int blocks, int sms, cudaStream_t stream) {
   const size_t smem = NWARPS * 2 * TILE_BYTES + 2 * (1 + NWARPS) * R * T * sizeof(float) + 256 + 1024;
@@ -230,9 +380,6 @@ int launch_decode_r(const DecParams& p, int blocks, int sms, cudaStream_t stream
 int launch_decode(const GcaFwdArgs& a, int sms, cudaStream_t stream) {
   if (a.dtype != GCA_BF16) return GCA_ERR_ALGO;
   DecParams p;
-  int rc;
-  if ((rc = make_tile_map_5d(&p.tm_k, a.k_cache, 64, 64, a.Hkv, a.C, a.N, a.k_stride[2], a.k_stride[3], a.k_stride[1], a.k_stride[0], 1, true))) return rc;
-  if ((rc = make_tile_map_5d(&p.tm_v, a.v_cache, 64, 64, a.Hkv, a.C, a.N, a.v_stride[2], a.v_stride[3], a.v_stride[1], a.v_stride[0], 1, false))) return rc;
   p.q = (const __nv_bfloat16*)a.q; p.indices = a.indices; p.weights = a.weights;
   p.out = (__nv_bfloat16*)a.out; p.status = a.status;
   Geom& g = p.g;
@@ -242,9 +389,22 @@ int launch_decode(const GcaFwdArgs& a, int sms, cudaStream_t stream) {
   g.sm_scale = a.sm_scale; g.off_by_one = a.off_by_one;
   const int rows = g.G * a.S;
   const int blocks = a.N * a.J * a.Hkv;
-  if (rows <= 1) return launch_decode_r<1>(p, blocks, sms, stream);
-  if (rows <= 2) return launch_decode_r<2>(p, blocks, sms, stream);
-  if (rows <= 4) return launch_decode_r<4>(p, blocks, sms, stream);
+  // up to four rows: the register-streaming kernel (needs 16-byte aligned 128-byte head rows, which
+  // the argument checks of the entry point guarantee for q and the caches)
+  bool vec16 = true;                  // every 64-element head row of q and the caches starts on a 16-byte boundary
+  for (int i = 0; i < 4; ++i) vec16 = vec16 && a.q_stride[i] % 8 == 0 && a.k_stride[i] % 8 == 0 && a.v_stride[i] % 8 == 0;
+  vec16 = vec16 && ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k_cache) | reinterpret_cast<uintptr_t>(a.v_cache)) & 15u) == 0;
+  if (rows <= 4 && blocks > 0 && a.D == 64 && a.L == 64 && vec16) {
+    auto q = (const __nv_bfloat16*)a.q; auto kc = (const __nv_bfloat16*)a.k_cache; auto vc = (const __nv_bfloat16*)a.v_cache;
+    auto out = (__nv_bfloat16*)a.out;
+    if (rows <= 1) decode_rows_kernel<1><<<(unsigned)blocks, NWARPS * 32, 0, stream>>>(q, kc, vc, a.indices, a.weights, out, a.status, g);
+    else if (rows <= 2) decode_rows_kernel<2><<<(unsigned)blocks, NWARPS * 32, 0, stream>>>(q, kc, vc, a.indices, a.weights, out, a.status, g);
+    else decode_rows_kernel<4><<<(unsigned)blocks, NWARPS * 32, 0, stream>>>(q, kc, vc, a.indices, a.weights, out, a.status, g);
+    return (int)cudaGetLastError();
+  }
+  int rc;
+  if ((rc = make_tile_map_5d(&p.tm_k, a.k_cache, 64, 64, a.Hkv, a.C, a.N, a.k_stride[2], a.k_stride[3], a.k_stride[1], a.k_stride[0], 1, true))) return rc;
+  if ((rc = make_tile_map_5d(&p.tm_v, a.v_cache, 64, 64, a.Hkv, a.C, a.N, a.v_stride[2], a.v_stride[3], a.v_stride[1], a.v_stride[0], 1, false))) return rc;
   if (rows <= 8) return launch_decode_r<8>(p, blocks, sms, stream);
   if (rows <= 16) return launch_decode_r<16>(p, blocks, sms, stream);
   return GCA_ERR_ALGO;
