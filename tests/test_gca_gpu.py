@@ -145,6 +145,26 @@ def test_decode_dynamic_k_and_padding(lcm):
         assert rel(out, ref) <= BF16_REL
 
 
+@pytest.mark.parametrize("hq,hkv,sq,k,obo", [(12, 12, 1, 11, False), (8, 4, 1, 8, False), (8, 4, 2, 5, True), (4, 1, 1, 3, True),
+                                            (6, 6, 3, 9, False), (2, 2, 4, 2, False)])
+def test_decode_rows_kernel_shapes(lcm, hq, hkv, sq, k, obo):
+    """The register-streaming decode kernel (up to four rows per kv head): more slots than warps, padding
+    slots, grouped-query heads, two to four rows, the off-by-one softmax, against the oracle."""
+    g = torch.Generator().manual_seed(100 * hq + 10 * sq + k)
+    n, c = 3, 20
+    kc = torch.randn(n, c, 64, hkv * 64, generator=g).bfloat16()
+    vc = torch.randn(n, c, 64, hkv * 64, generator=g).bfloat16()
+    q = torch.randn(n, 1, hq, sq, 64, generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(c, generator=g)[:k] for _ in range(n)]).view(n, 1, k)
+    idx[0, 0, k - 1] = -1                                    # a padding slot
+    w = torch.softmax(torch.randn(n, 1, k, generator=g), -1)
+    ref = G.gca_indexed(q.float(), kc.float(), vc.float(), idx, w, 0.125, off_by_one=1.0 if obo else 0.0)
+    out = lcm.gca_indexed_nograd(q.cuda(), kc.cuda(), vc.cuda(), idx.cuda(), w.cuda(), 0.125, softmax_off_by_one=obo)
+    assert out.shape == ref.shape
+    assert rel(out, ref) <= BF16_REL
+    assert lcm.read_status() == 0
+
+
 @pytest.mark.parametrize("algo", ALGOS)
 def test_indexed_equals_gathered_and_scatter_add(lcm, algo):
     """gca_indexed(cache, idx) == attention(gather(cache, idx)); dK/dV into the cache equal
