@@ -66,6 +66,13 @@ static_assert(NBUF == 2 || NBUF == 3, "score buffers");
 #endif
 constexpr int NWG = GCA_Q_NWG;              // measured: 2 groups 0.653 ms, 3 groups 0.55-0.57 ms
 static_assert(NWG >= 2 && NWG <= NBUF, "worker groups");
+// The issuers probe the NEXT slot's barriers before they issue the current slot's MMAs, so that the
+// probes' shared-memory round trip runs under the issue: 0.562 -> 0.538 ms.  (The same in the
+// forward and in the kv-major kernel was measured slower: 0.434 against 0.414 and 0.634 against
+// 0.613 ms.)
+#ifndef GCA_Q_PREPROBE
+#define GCA_Q_PREPROBE 1
+#endif
 constexpr int PROD_WARP = 4 * NWG, ISSUE_S = PROD_WARP + 1, ISSUE_DP = ISSUE_S + 1, ISSUE_DQ = ISSUE_DP + 1;
 constexpr int WRITER_WARP = (ISSUE_DQ + 1 + 3) / 4 * 4;   // a multiple of 4: warp % 4 = its TMEM lane quarter
 constexpr int NTHREADS = (WRITER_WARP + 4) * 32;
@@ -252,17 +259,27 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
     const uint32_t kt1 = t.share ? 0u : TILE16;            // head B's K / V tile inside the stage
     if (ROLE != 2) ok = mbar_wait_warp(&bars[QDO_FULL + ub], uph, abort_flag, lane);
     else ok = mbar_wait_warp(&bars[ACC_EMPTY + ub], uph ^ 1, abort_flag, lane);
+    bool pre_a = false, pre_b = false;           // early probe results for the coming slot
     for (int i = 0; i < nv && ok; ++i, ++g) {
       const uint32_t tbuf = tmem_base + b * BUF_COLS;
       if (ROLE != 2) {
         if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 0, g);
         // the tile has landed AND the buffer's previous contents (the packed dS of slot g - NBUF)
         // have been consumed: both barriers are probed at once (one shared-memory round trip)
-        ok = mbar_wait_warp2(&bars[(ROLE == 0 ? K_FULL : V_FULL) + ring.st], ring.ph, &bars[BUF_FREE + b], bph ^ 1, abort_flag, lane);
+        // (probed while the previous slot's MMAs were being issued, when there was one in this unit)
+        ok = mbar_wait_warp2_probed(&bars[(ROLE == 0 ? K_FULL : V_FULL) + ring.st], ring.ph, pre_a, &bars[BUF_FREE + b], bph ^ 1,
+                                    pre_b, abort_flag);
         if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 3, g);
         if (!ok) break;
         if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 1, g);
         tc_fence_after();
+        pre_a = pre_b = false;
+        if (GCA_Q_PREPROBE && i + 1 < nv) {              // the next slot's two barriers
+          const uint32_t nst = ring.st + 1 == (uint32_t)ring.depth ? 0u : ring.st + 1, nph = nst ? ring.ph : ring.ph ^ 1;
+          const uint32_t nb = b + 1 == NBUF ? 0u : b + 1, nbph = nb ? bph : bph ^ 1;
+          pre_a = mbar_test_wait(&bars[(ROLE == 0 ? K_FULL : V_FULL) + nst], nph);
+          pre_b = mbar_test_wait(&bars[BUF_FREE + nb], nbph ^ 1);
+        }
         const uint64_t a = dQDO + ub * 2 * PAIR16 + (ROLE == 0 ? 0u : PAIR16);          // Q pair | dO pair
         const uint64_t bt = (ROLE == 0 ? dK : dV) + ring.st * PAIR16;
         const uint32_t d = tbuf + (ROLE == 0 ? 0u : COL_DPT);
@@ -278,10 +295,15 @@ __device__ void q_issuer(const BwdQParams& p, uint8_t* smem, uint64_t* bars, vol
         if (i == nv - 1) umma_commit_elect(&bars[QDO_EMPTY + ub]);    // expects both issuers' commits
         if (lane == 0 && ROLE == 0) GCA_TRACE_BUF(p.prof, 2, g);
       } else {
-        ok = mbar_wait_warp(&bars[PDS_FULL + b], bph, abort_flag, lane);
+        ok = mbar_wait_warp2_probed(&bars[PDS_FULL + b], bph, pre_a, &bars[PDS_FULL + b], bph, true, abort_flag);
         if (!ok) break;
         if (lane == 0) GCA_TRACE_BUF(p.prof, 5, g);
         tc_fence_after();
+        pre_a = false;
+        if (GCA_Q_PREPROBE && i + 1 < nv) {
+          const uint32_t nb = b + 1 == NBUF ? 0u : b + 1, nbph = nb ? bph : bph ^ 1;
+          pre_a = mbar_test_wait(&bars[PDS_FULL + nb], nbph);
+        }
         // dQ += dS K_k per head: A = dS from tensor memory (lane = query row, 8 columns per K step
         // of 16 keys), B = the head's K tile read N-contiguous (MN-major)
         const uint32_t acc = tmem_base + COL_DQ + ub * 64;

@@ -113,6 +113,16 @@ __device__ __forceinline__ bool mbar_wait_warp2(uint64_t* bar_a, uint32_t parity
   if (ok && !rb) ok = mbar_wait_bounded(bar_b, parity_b, abort_flag);
   return __all_sync(0xffffffffu, ok);
 }
+// The same when the two probes were made EARLIER (ra, rb: their results): an MMA-issuing warp probes
+// the barriers of its next slot before it issues the current slot's MMAs, so that the probes'
+// shared-memory round trip (~300 cycles while the MMAs saturate shared memory) runs under the issue.
+__device__ __forceinline__ bool mbar_wait_warp2_probed(uint64_t* bar_a, uint32_t parity_a, bool ra, uint64_t* bar_b, uint32_t parity_b,
+                                                       bool rb, volatile int* abort_flag) {
+  bool ok = true;
+  if (!ra) ok = mbar_wait_bounded(bar_a, parity_a, abort_flag);
+  if (ok && !rb) ok = mbar_wait_bounded(bar_b, parity_b, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
 __device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
