@@ -380,7 +380,8 @@ def gpu_arm(args):
                          "local_scan_us": r["roofline"]["us_per_launch"], "local_scan_gbs_per_gpu": r["roofline"]["achieved"],
                          "local_scan_frac_of_hbm_peak": r["roofline"]["frac"], "whole_cache_gbs": r["value"]}
         line["retrieval"] = {"what": "landmark top-8 over 262,144 cached chunks (16M tokens), batch 1, cache sharded by chunk "
-                                     "range over the ranks; CUDA-graph replay of scan + all-gather + merge, max over ranks",
+                                     "range over the ranks; CUDA-graph replay of the local scan + the fused peer-store exchange and merge kernel, "
+                                     "max over ranks (n_gpu_eager_us: the NCCL all-gather path issued from Python)",
                              **sub}
     if rank == 0 and world == 1 and args.triton_ref:
         del dev_sets, fwd_out, bufs
