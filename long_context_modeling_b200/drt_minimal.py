@@ -44,6 +44,10 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .chunk_cache import ChunkKVManager
+try:                                        # optional: the library the reference uses for its windowed self-attention
+    from flash_attn import flash_attn_func as _flash_attn_func
+except Exception:                           # not installed / not loadable: the block-banded torch path below
+    _flash_attn_func = None
 from .modules import RMSNorm, TritonGroupCrossAttention
 from .retrieval import lmk_score_topk, retrieve
 
@@ -146,9 +150,21 @@ class SelfAttention(nn.Module):
             # a later SEGMENT of a long prompt: the cached window of the previous segment goes in front
             # (window and ALiBi bias are relative, so positions need no offset)
             kc, vc = torch.cat([cache[0], k], 2), torch.cat([cache[1], v], 2)
-            qc = torch.cat([torch.zeros_like(cache[0]), q], 2)
-            o = windowed_alibi_attention(qc, kc, vc, self.window, self.slopes)[:, :, -l:]
+            if _flash_attn_func is not None and q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and self.d <= 256:
+                # queries are the LAST l positions of the keys (flash-attn aligns causal mask, window and
+                # ALiBi distances bottom-right)
+                o = _flash_attn_func(q.transpose(1, 2), kc.transpose(1, 2), vc.transpose(1, 2), 0.0, causal=True,
+                                     window_size=(self.window, 0), alibi_slopes=self.slopes.float()).transpose(1, 2)
+            else:
+                qc = torch.cat([torch.zeros_like(cache[0]), q], 2)
+                o = windowed_alibi_attention(qc, kc, vc, self.window, self.slopes)[:, :, -l:]
             new_cache = (kc[:, :, -(self.window + 1):], vc[:, :, -(self.window + 1):])
+        elif cache is None and _flash_attn_func is not None and q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and self.d <= 256:
+            # what the reference itself calls here (model/llama.py:661-683): the flash-attn library's
+            # sliding-window causal attention with ALiBi, forward and backward; (N, L, H, d) layout
+            o = _flash_attn_func(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), 0.0, causal=True,
+                                 window_size=(self.window, 0), alibi_slopes=self.slopes.float()).transpose(1, 2)
+            new_cache = (k[:, :, -(self.window + 1):], v[:, :, -(self.window + 1):]) if use_cache else None
         elif cache is None:
             if torch.is_grad_enabled() and q.requires_grad:
                 # SDPA with an explicit bias keeps the (window x 2 window) score blocks for its backward:
@@ -371,6 +387,18 @@ class DRTMinimal(nn.Module):
         return self.logits(x[:, 0])
 
     @torch.no_grad()
+    def generate_graphed(self, prompt: torch.Tensor, new_tokens: int, fused: bool = False) -> torch.Tensor:
+        """``generate`` with the token steps between two chunk boundaries replayed from a CUDA graph
+        (see ``GraphedDecoder``); boundary steps, and every step while the self-attention window is not
+        full yet, run eagerly.  Same tokens as ``generate``; with ``fused`` the token steps also take the
+        fused projections (bf16 rounding differs slightly from the unfused modules)."""
+        state = DecodeState(self.cfg)
+        logits = self.forward(prompt, state=state)
+        tok = logits[:, -1].argmax(-1)
+        dec = GraphedDecoder(self, state, fused=fused)
+        return torch.cat([prompt, tok.view(-1, 1), dec.run(tok, new_tokens - 1)[:, :new_tokens - 1]], dim=1) if new_tokens > 0 else prompt
+
+    @torch.no_grad()
     def prefill_segmented(self, prompt: torch.Tensor, segment_tokens: int, state: Optional[DecodeState] = None):
         """Prefill a long prompt segment by segment (``segment_tokens`` a multiple of 63), carrying the
         self-attention window and the growing chunk cache between segments, so that activation memory is
@@ -395,3 +423,201 @@ class DRTMinimal(nn.Module):
             out.append(tok.view(-1, 1))
             tok = self.decode_step(tok, state).argmax(-1)
         return torch.cat(out, dim=1)
+
+
+class GraphedDecoder:
+    """Greedy decoding of ``DRTMinimal`` with the launch overhead taken out of the token steps.
+
+    A decode step of the 12-layer body is ~300 small launches; eager PyTorch issues them at ~10 us
+    each, so a step costs ~11 ms while its HBM traffic (weights, 12 self-attention windows, 6 GCA
+    reads) is worth ~0.2 ms.  Between two chunk boundaries (62 token steps) nothing changes shape:
+    the window caches are full, the retrieved chunk ids are fixed, the chunk cache is not appended to.
+    Those steps are captured ONCE per span as a CUDA graph over static buffers -- the token, the
+    self-attention windows (updated in place), the staged lower hidden states of the growing chunk
+    and a device-side slot counter -- and replayed; the next token is produced and consumed on the
+    device, the host only counts.  The boundary step (chunk encoder, cache append, landmark
+    retrieval) runs eagerly through ``DRTMinimal.decode_step`` and invalidates the graph.
+    """
+
+    def __init__(self, model: DRTMinimal, state: DecodeState, fused: bool = False):
+        self.model, self.state = model, state
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.warmed = False
+        self.fused = bool(fused) and self._fusable()
+        if self.fused:
+            self._fold()
+        self.tok = self.stage = self.slot = self.toks = None
+
+    # ---- the fused form of a token step (bf16 on a GPU, no projection biases): per layer the small
+    # operations ride on the library's GEMM -- RMSNorm's row scale in the epilogue of one q|k|v (and one
+    # gate|up) projection whose weights carry the norm's gain, the residual add in the epilogue of o_proj
+    # and down_proj -- and the windowed attention is the library's decode kernel: ~15 launches per layer
+    # instead of ~45.  Off by default: at 32 rows per step the library's GEMM (128 x 256 tiles, one CTA
+    # per tile: 9 busy CTAs for the q|k|v projection) is slower than cuBLAS's small-M kernels, and the
+    # whole step measured 6,500 against 12,008 tokens/s for the plain graphed step at 32 sequences.
+    def _fusable(self) -> bool:
+        m = self.model
+        w = m.embed_tokens.weight
+        return (w.is_cuda and w.dtype == torch.bfloat16 and not m.cfg.attention_bias and m.cfg.head_dim == 64
+                and m.cfg.hidden_size % 64 == 0 and m.cfg.intermediate_size % 64 == 0)
+
+    def _fold(self) -> None:
+        from . import fused_ops as FO
+        self.folded = []
+        layers = list(self.model.lower_layers) + [l for grp in self.model.upper_layers for l in grp]
+        for l in layers:
+            a, mlp = l.self_attn, l.mlp
+            qkv = torch.cat([a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], 0).detach()
+            gu = torch.cat([mlp.gate_proj.weight, mlp.up_proj.weight], 0).detach()
+            self.folded.append((FO.fold_gain(qkv, l.input_layernorm.weight.detach()),
+                                FO.fold_gain(gu, l.post_attention_layernorm.weight.detach()), a.slopes.float().contiguous()))
+
+    def _attn_fused(self, layer, fw, x2, li):
+        from . import fused_ops as FO
+        a = layer.self_attn
+        n, dim = x2.shape
+        qkv = FO.rmsnorm_linear(x2, fw[0], layer.input_layernorm.eps)                      # (N, 3 dim)
+        q, k, v = (qkv[:, i * dim:(i + 1) * dim].view(n, 1, a.h, a.d).transpose(1, 2) for i in range(3))
+        k_old, v_old = self.state.self_attn[li]
+        kc, vc = torch.cat([k_old, k], 2), torch.cat([v_old, v], 2)
+        o = FO.window_decode(q, kc, vc, a.window, fw[2], 1.0 / math.sqrt(a.d))             # (N, H, 1, 64)
+        k_old.copy_(kc[:, :, 1:])
+        v_old.copy_(vc[:, :, 1:])
+        return FO.linear(o.view(n, dim), a.o_proj.weight, residual=x2)                     # x + self_attn(norm(x))
+
+    def _mlp_fused(self, layer, fw, t2, r2):
+        from . import fused_ops as FO
+        gu = FO.rmsnorm_linear(t2, fw[1], layer.post_attention_layernorm.eps)
+        inter = gu.shape[1] // 2
+        h = F.silu(gu[:, :inter]) * gu[:, inter:]
+        return FO.linear(h, layer.mlp.down_proj.weight, residual=r2)                       # r + mlp(norm(t))
+
+    def _hidden_fused(self) -> torch.Tensor:
+        """The final hidden state (N, dim) of one token step on the static buffers, fused form."""
+        m, st = self.model, self.state
+        n = self.tok.shape[0]
+        x = m.embed_tokens(self.tok)                                                        # (N, dim)
+        li = 0
+        for layer in m.lower_layers:
+            x = self._attn_fused(layer, self.folded[li], x, li)
+            x = self._mlp_fused(layer, self.folded[li], x, x)
+            li += 1
+        self.stage.index_copy_(1, self.slot, x.view(n, 1, -1))
+        for g, layers in enumerate(m.upper_layers):
+            idx, w = st.chunks.current_retrieved_indices(g)
+            for layer in layers:
+                r = self._attn_fused(layer, self.folded[li], x, li)
+                if idx is None:
+                    t = r
+                else:                                                                       # r + gca(r)
+                    t = layer.gca.forward_fused(r.view(n, 1, 1, -1), st.chunks.chunk_k, st.chunks.chunk_v, idx.unsqueeze(1), w,
+                                                residual=r.view(n, 1, -1)).view(n, -1)
+                x = self._mlp_fused(layer, self.folded[li], t, r)
+                li += 1
+        return x
+
+    # one token step (not a boundary) on the static buffers; everything it launches is capturable
+    def _step(self) -> None:
+        x = self._hidden_fused() if self.fused else self._hidden_plain()
+        nxt = self.model.logits(x).argmax(-1)
+        self.toks.index_copy_(1, self.slot, nxt.view(-1, 1))
+        self.tok.copy_(nxt)
+        self.slot += 1
+
+    def _hidden_plain(self) -> torch.Tensor:
+        m, st = self.model, self.state
+        x = m.embed_tokens(self.tok.view(-1, 1))
+        li = 0
+        for layer in m.lower_layers:
+            x, kv = layer(x, st.self_attn[li])
+            self._keep(li, kv)
+            li += 1
+        self.stage.index_copy_(1, self.slot, x)
+        for g, layers in enumerate(m.upper_layers):
+            idx, w = st.chunks.current_retrieved_indices(g)
+            for layer in layers:
+                x, kv = layer(x, st.chunks.chunk_k, st.chunks.chunk_v, None if idx is None else idx.unsqueeze(1), w, st.self_attn[li])
+                self._keep(li, kv)
+                li += 1
+        return x[:, 0]
+
+    def _keep(self, li: int, kv) -> None:
+        k_old, v_old = self.state.self_attn[li]
+        k_old.copy_(kv[0])                       # the new window (a view of a fresh concatenation) back into the static buffer
+        v_old.copy_(kv[1])
+
+    def _window_full(self) -> bool:
+        """Every layer's cached window has its final length; the caches become owned, contiguous buffers."""
+        w = self.model.cfg.slide_window + 1
+        caches = self.state.self_attn
+        if not caches or any(c is None or c[0].shape[2] != w for c in caches):
+            return False
+        for i, (k, v) in enumerate(caches):
+            if not (k.is_contiguous() and v.is_contiguous()):
+                caches[i] = (k.contiguous(), v.contiguous())
+        return True
+
+    def _capture(self) -> None:
+        self.graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        if not self.warmed:                        # first capture: one real step on a side stream for lazy initialisations
+            saved = [t.clone() for t in (self.tok, self.slot)] + [t.clone() for c in self.state.self_attn for t in c]
+            with torch.cuda.stream(side):
+                self._step()
+            torch.cuda.current_stream().wait_stream(side)
+            self._restore(saved)
+            self.warmed = True
+        with torch.cuda.graph(self.graph):         # (the previous span's graph and its memory were released at the boundary)
+            self._step()                           # captured, not executed
+
+    def _restore(self, saved) -> None:
+        self.tok.copy_(saved[0]); self.slot.copy_(saved[1])
+        flat = [t for c in self.state.self_attn for t in c]
+        for dst, src in zip(flat, saved[2:]):
+            dst.copy_(src)
+
+    @torch.no_grad()
+    def run(self, token: torch.Tensor, steps: int) -> torch.Tensor:
+        """Decode ``steps`` tokens after ``token`` (N,).  Returns the (N, steps) generated tokens."""
+        m, st, cfg = self.model, self.state, self.model.cfg
+        n = token.shape[0]
+        out = []
+        tok = token
+        done = 0
+        while done < steps:
+            in_chunk = st.position % m.chunk                     # tokens of the current chunk already processed
+            boundary = in_chunk == cfg.enc_chunk_size - 1
+            if boundary or not token.is_cuda or not self._window_full():
+                if self.stage is not None and self.graph is not None and in_chunk > 0 and st.chunks.lower_hidden_states is None:
+                    st.chunks.cache_lower_hidden_states(self.stage[:, :in_chunk].clone())
+                tok = m.decode_step(tok, st).argmax(-1)
+                out.append(tok.view(-1, 1))
+                done += 1
+                self.graph = None                                # the chunk cache / retrieved ids / staging may have changed
+                continue
+            span = min(cfg.enc_chunk_size - 1 - in_chunk, steps - done)
+            if self.tok is None:
+                dim = cfg.hidden_size
+                self.tok = torch.empty_like(tok)
+                self.stage = torch.zeros(n, m.chunk, dim, dtype=m.embed_tokens.weight.dtype, device=tok.device)
+                self.slot = torch.zeros(1, dtype=torch.int64, device=tok.device)
+                self.toks = torch.zeros(n, m.chunk, dtype=torch.int64, device=tok.device)
+            if self.graph is None:
+                # hidden states the manager has already staged for this chunk move into the static buffer
+                staged = st.chunks.lower_hidden_states
+                if staged is not None:
+                    self.stage[:, :staged.shape[1]].copy_(staged)
+                    st.chunks.clear_lower_hidden_states()
+                self.slot.fill_(in_chunk)
+                self.tok.copy_(tok)
+                self._capture()
+            else:
+                self.tok.copy_(tok)
+            for _ in range(span):
+                self.graph.replay()
+            st.position += span
+            out.append(self.toks[:, in_chunk:in_chunk + span].clone())
+            tok = self.tok.clone()
+            done += span
+        return torch.cat(out, dim=1) if out else token.new_zeros((n, 0))

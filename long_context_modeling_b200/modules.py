@@ -154,6 +154,9 @@ class TritonGroupCrossAttention(nn.Module):
         vals = vals.permute(0, 1, 3, 2, 4).reshape(n, -1, self.hidden_size)
         first = s if skip_first else 0
         w = self.o_proj.weight.detach()
+        if first == 0:                           # no skipped chunk: all rows share one row stride, one GEMM
+            fused_ops.linear(vals, w, residual=residual, out=out)
+            return out
         for b in range(n):                       # one GEMM per sequence: a sequence's rows share one row stride
             fused_ops.linear(vals[b], w, residual=None if residual is None else residual[b, first:], out=out[b, first:])
         return out

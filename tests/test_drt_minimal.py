@@ -123,3 +123,89 @@ def test_fused_evaluation_loss_matches_the_unfused_loss():
         fused = model(tok, labels=tok)
     unfused = model(tok, labels=tok)                    # autograd on: the chunked torch cross-entropy
     assert abs(fused.item() - unfused.item()) <= 2e-2 * abs(unfused.item()), (fused.item(), unfused.item())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_graphed_generation_equals_eager_generation(dtype):
+    """The CUDA-graph decoder (token steps between chunk boundaries replayed, boundary steps eager) must
+    produce exactly the tokens of the eager loop: across two chunk boundaries, starting with a full
+    self-attention window."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from long_context_modeling_b200 import drt_minimal as D
+    torch.manual_seed(5)
+    cfg = D.DRTConfig(hidden_size=128, num_attention_heads=2, intermediate_size=256, decoder_layers=[1, 2], encoder_layers=1,
+                      vocab_size=500, chunk_topk=2, slide_window=40, chunk_id=499)
+    model = D.DRTMinimal(cfg).cuda().to(dtype).eval()
+    prompt = torch.randint(0, 499, (2, 63 * 3), device="cuda")
+    eager = model.generate(prompt, 150)
+    graphed = model.generate_graphed(prompt, 150)
+    assert graphed.shape == eager.shape == (2, 63 * 3 + 150)
+    assert torch.equal(graphed, eager)
+
+
+@pytest.mark.gpu
+def test_flash_attn_path_matches_torch_path():
+    """Where the flash-attn library loads, the body's windowed ALiBi self-attention goes through it (as in the
+    reference); the block-banded torch path is the fallback.  Both must agree in bf16: a full sequence, and a
+    later segment whose queries sit behind the cached window."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from long_context_modeling_b200 import drt_minimal as D
+    if D._flash_attn_func is None:
+        pytest.skip("flash-attn is not loadable here")
+    torch.manual_seed(2)
+    cfg = D.DRTConfig(hidden_size=128, num_attention_heads=2, intermediate_size=256, slide_window=48)
+    att = D.SelfAttention(cfg).cuda().bfloat16()
+    x = torch.randn(2, 200, 128, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        o_fa, cache = att(x, use_cache=True)
+        seg_fa, _ = att(x[:, :70], cache=cache)
+        saved, D._flash_attn_func = D._flash_attn_func, None
+        try:
+            o_t, cache_t = att(x, use_cache=True)
+            seg_t, _ = att(x[:, :70], cache=cache_t)
+        finally:
+            D._flash_attn_func = saved
+    assert (o_fa.float() - o_t.float()).abs().max().item() <= 2e-2 * o_t.float().abs().max().item()
+    assert (seg_fa.float() - seg_t.float()).abs().max().item() <= 2e-2 * seg_t.float().abs().max().item()
+
+
+@pytest.mark.gpu
+def test_fused_token_step_matches_the_module_path():
+    """The graphed decoder's fused token step (norm folded into one q|k|v and one gate|up GEMM, residual adds in
+    the o_proj / down_proj epilogues, the library's windowed decode attention and fused GCA sub-layer) against the
+    same step through the unfused modules: same state, same token, logits within bf16 accuracy -- and a whole
+    graphed generation in fused form runs and keeps the device status clean."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import long_context_modeling_b200 as lcm
+    from long_context_modeling_b200 import drt_minimal as D
+    torch.manual_seed(9)
+    cfg = D.DRTConfig(hidden_size=128, num_attention_heads=2, intermediate_size=256, decoder_layers=[1, 2], encoder_layers=1,
+                      vocab_size=500, chunk_topk=2, slide_window=40, chunk_id=499)
+    model = D.DRTMinimal(cfg).cuda().bfloat16().eval()
+    prompt = torch.randint(0, 499, (3, 63 * 3), device="cuda")
+    hidden = []
+    with torch.no_grad():
+        for fused in (False, True):
+            state = D.DecodeState(cfg)
+            tok = model(prompt, state=state)[:, -1].argmax(-1)
+            dec = D.GraphedDecoder(model, state, fused=fused)
+            assert dec.fused == fused
+            assert dec._window_full()
+            dec.tok = tok.clone()
+            dec.stage = torch.zeros(3, model.chunk, 128, dtype=torch.bfloat16, device="cuda")
+            dec.slot = torch.zeros(1, dtype=torch.int64, device="cuda")
+            steps = []
+            for t in range(3):                                   # three consecutive token steps, teacher-forced
+                steps.append(model.logits(dec._hidden_fused() if fused else dec._hidden_plain()).float())
+                dec.tok.copy_(prompt[:, t])
+                dec.slot += 1
+            hidden.append(torch.stack(steps))
+        a, b = hidden
+        assert (a - b).abs().max().item() <= 3e-2 * a.abs().max().item(), ((a - b).abs().max().item(), a.abs().max().item())
+        out = model.generate_graphed(prompt, 100, fused=True)
+    assert out.shape == (3, 63 * 3 + 100)
+    assert lcm.read_status() == 0
