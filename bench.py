@@ -378,7 +378,9 @@ def gpu_arm(args):
             r = measure_retrieval(dev, world, rank, local, per_head, 100, 10, peaks)
             sub[mode] = {"n_gpu_us": r["ms_per_step"] * 1e3, "n_gpu_eager_us": (r["eager_ms_per_step"] or 0) * 1e3,
                          "local_scan_us": r["roofline"]["us_per_launch"], "local_scan_gbs_per_gpu": r["roofline"]["achieved"],
-                         "local_scan_frac_of_hbm_peak": r["roofline"]["frac"], "whole_cache_gbs": r["value"]}
+                         "local_scan_frac_of_hbm_peak": r["roofline"]["frac"], "whole_cache_gbs": r["value"],
+                         "sharded_gca_decode_us": None if r.get("sharded_gca_decode_ms_per_step") is None
+                         else r["sharded_gca_decode_ms_per_step"] * 1e3}
         line["retrieval"] = {"what": "landmark top-8 over 262,144 cached chunks (16M tokens), batch 1, cache sharded by chunk "
                                      "range over the ranks; CUDA-graph replay of the local scan + the fused peer-store exchange and merge kernel, "
                                      "max over ranks (n_gpu_eager_us: the NCCL all-gather path issued from Python)",
@@ -568,6 +570,16 @@ def measure_retrieval(dev, world, rank, local, per_head, steps, warmup, peaks, w
     ms_eager = timed(eager_step, steps, warmup)[0] if world > 1 else None            # NCCL all-gather + merge, issued from Python
     ms_p2p_eager = (timed(lambda: sharded.sharded_lmk_topk(lq, lk, topk, e_total=e_total, head_dim=head_dim, exchange=exchange),
                           steps, warmup)[0] if world > 1 else None)
+    # GCA decode over the winners with the K/V cache sharded the same way: every rank attends over the
+    # retrieved chunks it owns, the (1, 12, 1, 64) partial outputs are summed with one all-reduce
+    ms_gca = None
+    if world > 1 and not per_head:
+        kv_shard = [torch.empty(1, hi - lo, 64, d, dtype=torch.bfloat16, device=dev).normal_(generator=g) for _ in range(2)]
+        qd = torch.randn(1, 1, d // 64, 1, 64, generator=g, device=dev).bfloat16()
+        won = retriever(lq)
+        gi, gw = won.indices.view(1, 1, topk).clone(), won.weights.view(1, 1, topk).clone()
+        ms_gca = timed(lambda: sharded.sharded_gca_decode(qd, kv_shard[0], kv_shard[1], gi, gw, 0.125, e_total=e_total), steps, warmup)[0]
+        del kv_shard
     # the scan + finalize kernels of this rank alone, launch overhead removed
     ms_scan = _graph_time(lambda: lcm.lmk_score_topk(lq, lk, topk, head_dim=head_dim), flush)
     bytes_total = e_total * d * 2
@@ -589,6 +601,7 @@ def measure_retrieval(dev, world, rank, local, per_head, steps, warmup, peaks, w
             "e2e": {"value": bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": lq_host.numel() * 2,
                     "d2h_bytes_per_step": topk * 8 * (d // 64 if head_dim else 1), "ms_per_step": ms_e2e},
             "eager_ms_per_step": ms_eager, "eager_peer_exchange_ms_per_step": ms_p2p_eager,
+            "sharded_gca_decode_ms_per_step": ms_gca,      # owner-computes decode over the sharded K/V cache + all-reduce, eager
             "gpu_launches": (2 if world == 1 else 3) * steps,      # scan, finalize (+ exchange-and-merge)
             "roofline": {"kernel": "lmk_scan_kernel + lmk_finalize_kernel", "bound": "hbm", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
