@@ -1,7 +1,7 @@
 """Stage the reference's own Triton GCA file for use as a SECOND oracle on a GPU box.
 TEST INFRASTRUCTURE ONLY.
 
-    python oracle/make_ref.py [reference checkout, default: the path in $GCA_REFERENCE or /root/reference]
+    python oracle/make_ref.py [reference checkout; default: $GCA_REFERENCE, else a `reference` directory beside this repository]
 
 The reference project ships its GCA operator as one Triton file, ``ltriton/gca.py`` (public
 callables ``attention`` = ``_attention.apply`` at line 844 and ``gca_kv_cache`` at line 846).  That
@@ -26,7 +26,7 @@ DEST = os.path.join(DEST_DIR, "ltriton_gca.py")
 def stage(reference_root: str | None = None) -> str | None:
     """Copy ``<reference_root>/ltriton/gca.py`` to ``oracle/_ref/ltriton_gca.py``.
     Returns the destination path, or None when no reference checkout is present."""
-    root = reference_root or os.environ.get("GCA_REFERENCE", "/root/reference")
+    root = reference_root or os.environ.get("GCA_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     src = os.path.join(root, "ltriton", "gca.py")
     if not os.path.isfile(src):
         return None

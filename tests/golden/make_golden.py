@@ -303,4 +303,6 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    # the reference checkout: argument, else $GCA_REFERENCE, else a `reference` directory beside this repository
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("GCA_REFERENCE") or
+         os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))
