@@ -270,3 +270,26 @@ def test_sharded_exchange_rank_absent_times_out_with_error():
     res = _run_two_ranks("absent", 29630)
     assert res[1][0] == "left"
     assert res[0][0] == "error" and "exchange failed" in res[0][1]
+
+
+def test_fused_ops_refuse_cpu_tensors_and_wrong_dtypes(lib):
+    """The fused projections, the windowed decode attention and the fused LM-head loss exist on the GPU
+    only: CPU tensors raise instead of taking another path, other dtypes are rejected."""
+    import torch
+    from long_context_modeling_b200 import fused_ops as F
+    x = torch.zeros(4, 128, dtype=torch.bfloat16)
+    w = torch.zeros(64, 128, dtype=torch.bfloat16)
+    for call in (lambda: F.row_rms(x, 1e-5), lambda: F.linear(x, w), lambda: F.rmsnorm_linear(x, w, 1e-5),
+                 lambda: F.linear_cross_entropy(x, w, torch.zeros(4, dtype=torch.int64)),
+                 lambda: F.window_decode(torch.zeros(1, 1, 1, 64, dtype=torch.bfloat16), torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16),
+                                         torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16), 4)):
+        with pytest.raises(RuntimeError):
+            call()
+    assert F.fold_gain(torch.ones(3, 4), torch.full((4,), 2.0)).dtype == torch.bfloat16
+    assert float(F.fold_gain(torch.ones(3, 4), torch.full((4,), 2.0))[0, 0]) == 2.0
+
+
+def test_nvtx_switch_and_call_helper(lib):
+    lib.set_nvtx(False)
+    with pytest.raises(ValueError):                      # a negative return code from the library -> ValueError
+        lib.call("gca_linear", None, None)
