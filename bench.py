@@ -972,7 +972,8 @@ def generate_arm(args):
     c = args.cache_chunks
     new_tokens = 256
     state = D.DecodeState(cfg)
-    state.chunks = lcm.ChunkKVManager(group_size=1, capacity=c + 8, zero_landmark=True)
+    # K and V in a virtual-address reservation: memory is mapped behind it as the cache fills, nothing is re-copied
+    state.chunks = lcm.ChunkKVManager(group_size=1, capacity=512, zero_landmark=True, max_chunks=c + 64)
     g = torch.Generator(device=dev).manual_seed(7 + rank)
     piece = 512
     with torch.no_grad():

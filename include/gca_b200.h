@@ -453,6 +453,23 @@ typedef struct WindowDecodeArgs {
 
 int gca_window_decode(const WindowDecodeArgs* args, void* stream);
 
+/* ---- growable device buffers without copies (what the chunk cache of a growing context sits on;
+ * the reference grows its cache with torch.cat on every append, model/DRT.py:87-133) ----
+ *
+ * A range of virtual addresses is reserved once for the largest size the buffer may reach;
+ * physical memory is mapped behind it in multiples of gca_vmem_granularity() as the buffer grows.
+ * Addresses never change, nothing is ever re-copied.  These are the library's only entry points,
+ * besides lmk_exchange_mailbox_create, that obtain device memory, and they do so only when called.
+ *   gca_vmem_reserve(bytes, alignment, &va)            reserve addresses (no memory yet)
+ *   gca_vmem_map(va + off, bytes, device, &handle)     back a sub-range with new physical memory
+ *   gca_vmem_unmap(va + off, bytes, handle)            undo one map (caller has synchronised)
+ *   gca_vmem_free(va, bytes)                           give the addresses back (everything unmapped) */
+size_t gca_vmem_granularity(int device);
+int gca_vmem_reserve(size_t bytes, size_t alignment, void** va_out);
+int gca_vmem_map(void* va, size_t bytes, int device, unsigned long long* handle_out);
+int gca_vmem_unmap(void* va, size_t bytes, unsigned long long handle);
+int gca_vmem_free(void* va, size_t bytes);
+
 const char* gca_strerror(int code);
 int gca_abi_version(void);
 /* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,

@@ -157,6 +157,11 @@ EXPORTS = {
     "lmk_exchange_mailbox_destroy": (C.c_int, [C.c_void_p]),
     "lmk_exchange_mailbox_reset": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "lmk_topk_exchange": (C.c_int, [C.POINTER(LmkExchangeArgs), C.c_void_p]),
+    "gca_vmem_granularity": (C.c_size_t, [C.c_int]),
+    "gca_vmem_reserve": (C.c_int, [C.c_size_t, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "gca_vmem_map": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_ulonglong)]),
+    "gca_vmem_unmap": (C.c_int, [C.c_void_p, C.c_size_t, C.c_ulonglong]),
+    "gca_vmem_free": (C.c_int, [C.c_void_p, C.c_size_t]),
     "gca_strerror": (C.c_char_p, [C.c_int]),
     "gca_abi_version": (C.c_int, []),
     "gca_sizeof": (C.c_size_t, [C.c_int]),

@@ -17,7 +17,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libgca_b200.so")
 
 SOURCES = ["api.cu", "gca_simt.cu", "gca_csr.cu", "gca_decode.cu", "gca_cache.cu", "lmk_topk.cu",
-           "gca_fwd_sm100.cu", "gca_bwd_sm100.cu", "gca_bwd_q_sm100.cu", "gca_bwd_kv_sm100.cu", "kv_project_sm100.cu", "win_attn_decode.cu"]
+           "gca_fwd_sm100.cu", "gca_bwd_sm100.cu", "gca_bwd_q_sm100.cu", "gca_bwd_kv_sm100.cu", "kv_project_sm100.cu", "win_attn_decode.cu", "vmem.cu"]
 
 
 def _stale() -> bool:

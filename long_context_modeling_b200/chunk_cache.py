@@ -3,7 +3,9 @@
 
 The reference grows its cache with ``torch.cat`` on every append (quadratic copying over a
 long generation) and can park K/V on the host.  Here the cache is a preallocated device
-buffer that is filled in place by one CUDA kernel per append and doubled when full; the
+buffer that is filled in place by one CUDA kernel per append and doubled when full -- or, with
+``max_chunks``, a virtual-address reservation behind which memory is mapped as the cache fills, so
+that nothing is ever re-copied and addresses never change (``virtual_memory.py``); the
 kernels read it by chunk index, so ``retrieve_chunks`` (the materialised gather) is needed
 only by callers that want the reference's gathered tensors.  The public methods keep the
 reference's names and argument meaning.
@@ -30,13 +32,18 @@ from . import _lib
 
 class ChunkKVManager:
     def __init__(self, offloading: bool = False, group_size: int = 1, capacity: int = 0,
-                 zero_landmark: bool = False):
+                 zero_landmark: bool = False, max_chunks: int = 0):
         # `offloading` is accepted for signature compatibility; the cache always stays in
         # device memory (180 GB of HBM hold > 50 sequences of 1M tokens at DRT-small scale).
         self._offloading = offloading
         self.group_size = group_size
         self._capacity_hint = capacity
         self._zero_landmark = zero_landmark
+        # max_chunks > 0: K and V live in a virtual-address reservation for that many chunks per sequence
+        # and physical memory is mapped behind it as the cache fills (no copy on growth, ever)
+        self._max_chunks = int(max_chunks)
+        self._vk = self._vv = None
+        self._mapped = 0                             # chunks per sequence that are backed by memory (virtual mode)
         self._k: Optional[torch.Tensor] = None       # (N, capacity, L, HD)
         self._v: Optional[torch.Tensor] = None
         self._lmk: Optional[torch.Tensor] = None     # (N, capacity, Dm)
@@ -87,6 +94,11 @@ class ChunkKVManager:
                 self._gk, self._gv = self._k[:, :self._len].clone(), self._v[:, :self._len].clone()
                 self._glmk = self._lmk[:, :self._len].clone()
             self._k = self._v = self._lmk = None
+            for vb in (self._vk, self._vv):       # a virtual reservation is given back: functional storage from here on
+                if vb is not None:
+                    vb.close()
+            self._vk = self._vv = None
+            self._max_chunks = self._mapped = 0
         if self._gk is None:
             self._gk, self._gv, self._glmk = chunk_k, chunk_v, lmk_embs
         else:
@@ -99,7 +111,46 @@ class ChunkKVManager:
     def past_lmk_embeds(self) -> Optional[torch.Tensor]:
         return self.lmk_embs
 
+    def _capacity(self) -> int:
+        """Chunks per sequence the K / V buffers can hold right now."""
+        if self._vk is not None:
+            return self._mapped
+        return 0 if self._k is None else self._k.shape[1]
+
+    def _reserve_virtual(self, need: int, like_k: torch.Tensor, like_lmk: torch.Tensor) -> None:
+        from .virtual_memory import VirtualBuffer
+        n, _, l, hd = like_k.shape
+        if need > self._max_chunks:
+            raise ValueError(f"the cache was reserved for {self._max_chunks} chunks per sequence, {need} needed")
+        chunk_bytes = l * hd * like_k.element_size()
+        if self._vk is None:
+            self._vk = VirtualBuffer(like_k.device, n, self._max_chunks * chunk_bytes)
+            self._vv = VirtualBuffer(like_k.device, n, self._max_chunks * chunk_bytes)
+            self._k, self._v = self._vk.view(like_k.dtype, (l, hd)), self._vv.view(like_k.dtype, (l, hd))
+        if need > self._mapped:
+            want = max(need, min(self._max_chunks, self._mapped + max(16, self._capacity_hint)))     # grow in steps, not per append
+            self._vv.ensure(want * chunk_bytes)
+            self._mapped = self._vk.ensure(want * chunk_bytes) // chunk_bytes
+        cap = 0 if self._lmk is None else self._lmk.shape[1]
+        if need > cap:                                # landmarks are 1.5 KB per chunk: a plain doubling buffer
+            lmk = torch.empty((n, min(self._max_chunks, max(need, 2 * cap, 64)), like_lmk.shape[-1]), dtype=like_lmk.dtype,
+                              device=like_lmk.device)
+            if self._len:
+                lmk[:, :self._len].copy_(self._lmk[:, :self._len])
+            self._lmk = lmk
+
+    def close(self) -> None:
+        """Give the cache's memory back (virtual mode: unmap and release the reservation)."""
+        self._k = self._v = self._lmk = None
+        for vb in (self._vk, self._vv):
+            if vb is not None:
+                vb.close()
+        self._vk = self._vv = None
+        self._len = self._mapped = 0
+
     def _reserve(self, need: int, like_k: torch.Tensor, like_lmk: torch.Tensor) -> None:
+        if self._max_chunks:
+            return self._reserve_virtual(need, like_k, like_lmk)
         cap = 0 if self._k is None else self._k.shape[1]
         if need <= cap:
             return
@@ -150,7 +201,7 @@ class ChunkKVManager:
         if chunk_k.dtype not in (torch.bfloat16, torch.float32):
             raise ValueError(f"unsupported cache dtype {chunk_k.dtype}")
         a.zero_landmark = 1 if self._zero_landmark else 0
-        a.capacity, a.lmk_capacity = self._k.shape[1], self._lmk.shape[1]
+        a.capacity, a.lmk_capacity = self._capacity(), self._lmk.shape[1]
         with torch.cuda.device(chunk_k.device):
             _lib.call("gca_cache_append", C.byref(a), torch.cuda.current_stream().cuda_stream)
         self._len += count
@@ -181,7 +232,7 @@ class ChunkKVManager:
         a.status = _status(x.device).data_ptr()
         a.cache_batch_stride, a.lmk_cache_batch_stride = self._k.stride(0), self._lmk.stride(0)
         a.N, a.count, a.pos, a.D = n, count, self._len, dim
-        a.capacity, a.lmk_capacity = self._k.shape[1], self._lmk.shape[1]
+        a.capacity, a.lmk_capacity = self._capacity(), self._lmk.shape[1]
         a.zero_landmark = 1 if self._zero_landmark else 0
         with torch.cuda.device(x.device):
             _lib.call("gca_kv_project_append", C.byref(a), torch.cuda.current_stream().cuda_stream)

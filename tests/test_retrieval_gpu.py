@@ -278,3 +278,60 @@ def test_projection_with_append_epilogue_matches_reference_statements(lcm, golde
     err = (big.chunk_k.float().cpu() - want_k).abs().max().item() / want_k.abs().max().item()
     assert err <= 1e-2, err
     assert lcm.read_status() == 0
+
+
+def test_virtual_memory_cache_grows_in_place():
+    """``ChunkKVManager(max_chunks=...)``: K and V sit in a virtual-address reservation, memory is mapped
+    behind it as the cache fills.  Same contents as the doubling buffer after every append (plain and
+    projected), addresses never change, the kernels read it like any cache, the reservation's limit is
+    enforced, and the memory comes back on close()."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import long_context_modeling_b200 as lcm
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(21)
+    n, l, hd = 3, 64, 256                                    # 32 KB per chunk: a 2 MB page holds 64 of them
+    virt = lcm.ChunkKVManager(zero_landmark=True, max_chunks=200, capacity=16)
+    plain = lcm.ChunkKVManager(zero_landmark=True)
+    free0 = torch.cuda.mem_get_info(dev)[0]
+    ptr = None
+    wk = (torch.randn(hd, hd, generator=g) / 16).bfloat16().to(dev)
+    wv = (torch.randn(hd, hd, generator=g) / 16).bfloat16().to(dev)
+    for step in range(7):
+        count = 23 + step
+        if step % 2 == 0:
+            k = torch.randn(n, count, l, hd, generator=g).bfloat16().to(dev)
+            v = torch.randn(n, count, l, hd, generator=g).bfloat16().to(dev)
+            lm = torch.randn(n, count, hd, generator=g).bfloat16().to(dev)
+            virt.append(k, v, lm)
+            plain.append(k, v, lm)
+        else:
+            x = torch.randn(n, count, l, hd, generator=g).bfloat16().to(dev)
+            virt.append_projected(x, wk, wv)
+            plain.append_projected(x, wk, wv)
+        assert len(virt) == len(plain)
+        assert torch.equal(virt.chunk_k, plain.chunk_k) and torch.equal(virt.chunk_v, plain.chunk_v)
+        assert torch.equal(virt.past_lmk_embeds, plain.past_lmk_embeds)
+        if ptr is None:
+            ptr = virt.chunk_k.data_ptr()
+        assert virt.chunk_k.data_ptr() == ptr                # grown in place
+    c = len(virt)
+    assert c == sum(23 + s for s in range(7)) and c <= 200
+    # the kernels read the virtual cache like any other: retrieval + indexed GCA
+    q = torch.randn(n, 1, 4, 1, 64, generator=g).bfloat16().to(dev)
+    lq = torch.randn(n, 1, hd, generator=g).bfloat16().to(dev)
+    r = lcm.lmk_score_topk(lq, virt.past_lmk_embeds, 8)
+    rp = lcm.lmk_score_topk(lq, plain.past_lmk_embeds, 8)
+    assert torch.equal(r.indices, rp.indices)
+    o = lcm.gca_indexed_nograd(q, virt.chunk_k, virt.chunk_v, r.indices, r.weights, 0.125)
+    op = lcm.gca_indexed_nograd(q, plain.chunk_k, plain.chunk_v, rp.indices, rp.weights, 0.125)
+    assert torch.equal(o, op)
+    with pytest.raises(ValueError):                           # beyond the reservation
+        virt.append(torch.zeros(n, 60, l, hd, dtype=torch.bfloat16, device=dev), torch.zeros(n, 60, l, hd, dtype=torch.bfloat16, device=dev),
+                    torch.zeros(n, 60, hd, dtype=torch.bfloat16, device=dev))
+    torch.cuda.synchronize()
+    used = free0 - torch.cuda.mem_get_info(dev)[0]
+    del o, r
+    virt.close()
+    assert len(virt) == 0
+    assert torch.cuda.mem_get_info(dev)[0] > free0 - used + 2 * n * (1 << 21)        # the mapped pages were released
