@@ -1032,6 +1032,8 @@ def generate_arm(args):
                                    f"gpt2-small scale, {c} cached chunks per sequence ({c * 64} positions), top-k 8",
                        "sequences_per_gpu": n_seq, "cache_chunks": c, "new_tokens": new_tokens,
                        "cache_gb_per_gpu": n_seq * c * 64 * cfg.hidden_size * 2 * 2 / 1e9,
+                       "cache_memory": "K / V in a virtual-address reservation grown 2 MB page by page (outside torch's allocator: "
+                                       "not part of max_memory_gb)",
                        "cache_policy": "the chunk cache (GBs per sequence) exceeds the 126 MB L2; every boundary step scans all landmarks",
                        "parallelism": "sequences split over ranks, no collective per token",
                        "note": "the 62 token steps between two chunk boundaries are replayed from a CUDA graph (re-captured after "
