@@ -1004,7 +1004,8 @@ def generate_arm(args):
         eager_ms = ee0.elapsed_time(ee1) / 24
         # ... then the product path: token steps between chunk boundaries replayed from a CUDA graph, boundary
         # steps (chunk encoder, cache append, landmark retrieval over all cached chunks) eager
-        decoder = D.GraphedDecoder(model, state, fused=False)    # the fused token step was measured slower at 32 rows: 6,500 against 12,008 tokens/s
+        # (the fused token step is slower at 32 rows per step: 6,500-7,400 against 11,900-12,000 tokens/s)
+        decoder = D.GraphedDecoder(model, state, fused=args.fused_decode)
         tok = decoder.run(tok, 40)[:, -1].contiguous()      # warm-up across one chunk boundary (not counted)
         if world > 1:
             dist.barrier()
@@ -1066,6 +1067,7 @@ def main():
     ap.add_argument("--cache-chunks", type=int, default=16384,
                     help="generate workload: cached chunks per sequence (16,384 = a 1M-token context)")
     ap.add_argument("--per-head", action="store_true", help="retrieval workload: one 64-d score and top-k per head")
+    ap.add_argument("--fused-decode", action="store_true", help="generate workload: the fused form of the graphed token step")
     ap.add_argument("--n-seq", type=int, default=N_SEQ,
                     help="sequences per GPU (default: the DRT-16K batch of 8; smaller values are for profiling captures)")
     args = ap.parse_args()

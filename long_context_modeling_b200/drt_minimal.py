@@ -452,9 +452,9 @@ class GraphedDecoder:
     # operations ride on the library's GEMM -- RMSNorm's row scale in the epilogue of one q|k|v (and one
     # gate|up) projection whose weights carry the norm's gain, the residual add in the epilogue of o_proj
     # and down_proj -- and the windowed attention is the library's decode kernel: ~15 launches per layer
-    # instead of ~45.  Off by default: at 32 rows per step the library's GEMM (128 x 256 tiles, one CTA
-    # per tile: 9 busy CTAs for the q|k|v projection) is slower than cuBLAS's small-M kernels, and the
-    # whole step measured 6,500 against 12,008 tokens/s for the plain graphed step at 32 sequences.
+    # instead of ~45.  Off by default: at 32 rows per step it measured 6,500 tokens/s with the library's
+    # GEMM (128 x 256 tiles, one CTA per tile: 9 busy CTAs for the q|k|v projection) and 7,400 with the
+    # small-row products on cuBLAS, against 12,000 for the plain graphed step at 32 sequences.
     def _fusable(self) -> bool:
         m = self.model
         w = m.embed_tokens.weight
@@ -472,25 +472,43 @@ class GraphedDecoder:
             self.folded.append((FO.fold_gain(qkv, l.input_layernorm.weight.detach()),
                                 FO.fold_gain(gu, l.post_attention_layernorm.weight.detach()), a.slopes.float().contiguous()))
 
+    # With few rows (a decode step has one per sequence) the library's 128 x 256-tile GEMM keeps only a
+    # handful of CTAs busy, so below SMALL_M rows the products go to cuBLAS (whose small-M kernels split
+    # the work finer) and the fusion that remains is algebraic: one q|k|v and one gate|up product with
+    # the norm's gain folded into the weights, 1 / rms applied to the product's rows.
+    SMALL_M = 128
+
+    def _norm_linear(self, x2, folded_w, eps):
+        from . import fused_ops as FO
+        if x2.shape[0] >= self.SMALL_M:
+            return FO.rmsnorm_linear(x2, folded_w, eps)
+        return F.linear(x2, folded_w) * FO.row_rms(x2, eps).to(x2.dtype).unsqueeze(1)
+
+    def _linear_residual(self, x2, w, res):
+        from . import fused_ops as FO
+        if x2.shape[0] >= self.SMALL_M:
+            return FO.linear(x2, w, residual=res)
+        return torch.addmm(res, x2, w.t())
+
     def _attn_fused(self, layer, fw, x2, li):
         from . import fused_ops as FO
         a = layer.self_attn
         n, dim = x2.shape
-        qkv = FO.rmsnorm_linear(x2, fw[0], layer.input_layernorm.eps)                      # (N, 3 dim)
+        qkv = self._norm_linear(x2, fw[0], layer.input_layernorm.eps)                      # (N, 3 dim)
         q, k, v = (qkv[:, i * dim:(i + 1) * dim].view(n, 1, a.h, a.d).transpose(1, 2) for i in range(3))
         k_old, v_old = self.state.self_attn[li]
         kc, vc = torch.cat([k_old, k], 2), torch.cat([v_old, v], 2)
         o = FO.window_decode(q, kc, vc, a.window, fw[2], 1.0 / math.sqrt(a.d))             # (N, H, 1, 64)
         k_old.copy_(kc[:, :, 1:])
         v_old.copy_(vc[:, :, 1:])
-        return FO.linear(o.view(n, dim), a.o_proj.weight, residual=x2)                     # x + self_attn(norm(x))
+        return self._linear_residual(o.view(n, dim), a.o_proj.weight, x2)                  # x + self_attn(norm(x))
 
     def _mlp_fused(self, layer, fw, t2, r2):
         from . import fused_ops as FO
-        gu = FO.rmsnorm_linear(t2, fw[1], layer.post_attention_layernorm.eps)
+        gu = self._norm_linear(t2, fw[1], layer.post_attention_layernorm.eps)
         inter = gu.shape[1] // 2
         h = F.silu(gu[:, :inter]) * gu[:, inter:]
-        return FO.linear(h, layer.mlp.down_proj.weight, residual=r2)                       # r + mlp(norm(t))
+        return self._linear_residual(h, layer.mlp.down_proj.weight, r2)                    # r + mlp(norm(t))
 
     def _hidden_fused(self) -> torch.Tensor:
         """The final hidden state (N, dim) of one token step on the static buffers, fused form."""
@@ -509,9 +527,12 @@ class GraphedDecoder:
                 r = self._attn_fused(layer, self.folded[li], x, li)
                 if idx is None:
                     t = r
-                else:                                                                       # r + gca(r)
+                elif n >= self.SMALL_M:                                                     # r + gca(r)
                     t = layer.gca.forward_fused(r.view(n, 1, 1, -1), st.chunks.chunk_k, st.chunks.chunk_v, idx.unsqueeze(1), w,
                                                 residual=r.view(n, 1, -1)).view(n, -1)
+                else:
+                    t = r + layer.gca.forward_indexed(r.view(n, 1, 1, -1), st.chunks.chunk_k, st.chunks.chunk_v, idx.unsqueeze(1),
+                                                      w).view(n, -1)
                 x = self._mlp_fused(layer, self.folded[li], t, r)
                 li += 1
         return x
