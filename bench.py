@@ -1004,8 +1004,8 @@ def generate_arm(args):
         eager_ms = ee0.elapsed_time(ee1) / 24
         # ... then the product path: token steps between chunk boundaries replayed from a CUDA graph, boundary
         # steps (chunk encoder, cache append, landmark retrieval over all cached chunks) eager
-        # (the fused token step is slower at 32 rows per step: 6,500-7,400 against 11,900-12,000 tokens/s)
-        decoder = D.GraphedDecoder(model, state, fused=args.fused_decode)
+        # fused token step by default (21,100 tokens/s; the plain graphed step through the unfused modules: 14,700)
+        decoder = D.GraphedDecoder(model, state, fused=not args.plain_decode)
         tok = decoder.run(tok, 40)[:, -1].contiguous()      # warm-up across one chunk boundary (not counted)
         if world > 1:
             dist.barrier()
@@ -1038,7 +1038,9 @@ def generate_arm(args):
                        "cache_policy": "the chunk cache (GBs per sequence) exceeds the 126 MB L2; every boundary step scans all landmarks",
                        "parallelism": "sequences split over ranks, no collective per token",
                        "note": "the 62 token steps between two chunk boundaries are replayed from a CUDA graph (re-captured after "
-                               "every boundary, inside the timed region); boundary steps run eagerly",
+                               "every boundary, inside the timed region); boundary steps run eagerly; token step: "
+                               + ("unfused modules" if args.plain_decode else "fused (one q|k|v and one gate|up product with the norm folded in, "
+                                  "windows moved on in place)"),
                        "eager_ms_per_step": eager_ms},
             "clocks": clocks, "device_status": lcm.read_status(),
             "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
@@ -1067,7 +1069,7 @@ def main():
     ap.add_argument("--cache-chunks", type=int, default=16384,
                     help="generate workload: cached chunks per sequence (16,384 = a 1M-token context)")
     ap.add_argument("--per-head", action="store_true", help="retrieval workload: one 64-d score and top-k per head")
-    ap.add_argument("--fused-decode", action="store_true", help="generate workload: the fused form of the graphed token step")
+    ap.add_argument("--plain-decode", action="store_true", help="generate workload: graphed token steps through the unfused modules")
     ap.add_argument("--n-seq", type=int, default=N_SEQ,
                     help="sequences per GPU (default: the DRT-16K batch of 8; smaller values are for profiling captures)")
     args = ap.parse_args()

@@ -453,6 +453,21 @@ typedef struct WindowDecodeArgs {
 
 int gca_window_decode(const WindowDecodeArgs* args, void* stream);
 
+/* The cached window moved on by one position, in place: every (n, head) block of T rows (64 bf16 each,
+ * contiguous: position stride 64) drops its oldest row and takes the new position's row at the end
+ * (what the reference's KV cache does with torch.cat and a slice).  k_window / v_window (N, H, T, 64)
+ * with strides (n, head) in elements; k_new / v_new (N, H, 64) rows with strides (n, head); T <= 640. */
+typedef struct WindowAppendArgs {
+  void* k_window;
+  void* v_window;
+  const void* k_new;
+  const void* v_new;
+  int64_t window_stride[2], new_stride[2];
+  int32_t N, H, T;
+} WindowAppendArgs;
+
+int gca_window_shift_append(const WindowAppendArgs* args, void* stream);
+
 /* ---- growable device buffers without copies (what the chunk cache of a growing context sits on;
  * the reference grows its cache with torch.cat on every append, model/DRT.py:87-133) ----
  *
@@ -473,7 +488,7 @@ int gca_vmem_free(void* va, size_t bytes);
 const char* gca_strerror(int code);
 int gca_abi_version(void);
 /* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,
- * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs, 7 RowRmsArgs, 8 LinearArgs, 9 WindowDecodeArgs, 10 LinearCeArgs): lets a foreign-language binding verify
+ * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs, 7 RowRmsArgs, 8 LinearArgs, 9 WindowDecodeArgs, 10 LinearCeArgs, 11 WindowAppendArgs): lets a foreign-language binding verify
  * its struct layout before the first call. */
 size_t gca_sizeof(int which);
 

@@ -133,6 +133,11 @@ class LinearCeArgs(C.Structure):
         ("x_stride", C.c_int64), ("w_stride", C.c_int64), ("workspace_bytes", C.c_int64), ("N", C.c_int32), ("K", C.c_int32),
     ]
 
+
+class WindowAppendArgs(C.Structure):
+    _fields_ = [("k_window", C.c_void_p), ("v_window", C.c_void_p), ("k_new", C.c_void_p), ("v_new", C.c_void_p),
+                ("window_stride", C.c_int64 * 2), ("new_stride", C.c_int64 * 2), ("N", C.c_int32), ("H", C.c_int32), ("T", C.c_int32)]
+
 EXPORTS = {
     "gca_fwd": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
     "gca_decode": (C.c_int, [C.POINTER(GcaFwdArgs), C.c_void_p]),
@@ -148,6 +153,7 @@ EXPORTS = {
     "gca_row_rms": (C.c_int, [C.POINTER(RowRmsArgs), C.c_void_p]),
     "gca_linear": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "gca_window_decode": (C.c_int, [C.POINTER(WindowDecodeArgs), C.c_void_p]),
+    "gca_window_shift_append": (C.c_int, [C.POINTER(WindowAppendArgs), C.c_void_p]),
     "gca_linear_ce_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "gca_linear_cross_entropy": (C.c_int, [C.POINTER(LinearCeArgs), C.c_void_p]),
     "lmk_exchange_mailbox_bytes": (C.c_size_t, [C.c_int, C.c_int]),
@@ -186,7 +192,7 @@ def lib() -> C.CDLL:
         if handle.gca_abi_version() != ABI_VERSION:
             raise RuntimeError("libgca_b200.so has an unexpected ABI version")
         for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs, LmkExchangeArgs,
-                                       KvProjectArgs, RowRmsArgs, LinearArgs, WindowDecodeArgs, LinearCeArgs)):
+                                       KvProjectArgs, RowRmsArgs, LinearArgs, WindowDecodeArgs, LinearCeArgs, WindowAppendArgs)):
             if handle.gca_sizeof(which) != C.sizeof(struct):
                 raise RuntimeError(f"struct layout mismatch for {struct.__name__}: "
                                    f"library {handle.gca_sizeof(which)} vs binding {C.sizeof(struct)}")

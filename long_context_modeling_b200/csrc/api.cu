@@ -17,6 +17,7 @@ int launch_row_rms(const RowRmsArgs& a, cudaStream_t stream);
 int launch_linear(const LinearArgs& a, int sms, cudaStream_t stream);
 int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream);
 int launch_linear_ce(const LinearCeArgs& a, int sms, cudaStream_t stream);
+int launch_window_shift_append(const WindowAppendArgs& a, cudaStream_t stream);
 
 DeviceScope::DeviceScope(const void* device_ptr) {
   cudaPointerAttributes at;
@@ -119,6 +120,7 @@ size_t gca_sizeof(int which) {
     case 8: return sizeof(LinearArgs);
     case 9: return sizeof(WindowDecodeArgs);
     case 10: return sizeof(LinearCeArgs);
+    case 11: return sizeof(WindowAppendArgs);
     default: return 0;
   }
 }
@@ -363,6 +365,19 @@ int gca_linear_cross_entropy(const LinearCeArgs* a, void* stream) {
                                   (size_t)a->M * sizeof(float), (cudaStream_t)stream);
   if (e != cudaSuccess) return (int)e;
   return gca::launch_linear_ce(*a, gca::sm_count(scope.dev), (cudaStream_t)stream);
+}
+
+int gca_window_shift_append(const WindowAppendArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (!a->k_window || !a->v_window || !a->k_new || !a->v_new) return GCA_ERR_NULL;
+  if (a->N < 0 || a->H <= 0 || a->T < 1 || a->T > 640) return GCA_ERR_SHAPE;
+  for (int i = 0; i < 2; ++i)
+    if (a->window_stride[i] % 8 || a->new_stride[i] % 8) return GCA_ERR_STRIDE;
+  if (!aligned16(a->k_window) || !aligned16(a->v_window) || !aligned16(a->k_new) || !aligned16(a->v_new)) return GCA_ERR_ALIGN;
+  if (a->N == 0) return 0;
+  gca::DeviceScope scope(a->k_window);
+  if (scope.rc) return scope.rc;
+  return gca::launch_window_shift_append(*a, (cudaStream_t)stream);
 }
 
 int gca_window_decode(const WindowDecodeArgs* a, void* stream) {

@@ -180,7 +180,47 @@ win_decode_kernel(const WinParams p) {
   }
 }
 
+// The cached window of one decode step, moved on IN PLACE: every (sequence, head) block of T rows drops
+// its oldest row and takes the new position's row at the end.  One CTA owns one block of K or V,
+// reads it whole into registers (T <= 16 x 256 rows of 128 bytes... 16 bytes per thread and pass),
+// synchronises, and writes it back one row down: no second buffer, no concatenation, 2 x T x 128 bytes of
+// traffic per block (the torch.cat + copy it replaces moves twice that through slower kernels).
+constexpr int SHIFT_THREADS = 256, SHIFT_MAX_VEC = 20;        // 16-byte vectors per thread: blocks of up to 640 rows
+__global__ void __launch_bounds__(SHIFT_THREADS)
+window_shift_append_kernel(__nv_bfloat16* __restrict__ kwin, __nv_bfloat16* __restrict__ vwin, const __nv_bfloat16* __restrict__ knew,
+                           const __nv_bfloat16* __restrict__ vnew, int H, int T, long long ws0, long long ws1, long long ns0,
+                           long long ns1) {
+  const bool is_v = blockIdx.y != 0;
+  const int n = blockIdx.x / H, h = blockIdx.x - n * H;
+  uint4* win = reinterpret_cast<uint4*>((is_v ? vwin : kwin) + n * ws0 + h * ws1);     // T rows x 8 vectors, contiguous
+  const uint4* fresh = reinterpret_cast<const uint4*>((is_v ? vnew : knew) + n * ns0 + h * ns1);
+  const int total = T * 8;                        // vectors in the block
+  uint4 r[SHIFT_MAX_VEC];
+#pragma unroll
+  for (int i = 0; i < SHIFT_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * SHIFT_THREADS + 8;          // the vector one ROW further on
+    if (v < total) r[i] = win[v];
+    else if (v < total + 8) r[i] = fresh[v - total];            // the last row comes from the new position
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < SHIFT_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * SHIFT_THREADS;
+    if (v < total) win[v] = r[i];
+  }
+}
+
 }  // namespace
+
+int launch_window_shift_append(const WindowAppendArgs& a, cudaStream_t stream) {
+  if (a.T * 8 > SHIFT_THREADS * SHIFT_MAX_VEC) return GCA_ERR_SHAPE;
+  const dim3 grid((unsigned)(a.N * a.H), 2);
+  if (grid.x == 0) return 0;
+  window_shift_append_kernel<<<grid, SHIFT_THREADS, 0, stream>>>((__nv_bfloat16*)a.k_window, (__nv_bfloat16*)a.v_window,
+                                                                  (const __nv_bfloat16*)a.k_new, (const __nv_bfloat16*)a.v_new, a.H, a.T,
+                                                                  a.window_stride[0], a.window_stride[1], a.new_stride[0], a.new_stride[1]);
+  return (int)cudaGetLastError();
+}
 
 int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream) {
   WinParams p;

@@ -139,6 +139,7 @@ class SelfAttention(nn.Module):
         self.v_proj = nn.Linear(cfg.hidden_size, cfg.hidden_size, bias=cfg.attention_bias)
         self.o_proj = nn.Linear(cfg.hidden_size, cfg.hidden_size, bias=cfg.attention_bias)
         self.register_buffer("slopes", alibi_slopes(self.h), persistent=False)
+        self.inplace_window = False        # set by GraphedDecoder: a full cached window is updated in place while decoding
 
     def forward(self, x: torch.Tensor, cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, use_cache: bool = False):
         n, l, _ = x.shape
@@ -177,6 +178,15 @@ class SelfAttention(nn.Module):
         else:                                                    # a few new positions against the cached window
             kc, vc = torch.cat([cache[0], k], 2), torch.cat([cache[1], v], 2)
             t = kc.shape[2]
+            if (self.inplace_window and l == 1 and q.dtype == torch.bfloat16 and q.is_cuda and self.d == 64
+                    and not torch.is_grad_enabled() and cache[0].shape[2] == self.window + 1 and cache[0].is_contiguous()
+                    and cache[1].is_contiguous()):
+                # a full window moves on IN PLACE (oldest row out, the new position's row in: one kernel instead of
+                # concatenation + copy), then the library's decode kernel attends over it
+                from . import fused_ops
+                fused_ops.window_shift_append(cache[0], cache[1], k, v)
+                o = fused_ops.window_decode(q, cache[0], cache[1], self.window, self.slopes.float().contiguous(), 1.0 / math.sqrt(self.d))
+                return self.o_proj(o.transpose(1, 2).reshape(n, l, -1)), cache
             if q.dtype == torch.bfloat16 and q.is_cuda and l <= 4 and self.d == 64 and not torch.is_grad_enabled():
                 # the library's decode kernel for windowed ALiBi attention (flash_attn_with_kvcache in the reference)
                 from . import fused_ops
@@ -452,9 +462,13 @@ class GraphedDecoder:
     # operations ride on the library's GEMM -- RMSNorm's row scale in the epilogue of one q|k|v (and one
     # gate|up) projection whose weights carry the norm's gain, the residual add in the epilogue of o_proj
     # and down_proj -- and the windowed attention is the library's decode kernel: ~15 launches per layer
-    # instead of ~45.  Off by default: at 32 rows per step it measured 6,500 tokens/s with the library's
-    # GEMM (128 x 256 tiles, one CTA per tile: 9 busy CTAs for the q|k|v projection) and 7,400 with the
-    # small-row products on cuBLAS, against 12,000 for the plain graphed step at 32 sequences.
+    # instead of ~45.  At 32 sequences and a 1M-token cache: 21,100 tokens/s, against 14,700 for the
+    # graphed step through the unfused modules and 5,500 eager.  (Two things had hidden that gain at first:
+    # with the library's 128 x 256-tile GEMM on 32 rows -- 9 busy CTAs for the q|k|v projection -- the step
+    # ran at 6,500 tokens/s, hence cuBLAS below SMALL_M rows; and concatenating the cached window with a
+    # strided view of the projection output took torch's slow generic copy, 100 us per layer, hence the
+    # in-place window update.)  Off by default in `generate_graphed` because its bf16 rounding differs
+    # from the unfused modules'.
     def _fusable(self) -> bool:
         m = self.model
         w = m.embed_tokens.weight
@@ -497,10 +511,8 @@ class GraphedDecoder:
         qkv = self._norm_linear(x2, fw[0], layer.input_layernorm.eps)                      # (N, 3 dim)
         q, k, v = (qkv[:, i * dim:(i + 1) * dim].view(n, 1, a.h, a.d).transpose(1, 2) for i in range(3))
         k_old, v_old = self.state.self_attn[li]
-        kc, vc = torch.cat([k_old, k], 2), torch.cat([v_old, v], 2)
-        o = FO.window_decode(q, kc, vc, a.window, fw[2], 1.0 / math.sqrt(a.d))             # (N, H, 1, 64)
-        k_old.copy_(kc[:, :, 1:])
-        v_old.copy_(vc[:, :, 1:])
+        FO.window_shift_append(k_old, v_old, k, v)                                         # in place: oldest row out, new row in
+        o = FO.window_decode(q, k_old, v_old, a.window, fw[2], 1.0 / math.sqrt(a.d))       # (N, H, 1, 64)
         return self._linear_residual(o.view(n, dim), a.o_proj.weight, x2)                  # x + self_attn(norm(x))
 
     def _mlp_fused(self, layer, fw, t2, r2):
@@ -539,7 +551,14 @@ class GraphedDecoder:
 
     # one token step (not a boundary) on the static buffers; everything it launches is capturable
     def _step(self) -> None:
-        x = self._hidden_fused() if self.fused else self._hidden_plain()
+        attns = [l.self_attn for l in self.model.lower_layers] + [l.self_attn for grp in self.model.upper_layers for l in grp]
+        for a in attns:
+            a.inplace_window = True
+        try:
+            x = self._hidden_fused() if self.fused else self._hidden_plain()
+        finally:
+            for a in attns:
+                a.inplace_window = False
         nxt = self.model.logits(x).argmax(-1)
         self.toks.index_copy_(1, self.slot, nxt.view(-1, 1))
         self.tok.copy_(nxt)
@@ -564,6 +583,8 @@ class GraphedDecoder:
 
     def _keep(self, li: int, kv) -> None:
         k_old, v_old = self.state.self_attn[li]
+        if kv[0] is k_old:                       # the window was moved on in place
+            return
         k_old.copy_(kv[0])                       # the new window (a view of a fresh concatenation) back into the static buffer
         v_old.copy_(kv[1])
 

@@ -146,3 +146,25 @@ def linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.T
     _lib.call("gca_linear_cross_entropy", C.byref(a), _stream())
     loss = loss.view(targets.shape)
     return (loss, lse.view(targets.shape)) if return_lse else loss
+
+
+def window_shift_append(k_window: torch.Tensor, v_window: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor) -> None:
+    """Move a full cached window on by one position IN PLACE: every (n, head) block of ``k_window`` /
+    ``v_window`` (N, H, T, 64; the T x 64 block contiguous) drops its oldest row and takes the row of
+    ``k_new`` / ``v_new`` (N, H, 1, 64) or (N, H, 64) at the end -- the reference's ``torch.cat`` + slice of
+    its KV cache without a second buffer."""
+    for t, name in ((k_window, "k_window"), (v_window, "v_window"), (k_new, "k_new"), (v_new, "v_new")):
+        _require(t, f"window_shift_append {name}")
+    n, h, t_len, d = k_window.shape
+    if d != 64 or v_window.shape != k_window.shape or k_window.stride(3) != 1 or k_window.stride(2) != 64 or \
+            v_window.stride(3) != 1 or v_window.stride(2) != 64 or v_window.stride()[:2] != k_window.stride()[:2]:
+        raise ValueError("window_shift_append: windows must be (N, H, T, 64) with contiguous (T, 64) blocks and equal strides")
+    kn, vn = k_new.reshape(n, h, 64) if k_new.dim() == 4 else k_new, v_new.reshape(n, h, 64) if v_new.dim() == 4 else v_new
+    if kn.stride(2) != 1 or vn.stride(2) != 1 or kn.stride()[:2] != vn.stride()[:2]:
+        raise ValueError("window_shift_append: new rows must have a contiguous head dimension and equal strides")
+    a = _lib.WindowAppendArgs()
+    a.k_window, a.v_window, a.k_new, a.v_new = k_window.data_ptr(), v_window.data_ptr(), kn.data_ptr(), vn.data_ptr()
+    a.window_stride[0], a.window_stride[1] = k_window.stride(0), k_window.stride(1)
+    a.new_stride[0], a.new_stride[1] = kn.stride(0), kn.stride(1)
+    a.N, a.H, a.T = n, h, t_len
+    _lib.call("gca_window_shift_append", C.byref(a), _stream())

@@ -230,3 +230,23 @@ def test_linear_cross_entropy_with_rmsnorm_scale_and_bad_target():
     assert torch.allclose(loss, ref, rtol=3e-4, atol=3e-4)
     t[0, 0] = 513                                   # outside the vocabulary: the loss says so
     assert torch.isnan(F.linear_cross_entropy(x, w, t)[0, 0])
+
+
+@pytest.mark.parametrize("n,h,t", [(2, 3, 513), (1, 1, 1), (3, 2, 41), (2, 12, 640)])
+def test_window_shift_append_in_place(n, h, t):
+    """Oldest row out, new row in, in place, against torch.cat + slice; batch-strided windows and new rows that
+    are views of a wider projection output."""
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    g = torch.Generator().manual_seed(t)
+    big_k = torch.randn(n + 1, h, t, 64, generator=g).bfloat16().cuda()
+    big_v = torch.randn(n + 1, h, t, 64, generator=g).bfloat16().cuda()
+    kw, vw = big_k[1:], big_v[1:]                                   # views with an offset
+    qkv = torch.randn(n, 3 * h * 64, generator=g).bfloat16().cuda()
+    kn = qkv[:, h * 64:2 * h * 64].view(n, 1, h, 64).transpose(1, 2)  # (N, H, 1, 64) strided views
+    vn = qkv[:, 2 * h * 64:].view(n, 1, h, 64).transpose(1, 2)
+    ref_k, ref_v = torch.cat([kw, kn], 2)[:, :, 1:].clone(), torch.cat([vw, vn], 2)[:, :, 1:].clone()
+    guard = big_k[0].clone()
+    F.window_shift_append(kw, vw, kn, vn)
+    assert torch.equal(kw, ref_k) and torch.equal(vw, ref_v)
+    assert torch.equal(big_k[0], guard)                              # nothing outside the windows moved
