@@ -78,6 +78,16 @@ class ChunkKVManager:
             return self._glmk
         return None if self._lmk is None else self._lmk[:, :self._len]
 
+    def backed_views(self):
+        """(chunk_k, chunk_v) over EVERY chunk slot that has memory behind it, filled or not: a view whose
+        address and shape stay the same while chunks are appended (until the buffer is re-allocated or the
+        next pages are mapped), for callers that bake tensor arguments into a CUDA graph.  Only chunks
+        below ``len(self)`` hold data; retrieved indices never point past them."""
+        if self._grad_mode or self._k is None:
+            return self.chunk_k, self.chunk_v
+        cap = self._capacity()
+        return self._k[:, :cap], self._v[:, :cap]
+
     @property
     def tracks_gradients(self) -> bool:
         """True once an append with grad-requiring inputs switched the manager to functional storage."""

@@ -442,17 +442,25 @@ class GraphedDecoder:
     each, so a step costs ~11 ms while its HBM traffic (weights, 12 self-attention windows, 6 GCA
     reads) is worth ~0.2 ms.  Between two chunk boundaries (62 token steps) nothing changes shape:
     the window caches are full, the retrieved chunk ids are fixed, the chunk cache is not appended to.
-    Those steps are captured ONCE per span as a CUDA graph over static buffers -- the token, the
-    self-attention windows (updated in place), the staged lower hidden states of the growing chunk
-    and a device-side slot counter -- and replayed; the next token is produced and consumed on the
-    device, the host only counts.  The boundary step (chunk encoder, cache append, landmark
-    retrieval) runs eagerly through ``DRTMinimal.decode_step`` and invalidates the graph.
+    Those steps are captured as a CUDA graph over static buffers -- the token, the self-attention
+    windows (updated in place), the staged lower hidden states of the growing chunk, the retrieved
+    ids and weights, a device-side slot counter -- and replayed; the next token is produced and
+    consumed on the device, the host only counts.  The boundary step (chunk encoder, cache append,
+    landmark retrieval) runs eagerly through ``DRTMinimal.decode_step``; afterwards the static
+    buffers are refreshed and the SAME graph serves the next span, unless the chunk cache moved
+    (a re-allocation, newly mapped pages) or the number of retrieved chunks changed.
     """
 
     def __init__(self, model: DRTMinimal, state: DecodeState, fused: bool = False):
         self.model, self.state = model, state
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.warmed = False
+        self.retrieved: list = []                  # per layer group: static (indices, weights) the captured step reads
+        self.cache_k = self.cache_v = None         # the chunk cache as the captured step sees it
+        self.cache_key = None
+        self.need_slot_reset = True
+        self.captures = 0                          # graphs captured so far (a span that finds its inputs unchanged replays the last one)
+        self.windows: list = []                    # per layer: the (k, v) window buffers the captured step updates in place
         self.fused = bool(fused) and self._fusable()
         if self.fused:
             self._fold()
@@ -462,7 +470,7 @@ class GraphedDecoder:
     # operations ride on the library's GEMM -- RMSNorm's row scale in the epilogue of one q|k|v (and one
     # gate|up) projection whose weights carry the norm's gain, the residual add in the epilogue of o_proj
     # and down_proj -- and the windowed attention is the library's decode kernel: ~15 launches per layer
-    # instead of ~45.  At 32 sequences and a 1M-token cache: 21,100 tokens/s, against 14,700 for the
+    # instead of ~45.  At 32 sequences and a 1M-token cache: 21,100 tokens/s (24,000 once the graph is kept across boundaries), against 14,700 for the
     # graphed step through the unfused modules and 5,500 eager.  (Two things had hidden that gain at first:
     # with the library's 128 x 256-tile GEMM on 32 rows -- 9 busy CTAs for the q|k|v projection -- the step
     # ran at 6,500 tokens/s, hence cuBLAS below SMALL_M rows; and concatenating the cached window with a
@@ -534,17 +542,16 @@ class GraphedDecoder:
             li += 1
         self.stage.index_copy_(1, self.slot, x.view(n, 1, -1))
         for g, layers in enumerate(m.upper_layers):
-            idx, w = st.chunks.current_retrieved_indices(g)
+            idx, w = self.retrieved[g]
             for layer in layers:
                 r = self._attn_fused(layer, self.folded[li], x, li)
                 if idx is None:
                     t = r
                 elif n >= self.SMALL_M:                                                     # r + gca(r)
-                    t = layer.gca.forward_fused(r.view(n, 1, 1, -1), st.chunks.chunk_k, st.chunks.chunk_v, idx.unsqueeze(1), w,
+                    t = layer.gca.forward_fused(r.view(n, 1, 1, -1), self.cache_k, self.cache_v, idx.unsqueeze(1), w,
                                                 residual=r.view(n, 1, -1)).view(n, -1)
                 else:
-                    t = r + layer.gca.forward_indexed(r.view(n, 1, 1, -1), st.chunks.chunk_k, st.chunks.chunk_v, idx.unsqueeze(1),
-                                                      w).view(n, -1)
+                    t = r + layer.gca.forward_indexed(r.view(n, 1, 1, -1), self.cache_k, self.cache_v, idx.unsqueeze(1), w).view(n, -1)
                 x = self._mlp_fused(layer, self.folded[li], t, r)
                 li += 1
         return x
@@ -574,12 +581,55 @@ class GraphedDecoder:
             li += 1
         self.stage.index_copy_(1, self.slot, x)
         for g, layers in enumerate(m.upper_layers):
-            idx, w = st.chunks.current_retrieved_indices(g)
+            idx, w = self.retrieved[g]
             for layer in layers:
-                x, kv = layer(x, st.chunks.chunk_k, st.chunks.chunk_v, None if idx is None else idx.unsqueeze(1), w, st.self_attn[li])
+                x, kv = layer(x, self.cache_k, self.cache_v, None if idx is None else idx.unsqueeze(1), w, st.self_attn[li])
                 self._keep(li, kv)
                 li += 1
         return x[:, 0]
+
+    def _bind_inputs(self) -> bool:
+        """Point the step at the chunk cache and the retrieved ids.  The cache goes in as the view over every
+        BACKED chunk slot, whose address and shape survive appends, and the retrieved ids / weights go
+        through static buffers that are overwritten after every boundary: so the graph captured for one
+        span is replayed for the following spans too, until the cache is re-allocated, new pages are
+        mapped or the number of retrieved chunks changes.  Returns False when a captured graph would no
+        longer be valid."""
+        ch = self.state.chunks
+        k, v = ch.backed_views()
+        key = (k.data_ptr(), v.data_ptr(), tuple(k.shape), tuple(k.stride()))
+        same = key == self.cache_key
+        # the cached windows: a step outside the graph leaves fresh tensors in the state; their contents move
+        # into the buffers the graph was captured on, which go back into the state
+        caches = self.state.self_attn
+        if len(self.windows) != len(caches) or any(o[0].shape != c[0].shape for o, c in zip(self.windows, caches)):
+            self.windows = list(caches)
+            same = False
+        else:
+            for i, (own, cur) in enumerate(zip(self.windows, caches)):
+                if cur[0] is not own[0]:
+                    own[0].copy_(cur[0])
+                    own[1].copy_(cur[1])
+                    caches[i] = own
+        self.cache_k, self.cache_v, self.cache_key = k, v, key
+        for g in range(len(self.model.upper_layers)):
+            idx, w = ch.current_retrieved_indices(g)
+            old = self.retrieved[g] if g < len(self.retrieved) else None
+            if idx is None:
+                new = (None, None)
+                same = same and old is not None and old[0] is None
+            elif old is not None and old[0] is not None and old[0].shape == idx.shape and old[1].shape == w.shape:
+                old[0].copy_(idx)
+                old[1].copy_(w)
+                new = old
+            else:
+                new = (idx.clone(), w.clone())
+                same = False
+            if g < len(self.retrieved):
+                self.retrieved[g] = new
+            else:
+                self.retrieved.append(new)
+        return same
 
     def _keep(self, li: int, kv) -> None:
         k_old, v_old = self.state.self_attn[li]
@@ -600,6 +650,7 @@ class GraphedDecoder:
         return True
 
     def _capture(self) -> None:
+        self.captures += 1
         self.graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -636,7 +687,7 @@ class GraphedDecoder:
                 tok = m.decode_step(tok, st).argmax(-1)
                 out.append(tok.view(-1, 1))
                 done += 1
-                self.graph = None                                # the chunk cache / retrieved ids / staging may have changed
+                self.need_slot_reset = True                      # the graph survives if its tensor arguments still hold (_bind_inputs)
                 continue
             span = min(cfg.enc_chunk_size - 1 - in_chunk, steps - done)
             if self.tok is None:
@@ -645,17 +696,20 @@ class GraphedDecoder:
                 self.stage = torch.zeros(n, m.chunk, dim, dtype=m.embed_tokens.weight.dtype, device=tok.device)
                 self.slot = torch.zeros(1, dtype=torch.int64, device=tok.device)
                 self.toks = torch.zeros(n, m.chunk, dtype=torch.int64, device=tok.device)
+            # hidden states the manager has already staged for this chunk move into the static buffer
+            staged = st.chunks.lower_hidden_states
+            if staged is not None:
+                self.stage[:, :staged.shape[1]].copy_(staged)
+                st.chunks.clear_lower_hidden_states()
+            if not self._bind_inputs():                          # the captured graph's tensor arguments no longer hold
+                self.graph = None
+            self.tok.copy_(tok)
             if self.graph is None:
-                # hidden states the manager has already staged for this chunk move into the static buffer
-                staged = st.chunks.lower_hidden_states
-                if staged is not None:
-                    self.stage[:, :staged.shape[1]].copy_(staged)
-                    st.chunks.clear_lower_hidden_states()
                 self.slot.fill_(in_chunk)
-                self.tok.copy_(tok)
                 self._capture()
-            else:
-                self.tok.copy_(tok)
+            elif self.need_slot_reset:
+                self.slot.fill_(in_chunk)
+            self.need_slot_reset = False
             for _ in range(span):
                 self.graph.replay()
             st.position += span

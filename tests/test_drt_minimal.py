@@ -146,6 +146,37 @@ def test_graphed_generation_equals_eager_generation(dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("virtual", [False, True])
+def test_graph_is_reused_across_chunk_boundaries(virtual):
+    """The captured token step reads the chunk cache through the view over all backed chunk slots and the
+    retrieved ids through static buffers, so one graph serves the spans after later boundaries too: with a
+    page-mapped cache (nothing moves) five boundaries need one capture, with the doubling cache a capture
+    only follows a re-allocation -- and the tokens stay those of the eager loop."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from long_context_modeling_b200 import drt_minimal as D
+    torch.manual_seed(6)
+    cfg = D.DRTConfig(hidden_size=128, num_attention_heads=2, intermediate_size=256, decoder_layers=[1, 2], encoder_layers=1,
+                      vocab_size=500, chunk_topk=2, slide_window=40, chunk_id=499)
+    model = D.DRTMinimal(cfg).cuda().bfloat16().eval()
+    prompt = torch.randint(0, 499, (2, 63 * 3), device="cuda")
+    new = 330                                                     # five chunk boundaries
+    eager = model.generate(prompt, new)
+    with torch.no_grad():
+        state = D.DecodeState(cfg)
+        if virtual:
+            import long_context_modeling_b200 as lcm
+            state.chunks = lcm.ChunkKVManager(group_size=1, capacity=4, zero_landmark=True, max_chunks=64)
+        tok = model(prompt, state=state)[:, -1].argmax(-1)
+        dec = D.GraphedDecoder(model, state)
+        out = torch.cat([prompt, tok.view(-1, 1), dec.run(tok, new - 1)], dim=1)
+    assert torch.equal(out, eager)
+    assert dec.captures == 1 if virtual else 1 <= dec.captures <= 3, dec.captures
+    if virtual:
+        state.chunks.close()
+
+
+@pytest.mark.gpu
 def test_flash_attn_path_matches_torch_path():
     """Where the flash-attn library loads, the body's windowed ALiBi self-attention goes through it (as in the
     reference); the block-banded torch path is the fallback.  Both must agree in bf16: a full sequence, and a
@@ -198,6 +229,7 @@ def test_fused_token_step_matches_the_module_path():
             dec.tok = tok.clone()
             dec.stage = torch.zeros(3, model.chunk, 128, dtype=torch.bfloat16, device="cuda")
             dec.slot = torch.zeros(1, dtype=torch.int64, device="cuda")
+            dec._bind_inputs()
             steps = []
             for t in range(3):                                   # three consecutive token steps, teacher-forced
                 steps.append(model.logits(dec._hidden_fused() if fused else dec._hidden_plain()).float())
