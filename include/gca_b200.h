@@ -453,6 +453,24 @@ typedef struct WindowDecodeArgs {
 
 int gca_window_decode(const WindowDecodeArgs* args, void* stream);
 
+/* The same attention for ONE new position per sequence (Sq = 1) over a window kept as a RING, with the
+ * append folded in: attn.k / attn.v are the (N, Hkv, T, 64) ring buffers with T <= window + 1 valid rows,
+ * k_new / v_new the new position's (N, Hkv, 64) rows by strides (n, kv head).  *rows_written (a device
+ * int64 the caller advances by one per call sequence, e.g. inside a captured CUDA graph) gives the slot
+ * p = rows_written mod T that holds the oldest row: the new rows are attended to as the newest
+ * position and stored at p; physical row j counts as logical position (j - p - 1) mod T.  With
+ * rows_written = 0 and a linear window the result equals gca_window_shift_append followed by
+ * gca_window_decode, without moving the window (which costs a read + write of the whole window per call). */
+typedef struct WindowRingDecodeArgs {
+  WindowDecodeArgs attn;
+  const void* k_new;
+  const void* v_new;
+  const int64_t* rows_written;  /* device memory */
+  int64_t new_stride[2];
+} WindowRingDecodeArgs;
+
+int gca_window_ring_decode(const WindowRingDecodeArgs* args, void* stream);
+
 /* The cached window moved on by one position, in place: every (n, head) block of T rows (64 bf16 each,
  * contiguous: position stride 64) drops its oldest row and takes the new position's row at the end
  * (what the reference's KV cache does with torch.cat and a slice).  k_window / v_window (N, H, T, 64)
@@ -488,7 +506,7 @@ int gca_vmem_free(void* va, size_t bytes);
 const char* gca_strerror(int code);
 int gca_abi_version(void);
 /* sizeof() of an argument block as the library was compiled (0 GcaFwdArgs, 1 GcaBwdArgs,
- * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs, 7 RowRmsArgs, 8 LinearArgs, 9 WindowDecodeArgs, 10 LinearCeArgs, 11 WindowAppendArgs): lets a foreign-language binding verify
+ * 2 LmkTopkArgs, 3 LmkMergeArgs, 4 CacheAppendArgs, 5 LmkExchangeArgs, 6 KvProjectArgs, 7 RowRmsArgs, 8 LinearArgs, 9 WindowDecodeArgs, 10 LinearCeArgs, 11 WindowAppendArgs, 12 WindowRingDecodeArgs): lets a foreign-language binding verify
  * its struct layout before the first call. */
 size_t gca_sizeof(int which);
 

@@ -126,6 +126,11 @@ class WindowDecodeArgs(C.Structure):
     ]
 
 
+class WindowRingDecodeArgs(C.Structure):
+    _fields_ = [("attn", WindowDecodeArgs), ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("rows_written", C.c_void_p),
+                ("new_stride", C.c_int64 * 2)]
+
+
 class LinearCeArgs(C.Structure):
     _fields_ = [
         ("x", C.c_void_p), ("w", C.c_void_p), ("targets", C.c_void_p), ("row_scale", C.c_void_p), ("loss", C.c_void_p),
@@ -154,6 +159,7 @@ EXPORTS = {
     "gca_linear": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "gca_window_decode": (C.c_int, [C.POINTER(WindowDecodeArgs), C.c_void_p]),
     "gca_window_shift_append": (C.c_int, [C.POINTER(WindowAppendArgs), C.c_void_p]),
+    "gca_window_ring_decode": (C.c_int, [C.POINTER(WindowRingDecodeArgs), C.c_void_p]),
     "gca_linear_ce_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "gca_linear_cross_entropy": (C.c_int, [C.POINTER(LinearCeArgs), C.c_void_p]),
     "lmk_exchange_mailbox_bytes": (C.c_size_t, [C.c_int, C.c_int]),
@@ -192,7 +198,8 @@ def lib() -> C.CDLL:
         if handle.gca_abi_version() != ABI_VERSION:
             raise RuntimeError("libgca_b200.so has an unexpected ABI version")
         for which, struct in enumerate((GcaFwdArgs, GcaBwdArgs, LmkTopkArgs, LmkMergeArgs, CacheAppendArgs, LmkExchangeArgs,
-                                       KvProjectArgs, RowRmsArgs, LinearArgs, WindowDecodeArgs, LinearCeArgs, WindowAppendArgs)):
+                                       KvProjectArgs, RowRmsArgs, LinearArgs, WindowDecodeArgs, LinearCeArgs, WindowAppendArgs,
+                                       WindowRingDecodeArgs)):
             if handle.gca_sizeof(which) != C.sizeof(struct):
                 raise RuntimeError(f"struct layout mismatch for {struct.__name__}: "
                                    f"library {handle.gca_sizeof(which)} vs binding {C.sizeof(struct)}")

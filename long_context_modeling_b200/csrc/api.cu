@@ -16,6 +16,7 @@ int launch_kv_project_append(const KvProjectArgs& a, int sms, cudaStream_t strea
 int launch_row_rms(const RowRmsArgs& a, cudaStream_t stream);
 int launch_linear(const LinearArgs& a, int sms, cudaStream_t stream);
 int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream);
+int launch_window_ring_decode(const WindowRingDecodeArgs& a, cudaStream_t stream);
 int launch_linear_ce(const LinearCeArgs& a, int sms, cudaStream_t stream);
 int launch_window_shift_append(const WindowAppendArgs& a, cudaStream_t stream);
 
@@ -121,6 +122,7 @@ size_t gca_sizeof(int which) {
     case 9: return sizeof(WindowDecodeArgs);
     case 10: return sizeof(LinearCeArgs);
     case 11: return sizeof(WindowAppendArgs);
+    case 12: return sizeof(WindowRingDecodeArgs);
     default: return 0;
   }
 }
@@ -380,18 +382,36 @@ int gca_window_shift_append(const WindowAppendArgs* a, void* stream) {
   return gca::launch_window_shift_append(*a, (cudaStream_t)stream);
 }
 
-int gca_window_decode(const WindowDecodeArgs* a, void* stream) {
-  if (!a) return GCA_ERR_NULL;
+static int check_window_decode(const WindowDecodeArgs* a) {
   if (!a->q || !a->k || !a->v || !a->out) return GCA_ERR_NULL;
   if (a->N < 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Hq % a->Hkv || a->Sq <= 0 || a->T < a->Sq || a->window < 0) return GCA_ERR_SHAPE;
   if ((a->Hq / a->Hkv) * a->Sq > 4) return GCA_ERR_SHAPE;
   for (int i = 0; i < 3; ++i)
     if (a->q_stride[i] % 8 || a->o_stride[i] % 8 || a->k_stride[i] % 8 || a->v_stride[i] % 8) return GCA_ERR_STRIDE;
   if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out)) return GCA_ERR_ALIGN;
+  return 0;
+}
+
+int gca_window_decode(const WindowDecodeArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (int rc = check_window_decode(a)) return rc;
   if (a->N == 0) return 0;
   gca::DeviceScope scope(a->out);
   if (scope.rc) return scope.rc;
   return gca::launch_window_decode(*a, (cudaStream_t)stream);
+}
+
+int gca_window_ring_decode(const WindowRingDecodeArgs* a, void* stream) {
+  if (!a) return GCA_ERR_NULL;
+  if (int rc = check_window_decode(&a->attn)) return rc;
+  if (!a->k_new || !a->v_new || !a->rows_written) return GCA_ERR_NULL;
+  if (a->attn.Sq != 1 || a->attn.T > a->attn.window + 1) return GCA_ERR_SHAPE;   // every row of the ring is visible
+  if (a->new_stride[0] % 8 || a->new_stride[1] % 8) return GCA_ERR_STRIDE;
+  if (!aligned16(a->k_new) || !aligned16(a->v_new)) return GCA_ERR_ALIGN;
+  if (a->attn.N == 0) return 0;
+  gca::DeviceScope scope(a->attn.out);
+  if (scope.rc) return scope.rc;
+  return gca::launch_window_ring_decode(*a, (cudaStream_t)stream);
 }
 
 int gca_linear(const LinearArgs* a, void* stream) {

@@ -14,6 +14,14 @@
 // PREFETCH steps ahead of the arithmetic (registers), which keeps ~64 KB per SM in flight.  At the
 // end the 4 streams of a warp and the 8 warps are merged in a fixed order: the result does not
 // depend on scheduling.
+//
+// RING form (decode of one position per sequence against a FULL window): the window buffer is a
+// ring, the step's new K / V row arrives separately and replaces the oldest row.  With a
+// device-side count c of rows written so far, the new row goes to physical row p = c mod T, and
+// physical row j holds logical position (j - p - 1) mod T.  The CTA that owns the (sequence, kv head)
+// block takes row p from the new-row operands, stores it into the ring, and reads every other
+// row in place: the window never moves (shifting it costs a full read + write of the window per
+// token and layer, more than the attention itself reads).
 #include "gca_common.cuh"
 
 namespace gca {
@@ -40,6 +48,11 @@ struct WinParams {
   long long ks[3], vs[3];     // strides of (n, kv head, position)
   int N, Hq, Hkv, G, Sq, T, window;
   float c2;                   // scale * log2(e)
+  // ring form (else nullptr): the new position's rows by strides (n, kv head) and the count of rows written
+  const __nv_bfloat16* knew;
+  const __nv_bfloat16* vnew;
+  const long long* ring;
+  long long ns[2];
 };
 
 struct State { float m, l, acc[8]; };
@@ -56,7 +69,7 @@ __device__ __forceinline__ void merge(State& a, float m2, float l2, const float*
 // Registers are capped so that three CTAs of the one-row kernel share an SM: 32 sequences x 12
 // heads = 384 CTAs then run as ONE wave on 148 SMs (with two per SM a second wave of 88 CTAs
 // doubled the kernel's duration).
-template <int R>
+template <int R, bool RING>
 __global__ void __launch_bounds__(NWARPS * 32, R == 1 ? 3 : (R == 2 ? 2 : 1))
 win_decode_kernel(const WinParams p) {
   __shared__ float part[NWARPS][R][2 + 64];
@@ -94,14 +107,19 @@ win_decode_kernel(const WinParams p) {
   const __nv_bfloat16* vb = p.v + n * p.vs[0] + hk * p.vs[1] + sub * 8;
   const int stride = NWARPS * 4;                     // keys per CTA step
   const int base = first + warp * 4;                 // warp-uniform: every lane runs the same steps
+  // ring form: physical row `newest` is this step's new row (read from knew / vnew, never from the ring);
+  // the linear form is the ring whose newest row is the last one
+  const int newest = RING ? (int)(*p.ring % p.T) : p.T - 1;
+  const long long noff = RING ? n * p.ns[0] + hk * p.ns[1] + sub * 8 : 0;       // this lane's 16 bytes of the new rows
   uint4 kq[PREFETCH], vq[PREFETCH];
 #pragma unroll
   for (int s = 0; s < PREFETCH; ++s) {
     const int j = base + grp + s * stride;
     kq[s] = vq[s] = make_uint4(0, 0, 0, 0);
     if (j < p.T) {
-      kq[s] = *reinterpret_cast<const uint4*>(kb + j * p.ks[2]);
-      vq[s] = *reinterpret_cast<const uint4*>(vb + j * p.vs[2]);
+      const bool fresh = RING && j == newest;
+      kq[s] = *reinterpret_cast<const uint4*>(fresh ? p.knew + noff : kb + j * p.ks[2]);
+      vq[s] = *reinterpret_cast<const uint4*>(fresh ? p.vnew + noff : vb + j * p.vs[2]);
     }
   }
   for (int jb = base; jb < p.T; jb += PREFETCH * stride) {
@@ -111,8 +129,9 @@ win_decode_kernel(const WinParams p) {
       const uint4 kc = kq[s], vc = vq[s];
       const int jn = j + PREFETCH * stride;             // refill this register slot
       if (jn < p.T) {
-        kq[s] = *reinterpret_cast<const uint4*>(kb + jn * p.ks[2]);
-        vq[s] = *reinterpret_cast<const uint4*>(vb + jn * p.vs[2]);
+        const bool fresh = RING && jn == newest;
+        kq[s] = *reinterpret_cast<const uint4*>(fresh ? p.knew + noff : kb + jn * p.ks[2]);
+        vq[s] = *reinterpret_cast<const uint4*>(fresh ? p.vnew + noff : vb + jn * p.vs[2]);
       }
       // every lane of a warp runs the same number of steps (the reduction below uses shuffles);
       // keys past the end are masked
@@ -129,7 +148,9 @@ win_decode_kernel(const WinParams p) {
         sc += __shfl_xor_sync(0xffffffffu, sc, 1);
         sc += __shfl_xor_sync(0xffffffffu, sc, 2);
         sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-        const int dist = pos[r] - j;
+        int lj = j;                                     // logical position of physical row j
+        if (RING) { lj = j - newest - 1; if (lj < 0) lj += p.T; }
+        const int dist = pos[r] - lj;
         if (r < rows && in_range && dist >= 0 && dist <= p.window) {
           sc -= slope[r] * (float)dist;
           const float m = fmaxf(st[r].m, sc);
@@ -141,6 +162,11 @@ win_decode_kernel(const WinParams p) {
         }
       }
     }
+  }
+  // ring form: the new row takes the oldest row's place (no thread of this or another CTA reads that row of the ring)
+  if (RING && warp == 0 && grp == 0) {
+    *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(kb) + newest * p.ks[2]) = *reinterpret_cast<const uint4*>(p.knew + noff);
+    *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(vb) + newest * p.vs[2]) = *reinterpret_cast<const uint4*>(p.vnew + noff);
   }
   // merge the 4 key streams of the warp (groups 8 and 16 lanes apart), then the warps
 #pragma unroll
@@ -222,8 +248,13 @@ int launch_window_shift_append(const WindowAppendArgs& a, cudaStream_t stream) {
   return (int)cudaGetLastError();
 }
 
-int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream) {
+static int launch_window(const WindowDecodeArgs& a, const WindowRingDecodeArgs* ring, cudaStream_t stream) {
   WinParams p;
+  p.knew = p.vnew = nullptr; p.ring = nullptr; p.ns[0] = p.ns[1] = 0;
+  if (ring) {
+    p.knew = (const __nv_bfloat16*)ring->k_new; p.vnew = (const __nv_bfloat16*)ring->v_new;
+    p.ring = (const long long*)ring->rows_written; p.ns[0] = ring->new_stride[0]; p.ns[1] = ring->new_stride[1];
+  }
   p.q = (const __nv_bfloat16*)a.q; p.k = (const __nv_bfloat16*)a.k; p.v = (const __nv_bfloat16*)a.v;
   p.slopes = a.alibi_slopes; p.out = (__nv_bfloat16*)a.out;
   for (int i = 0; i < 3; ++i) { p.qs[i] = a.q_stride[i]; p.os[i] = a.o_stride[i]; p.ks[i] = a.k_stride[i]; p.vs[i] = a.v_stride[i]; }
@@ -232,11 +263,20 @@ int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream) {
   const int rows = p.G * a.Sq;
   const unsigned grid = (unsigned)(a.N * a.Hkv);
   if (grid == 0) return 0;
-  if (rows <= 1) win_decode_kernel<1><<<grid, NWARPS * 32, 0, stream>>>(p);
-  else if (rows <= 2) win_decode_kernel<2><<<grid, NWARPS * 32, 0, stream>>>(p);
-  else if (rows <= 4) win_decode_kernel<4><<<grid, NWARPS * 32, 0, stream>>>(p);
+  if (ring) {                                      // one new position: G rows per kv head
+    if (rows <= 1) win_decode_kernel<1, true><<<grid, NWARPS * 32, 0, stream>>>(p);
+    else if (rows <= 2) win_decode_kernel<2, true><<<grid, NWARPS * 32, 0, stream>>>(p);
+    else if (rows <= 4) win_decode_kernel<4, true><<<grid, NWARPS * 32, 0, stream>>>(p);
+    else return GCA_ERR_SHAPE;
+  } else if (rows <= 1) win_decode_kernel<1, false><<<grid, NWARPS * 32, 0, stream>>>(p);
+  else if (rows <= 2) win_decode_kernel<2, false><<<grid, NWARPS * 32, 0, stream>>>(p);
+  else if (rows <= 4) win_decode_kernel<4, false><<<grid, NWARPS * 32, 0, stream>>>(p);
   else return GCA_ERR_SHAPE;
   return (int)cudaGetLastError();
 }
+
+int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream) { return launch_window(a, nullptr, stream); }
+
+int launch_window_ring_decode(const WindowRingDecodeArgs& a, cudaStream_t stream) { return launch_window(a.attn, &a, stream); }
 
 }  // namespace gca

@@ -464,7 +464,7 @@ class GraphedDecoder:
         self.fused = bool(fused) and self._fusable()
         if self.fused:
             self._fold()
-        self.tok = self.stage = self.slot = self.toks = None
+        self.tok = self.stage = self.slot = self.toks = self.counters = self.ring = None
 
     # ---- the fused form of a token step (bf16 on a GPU, no projection biases): per layer the small
     # operations ride on the library's GEMM -- RMSNorm's row scale in the epilogue of one q|k|v (and one
@@ -493,6 +493,8 @@ class GraphedDecoder:
             gu = torch.cat([mlp.gate_proj.weight, mlp.up_proj.weight], 0).detach()
             self.folded.append((FO.fold_gain(qkv, l.input_layernorm.weight.detach()),
                                 FO.fold_gain(gu, l.post_attention_layernorm.weight.detach()), a.slopes.float().contiguous()))
+        head = FO.fold_gain(self.model.embed_tokens.weight.detach(), self.model.norm.weight.detach())
+        self.lm_w = F.pad(head, (0, 0, 0, -head.shape[0] % 64))
 
     # With few rows (a decode step has one per sequence) the library's 128 x 256-tile GEMM keeps only a
     # handful of CTAs busy, so below SMALL_M rows the products go to cuBLAS (whose small-M kernels split
@@ -504,13 +506,35 @@ class GraphedDecoder:
         from . import fused_ops as FO
         if x2.shape[0] >= self.SMALL_M:
             return FO.rmsnorm_linear(x2, folded_w, eps)
-        return F.linear(x2, folded_w) * FO.row_rms(x2, eps).to(x2.dtype).unsqueeze(1)
+        return F.linear(F.rms_norm(x2, (x2.shape[1],), None, eps), folded_w)               # two launches
 
-    def _linear_residual(self, x2, w, res):
+    def _linear_residual(self, x2, w, res, inplace=False):
+        """res + x2 w^T; ``inplace``: the caller has no further use for ``res`` (saves addmm's copy of it)."""
         from . import fused_ops as FO
         if x2.shape[0] >= self.SMALL_M:
             return FO.linear(x2, w, residual=res)
-        return torch.addmm(res, x2, w.t())
+        return res.addmm_(x2, w.t()) if inplace else torch.addmm(res, x2, w.t())
+
+    def _gca_small(self, layer, r, idx, w):
+        """r + gca(r) for a handful of rows: fused norm, q projection, the decode kernel, o_proj with the
+        residual added in its epilogue (5 launches; the module path takes ~14)."""
+        from . import gca
+        g = layer.gca
+        n, dim = r.shape
+        q = F.linear(F.rms_norm(r, (dim,), g.pre_norm.weight, g.pre_norm.eps), g.q_proj.weight)
+        q5 = q.view(n, 1, 1, g.num_heads, g.head_dim).permute(0, 1, 3, 2, 4)
+        vals = gca.gca_indexed_nograd(q5, self.cache_k, self.cache_v, idx.unsqueeze(1), w, 1.0 / math.sqrt(g.head_dim), g.sm_n)
+        vals = vals.permute(0, 1, 3, 2, 4).reshape(n, dim)
+        return torch.addmm(r, vals, g.o_proj.weight.t())
+
+    def _logits(self, x):
+        """The tied LM head on the final norm of x (N, dim).  With few rows: fused norm and the head's weights
+        with the norm's gain folded in, PADDED to a multiple of 64 rows -- a vocabulary like 50,257 leaves
+        cuBLAS only its unaligned kernels, several times slower than the aligned ones."""
+        m = self.model
+        if x.shape[0] >= self.SMALL_M:
+            return m.logits(x)
+        return F.linear(F.rms_norm(x, (x.shape[1],), None, m.norm.eps), self.lm_w)[:, :m.cfg.vocab_size]
 
     def _attn_fused(self, layer, fw, x2, li):
         from . import fused_ops as FO
@@ -518,17 +542,17 @@ class GraphedDecoder:
         n, dim = x2.shape
         qkv = self._norm_linear(x2, fw[0], layer.input_layernorm.eps)                      # (N, 3 dim)
         q, k, v = (qkv[:, i * dim:(i + 1) * dim].view(n, 1, a.h, a.d).transpose(1, 2) for i in range(3))
-        k_old, v_old = self.state.self_attn[li]
-        FO.window_shift_append(k_old, v_old, k, v)                                         # in place: oldest row out, new row in
-        o = FO.window_decode(q, k_old, v_old, a.window, fw[2], 1.0 / math.sqrt(a.d))       # (N, H, 1, 64)
-        return self._linear_residual(o.view(n, dim), a.o_proj.weight, x2)                  # x + self_attn(norm(x))
+        k_ring, v_ring = self.state.self_attn[li]
+        # the window as a ring: the new row replaces the oldest inside the attention kernel, nothing moves
+        o = FO.window_ring_decode(q, k_ring, v_ring, k, v, self.ring, a.window, fw[2], 1.0 / math.sqrt(a.d))   # (N, H, 1, 64)
+        return self._linear_residual(o.view(n, dim), a.o_proj.weight, x2, inplace=True)    # x + self_attn(norm(x))
 
     def _mlp_fused(self, layer, fw, t2, r2):
         from . import fused_ops as FO
         gu = self._norm_linear(t2, fw[1], layer.post_attention_layernorm.eps)
         inter = gu.shape[1] // 2
         h = F.silu(gu[:, :inter]) * gu[:, inter:]
-        return self._linear_residual(h, layer.mlp.down_proj.weight, r2)                    # r + mlp(norm(t))
+        return self._linear_residual(h, layer.mlp.down_proj.weight, r2, inplace=True)      # r + mlp(norm(t))
 
     def _hidden_fused(self) -> torch.Tensor:
         """The final hidden state (N, dim) of one token step on the static buffers, fused form."""
@@ -551,7 +575,7 @@ class GraphedDecoder:
                     t = layer.gca.forward_fused(r.view(n, 1, 1, -1), self.cache_k, self.cache_v, idx.unsqueeze(1), w,
                                                 residual=r.view(n, 1, -1)).view(n, -1)
                 else:
-                    t = r + layer.gca.forward_indexed(r.view(n, 1, 1, -1), self.cache_k, self.cache_v, idx.unsqueeze(1), w).view(n, -1)
+                    t = self._gca_small(layer, r, idx, w)
                 x = self._mlp_fused(layer, self.folded[li], t, r)
                 li += 1
         return x
@@ -566,10 +590,10 @@ class GraphedDecoder:
         finally:
             for a in attns:
                 a.inplace_window = False
-        nxt = self.model.logits(x).argmax(-1)
+        nxt = (self._logits(x) if self.fused else self.model.logits(x)).argmax(-1)
         self.toks.index_copy_(1, self.slot, nxt.view(-1, 1))
         self.tok.copy_(nxt)
-        self.slot += 1
+        self.counters += 1                         # the slot in the chunk and the rows written into the window rings
 
     def _hidden_plain(self) -> torch.Tensor:
         m, st = self.model, self.state
@@ -631,6 +655,23 @@ class GraphedDecoder:
                 self.retrieved.append(new)
         return same
 
+    def _make_counters(self, device) -> None:
+        self.counters = torch.zeros(2, dtype=torch.int64, device=device)
+        self.slot, self.ring = self.counters[:1], self.counters[1:]
+
+    def _linearise(self, written: int) -> None:
+        """The fused step keeps each cached window as a ring (``fused_ops.window_ring_decode``); after a span
+        that wrote ``written`` rows the rings are rolled back into position order, which is what every other
+        user of the state expects, and the ring counter restarts.  Once per span: 1/62 of what shifting the
+        window at every token moved."""
+        t = self.windows[0][0].shape[2]
+        shift = written % t
+        if shift:
+            for k, v in self.windows:
+                k.copy_(torch.roll(k, -shift, 2))
+                v.copy_(torch.roll(v, -shift, 2))
+        self.ring.zero_()
+
     def _keep(self, li: int, kv) -> None:
         k_old, v_old = self.state.self_attn[li]
         if kv[0] is k_old:                       # the window was moved on in place
@@ -655,7 +696,7 @@ class GraphedDecoder:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         if not self.warmed:                        # first capture: one real step on a side stream for lazy initialisations
-            saved = [t.clone() for t in (self.tok, self.slot)] + [t.clone() for c in self.state.self_attn for t in c]
+            saved = [t.clone() for t in (self.tok, self.counters)] + [t.clone() for c in self.state.self_attn for t in c]
             with torch.cuda.stream(side):
                 self._step()
             torch.cuda.current_stream().wait_stream(side)
@@ -665,7 +706,7 @@ class GraphedDecoder:
             self._step()                           # captured, not executed
 
     def _restore(self, saved) -> None:
-        self.tok.copy_(saved[0]); self.slot.copy_(saved[1])
+        self.tok.copy_(saved[0]); self.counters.copy_(saved[1])
         flat = [t for c in self.state.self_attn for t in c]
         for dst, src in zip(flat, saved[2:]):
             dst.copy_(src)
@@ -694,7 +735,7 @@ class GraphedDecoder:
                 dim = cfg.hidden_size
                 self.tok = torch.empty_like(tok)
                 self.stage = torch.zeros(n, m.chunk, dim, dtype=m.embed_tokens.weight.dtype, device=tok.device)
-                self.slot = torch.zeros(1, dtype=torch.int64, device=tok.device)
+                self._make_counters(tok.device)
                 self.toks = torch.zeros(n, m.chunk, dtype=torch.int64, device=tok.device)
             # hidden states the manager has already staged for this chunk move into the static buffer
             staged = st.chunks.lower_hidden_states
@@ -712,6 +753,8 @@ class GraphedDecoder:
             self.need_slot_reset = False
             for _ in range(span):
                 self.graph.replay()
+            if self.fused:
+                self._linearise(span)
             st.position += span
             out.append(self.toks[:, in_chunk:in_chunk + span].clone())
             tok = self.tok.clone()

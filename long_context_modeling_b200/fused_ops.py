@@ -94,6 +94,13 @@ def window_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int
     (``flash_attn_with_kvcache(..., causal=True, window_size=(window, 0), alibi_slopes=slopes)``,
     ``model/llama.py:684-688``).  q (N, Hq, Sq, 64), k / v (N, Hkv, T, 64) bf16 -- any strides with the
     head dimension contiguous; the query rows stand at positions T - Sq .. T - 1.  Returns (N, Hq, Sq, 64)."""
+    a = _lib.WindowDecodeArgs()
+    out = _fill_window_args(a, q, k, v, window, slopes, sm_scale)
+    _lib.call("gca_window_decode", C.byref(a), _stream())
+    return out
+
+
+def _fill_window_args(a, q, k, v, window, slopes, sm_scale) -> torch.Tensor:
     for t, name in ((q, "q"), (k, "k"), (v, "v")):
         _require(t, f"window_decode {name}")
         if t.dim() != 4 or t.shape[-1] != 64 or t.stride(-1) != 1:
@@ -101,7 +108,6 @@ def window_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int
     n, hq, sq, _ = q.shape
     hkv, t_len = k.shape[1], k.shape[2]
     out = torch.empty((n, hq, sq, 64), dtype=torch.bfloat16, device=q.device)
-    a = _lib.WindowDecodeArgs()
     a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
     if slopes is not None:
         if slopes.dtype != torch.float32 or slopes.numel() != hq or not slopes.is_contiguous() or not slopes.is_cuda:
@@ -111,7 +117,34 @@ def window_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int
         a.q_stride[i], a.o_stride[i], a.k_stride[i], a.v_stride[i] = q.stride(i), out.stride(i), k.stride(i), v.stride(i)
     a.N, a.Hq, a.Hkv, a.Sq, a.T, a.window = n, hq, hkv, sq, t_len, int(window)
     a.sm_scale = float(sm_scale) if sm_scale is not None else 0.125
-    _lib.call("gca_window_decode", C.byref(a), _stream())
+    return out
+
+
+def window_ring_decode(q: torch.Tensor, k_ring: torch.Tensor, v_ring: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                       rows_written: torch.Tensor, window: int, slopes: Optional[torch.Tensor] = None,
+                       sm_scale: Optional[float] = None) -> torch.Tensor:
+    """``window_decode`` for one new position per sequence with the append folded in and the window
+    kept as a RING that never moves: ``k_ring`` / ``v_ring`` (N, Hkv, T, 64) hold the last T positions,
+    the oldest at row ``rows_written mod T``; ``k_new`` / ``v_new`` (N, Hkv, 1, 64) or (N, Hkv, 64) are
+    attended to as the newest position and stored over the oldest row.  ``rows_written`` is a device int64
+    scalar the CALLER advances by one after the step (all layers of a model share one counter), so that a
+    captured CUDA graph can replay the step.  q (N, Hq, 1, 64).  ``torch.roll(ring, -(rows_written % T), 2)``
+    gives the window back in order."""
+    for t, name in ((k_new, "k_new"), (v_new, "v_new")):
+        _require(t, f"window_ring_decode {name}")
+    if not rows_written.is_cuda:
+        raise RuntimeError("window_ring_decode rows_written: the fused projections run on a CUDA device only (no CPU fallback)")
+    if rows_written.dtype != torch.int64 or rows_written.numel() != 1:
+        raise ValueError("window_ring_decode: rows_written must be one int64 on the device")
+    n, hkv = k_ring.shape[0], k_ring.shape[1]
+    kn, vn = k_new.reshape(n, hkv, 64) if k_new.dim() == 4 else k_new, v_new.reshape(n, hkv, 64) if v_new.dim() == 4 else v_new
+    if kn.stride(2) != 1 or vn.stride(2) != 1 or kn.stride()[:2] != vn.stride()[:2]:
+        raise ValueError("window_ring_decode: new rows must be bf16 with a contiguous head dimension and equal strides")
+    a = _lib.WindowRingDecodeArgs()
+    out = _fill_window_args(a.attn, q, k_ring, v_ring, window, slopes, sm_scale)
+    a.k_new, a.v_new, a.rows_written = kn.data_ptr(), vn.data_ptr(), rows_written.data_ptr()
+    a.new_stride[0], a.new_stride[1] = kn.stride(0), kn.stride(1)
+    _lib.call("gca_window_ring_decode", C.byref(a), _stream())
     return out
 
 

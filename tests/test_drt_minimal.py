@@ -228,13 +228,13 @@ def test_fused_token_step_matches_the_module_path():
             assert dec._window_full()
             dec.tok = tok.clone()
             dec.stage = torch.zeros(3, model.chunk, 128, dtype=torch.bfloat16, device="cuda")
-            dec.slot = torch.zeros(1, dtype=torch.int64, device="cuda")
+            dec._make_counters("cuda")
             dec._bind_inputs()
             steps = []
             for t in range(3):                                   # three consecutive token steps, teacher-forced
                 steps.append(model.logits(dec._hidden_fused() if fused else dec._hidden_plain()).float())
                 dec.tok.copy_(prompt[:, t])
-                dec.slot += 1
+                dec.counters += 1
             hidden.append(torch.stack(steps))
         a, b = hidden
         assert (a - b).abs().max().item() <= 3e-2 * a.abs().max().item(), ((a - b).abs().max().item(), a.abs().max().item())

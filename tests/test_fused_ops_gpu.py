@@ -250,3 +250,48 @@ def test_window_shift_append_in_place(n, h, t):
     F.window_shift_append(kw, vw, kn, vn)
     assert torch.equal(kw, ref_k) and torch.equal(vw, ref_v)
     assert torch.equal(big_k[0], guard)                              # nothing outside the windows moved
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,hq,hkv,t,steps", [(3, 2, 2, 41, 5), (2, 4, 2, 64, 70), (32, 12, 12, 513, 3)])
+def test_window_ring_decode_equals_shift_then_decode(n, hq, hkv, t, steps):
+    """The ring form (new row replaces the oldest inside the attention kernel, a device counter gives the
+    phase) against moving the window and attending to it, step by step: outputs equal within bf16 rounding
+    (the keys reach the online softmax in another order), and the ring rolled back by the phase IS the moved
+    window -- also after the counter has wrapped around the ring."""
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    g = torch.Generator().manual_seed(t + steps)
+    ring_k = torch.randn(n, hkv, t, 64, generator=g).bfloat16().cuda()
+    ring_v = torch.randn(n, hkv, t, 64, generator=g).bfloat16().cuda()
+    lin_k, lin_v = ring_k.clone(), ring_v.clone()
+    slopes = (2.0 ** -torch.arange(1, hq + 1).float()).cuda()
+    written = torch.zeros(1, dtype=torch.int64, device="cuda")
+    for s in range(steps):
+        qkv = torch.randn(n, (hq + 2 * hkv) * 64, generator=g).bfloat16().cuda()
+        q = qkv[:, :hq * 64].view(n, 1, hq, 64).transpose(1, 2)
+        kn = qkv[:, hq * 64:(hq + hkv) * 64].view(n, 1, hkv, 64).transpose(1, 2)
+        vn = qkv[:, (hq + hkv) * 64:].view(n, 1, hkv, 64).transpose(1, 2)
+        F.window_shift_append(lin_k, lin_v, kn, vn)
+        want = F.window_decode(q, lin_k, lin_v, t - 1, slopes, 0.125)
+        got = F.window_ring_decode(q, ring_k, ring_v, kn, vn, written, t - 1, slopes, 0.125)
+        written += 1
+        assert (got.float() - want.float()).abs().max().item() <= 1e-2 * want.float().abs().max().item(), s
+    assert torch.equal(torch.roll(ring_k, -(steps % t), 2), lin_k)
+    assert torch.equal(torch.roll(ring_v, -(steps % t), 2), lin_v)
+
+
+@pytest.mark.gpu
+def test_window_ring_decode_rejects_bad_arguments():
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    q = torch.zeros(1, 1, 1, 64, dtype=torch.bfloat16, device="cuda")
+    ring = torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16, device="cuda")
+    new = torch.zeros(1, 1, 64, dtype=torch.bfloat16, device="cuda")
+    cnt = torch.zeros(1, dtype=torch.int64, device="cuda")
+    with pytest.raises(ValueError):
+        F.window_ring_decode(q, ring, ring, new, new, cnt.int(), 7)                    # counter must be int64
+    with pytest.raises(ValueError):
+        F.window_ring_decode(q, ring, ring, new, new, cnt, 3)                          # rows of the ring outside the window
+    with pytest.raises(ValueError):
+        F.window_ring_decode(q.expand(1, 1, 2, 64).contiguous(), ring, ring, new, new, cnt, 7)      # one new position only
