@@ -405,6 +405,11 @@ typedef struct LinearArgs {
 int gca_row_rms(const RowRmsArgs* args, void* stream);
 int gca_linear(const LinearArgs* args, void* stream);
 
+/* out[m, c] = silu(gate_up[m, c]) * gate_up[m, I + c] for c < I: the activation between ONE gate|up
+ * projection (weights stacked) and down_proj -- the reference's fused SwiGLU, model/llama.py:290-300.
+ * bf16; gate_up (M, 2 I) and out (M, I) by row strides in elements (multiples of 8); I % 8 == 0. */
+int gca_silu_mul(const void* gate_up, void* out, int64_t M, int32_t I, int64_t in_stride, int64_t out_stride, void* stream);
+
 /* ---- LM head fused with the cross-entropy loss, forward only (reference: model/DRT.py:1055-1064,
  * `logits = lm_head(hidden)` followed by CrossEntropyLoss(ignore_index=-100); evaluation / perplexity) ----
  *

@@ -157,6 +157,7 @@ EXPORTS = {
     "gca_kv_project_append": (C.c_int, [C.POINTER(KvProjectArgs), C.c_void_p]),
     "gca_row_rms": (C.c_int, [C.POINTER(RowRmsArgs), C.c_void_p]),
     "gca_linear": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
+    "gca_silu_mul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_void_p]),
     "gca_window_decode": (C.c_int, [C.POINTER(WindowDecodeArgs), C.c_void_p]),
     "gca_window_shift_append": (C.c_int, [C.POINTER(WindowAppendArgs), C.c_void_p]),
     "gca_window_ring_decode": (C.c_int, [C.POINTER(WindowRingDecodeArgs), C.c_void_p]),

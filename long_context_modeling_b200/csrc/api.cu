@@ -14,6 +14,7 @@ void set_fwd_profile_buffer(void* device_ptr);
 int launch_cache_append(const CacheAppendArgs& a, cudaStream_t stream);
 int launch_kv_project_append(const KvProjectArgs& a, int sms, cudaStream_t stream);
 int launch_row_rms(const RowRmsArgs& a, cudaStream_t stream);
+int launch_silu_mul(const void* gu, void* out, long long M, int I, long long in_stride, long long out_stride, cudaStream_t stream);
 int launch_linear(const LinearArgs& a, int sms, cudaStream_t stream);
 int launch_window_decode(const WindowDecodeArgs& a, cudaStream_t stream);
 int launch_window_ring_decode(const WindowRingDecodeArgs& a, cudaStream_t stream);
@@ -342,6 +343,17 @@ int gca_row_rms(const RowRmsArgs* a, void* stream) {
   gca::DeviceScope scope(a->x);
   if (scope.rc) return scope.rc;
   return gca::launch_row_rms(*a, (cudaStream_t)stream);
+}
+
+int gca_silu_mul(const void* gate_up, void* out, int64_t M, int32_t I, int64_t in_stride, int64_t out_stride, void* stream) {
+  if (!gate_up || !out) return GCA_ERR_NULL;
+  if (M < 0 || I < 8 || I % 8 != 0) return GCA_ERR_SHAPE;
+  if (in_stride % 8 != 0 || in_stride < 2 * (int64_t)I || out_stride % 8 != 0 || out_stride < I) return GCA_ERR_STRIDE;
+  if (!aligned16(gate_up) || !aligned16(out)) return GCA_ERR_ALIGN;
+  if (M == 0) return 0;
+  gca::DeviceScope scope(out);
+  if (scope.rc) return scope.rc;
+  return gca::launch_silu_mul(gate_up, out, M, I, in_stride, out_stride, (cudaStream_t)stream);
 }
 
 size_t gca_linear_ce_workspace_bytes(int64_t M, int32_t N) {

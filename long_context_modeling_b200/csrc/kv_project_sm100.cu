@@ -316,6 +316,29 @@ __global__ void row_rms_kernel(const __nv_bfloat16* __restrict__ x, float* __res
   if (lane == 0) row_scale[m] = rsqrtf(acc / (float)D + eps);
 }
 
+// out[m, c] = silu(gu[m, c]) * gu[m, I + c]: the activation between one gate|up product and down_proj
+// (the reference's fused SwiGLU, model/llama.py:290-300).  One thread per 8 columns, 16-byte accesses.
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long M, int I,
+                                long long in_stride, long long out_stride) {
+  const int per_row = I / 8;
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= M * per_row) return;
+  const long long m = t / per_row;
+  const int c = (int)(t - m * per_row) * 8;
+  const uint4 g = *reinterpret_cast<const uint4*>(gu + m * in_stride + c);
+  const uint4 u = *reinterpret_cast<const uint4*>(gu + m * in_stride + I + c);
+  const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
+    const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xffff0000u);
+    const __nv_bfloat162 b = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+    o[j] = *reinterpret_cast<const uint32_t*>(&b);
+  }
+  *reinterpret_cast<uint4*>(out + m * out_stride + c) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // loss[m] = ln(sum_j exp(logit_j)) - logit_target from the per-tile partials (base 2 inside); ignored rows: 0.
 __global__ void ce_combine_kernel(const float2* __restrict__ part, const float* __restrict__ tlogit, const long long* __restrict__ targets,
                                   float* __restrict__ loss, float* __restrict__ lse_out, long long M, int tiles) {
@@ -378,6 +401,14 @@ int launch_row_rms(const RowRmsArgs& a, cudaStream_t stream) {
   const int warps = 8;
   row_rms_kernel<<<(unsigned)((a.M + warps - 1) / warps), warps * 32, 0, stream>>>(
       (const __nv_bfloat16*)a.x, a.row_scale, a.M, a.D, a.x_stride, a.eps);
+  return (int)cudaGetLastError();
+}
+
+int launch_silu_mul(const void* gu, void* out, long long M, int I, long long in_stride, long long out_stride, cudaStream_t stream) {
+  const long long threads = M * (I / 8);
+  if (threads == 0) return 0;
+  silu_mul_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, M, I, in_stride,
+                                                                            out_stride);
   return (int)cudaGetLastError();
 }
 

@@ -550,8 +550,7 @@ class GraphedDecoder:
     def _mlp_fused(self, layer, fw, t2, r2):
         from . import fused_ops as FO
         gu = self._norm_linear(t2, fw[1], layer.post_attention_layernorm.eps)
-        inter = gu.shape[1] // 2
-        h = F.silu(gu[:, :inter]) * gu[:, inter:]
+        h = FO.silu_mul(gu)
         return self._linear_residual(h, layer.mlp.down_proj.weight, r2, inplace=True)      # r + mlp(norm(t))
 
     def _hidden_fused(self) -> torch.Tensor:

@@ -88,6 +88,19 @@ def rmsnorm_linear(x: torch.Tensor, folded_weight: torch.Tensor, eps: float) -> 
     return linear(x, folded_weight, row_scale=row_rms(x, eps))
 
 
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate_up[..., :I]) * gate_up[..., I:] for the output (..., 2 I) of one stacked gate|up projection
+    (the reference's fused SwiGLU activation, ``model/llama.py:290-300``): one launch, one rounding."""
+    _require(gate_up, "silu_mul")
+    x2 = _rows(gate_up)
+    inter = x2.shape[1] // 2
+    if x2.shape[1] != 2 * inter:
+        raise ValueError("silu_mul: the last dimension must hold gate and up halves of equal width")
+    out = torch.empty((x2.shape[0], inter), dtype=torch.bfloat16, device=gate_up.device)
+    _lib.call("gca_silu_mul", x2.data_ptr(), out.data_ptr(), x2.shape[0], inter, x2.stride(0), out.stride(0), _stream())
+    return out.view(*gate_up.shape[:-1], inter)
+
+
 def window_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int, slopes: Optional[torch.Tensor] = None,
                   sm_scale: Optional[float] = None) -> torch.Tensor:
     """Sliding-window causal attention with ALiBi for a few new positions against the cached window

@@ -295,3 +295,22 @@ def test_window_ring_decode_rejects_bad_arguments():
         F.window_ring_decode(q, ring, ring, new, new, cnt, 3)                          # rows of the ring outside the window
     with pytest.raises(ValueError):
         F.window_ring_decode(q.expand(1, 1, 2, 64).contiguous(), ring, ring, new, new, cnt, 7)      # one new position only
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,inter", [(1, 8), (32, 2048), (257, 1536)])
+def test_silu_mul_against_float32(m, inter):
+    """silu(gate) * up over the output of one stacked gate|up projection, against float32 (one bf16 rounding),
+    from a row-strided input; argument checks."""
+    need_gpu()
+    from long_context_modeling_b200 import fused_ops as F
+    g = torch.Generator().manual_seed(m + inter)
+    wide = (torch.randn(m, 2 * inter + 16, generator=g) * 3).bfloat16().cuda()
+    gu = wide[:, :2 * inter]                                        # row stride wider than the row
+    want = torch.nn.functional.silu(gu[:, :inter].float()) * gu[:, inter:].float()
+    got = F.silu_mul(gu)
+    assert got.shape == (m, inter) and got.dtype == torch.bfloat16
+    assert (got.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+    assert torch.equal(F.silu_mul(gu.view(1, m, 2 * inter).contiguous()).view(m, inter), got)
+    with pytest.raises(ValueError):
+        F.silu_mul(gu[:, :2 * inter - 8].contiguous()[:, :2 * inter - 12])   # halves not a multiple of 8 wide

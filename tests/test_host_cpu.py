@@ -282,7 +282,11 @@ def test_fused_ops_refuse_cpu_tensors_and_wrong_dtypes(lib):
     for call in (lambda: F.row_rms(x, 1e-5), lambda: F.linear(x, w), lambda: F.rmsnorm_linear(x, w, 1e-5),
                  lambda: F.linear_cross_entropy(x, w, torch.zeros(4, dtype=torch.int64)),
                  lambda: F.window_decode(torch.zeros(1, 1, 1, 64, dtype=torch.bfloat16), torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16),
-                                         torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16), 4)):
+                                         torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16), 4),
+                 lambda: F.silu_mul(x),
+                 lambda: F.window_ring_decode(torch.zeros(1, 1, 1, 64, dtype=torch.bfloat16), torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16),
+                                              torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16), torch.zeros(1, 1, 64, dtype=torch.bfloat16),
+                                              torch.zeros(1, 1, 64, dtype=torch.bfloat16), torch.zeros(1, dtype=torch.int64), 7)):
         with pytest.raises(RuntimeError):
             call()
     assert F.fold_gain(torch.ones(3, 4), torch.full((4,), 2.0)).dtype == torch.bfloat16
