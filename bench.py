@@ -1004,7 +1004,7 @@ def generate_arm(args):
         eager_ms = ee0.elapsed_time(ee1) / 24
         # ... then the product path: token steps between chunk boundaries replayed from a CUDA graph, boundary
         # steps (chunk encoder, cache append, landmark retrieval over all cached chunks) eager
-        # fused token step by default (24,000 tokens/s; the plain graphed step through the unfused modules: 14,700 with a
+        # fused token step by default (38,700 tokens/s; the plain graphed step through the unfused modules: 14,700 with a
         # capture per span)
         decoder = D.GraphedDecoder(model, state, fused=not args.plain_decode)
         tok = decoder.run(tok, 40)[:, -1].contiguous()      # warm-up across one chunk boundary (not counted)
@@ -1043,7 +1043,7 @@ def generate_arm(args):
                                "buffers, so later spans replay it too; a capture inside the timed region only after new pages are "
                                "mapped); boundary steps run eagerly; token step: "
                                + ("unfused modules" if args.plain_decode else "fused (one q|k|v and one gate|up product with the norm folded in, "
-                                  "windows moved on in place)"),
+                                  "cached windows kept as rings that the attention kernel updates itself)"),
                        "eager_ms_per_step": eager_ms, "graph_captures": decoder.captures},
             "clocks": clocks, "device_status": lcm.read_status(),
             "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,

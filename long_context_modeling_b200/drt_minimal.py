@@ -470,13 +470,15 @@ class GraphedDecoder:
     # operations ride on the library's GEMM -- RMSNorm's row scale in the epilogue of one q|k|v (and one
     # gate|up) projection whose weights carry the norm's gain, the residual add in the epilogue of o_proj
     # and down_proj -- and the windowed attention is the library's decode kernel: ~15 launches per layer
-    # instead of ~45.  At 32 sequences and a 1M-token cache: 21,100 tokens/s (24,000 once the graph is kept across boundaries), against 14,700 for the
-    # graphed step through the unfused modules and 5,500 eager.  (Two things had hidden that gain at first:
-    # with the library's 128 x 256-tile GEMM on 32 rows -- 9 busy CTAs for the q|k|v projection -- the step
-    # ran at 6,500 tokens/s, hence cuBLAS below SMALL_M rows; and concatenating the cached window with a
-    # strided view of the projection output took torch's slow generic copy, 100 us per layer, hence the
-    # in-place window update.)  Off by default in `generate_graphed` because its bf16 rounding differs
-    # from the unfused modules'.
+    # instead of ~45.  The cached windows are rings that the attention kernel updates itself (nothing is
+    # shifted or concatenated per token; `_linearise` puts them back in order once per span).  At 32
+    # sequences and a 1M-token cache: 38,700 tokens/s, against 14,700 for the graphed step through the
+    # unfused modules and 5,500 eager.  (What had hidden that gain at first: with the library's 128 x 256-tile
+    # GEMM on 32 rows -- 9 busy CTAs for the q|k|v projection -- the step ran at 6,500 tokens/s, hence cuBLAS
+    # below SMALL_M rows; concatenating the cached window with a strided view of the projection output took
+    # torch's slow generic copy, 100 us per layer; moving the window in place still cost 16 us per layer,
+    # hence the rings; and a 50,257-row LM head leaves cuBLAS an unaligned kernel, hence the padded copy.)
+    # Off by default in `generate_graphed` because its bf16 rounding differs from the unfused modules'.
     def _fusable(self) -> bool:
         m = self.model
         w = m.embed_tokens.weight
