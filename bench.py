@@ -1004,7 +1004,7 @@ def generate_arm(args):
         eager_ms = ee0.elapsed_time(ee1) / 24
         # ... then the product path: token steps between chunk boundaries replayed from a CUDA graph, boundary
         # steps (chunk encoder, cache append, landmark retrieval over all cached chunks) eager
-        # fused token step by default (38,700 tokens/s; the plain graphed step through the unfused modules: 14,700 with a
+        # fused token step by default (44,600 tokens/s; the plain graphed step through the unfused modules: 14,700 with a
         # capture per span)
         decoder = D.GraphedDecoder(model, state, fused=not args.plain_decode)
         tok = decoder.run(tok, 40)[:, -1].contiguous()      # warm-up across one chunk boundary (not counted)
@@ -1041,7 +1041,8 @@ def generate_arm(args):
                        "note": "the 62 token steps between two chunk boundaries are replayed from a CUDA graph (captured once: it "
                                "reads the cache through the view over all mapped chunk slots and the retrieved ids through static "
                                "buffers, so later spans replay it too; a capture inside the timed region only after new pages are "
-                               "mapped); boundary steps run eagerly; token step: "
+                               "mapped); at a chunk boundary the landmark position is one more replay and only the chunk encoder, the "
+                               "cache append and the retrieval run eagerly (plain decode: the whole boundary step eager); token step: "
                                + ("unfused modules" if args.plain_decode else "fused (one q|k|v and one gate|up product with the norm folded in, "
                                   "cached windows kept as rings that the attention kernel updates itself)"),
                        "eager_ms_per_step": eager_ms, "graph_captures": decoder.captures},

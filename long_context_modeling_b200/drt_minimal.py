@@ -459,6 +459,7 @@ class GraphedDecoder:
         self.cache_k = self.cache_v = None         # the chunk cache as the captured step sees it
         self.cache_key = None
         self.need_slot_reset = True
+        self.ring_rows = 0                         # rows written into the window rings since they were last in position order
         self.captures = 0                          # graphs captured so far (a span that finds its inputs unchanged replays the last one)
         self.windows: list = []                    # per layer: the (k, v) window buffers the captured step updates in place
         self.fused = bool(fused) and self._fusable()
@@ -472,7 +473,7 @@ class GraphedDecoder:
     # and down_proj -- and the windowed attention is the library's decode kernel: ~15 launches per layer
     # instead of ~45.  The cached windows are rings that the attention kernel updates itself (nothing is
     # shifted or concatenated per token; `_linearise` puts them back in order once per span).  At 32
-    # sequences and a 1M-token cache: 38,700 tokens/s, against 14,700 for the graphed step through the
+    # sequences and a 1M-token cache: 44,600 tokens/s, against 14,700 for the graphed step through the
     # unfused modules and 5,500 eager.  (What had hidden that gain at first: with the library's 128 x 256-tile
     # GEMM on 32 rows -- 9 busy CTAs for the q|k|v projection -- the step ran at 6,500 tokens/s, hence cuBLAS
     # below SMALL_M rows; concatenating the cached window with a strided view of the projection output took
@@ -660,18 +661,20 @@ class GraphedDecoder:
         self.counters = torch.zeros(2, dtype=torch.int64, device=device)
         self.slot, self.ring = self.counters[:1], self.counters[1:]
 
-    def _linearise(self, written: int) -> None:
-        """The fused step keeps each cached window as a ring (``fused_ops.window_ring_decode``); after a span
-        that wrote ``written`` rows the rings are rolled back into position order, which is what every other
-        user of the state expects, and the ring counter restarts.  Once per span: 1/62 of what shifting the
-        window at every token moved."""
-        t = self.windows[0][0].shape[2]
-        shift = written % t
+    def _linearise(self) -> None:
+        """The fused step keeps each cached window as a ring (``fused_ops.window_ring_decode``).  Before
+        anything else reads the state -- an eager step, the caller after ``run`` -- the rings are rolled back
+        into position order and the ring counter restarts."""
+        if not self.fused or self.ring_rows == 0:
+            self.ring_rows = 0
+            return
+        shift = self.ring_rows % self.windows[0][0].shape[2]
         if shift:
             for k, v in self.windows:
                 k.copy_(torch.roll(k, -shift, 2))
                 v.copy_(torch.roll(v, -shift, 2))
         self.ring.zero_()
+        self.ring_rows = 0
 
     def _keep(self, li: int, kv) -> None:
         k_old, v_old = self.state.self_attn[li]
@@ -720,10 +723,14 @@ class GraphedDecoder:
         out = []
         tok = token
         done = 0
+        # fused form with one group of upper layers: the chunk's last token is a token step like any other and
+        # the landmark position a replay of the same graph (_landmark_step): no eager pass over the layers
+        fast_boundary = self.fused and len(m.upper_layers) == 1
         while done < steps:
             in_chunk = st.position % m.chunk                     # tokens of the current chunk already processed
             boundary = in_chunk == cfg.enc_chunk_size - 1
-            if boundary or not token.is_cuda or not self._window_full():
+            if (boundary and not fast_boundary) or not token.is_cuda or not self._window_full():
+                self._linearise()
                 if self.stage is not None and self.graph is not None and in_chunk > 0 and st.chunks.lower_hidden_states is None:
                     st.chunks.cache_lower_hidden_states(self.stage[:, :in_chunk].clone())
                 tok = m.decode_step(tok, st).argmax(-1)
@@ -731,7 +738,7 @@ class GraphedDecoder:
                 done += 1
                 self.need_slot_reset = True                      # the graph survives if its tensor arguments still hold (_bind_inputs)
                 continue
-            span = min(cfg.enc_chunk_size - 1 - in_chunk, steps - done)
+            span = min(cfg.enc_chunk_size - (0 if fast_boundary else 1) - in_chunk, steps - done)
             if self.tok is None:
                 dim = cfg.hidden_size
                 self.tok = torch.empty_like(tok)
@@ -754,10 +761,37 @@ class GraphedDecoder:
             self.need_slot_reset = False
             for _ in range(span):
                 self.graph.replay()
-            if self.fused:
-                self._linearise(span)
+            self.ring_rows += span
             st.position += span
             out.append(self.toks[:, in_chunk:in_chunk + span].clone())
+            if in_chunk + span == cfg.enc_chunk_size:            # (fast_boundary) the chunk's tokens are complete
+                self._landmark_step()
             tok = self.tok.clone()
             done += span
+        self._linearise()                                        # the state leaves this call with its windows in position order
         return torch.cat(out, dim=1) if out else token.new_zeros((n, 0))
+
+    def _landmark_step(self) -> None:
+        """The landmark position that closes a chunk, without an eager pass over the layers.  The reference
+        runs the chunk's last token and the landmark as one two-position step; causal attention makes that
+        equal to two one-position steps, so the landmark is ONE MORE REPLAY of the token-step graph with the
+        landmark id as its token (it stages the landmark's lower hidden state in slot 63, moves every
+        window on and runs the upper layers with the retrieval still in force; its logits are unused).
+        What remains eager is what changes the cache: the chunk encoder over the 64 staged rows, the
+        projection + append, and the retrieval for the next chunk (queried by the landmark's lower hidden
+        state, over all landmarks including the new one) -- the order of ``DRTMinimal.decode_step``."""
+        m, st, cfg = self.model, self.state, self.model.cfg
+        nxt = self.tok.clone()                                   # the token the last step produced
+        self.tok.fill_(cfg.chunk_id)
+        self.graph.replay()
+        self.ring_rows += 1
+        self.tok.copy_(nxt)
+        chunks = st.chunks
+        m.encode_chunks(self.stage.unsqueeze(1), chunks)
+        q_lmk = m.lmk_norms[0](self.stage[:, -1:])
+        res = lmk_score_topk(q_lmk, chunks.past_lmk_embeds, min(len(chunks), cfg.chunk_topk))
+        chunks.update_current_retrieved_chunk(res.indices[:, -1], res.weights[:, -1:], 0)
+        st.position += 1
+        self.slot.zero_()
+        if not self._bind_inputs():                              # e.g. new pages were mapped behind the cache
+            self.graph = None

@@ -177,6 +177,54 @@ def test_graph_is_reused_across_chunk_boundaries(virtual):
 
 
 @pytest.mark.gpu
+def test_replayed_landmark_step_matches_the_eager_boundary_step():
+    """In fused form the decoder closes a chunk without an eager pass over the layers: the chunk's last token
+    and then the landmark position are replays of the token-step graph, followed by the chunk encoder, the
+    append and the retrieval.  Against ``decode_step`` (one two-position step) from the same state: same cache
+    length and position, the appended chunk's K / V / landmark, every cached window and the staged-row state
+    equal within bf16 accuracy, and the retrieved chunk ids the same."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import copy
+    from long_context_modeling_b200 import drt_minimal as D
+    torch.manual_seed(12)
+    cfg = D.DRTConfig(hidden_size=128, num_attention_heads=2, intermediate_size=256, decoder_layers=[1, 2], encoder_layers=1,
+                      vocab_size=500, chunk_topk=2, slide_window=40, chunk_id=499)
+    model = D.DRTMinimal(cfg).cuda().bfloat16().eval()
+    prompt = torch.randint(0, 499, (3, 63 * 4), device="cuda")
+    forced = torch.randint(0, 499, (3, 63), device="cuda")
+    with torch.no_grad():
+        state = D.DecodeState(cfg)
+        model(prompt, state=state)
+        for t in range(62):                                       # up to the chunk's last token, teacher-forced
+            model.decode_step(forced[:, t], state)
+        assert state.position % model.chunk == 62
+        eager, fast = state, copy.deepcopy(state)
+        model.decode_step(forced[:, 62], eager)                   # token 62 + landmark, encoder, append, retrieval
+        dec = D.GraphedDecoder(model, fast, fused=True)
+        assert dec.fused
+        dec.run(forced[:, 62].contiguous(), 1)
+    assert dec.captures == 1
+    assert fast.position == eager.position and len(fast.chunks) == len(eager.chunks) == 5
+    assert fast.chunks.lower_hidden_states is None and eager.chunks.lower_hidden_states is None
+
+    def close(a, b, what):
+        err, ref = (a.float() - b.float()).abs().max().item(), b.float().abs().max().item()
+        assert err <= 3e-2 * ref, (what, err, ref)
+
+    close(fast.chunks.chunk_k[:, -1], eager.chunks.chunk_k[:, -1], "appended K")
+    close(fast.chunks.chunk_v[:, -1], eager.chunks.chunk_v[:, -1], "appended V")
+    close(fast.chunks.past_lmk_embeds[:, -1], eager.chunks.past_lmk_embeds[:, -1], "appended landmark")
+    for li, ((ka, va), (kb, vb)) in enumerate(zip(fast.self_attn, eager.self_attn)):
+        close(ka, kb, f"window K of layer {li}")
+        close(va, vb, f"window V of layer {li}")
+    ia, wa = fast.chunks.current_retrieved_indices(0)
+    ib, wb = eager.chunks.current_retrieved_indices(0)
+    assert torch.equal(ia.sort(-1).values, ib.sort(-1).values)
+    close(wa.sort(-1).values, wb.sort(-1).values, "retrieval weights")
+
+
+@pytest.mark.gpu
 def test_flash_attn_path_matches_torch_path():
     """Where the flash-attn library loads, the body's windowed ALiBi self-attention goes through it (as in the
     reference); the block-banded torch path is the fallback.  Both must agree in bf16: a full sequence, and a
