@@ -778,6 +778,10 @@ def window_decode_arm(args):
     ms, clocks = timed(step, steps, warmup)
     ms_e2e, _ = timed(e2e_step, steps, warmup)
     ms_k = _graph_time([(lambda i=i: F.window_decode(q, ks[i], vs[i], window, slopes, 0.125)) for i in range(10)], flush)
+    # the ring form the fused token step uses: the new K / V row replaces the oldest row inside the same kernel
+    kn, vn = torch.randn(n, h, 64, generator=g, device=dev).bfloat16(), torch.randn(n, h, 64, generator=g, device=dev).bfloat16()
+    count = torch.full((1,), 100, dtype=torch.int64, device=dev)
+    ms_ring = _graph_time([(lambda i=i: F.window_ring_decode(q, ks[i], vs[i], kn, vn, count, window, slopes, 0.125)) for i in range(10)], flush)
     nbytes = 2 * n * h * t * 128
     achieved = nbytes / (ms_k * 1e-3) / 1e9
     line = {"metric": "window_decode_gbs", "value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1, "steps": steps,
@@ -792,7 +796,10 @@ def window_decode_arm(args):
             "gpu_launches": steps,
             "roofline": {"kernel": "win_decode_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy bandwidth", "traffic": None,
-                         "algorithmic_bytes_per_launch": nbytes, "us_per_launch": ms_k * 1e3},
+                         "algorithmic_bytes_per_launch": nbytes, "us_per_launch": ms_k * 1e3,
+                         "ring_form": {"us_per_launch": ms_ring * 1e3, "achieved": nbytes / (ms_ring * 1e-3) / 1e9,
+                                       "frac": nbytes / (ms_ring * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                       "note": "append folded in: shift + decode of a linear window move 3 x these bytes"}},
             "device_status": lcm.read_status()}
     print(json.dumps(line), flush=True)
 
@@ -1004,7 +1011,7 @@ def generate_arm(args):
         eager_ms = ee0.elapsed_time(ee1) / 24
         # ... then the product path: token steps between chunk boundaries replayed from a CUDA graph, boundary
         # steps (chunk encoder, cache append, landmark retrieval over all cached chunks) eager
-        # fused token step by default (44,600 tokens/s; the plain graphed step through the unfused modules: 14,700 with a
+        # fused token step by default (45,500 tokens/s; the plain graphed step through the unfused modules: 14,700 with a
         # capture per span)
         decoder = D.GraphedDecoder(model, state, fused=not args.plain_decode)
         tok = decoder.run(tok, 40)[:, -1].contiguous()      # warm-up across one chunk boundary (not counted)

@@ -462,7 +462,7 @@ int gca_window_decode(const WindowDecodeArgs* args, void* stream);
  * append folded in: attn.k / attn.v are the (N, Hkv, T, 64) ring buffers with T <= window + 1 valid rows,
  * k_new / v_new the new position's (N, Hkv, 64) rows by strides (n, kv head).  *rows_written (a device
  * int64 the caller advances by one per call sequence, e.g. inside a captured CUDA graph) gives the slot
- * p = rows_written mod T that holds the oldest row: the new rows are attended to as the newest
+ * p = rows_written mod T (the count must stay below 2^32: subtract a multiple of T before it gets there) that holds the oldest row: the new rows are attended to as the newest
  * position and stored at p; physical row j counts as logical position (j - p - 1) mod T.  With
  * rows_written = 0 and a linear window the result equals gca_window_shift_append followed by
  * gca_window_decode, without moving the window (which costs a read + write of the whole window per call). */

@@ -107,21 +107,49 @@ win_decode_kernel(const WinParams p) {
   const __nv_bfloat16* vb = p.v + n * p.vs[0] + hk * p.vs[1] + sub * 8;
   const int stride = NWARPS * 4;                     // keys per CTA step
   const int base = first + warp * 4;                 // warp-uniform: every lane runs the same steps
-  // ring form: physical row `newest` is this step's new row (read from knew / vnew, never from the ring);
-  // the linear form is the ring whose newest row is the last one
-  const int newest = RING ? (int)(*p.ring % p.T) : p.T - 1;
-  const long long noff = RING ? n * p.ns[0] + hk * p.ns[1] + sub * 8 : 0;       // this lane's 16 bytes of the new rows
+  // Ring form: physical row `newest` is the slot of this step's new row.  The loop reads every row from
+  // the ring and skips that slot (it still holds the oldest row); the new row is visited afterwards from
+  // knew / vnew and stored into the slot.  The count is loaded first but needed only after the first
+  // loads have been issued.  The linear form is the ring whose newest row is the last one, nothing skipped.
+  const long long written = RING ? *p.ring : 0;
   uint4 kq[PREFETCH], vq[PREFETCH];
 #pragma unroll
   for (int s = 0; s < PREFETCH; ++s) {
     const int j = base + grp + s * stride;
     kq[s] = vq[s] = make_uint4(0, 0, 0, 0);
     if (j < p.T) {
-      const bool fresh = RING && j == newest;
-      kq[s] = *reinterpret_cast<const uint4*>(fresh ? p.knew + noff : kb + j * p.ks[2]);
-      vq[s] = *reinterpret_cast<const uint4*>(fresh ? p.vnew + noff : vb + j * p.vs[2]);
+      kq[s] = *reinterpret_cast<const uint4*>(kb + j * p.ks[2]);
+      vq[s] = *reinterpret_cast<const uint4*>(vb + j * p.vs[2]);
     }
   }
+  const int newest = RING ? (int)((unsigned)written % (unsigned)p.T) : p.T - 1;    // the count stays below 2^32 (caller's contract)
+  // one key against every row: `ok` = this lane's group counts it; dist[r] = back = pos[r] - (logical position)
+  auto visit = [&](const uint4& kc, const uint4& vc, bool ok, int back) {
+    const uint32_t kw[4] = {kc.x, kc.y, kc.z, kc.w}, vw[4] = {vc.x, vc.y, vc.z, vc.w};
+    float kf[8], vf[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { kf[2 * e] = lo(kw[e]); kf[2 * e + 1] = hi(kw[e]); vf[2 * e] = lo(vw[e]); vf[2 * e + 1] = hi(vw[e]); }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float sc = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sc = fmaf(qv[r][e], kf[e], sc);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+      // linear form: `back` is the key's position j; ring form: the distance itself (one query position)
+      const int dist = RING ? back : pos[r] - back;
+      if (r < rows && ok && (RING || (dist >= 0 && dist <= p.window))) {
+        sc -= slope[r] * (float)dist;
+        const float m = fmaxf(st[r].m, sc);
+        const float corr = ex2(st[r].m - m), pr = ex2(sc - m);       // ex2(-inf) = 0 on the first key
+        st[r].l = st[r].l * corr + pr;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) st[r].acc[e] = fmaf(pr, vf[e], st[r].acc[e] * corr);
+        st[r].m = m;
+      }
+    }
+  };
   for (int jb = base; jb < p.T; jb += PREFETCH * stride) {
 #pragma unroll
     for (int s = 0; s < PREFETCH; ++s) {
@@ -129,44 +157,30 @@ win_decode_kernel(const WinParams p) {
       const uint4 kc = kq[s], vc = vq[s];
       const int jn = j + PREFETCH * stride;             // refill this register slot
       if (jn < p.T) {
-        const bool fresh = RING && jn == newest;
-        kq[s] = *reinterpret_cast<const uint4*>(fresh ? p.knew + noff : kb + jn * p.ks[2]);
-        vq[s] = *reinterpret_cast<const uint4*>(fresh ? p.vnew + noff : vb + jn * p.vs[2]);
+        kq[s] = *reinterpret_cast<const uint4*>(kb + jn * p.ks[2]);
+        vq[s] = *reinterpret_cast<const uint4*>(vb + jn * p.vs[2]);
       }
-      // every lane of a warp runs the same number of steps (the reduction below uses shuffles);
-      // keys past the end are masked
-      const bool in_range = j < p.T;
-      const uint32_t kw[4] = {kc.x, kc.y, kc.z, kc.w}, vw[4] = {vc.x, vc.y, vc.z, vc.w};
-      float kf[8], vf[8];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) { kf[2 * e] = lo(kw[e]); kf[2 * e + 1] = hi(kw[e]); vf[2 * e] = lo(vw[e]); vf[2 * e + 1] = hi(vw[e]); }
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        float sc = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sc = fmaf(qv[r][e], kf[e], sc);
-        sc += __shfl_xor_sync(0xffffffffu, sc, 1);
-        sc += __shfl_xor_sync(0xffffffffu, sc, 2);
-        sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-        int lj = j;                                     // logical position of physical row j
-        if (RING) { lj = j - newest - 1; if (lj < 0) lj += p.T; }
-        const int dist = pos[r] - lj;
-        if (r < rows && in_range && dist >= 0 && dist <= p.window) {
-          sc -= slope[r] * (float)dist;
-          const float m = fmaxf(st[r].m, sc);
-          const float corr = ex2(st[r].m - m), pr = ex2(sc - m);       // ex2(-inf) = 0 on the first key
-          st[r].l = st[r].l * corr + pr;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) st[r].acc[e] = fmaf(pr, vf[e], st[r].acc[e] * corr);
-          st[r].m = m;
-        }
+      // every lane of a warp runs the same number of steps (the reduction uses shuffles); keys past the
+      // end are masked, and so is the ring's slot of the new row
+      if (RING) {
+        int dist = newest - j;                          // rows behind the new one, around the ring
+        if (dist < 0) dist += p.T;
+        visit(kc, vc, j < p.T && dist != 0, dist);
+      } else {
+        visit(kc, vc, j < p.T, j);
       }
     }
   }
-  // ring form: the new row takes the oldest row's place (no thread of this or another CTA reads that row of the ring)
-  if (RING && warp == 0 && grp == 0) {
-    *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(kb) + newest * p.ks[2]) = *reinterpret_cast<const uint4*>(p.knew + noff);
-    *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(vb) + newest * p.vs[2]) = *reinterpret_cast<const uint4*>(p.vnew + noff);
+  if (RING && warp == 0) {
+    // the new row: attended to at distance 0 (counted by the warp's first stream), then stored over the oldest
+    // row -- no thread of this or another CTA reads that row of the ring
+    const long long noff = n * p.ns[0] + hk * p.ns[1] + sub * 8;        // this lane's 16 bytes of the new rows
+    const uint4 kc = *reinterpret_cast<const uint4*>(p.knew + noff), vc = *reinterpret_cast<const uint4*>(p.vnew + noff);
+    visit(kc, vc, grp == 0, 0);
+    if (grp == 0) {
+      *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(kb) + newest * p.ks[2]) = kc;
+      *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(vb) + newest * p.vs[2]) = vc;
+    }
   }
   // merge the 4 key streams of the warp (groups 8 and 16 lanes apart), then the warps
 #pragma unroll

@@ -473,7 +473,7 @@ class GraphedDecoder:
     # and down_proj -- and the windowed attention is the library's decode kernel: ~15 launches per layer
     # instead of ~45.  The cached windows are rings that the attention kernel updates itself (nothing is
     # shifted or concatenated per token; `_linearise` puts them back in order once per span).  At 32
-    # sequences and a 1M-token cache: 44,600 tokens/s, against 14,700 for the graphed step through the
+    # sequences and a 1M-token cache: 45,500 tokens/s, against 14,700 for the graphed step through the
     # unfused modules and 5,500 eager.  (What had hidden that gain at first: with the library's 128 x 256-tile
     # GEMM on 32 rows -- 9 busy CTAs for the q|k|v projection -- the step ran at 6,500 tokens/s, hence cuBLAS
     # below SMALL_M rows; concatenating the cached window with a strided view of the projection output took
@@ -762,6 +762,10 @@ class GraphedDecoder:
             for _ in range(span):
                 self.graph.replay()
             self.ring_rows += span
+            if self.ring_rows >= 1 << 30:                        # the kernel reads the count modulo the ring length in 32 bits
+                whole = self.ring_rows - self.ring_rows % self.windows[0][0].shape[2]
+                self.ring -= whole
+                self.ring_rows -= whole
             st.position += span
             out.append(self.toks[:, in_chunk:in_chunk + span].clone())
             if in_chunk + span == cfg.enc_chunk_size:            # (fast_boundary) the chunk's tokens are complete

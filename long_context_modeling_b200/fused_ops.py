@@ -141,7 +141,8 @@ def window_ring_decode(q: torch.Tensor, k_ring: torch.Tensor, v_ring: torch.Tens
     the oldest at row ``rows_written mod T``; ``k_new`` / ``v_new`` (N, Hkv, 1, 64) or (N, Hkv, 64) are
     attended to as the newest position and stored over the oldest row.  ``rows_written`` is a device int64
     scalar the CALLER advances by one after the step (all layers of a model share one counter), so that a
-    captured CUDA graph can replay the step.  q (N, Hq, 1, 64).  ``torch.roll(ring, -(rows_written % T), 2)``
+    captured CUDA graph can replay the step; it must stay below 2^32 (subtract a multiple of T long before).
+    q (N, Hq, 1, 64).  ``torch.roll(ring, -(rows_written % T), 2)``
     gives the window back in order."""
     for t, name in ((k_new, "k_new"), (v_new, "v_new")):
         _require(t, f"window_ring_decode {name}")
