@@ -1011,8 +1011,8 @@ def generate_arm(args):
         eager_ms = ee0.elapsed_time(ee1) / 24
         # ... then the product path: token steps between chunk boundaries replayed from a CUDA graph, boundary
         # steps (chunk encoder, cache append, landmark retrieval over all cached chunks) eager
-        # fused token step by default (45,500 tokens/s; the plain graphed step through the unfused modules: 14,700 with a
-        # capture per span)
+        # fused token step by default (45,500 tokens/s; the plain graphed step through the unfused modules, with eager boundary
+        # steps: 15,700)
         decoder = D.GraphedDecoder(model, state, fused=not args.plain_decode)
         tok = decoder.run(tok, 40)[:, -1].contiguous()      # warm-up across one chunk boundary (not counted)
         if world > 1:

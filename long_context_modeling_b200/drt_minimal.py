@@ -473,7 +473,7 @@ class GraphedDecoder:
     # and down_proj -- and the windowed attention is the library's decode kernel: ~15 launches per layer
     # instead of ~45.  The cached windows are rings that the attention kernel updates itself (nothing is
     # shifted or concatenated per token; `_linearise` puts them back in order when something else reads the state).  At 32
-    # sequences and a 1M-token cache: 45,500 tokens/s, against 14,700 for the graphed step through the
+    # sequences and a 1M-token cache: 45,500 tokens/s, against 15,700 for the graphed step through the
     # unfused modules and 5,500 eager.  (What had hidden that gain at first: with the library's 128 x 256-tile
     # GEMM on 32 rows -- 9 busy CTAs for the q|k|v projection -- the step ran at 6,500 tokens/s, hence cuBLAS
     # below SMALL_M rows; concatenating the cached window with a strided view of the projection output took
